@@ -1,0 +1,261 @@
+/*
+ * bsp.h -- C ABI of the B200-native block-sparse hot path.
+ *
+ * Every entry point is extern "C", takes plain pointers / sizes / strides and
+ * returns an int status (BSP_OK == 0).  After a non-zero status,
+ * bsp_last_error() returns a thread-local, human readable message.
+ *
+ * Conventions
+ *   layout   int64 host array [H, Mb, Nb]; an entry != 0 means "block present".
+ *            Never modified by the library.
+ *   block    edge of a square block: 16, 32, 64 or 128.
+ *   block format  a sparse tensor is stored as [Z, nnz, block, block]; block b is
+ *            the b-th nonzero of the layout in (h, i, j) row-major order.
+ *   dtype    BSP_F32 / BSP_F16 / BSP_BF16; all operands of a call share it.
+ *            16-bit types accumulate in FP32.
+ *   strides  always in ELEMENTS.
+ *   stream   a cudaStream_t passed as void*; launches are asynchronous on it.
+ *   memory   the library never allocates device memory; every buffer (inputs,
+ *            outputs, tables, scratch) is owned by the caller.
+ *   meta     device copy of the buffer written by bsp_meta_build; meta_hdr is a
+ *            HOST pointer to (a copy of) its first BSP_META_HEADER ints, from
+ *            which the launch code reads the layout dimensions.
+ *
+ * The table builders run on the host and write host memory.  They are called
+ * twice: first with out == NULL to learn *total (number of int32 entries),
+ * then with a buffer of at least that capacity.
+ */
+#ifndef BSP_B200_H
+#define BSP_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define BSP_OK               0
+#define BSP_ERR_INVALID      1  /* bad argument (maps to ValueError)            */
+#define BSP_ERR_UNSUPPORTED  2  /* maps to NotImplementedError                  */
+#define BSP_ERR_CAPACITY     3  /* output buffer too small; *total says how big */
+#define BSP_ERR_CUDA         4  /* CUDA runtime error (maps to RuntimeError)    */
+#define BSP_ERR_EMPTY_HEAD   5  /* a head of the layout has no nonzero block    */
+#define BSP_ERR_TIMEOUT      6  /* a bounded device-side wait expired           */
+
+#define BSP_F32  0
+#define BSP_F16  1
+#define BSP_BF16 2
+
+#define BSP_MAX_PACKS 8
+
+/* Message for the last non-zero status returned on this thread. */
+const char* bsp_last_error(void);
+
+/* ABI version; bumped on any signature change. */
+int bsp_abi_version(void);
+
+/* ------------------------------------------------------------------------ */
+/* Layout -> table builders (host)                                          */
+/* ------------------------------------------------------------------------ */
+
+/*
+ * SDD table.  Replaces _sparse_matmul.make_sdd_lut (torch_blocksparse/matmul.py:281-297)
+ * together with the native sdd_segment / segment_blocks it calls
+ * (csrc/utils.cpp:11-120).  Bit-identical output: nonzero blocks greedily packed
+ * into w x w super-blocks for w = 64/block, w/2, ..., 1; four int32 per entry
+ * (head, row, col, block id).  The tables of the successive pack sizes are
+ * written back to back into `out`; packs[p], widths[p] (number of super-blocks)
+ * and offsets[p] (first int of that table inside `out`) describe them, *n_packs
+ * says how many there are (empty passes are omitted, as in the reference).
+ * block == 128 has start width 0 in the reference and yields no table at all;
+ * that behaviour is kept (n_packs == 0).
+ */
+int bsp_sdd_lut_build(const int64_t* layout, int H, int Mb, int Nb, int block,
+                      int32_t* out, int64_t out_cap,
+                      int32_t* packs, int64_t* widths, int64_t* offsets,
+                      int* n_packs, int64_t* total);
+
+/*
+ * DSD / DDS table.  Replaces _sparse_matmul.load_balance + make_dxx_lut
+ * (torch_blocksparse/matmul.py:221-267, 372-458).  Bit-identical output: six
+ * int32 of header per segment (offset, K extent, column, head, lock id, max id),
+ * then interleaved (dense increment, sparse increment) pairs and two trailing
+ * zeros.  `step` is 8 for FP32 and 16 otherwise (matmul.py:617); `trans`
+ * selects per-row (1) or per-column (0) reductions.  A head without any
+ * nonzero block is an error (BSP_ERR_EMPTY_HEAD), as in the reference.
+ */
+int bsp_dxx_lut_build(const int64_t* layout, int H, int Mb, int Nb, int block,
+                      int step, int trans,
+                      int32_t* out, int64_t out_cap, int64_t* total,
+                      int* num_locks, int* width);
+
+/*
+ * Softmax table.  Replaces _sparse_softmax.make_lut (torch_blocksparse/softmax.py:201-221).
+ * Bit-identical output: (size, offset) per (head, block-row), then
+ * (block id, column, row, head) per nonzero block.  *maxlut = largest number of
+ * nonzero blocks in any block-row.
+ */
+int bsp_softmax_lut_build(const int64_t* layout, int H, int Mb, int Nb,
+                          int32_t* out, int64_t out_cap, int64_t* total, int* maxlut);
+
+/*
+ * "fixed" sparse-transformer layout.  Replaces
+ * DeepSpeedSparseSelfAttention._make_layout
+ * (torch_blocksparse/deepspeedsparseselfattention.py:33-65).  mode: 0 dense,
+ * 1 fixed.  Writes int64 [num_heads, num_blocks, num_blocks] into `out`.
+ */
+int bsp_fixed_layout_build(int num_heads, int num_blocks, int mode, int block_stride,
+                           int unidirectional, int numverts, int vertsize, int64_t* out);
+
+/*
+ * Execution metadata consumed by the compute kernels (no counterpart in the
+ * reference, whose kernels read the tables above; those tables can contain
+ * duplicate / out-of-layout entries and are therefore never executed from).
+ * int32 layout of `out`:
+ *   [0] magic  [1] H  [2] Mb  [3] Nb  [4] nnz  [5] max nnz per block-row
+ *   [6] max nnz per block-column  [7] reserved
+ *   row_ptr [H*Mb+1]   CSR offsets; the canonical block id is the CSR position
+ *   blk_row [nnz]      block-row of every block
+ *   blk_col [nnz]      block-column of every block
+ *   blk_head[nnz]      head of every block
+ *   col_ptr [H*Nb+1]   CSC offsets
+ *   col_row [nnz]      block-row of every block in CSC order
+ *   col_bid [nnz]      canonical block id of every block in CSC order
+ *   row_order [H*Mb]   (head*Mb + row) sorted by descending nnz (stable)
+ *   col_order [H*Nb]   (head*Nb + col) sorted by descending nnz (stable)
+ */
+#define BSP_META_MAGIC 0x42535031
+#define BSP_META_HEADER 8
+int bsp_meta_build(const int64_t* layout, int H, int Mb, int Nb,
+                   int32_t* out, int64_t out_cap, int64_t* total);
+
+/* ------------------------------------------------------------------------ */
+/* Softmax (device)                                                         */
+/* ------------------------------------------------------------------------ */
+
+/*
+ * In-place block-sparse row softmax.  Replaces the softmax_fwd kernel and its
+ * launch code (torch_blocksparse/softmax.py:7-138, 253-313):
+ *   y = softmax_row(x*scale + rpe + kpm + attn_mask), stored over x.
+ * x      [Z, nnz, block, block], z-stride x_sz.
+ * lut    device copy of the table written by bsp_softmax_lut_build.
+ * rpe    optional [Z, H, M, N] (strides rpe_sz, rpe_sh, rpe_sr; unit column
+ *        stride; rpe_sz may be 0 for a broadcast), added after the scale.
+ * kpm    optional key-padding mask [Z, N] (stride kpm_sz).
+ * am     optional attention mask [M, N] (row stride am_sr).
+ * *_mul  0: the mask is added; 1: 'mul' mode, mask == 0 -> -inf, else 0
+ *        (softmax.py:104-110).
+ * Rows longer than 32767 elements are rejected with BSP_ERR_UNSUPPORTED
+ * (softmax.py:225-227).
+ */
+int bsp_softmax_fwd(void* x, int dtype, int Z, int64_t x_sz, int block,
+                    int H, int Mb, const int32_t* lut, int maxlut, float scale,
+                    const void* rpe, int64_t rpe_sz, int64_t rpe_sh, int64_t rpe_sr,
+                    const void* kpm, int64_t kpm_sz, int kpm_mul,
+                    const void* am, int64_t am_sr, int am_mul,
+                    void* stream);
+
+/*
+ * Softmax backward, in place over dy.  Replaces softmax_bwd
+ * (torch_blocksparse/softmax.py:144-194, 315-326):
+ *   dx = y * (dy - sum_row(y*dy)) * scale.
+ */
+int bsp_softmax_bwd(const void* y, void* dy, int dtype, int Z, int64_t y_sz, int64_t dy_sz,
+                    int block, int H, int Mb, const int32_t* lut, int maxlut, float scale,
+                    void* stream);
+
+/* ------------------------------------------------------------------------ */
+/* MatMul (device)                                                          */
+/* ------------------------------------------------------------------------ */
+
+/*
+ * SDD: C_sparse = A . B sampled on the layout.  Replaces the SDD variant of the
+ * reference kernel and _sdd_matmul (torch_blocksparse/matmul.py:30-54, 299-364).
+ * A is the logical [Z, H, Mb*block, K] operand and B the logical
+ * [Z, H, K, Nb*block] operand, both addressed through element strides, which is
+ * how trans_a / trans_b / trans_c of the reference are expressed (one of the
+ * two inner strides of each operand must be 1).  C is written in block format
+ * (z-stride c_sz), every block completely.  K must be a multiple of 16
+ * (matmul.py:318-319), else BSP_ERR_INVALID.
+ */
+int bsp_sdd(const void* a, const void* b, void* c, int dtype, int block,
+            int Z, int H, int K,
+            int64_t a_sz, int64_t a_sh, int64_t a_sm, int64_t a_sk,
+            int64_t b_sz, int64_t b_sh, int64_t b_sk, int64_t b_sn,
+            int64_t c_sz, const int32_t* meta_hdr, const int32_t* meta, void* stream);
+
+/*
+ * DSD: C_dense = op(S) . B.  Replaces the DSD variant and _dsd_matmul
+ * (torch_blocksparse/matmul.py:66-82, 507-552).  S is in block format (z-stride
+ * s_sz); trans_s != 0 uses S transposed.  B is the logical [Z, H, K, N] operand,
+ * C the logical [Z, H, M, N] result, both through element strides (trans_b and
+ * trans_c of the reference).  Every element of C is written, zeros where a
+ * block-row of op(S) is empty.
+ */
+int bsp_dsd(const void* s, const void* b, void* c, int dtype, int block,
+            int Z, int H, int N, int64_t s_sz, int trans_s,
+            int64_t b_sz, int64_t b_sh, int64_t b_sk, int64_t b_sn,
+            int64_t c_sz, int64_t c_sh, int64_t c_sm, int64_t c_sn,
+            const int32_t* meta_hdr, const int32_t* meta, void* stream);
+
+/*
+ * DDS: C_dense = A . op(S).  Replaces the DDS variant and _dds_matmul
+ * (torch_blocksparse/matmul.py:83-99, 460-505).  A is the logical [Z, H, M, K]
+ * operand, C the logical [Z, H, M, N] result.
+ */
+int bsp_dds(const void* a, const void* s, void* c, int dtype, int block,
+            int Z, int H, int M,
+            int64_t a_sz, int64_t a_sh, int64_t a_sm, int64_t a_sk,
+            int64_t s_sz, int trans_s,
+            int64_t c_sz, int64_t c_sh, int64_t c_sm, int64_t c_sn,
+            const int32_t* meta_hdr, const int32_t* meta, void* stream);
+
+/* ------------------------------------------------------------------------ */
+/* Fused sparse self-attention (device)                                     */
+/* ------------------------------------------------------------------------ */
+
+/*
+ * O = softmax(scale * Q K^T + rpe + kpm + attn_mask on the layout) . V in one
+ * kernel.  Replaces the three-launch chain of
+ * DeepSpeedSparseSelfAttention.forward
+ * (torch_blocksparse/deepspeedsparseselfattention.py:157-166) without writing
+ * the score tensor to memory.  q, k, v, o are [Z, H, L, D] with unit stride on
+ * D and the given z / h / row strides; lse is FP32 [Z, H, L] (log-sum-exp of
+ * every row, needed by the backward).  D is 64 or 128; dtype F16 or BF16.
+ */
+int bsp_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse,
+                 int dtype, int block, int Z, int H, int L, int D,
+                 int64_t q_sz, int64_t q_sh, int64_t q_sr,
+                 int64_t k_sz, int64_t k_sh, int64_t k_sr,
+                 int64_t v_sz, int64_t v_sh, int64_t v_sr,
+                 int64_t o_sz, int64_t o_sh, int64_t o_sr,
+                 const int32_t* meta_hdr, const int32_t* meta, float scale,
+                 const void* rpe, int64_t rpe_sz, int64_t rpe_sh, int64_t rpe_sr,
+                 const void* kpm, int64_t kpm_sz, int kpm_mul,
+                 const void* am, int64_t am_sr, int am_mul,
+                 void* stream);
+
+/*
+ * Backward of bsp_attn_fwd: dq, dk, dv from q, k, v, o, do and lse, recomputing
+ * the probabilities block by block.  `delta` is caller-provided FP32 scratch of
+ * Z*H*L elements (row sums of o*do).  dq/dk/dv are contiguous [Z, H, L, D].
+ */
+int bsp_attn_bwd(const void* q, const void* k, const void* v, const void* o,
+                 const void* dout, const float* lse, float* delta,
+                 void* dq, void* dk, void* dv,
+                 int dtype, int block, int Z, int H, int L, int D,
+                 int64_t q_sz, int64_t q_sh, int64_t q_sr,
+                 int64_t k_sz, int64_t k_sh, int64_t k_sr,
+                 int64_t v_sz, int64_t v_sh, int64_t v_sr,
+                 int64_t o_sz, int64_t o_sh, int64_t o_sr,
+                 int64_t do_sz, int64_t do_sh, int64_t do_sr,
+                 const int32_t* meta_hdr, const int32_t* meta, float scale,
+                 const void* rpe, int64_t rpe_sz, int64_t rpe_sh, int64_t rpe_sr,
+                 const void* kpm, int64_t kpm_sz, int kpm_mul,
+                 const void* am, int64_t am_sr, int am_mul,
+                 void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* BSP_B200_H */

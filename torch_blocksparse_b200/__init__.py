@@ -1,0 +1,13 @@
+"""B200-native block-sparse MatMul / Softmax / sparse self-attention.
+
+Same public names as the reference package (torch_blocksparse/__init__.py:1-5
+for the ops on this path, plus the attention wrapper of
+deepspeedsparseselfattention.py, also exported as SparseSelfAttention).
+"""
+from .softmax import Softmax
+from .matmul import MatMul
+from .attention import DeepSpeedSparseSelfAttention, SparseSelfAttention, SparsityConfig
+from . import layouts
+
+__all__ = ['Softmax', 'MatMul', 'DeepSpeedSparseSelfAttention', 'SparseSelfAttention',
+           'SparsityConfig', 'layouts']

@@ -1,0 +1,84 @@
+"""ctypes binding of libbsp_b200.so (the C ABI declared in include/bsp.h).
+
+The library is the only compute path of this package: there is no Python or
+CPU fallback.  If the shared object is missing it is compiled on first use
+(needs nvcc); if that fails the import error is raised to the caller.
+"""
+import ctypes
+import os
+from ctypes import POINTER, c_char_p, c_float, c_int, c_int32, c_int64, c_void_p
+
+from . import _build
+
+OK, ERR_INVALID, ERR_UNSUPPORTED, ERR_CAPACITY, ERR_CUDA, ERR_EMPTY_HEAD, ERR_TIMEOUT = range(7)
+F32, F16, BF16 = 0, 1, 2
+MAX_PACKS = 8
+META_HEADER = 8
+
+_lib = None
+
+_I64P = POINTER(c_int64)
+_I32P = POINTER(c_int32)
+_IP = POINTER(c_int)
+_STRIDE3 = [c_int64, c_int64, c_int64]
+_MASKS = [c_void_p] + _STRIDE3 + [c_void_p, c_int64, c_int, c_void_p, c_int64, c_int]
+
+_SIGNATURES = {
+    'bsp_last_error': (c_char_p, []),
+    'bsp_abi_version': (c_int, []),
+    'bsp_sdd_lut_build': (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int64,
+                                  _I32P, _I64P, _I64P, _IP, _I64P]),
+    'bsp_dxx_lut_build': (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                                  c_void_p, c_int64, _I64P, _IP, _IP]),
+    'bsp_softmax_lut_build': (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, c_int64, _I64P, _IP]),
+    'bsp_fixed_layout_build': (c_int, [c_int] * 7 + [c_void_p]),
+    'bsp_meta_build': (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, c_int64, _I64P]),
+    'bsp_softmax_fwd': (c_int, [c_void_p, c_int, c_int, c_int64, c_int, c_int, c_int, c_void_p, c_int, c_float]
+                        + _MASKS + [c_void_p]),
+    'bsp_softmax_bwd': (c_int, [c_void_p, c_void_p, c_int, c_int, c_int64, c_int64, c_int, c_int, c_int,
+                                c_void_p, c_int, c_float, c_void_p]),
+    'bsp_sdd': (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int]
+                + [c_int64] * 9 + [c_void_p, c_void_p, c_void_p]),
+    'bsp_dsd': (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int64, c_int]
+                + [c_int64] * 8 + [c_void_p, c_void_p, c_void_p]),
+    'bsp_dds': (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int]
+                + [c_int64] * 4 + [c_int64, c_int] + [c_int64] * 4 + [c_void_p, c_void_p, c_void_p]),
+    'bsp_attn_fwd': (c_int, [c_void_p] * 5 + [c_int] * 6 + [c_int64] * 12 + [c_void_p, c_void_p, c_float]
+                     + _MASKS + [c_void_p]),
+    'bsp_attn_bwd': (c_int, [c_void_p] * 10 + [c_int] * 6 + [c_int64] * 15 + [c_void_p, c_void_p, c_float]
+                     + _MASKS + [c_void_p]),
+}
+
+
+def exported_symbols():
+    """Names every build of the library must export (one per declaration in include/bsp.h)."""
+    return sorted(_SIGNATURES)
+
+
+def lib():
+    """Loads (building first if necessary) and returns the ctypes library handle."""
+    global _lib
+    if _lib is None:
+        path = _build.LIB_PATH
+        if not os.path.exists(path) or (os.environ.get('BSP_REBUILD') and _build.needs_build()):
+            path = _build.build()
+        handle = ctypes.CDLL(path)
+        for name, (res, args) in _SIGNATURES.items():
+            fn = getattr(handle, name, None)
+            if fn is None:
+                continue   # reported by the symbol test; calling it raises AttributeError
+            fn.restype = res
+            fn.argtypes = args
+        _lib = handle
+    return _lib
+
+
+_EXC = {ERR_INVALID: ValueError, ERR_UNSUPPORTED: NotImplementedError, ERR_CAPACITY: RuntimeError,
+        ERR_CUDA: RuntimeError, ERR_EMPTY_HEAD: RuntimeError, ERR_TIMEOUT: RuntimeError}
+
+
+def check(status):
+    """Raises the Python exception that corresponds to a non-zero C status."""
+    if status != OK:
+        msg = lib().bsp_last_error().decode('utf-8', 'replace')
+        raise _EXC.get(status, RuntimeError)(msg)

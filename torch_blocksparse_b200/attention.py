@@ -1,0 +1,137 @@
+"""Sparse self-attention wrapper with the reference's interface.
+
+Mirrors torch_blocksparse/deepspeedsparseselfattention.py:
+  SparsityConfig(mode, block, stride, attention, numverts, vertsize)          (8-26)
+  DeepSpeedSparseSelfAttention(sparsity_config, key_padding_mask_mode='add',
+                               attn_mask_mode='mul')                          (109-117)
+  forward(query, key, value, rpe=None, key_padding_mask=None, attn_mask=None) (135-166)
+and is also exported as SparseSelfAttention.
+
+Differences, all additive:
+  * an explicit `layout` (with `block`) may be given instead of a SparsityConfig,
+    for layouts the config cannot describe (e.g. BigBird-style);
+  * the op cache is per instance and keyed on (heads, sequence length), not a
+    class-level dict keyed on the length alone (deepspeedsparseselfattention.py:67-106),
+    so two modules with different layouts never share tables;
+  * `fused=True` (default) computes scores, softmax and the product with V in
+    one kernel without storing the score tensor; `fused=False` runs the
+    reference's three-op chain sdd -> softmax -> dsd.
+"""
+import torch
+import torch.nn as nn
+
+from . import tables
+from .matmul import MatMul
+from .softmax import Softmax
+
+
+class SparsityConfig:
+    """deepspeedsparseselfattention.py:8-26."""
+
+    def __init__(self, mode='fixed', block=16, stride=64, attention='unidirectional', numverts=1, vertsize=1):
+        if mode != 'dense' and mode != 'fixed':
+            raise NotImplementedError('only "dense" and "fixed" modes are supported for now')
+        self.mode = mode
+        self.block = block
+        self.stride = stride
+        if attention != 'unidirectional' and attention != 'bidirectional':
+            raise NotImplementedError('only "uni/bi-directional" attentions are supported for now')
+        self.attention = attention
+        self.numverts = numverts
+        self.vertsize = vertsize
+
+
+class DeepSpeedSparseSelfAttention(nn.Module):
+
+    @staticmethod
+    def _make_layout(num_heads, num_blocks, mode, block_stride, attention, numverts, vertsize):
+        """deepspeedsparseselfattention.py:51-65, built natively."""
+        return tables.make_fixed_layout(num_heads, num_blocks, mode, block_stride, attention, numverts, vertsize)
+
+    def __init__(self, sparsity_config=None, key_padding_mask_mode='add', attn_mask_mode='mul',
+                 layout=None, block=None, fused=True):
+        super().__init__()
+        if layout is not None:
+            if block is None:
+                raise ValueError('an explicit layout needs its block size')
+            if layout.dim() != 3 or layout.size(1) != layout.size(2):
+                raise ValueError('an attention layout must be [heads, L/block, L/block]')
+        self.sparsity_config = sparsity_config if sparsity_config is not None else SparsityConfig()
+        self.layout = layout
+        self.block = block if layout is not None else self.sparsity_config.block
+        self.key_padding_mask_mode = key_padding_mask_mode
+        self.attn_mask_mode = attn_mask_mode
+        self.fused = fused
+        self.ops = dict()
+
+    def get_layout(self, H, L):
+        """The [H, L/block, L/block] layout used for H heads and sequence length L."""
+        block = self.block
+        if L % block != 0:
+            raise ValueError(f'Sequence length {L} must be dividable by block size {block}')
+        if self.layout is not None:
+            if self.layout.size(0) != H or self.layout.size(1) * block != L:
+                raise ValueError(f'layout {tuple(self.layout.shape)} with block {block} does not fit {H} heads of length {L}')
+            return self.layout
+        cfg = self.sparsity_config
+        if cfg.stride % block != 0:
+            raise ValueError(f'Stride {cfg.stride} must be dividable by block size {block}')
+        return DeepSpeedSparseSelfAttention._make_layout(H, L // block, cfg.mode, cfg.stride // block,
+                                                         cfg.attention, cfg.numverts, cfg.vertsize)
+
+    def get_ops(self, H, L):
+        """(sdd_nt, dsd_nn, softmax) for H heads of length L, built once
+        (deepspeedsparseselfattention.py:67-106)."""
+        key = (H, L)
+        if key not in self.ops:
+            layout = self.get_layout(H, L)
+            sdd_nt = MatMul(layout, self.block, 'sdd', trans_a=False, trans_b=True)
+            dsd_nn = MatMul(layout, self.block, 'dsd', trans_a=False, trans_b=False)
+            dsd_nn._meta = sdd_nt.meta            # one metadata buffer per layout
+            self.ops[key] = (sdd_nt, dsd_nn, Softmax(layout, self.block))
+        return self.ops[key]
+
+    def transpose_key_for_scores(self, x, L):
+        """deepspeedsparseselfattention.py:119-123: a key given as [.., hd, L] is
+        viewed back as [.., L, hd]."""
+        bsz, num_heads, seq_len, head_dim = x.size()
+        if seq_len != L:
+            return x.permute(0, 1, 3, 2)
+        return x
+
+    def transpose_mask_for_sparse(self, qtype, x, is_key_padding_mask=False):
+        """deepspeedsparseselfattention.py:125-132."""
+        x = x.type(qtype)
+        if is_key_padding_mask:
+            xdim = x.dim()
+            for d in range(xdim - 1, 0, -1):
+                x = x.squeeze(dim=d)
+            return x
+        return x.squeeze()
+
+    def forward(self, query, key, value, rpe=None, key_padding_mask=None, attn_mask=None):
+        bsz, num_heads, tgt_len, head_dim = query.size()
+        key = self.transpose_key_for_scores(key, tgt_len)
+        if query.shape != key.shape or key.shape != value.shape:
+            raise NotImplementedError('only self-attention is supported for now')
+        if key_padding_mask is not None:
+            key_padding_mask = self.transpose_mask_for_sparse(query.dtype, key_padding_mask, is_key_padding_mask=True)
+            if key_padding_mask.dim() == 1:
+                key_padding_mask = key_padding_mask.unsqueeze(0)
+        if attn_mask is not None:
+            attn_mask = self.transpose_mask_for_sparse(query.dtype, attn_mask)
+        sdd_nt, dsd_nn, softmax = self.get_ops(num_heads, tgt_len)
+        scaling = float(head_dim) ** -0.5
+        if self.fused:
+            from .fused import fused_attention, fused_supported
+            if fused_supported(query, self.block):
+                return fused_attention(query, key, value, sdd_nt.meta, self.block, scaling, rpe,
+                                       key_padding_mask, attn_mask,
+                                       self.key_padding_mask_mode, self.attn_mask_mode)
+        w = sdd_nt(query, key)
+        w = softmax(w, scale=scaling, rpe=rpe, key_padding_mask=key_padding_mask, attn_mask=attn_mask,
+                    key_padding_mask_mode=self.key_padding_mask_mode, attn_mask_mode=self.attn_mask_mode)
+        return dsd_nn(w, value)
+
+
+SparseSelfAttention = DeepSpeedSparseSelfAttention

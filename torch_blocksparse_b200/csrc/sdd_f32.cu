@@ -1,0 +1,7 @@
+// SDD kernels (mma.sync / FFMA path) instantiated for float.
+#include "sdd_impl.cuh"
+namespace bsp {
+template int sdd_mma_t<float>(const void*, const void*, void*, int, int, int,
+                            int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t,
+                            int64_t, const Meta&, cudaStream_t);
+}

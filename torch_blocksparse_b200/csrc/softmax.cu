@@ -1,0 +1,426 @@
+// Block-sparse row softmax, forward and backward, for sm_100a.
+//
+// Replaces softmax_fwd / softmax_bwd of the reference
+// (torch_blocksparse/softmax.py:7-138, 144-194) and their launch code
+// (softmax.py:253-326).
+//
+// Work decomposition: one warp per matrix row.  A row of block-row (h, i) is
+// made of `size` chunks of `block` contiguous elements, one per nonzero block,
+// read with 16-byte vector loads; consecutive warps of a CTA take consecutive
+// rows of the same block-row, so a CTA streams whole blocks.  The row is kept
+// in registers (NV 16-byte vectors per lane, compile-time) between the
+// reduction and the write-back, so x is read once and written once; rows too
+// long for the largest NV fall back to a two-sweep loop that re-reads x.
+// The kernel is pure streaming: its roofline is HBM bandwidth.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <cstdint>
+#include "common.h"
+
+namespace bsp {
+namespace {
+
+constexpr int kWarpsPerCta = 8;
+constexpr float kNegInf = -__builtin_huge_valf();
+
+template <typename T> struct Vec;   // 16 bytes of T
+template <> struct Vec<float> { static constexpr int N = 4; };
+template <> struct Vec<__half> { static constexpr int N = 8; };
+template <> struct Vec<__nv_bfloat16> { static constexpr int N = 8; };
+
+__device__ __forceinline__ float to_f(float v) { return v; }
+__device__ __forceinline__ float to_f(__half v) { return __half2float(v); }
+__device__ __forceinline__ float to_f(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <typename T> __device__ __forceinline__ T from_f(float v);
+template <> __device__ __forceinline__ float from_f<float>(float v) { return v; }
+template <> __device__ __forceinline__ __half from_f<__half>(float v) { return __float2half_rn(v); }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+// 16-byte load of Vec<T>::N elements, converted to float.
+template <typename T>
+__device__ __forceinline__ void load_vec(const T* p, float (&f)[Vec<T>::N]) {
+  constexpr int N = Vec<T>::N;
+  uint4 raw = *reinterpret_cast<const uint4*>(p);
+  const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+  for (int i = 0; i < N; ++i) f[i] = to_f(e[i]);
+}
+
+// Streaming variant for data that is read exactly once (x, dy).
+template <typename T>
+__device__ __forceinline__ void load_vec_stream(const T* p, float (&f)[Vec<T>::N]) {
+  constexpr int N = Vec<T>::N;
+  uint4 raw = __ldcs(reinterpret_cast<const uint4*>(p));
+  const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+  for (int i = 0; i < N; ++i) f[i] = to_f(e[i]);
+}
+
+template <typename T>
+__device__ __forceinline__ void load_scalar(const T* p, float (&f)[Vec<T>::N]) {
+#pragma unroll
+  for (int i = 0; i < Vec<T>::N; ++i) f[i] = to_f(p[i]);
+}
+
+template <typename T>
+__device__ __forceinline__ void store_vec(T* p, const float (&f)[Vec<T>::N]) {
+  constexpr int N = Vec<T>::N;
+  uint4 raw;
+  T* e = reinterpret_cast<T*>(&raw);
+#pragma unroll
+  for (int i = 0; i < N; ++i) e[i] = from_f<T>(f[i]);
+  __stcs(reinterpret_cast<uint4*>(p), raw);
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+struct FwdArgs {
+  void* x; int64_t x_sz;
+  const int32_t* lut;
+  int rows;            // H * Mb * block
+  int block_log2;
+  float scale;
+  const void* rpe; int64_t rpe_sz, rpe_sh, rpe_sr;
+  const void* kpm; int64_t kpm_sz; int kpm_mul;
+  const void* am; int64_t am_sr; int am_mul;
+  int mask_vec;        // masks may be read with 16-byte loads
+};
+
+// Computes the pre-softmax values of one vector slot: x*scale + rpe + kpm + am.
+template <typename T>
+__device__ __forceinline__ void fwd_slot(const FwdArgs& a, const T* xrow, int z, int rxm, const int32_t* ent,
+                                         int c, int block_log2, float (&f)[Vec<T>::N]) {
+  constexpr int N = Vec<T>::N;
+  const int blockid = ent[0], col = ent[1], row = ent[2], head = ent[3];
+  load_vec_stream(xrow + ((int64_t)blockid << (2 * block_log2)) + c, f);
+#pragma unroll
+  for (int i = 0; i < N; ++i) f[i] *= a.scale;
+  const int64_t gcol = ((int64_t)col << block_log2) + c;
+  const int64_t grow = ((int64_t)row << block_log2) + rxm;
+  if (a.rpe) {
+    float r[N];
+    const T* p = reinterpret_cast<const T*>(a.rpe) + z * a.rpe_sz + head * a.rpe_sh + grow * a.rpe_sr + gcol;
+    if (a.mask_vec) load_vec(p, r); else load_scalar(p, r);
+#pragma unroll
+    for (int i = 0; i < N; ++i) f[i] += r[i];
+  }
+  if (a.kpm) {
+    float r[N];
+    const T* p = reinterpret_cast<const T*>(a.kpm) + z * a.kpm_sz + gcol;
+    if (a.mask_vec) load_vec(p, r); else load_scalar(p, r);
+#pragma unroll
+    for (int i = 0; i < N; ++i) f[i] += a.kpm_mul ? (r[i] == 0.f ? kNegInf : 0.f) : r[i];
+  }
+  if (a.am) {
+    float r[N];
+    const T* p = reinterpret_cast<const T*>(a.am) + grow * a.am_sr + gcol;
+    if (a.mask_vec) load_vec(p, r); else load_scalar(p, r);
+#pragma unroll
+    for (int i = 0; i < N; ++i) f[i] += a.am_mul ? (r[i] == 0.f ? kNegInf : 0.f) : r[i];
+  }
+}
+
+// Rows of up to 32 * NV vectors, held in registers.
+template <typename T, int NV>
+__global__ void __launch_bounds__(kWarpsPerCta * 32) softmax_fwd_reg(FwdArgs a) {
+  constexpr int N = Vec<T>::N;
+  const int lane = threadIdx.x & 31;
+  const int row = blockIdx.x * kWarpsPerCta + (threadIdx.x >> 5);
+  if (row >= a.rows) return;
+  const int z = blockIdx.y;
+  const int bl = a.block_log2;
+  const int rbm = row >> bl, rxm = row & ((1 << bl) - 1);
+  const int size = a.lut[2 * rbm], offset = a.lut[2 * rbm + 1];
+  if (size == 0) return;
+  const int nvec = size << (bl - (N == 8 ? 3 : 2));   // vectors in this row
+  T* xrow = reinterpret_cast<T*>(a.x) + z * a.x_sz + ((int64_t)rxm << bl);
+  float f[NV][N];
+  float m = kNegInf;
+#pragma unroll
+  for (int k = 0; k < NV; ++k) {
+    const int s = lane + 32 * k;
+    if (s < nvec) {
+      const int e = s * N;
+      fwd_slot<T>(a, xrow, z, rxm, a.lut + offset + 4 * (e >> bl), e & ((1 << bl) - 1), bl, f[k]);
+#pragma unroll
+      for (int i = 0; i < N; ++i) m = fmaxf(m, f[k][i]);
+    }
+  }
+  m = warp_max(m);
+  float sum = 0.f;
+#pragma unroll
+  for (int k = 0; k < NV; ++k) {
+    if (lane + 32 * k < nvec) {
+#pragma unroll
+      for (int i = 0; i < N; ++i) { f[k][i] = __expf(f[k][i] - m); sum += f[k][i]; }
+    }
+  }
+  sum = warp_sum(sum);
+  const float inv = 1.f / sum;
+#pragma unroll
+  for (int k = 0; k < NV; ++k) {
+    const int s = lane + 32 * k;
+    if (s < nvec) {
+      const int e = s * N;
+      const int blockid = a.lut[offset + 4 * (e >> bl)];
+#pragma unroll
+      for (int i = 0; i < N; ++i) f[k][i] *= inv;
+      store_vec(xrow + ((int64_t)blockid << (2 * bl)) + (e & ((1 << bl) - 1)), f[k]);
+    }
+  }
+}
+
+// Rows of any length: one sweep for max and sum (rescaled on the fly), one to
+// recompute and store.
+template <typename T>
+__global__ void __launch_bounds__(kWarpsPerCta * 32) softmax_fwd_loop(FwdArgs a) {
+  constexpr int N = Vec<T>::N;
+  const int lane = threadIdx.x & 31;
+  const int row = blockIdx.x * kWarpsPerCta + (threadIdx.x >> 5);
+  if (row >= a.rows) return;
+  const int z = blockIdx.y;
+  const int bl = a.block_log2;
+  const int rbm = row >> bl, rxm = row & ((1 << bl) - 1);
+  const int size = a.lut[2 * rbm], offset = a.lut[2 * rbm + 1];
+  if (size == 0) return;
+  const int nvec = size << (bl - (N == 8 ? 3 : 2));
+  T* xrow = reinterpret_cast<T*>(a.x) + z * a.x_sz + ((int64_t)rxm << bl);
+  float m = kNegInf, sum = 0.f;
+  for (int s = lane; s < nvec; s += 32) {
+    float f[N];
+    const int e = s * N;
+    fwd_slot<T>(a, xrow, z, rxm, a.lut + offset + 4 * (e >> bl), e & ((1 << bl) - 1), bl, f);
+    float vm = f[0];
+#pragma unroll
+    for (int i = 1; i < N; ++i) vm = fmaxf(vm, f[i]);
+    const float nm = fmaxf(m, vm);
+    if (nm != kNegInf) {
+      float part = 0.f;
+#pragma unroll
+      for (int i = 0; i < N; ++i) part += __expf(f[i] - nm);
+      sum = sum * __expf(m - nm) + part;
+      m = nm;
+    }
+  }
+  const float gm = warp_max(m);
+  sum = (m == kNegInf) ? 0.f : sum * __expf(m - gm);
+  sum = warp_sum(sum);
+  const float inv = 1.f / sum;
+  for (int s = lane; s < nvec; s += 32) {
+    float f[N];
+    const int e = s * N;
+    const int32_t* ent = a.lut + offset + 4 * (e >> bl);
+    fwd_slot<T>(a, xrow, z, rxm, ent, e & ((1 << bl) - 1), bl, f);
+#pragma unroll
+    for (int i = 0; i < N; ++i) f[i] = __expf(f[i] - gm) * inv;
+    store_vec(xrow + ((int64_t)ent[0] << (2 * bl)) + (e & ((1 << bl) - 1)), f);
+  }
+}
+
+struct BwdArgs {
+  const void* y; void* dy; int64_t y_sz, dy_sz;
+  const int32_t* lut;
+  int rows;
+  int block_log2;
+  float scale;
+};
+
+template <typename T, int NV>
+__global__ void __launch_bounds__(kWarpsPerCta * 32) softmax_bwd_reg(BwdArgs a) {
+  constexpr int N = Vec<T>::N;
+  const int lane = threadIdx.x & 31;
+  const int row = blockIdx.x * kWarpsPerCta + (threadIdx.x >> 5);
+  if (row >= a.rows) return;
+  const int z = blockIdx.y;
+  const int bl = a.block_log2;
+  const int rbm = row >> bl, rxm = row & ((1 << bl) - 1);
+  const int size = a.lut[2 * rbm], offset = a.lut[2 * rbm + 1];
+  if (size == 0) return;
+  const int nvec = size << (bl - (N == 8 ? 3 : 2));
+  const T* yrow = reinterpret_cast<const T*>(a.y) + z * a.y_sz + ((int64_t)rxm << bl);
+  T* drow = reinterpret_cast<T*>(a.dy) + z * a.dy_sz + ((int64_t)rxm << bl);
+  float y[NV][N], d[NV][N];
+  float dot = 0.f;
+#pragma unroll
+  for (int k = 0; k < NV; ++k) {
+    const int s = lane + 32 * k;
+    if (s < nvec) {
+      const int e = s * N;
+      const int64_t off = ((int64_t)a.lut[offset + 4 * (e >> bl)] << (2 * bl)) + (e & ((1 << bl) - 1));
+      load_vec_stream(yrow + off, y[k]);
+      load_vec_stream(drow + off, d[k]);
+#pragma unroll
+      for (int i = 0; i < N; ++i) dot += y[k][i] * d[k][i];
+    }
+  }
+  dot = warp_sum(dot);
+#pragma unroll
+  for (int k = 0; k < NV; ++k) {
+    const int s = lane + 32 * k;
+    if (s < nvec) {
+      const int e = s * N;
+      const int64_t off = ((int64_t)a.lut[offset + 4 * (e >> bl)] << (2 * bl)) + (e & ((1 << bl) - 1));
+#pragma unroll
+      for (int i = 0; i < N; ++i) d[k][i] = y[k][i] * (d[k][i] - dot) * a.scale;
+      store_vec(drow + off, d[k]);
+    }
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kWarpsPerCta * 32) softmax_bwd_loop(BwdArgs a) {
+  constexpr int N = Vec<T>::N;
+  const int lane = threadIdx.x & 31;
+  const int row = blockIdx.x * kWarpsPerCta + (threadIdx.x >> 5);
+  if (row >= a.rows) return;
+  const int z = blockIdx.y;
+  const int bl = a.block_log2;
+  const int rbm = row >> bl, rxm = row & ((1 << bl) - 1);
+  const int size = a.lut[2 * rbm], offset = a.lut[2 * rbm + 1];
+  if (size == 0) return;
+  const int nvec = size << (bl - (N == 8 ? 3 : 2));
+  const T* yrow = reinterpret_cast<const T*>(a.y) + z * a.y_sz + ((int64_t)rxm << bl);
+  T* drow = reinterpret_cast<T*>(a.dy) + z * a.dy_sz + ((int64_t)rxm << bl);
+  float dot = 0.f;
+  for (int s = lane; s < nvec; s += 32) {
+    float y[N], d[N];
+    const int e = s * N;
+    const int64_t off = ((int64_t)a.lut[offset + 4 * (e >> bl)] << (2 * bl)) + (e & ((1 << bl) - 1));
+    load_vec(yrow + off, y);
+    load_vec(drow + off, d);
+#pragma unroll
+    for (int i = 0; i < N; ++i) dot += y[i] * d[i];
+  }
+  dot = warp_sum(dot);
+  for (int s = lane; s < nvec; s += 32) {
+    float y[N], d[N];
+    const int e = s * N;
+    const int64_t off = ((int64_t)a.lut[offset + 4 * (e >> bl)] << (2 * bl)) + (e & ((1 << bl) - 1));
+    load_vec(yrow + off, y);
+    load_vec(drow + off, d);
+#pragma unroll
+    for (int i = 0; i < N; ++i) d[i] = y[i] * (d[i] - dot) * a.scale;
+    store_vec(drow + off, d);
+  }
+}
+
+inline int log2i(int v) { int l = 0; while ((1 << l) < v) ++l; return l; }
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+template <typename T, int NV>
+void launch_fwd_reg(const FwdArgs& a, dim3 grid, cudaStream_t st) {
+  softmax_fwd_reg<T, NV><<<grid, kWarpsPerCta * 32, 0, st>>>(a);
+}
+template <typename T, int NV>
+void launch_bwd_reg(const BwdArgs& a, dim3 grid, cudaStream_t st) {
+  softmax_bwd_reg<T, NV><<<grid, kWarpsPerCta * 32, 0, st>>>(a);
+}
+
+// Picks the smallest register variant that holds a row of `nvec` vectors.
+template <typename T>
+void dispatch_fwd(const FwdArgs& a, int nvec, dim3 grid, cudaStream_t st) {
+  const int need = (nvec + 31) / 32;
+  if (need <= 1) launch_fwd_reg<T, 1>(a, grid, st);
+  else if (need <= 2) launch_fwd_reg<T, 2>(a, grid, st);
+  else if (need <= 3) launch_fwd_reg<T, 3>(a, grid, st);
+  else if (need <= 4) launch_fwd_reg<T, 4>(a, grid, st);
+  else if (need <= 6) launch_fwd_reg<T, 6>(a, grid, st);
+  else if (need <= 9) launch_fwd_reg<T, 9>(a, grid, st);
+  else if (need <= 12) launch_fwd_reg<T, 12>(a, grid, st);
+  else if (need <= 16) launch_fwd_reg<T, 16>(a, grid, st);
+  else softmax_fwd_loop<T><<<grid, kWarpsPerCta * 32, 0, st>>>(a);
+}
+template <typename T>
+void dispatch_bwd(const BwdArgs& a, int nvec, dim3 grid, cudaStream_t st) {
+  const int need = (nvec + 31) / 32;
+  if (need <= 1) launch_bwd_reg<T, 1>(a, grid, st);
+  else if (need <= 2) launch_bwd_reg<T, 2>(a, grid, st);
+  else if (need <= 3) launch_bwd_reg<T, 3>(a, grid, st);
+  else if (need <= 4) launch_bwd_reg<T, 4>(a, grid, st);
+  else if (need <= 6) launch_bwd_reg<T, 6>(a, grid, st);
+  else if (need <= 8) launch_bwd_reg<T, 8>(a, grid, st);
+  else softmax_bwd_loop<T><<<grid, kWarpsPerCta * 32, 0, st>>>(a);
+}
+
+int check_common(int dtype, int Z, int block, int H, int Mb, const int32_t* lut, int maxlut) {
+  if (!valid_dtype(dtype)) return fail(BSP_ERR_INVALID, "unknown dtype %d", dtype);
+  if (!valid_block(block)) return fail(BSP_ERR_INVALID, "block must be 16, 32, 64 or 128 (got %d)", block);
+  if (Z <= 0 || H <= 0 || Mb <= 0 || maxlut < 0) return fail(BSP_ERR_INVALID, "non-positive size");
+  if (Z > 65535) return fail(BSP_ERR_UNSUPPORTED, "batch %d exceeds the grid limit 65535", Z);
+  if (!lut) return fail(BSP_ERR_INVALID, "lut is NULL");
+  if ((int64_t)maxlut * block >= 32768)
+    return fail(BSP_ERR_UNSUPPORTED, "Reductions larger than 32768 elements are not yet implemented");
+  return BSP_OK;
+}
+
+int finish(const char* what) {
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return fail(BSP_ERR_CUDA, "%s launch failed: %s", what, cudaGetErrorString(e));
+  return BSP_OK;
+}
+
+}  // namespace
+}  // namespace bsp
+
+using namespace bsp;
+
+extern "C" int bsp_softmax_fwd(void* x, int dtype, int Z, int64_t x_sz, int block,
+                               int H, int Mb, const int32_t* lut, int maxlut, float scale,
+                               const void* rpe, int64_t rpe_sz, int64_t rpe_sh, int64_t rpe_sr,
+                               const void* kpm, int64_t kpm_sz, int kpm_mul,
+                               const void* am, int64_t am_sr, int am_mul, void* stream) {
+  if (int rc = check_common(dtype, Z, block, H, Mb, lut, maxlut)) return rc;
+  if (!x) return fail(BSP_ERR_INVALID, "x is NULL");
+  if (!aligned16(x)) return fail(BSP_ERR_INVALID, "x must be 16-byte aligned");
+  if (maxlut == 0) return BSP_OK;
+  const int vec = dtype == BSP_F32 ? 4 : 8;
+  if (x_sz % vec) return fail(BSP_ERR_INVALID, "batch stride of x must be a multiple of %d elements", vec);
+  FwdArgs a;
+  a.x = x; a.x_sz = x_sz; a.lut = lut; a.rows = H * Mb * block; a.block_log2 = log2i(block); a.scale = scale;
+  a.rpe = rpe; a.rpe_sz = rpe_sz; a.rpe_sh = rpe_sh; a.rpe_sr = rpe_sr;
+  a.kpm = kpm; a.kpm_sz = kpm_sz; a.kpm_mul = kpm_mul;
+  a.am = am; a.am_sr = am_sr; a.am_mul = am_mul;
+  bool mv = true;
+  if (rpe) mv = mv && aligned16(rpe) && rpe_sz % vec == 0 && rpe_sh % vec == 0 && rpe_sr % vec == 0;
+  if (kpm) mv = mv && aligned16(kpm) && kpm_sz % vec == 0;
+  if (am) mv = mv && aligned16(am) && am_sr % vec == 0;
+  a.mask_vec = mv ? 1 : 0;
+  const dim3 grid((a.rows + kWarpsPerCta - 1) / kWarpsPerCta, Z);
+  const int nvec = maxlut * block / vec;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (dtype == BSP_F32) dispatch_fwd<float>(a, nvec, grid, st);
+  else if (dtype == BSP_F16) dispatch_fwd<__half>(a, nvec, grid, st);
+  else dispatch_fwd<__nv_bfloat16>(a, nvec, grid, st);
+  return finish("softmax forward");
+}
+
+extern "C" int bsp_softmax_bwd(const void* y, void* dy, int dtype, int Z, int64_t y_sz, int64_t dy_sz,
+                               int block, int H, int Mb, const int32_t* lut, int maxlut, float scale,
+                               void* stream) {
+  if (int rc = check_common(dtype, Z, block, H, Mb, lut, maxlut)) return rc;
+  if (!y || !dy) return fail(BSP_ERR_INVALID, "y or dy is NULL");
+  if (!aligned16(y) || !aligned16(dy)) return fail(BSP_ERR_INVALID, "y and dy must be 16-byte aligned");
+  if (maxlut == 0) return BSP_OK;
+  const int vec = dtype == BSP_F32 ? 4 : 8;
+  if (y_sz % vec || dy_sz % vec) return fail(BSP_ERR_INVALID, "batch strides must be multiples of %d elements", vec);
+  BwdArgs a;
+  a.y = y; a.dy = dy; a.y_sz = y_sz; a.dy_sz = dy_sz; a.lut = lut;
+  a.rows = H * Mb * block; a.block_log2 = log2i(block); a.scale = scale;
+  const dim3 grid((a.rows + kWarpsPerCta - 1) / kWarpsPerCta, Z);
+  const int nvec = maxlut * block / vec;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (dtype == BSP_F32) dispatch_bwd<float>(a, nvec, grid, st);
+  else if (dtype == BSP_F16) dispatch_bwd<__half>(a, nvec, grid, st);
+  else dispatch_bwd<__nv_bfloat16>(a, nvec, grid, st);
+  return finish("softmax backward");
+}
