@@ -255,6 +255,27 @@ int bsp_attn_bwd(const void* q, const void* k, const void* v, const void* o,
                  const void* am, int64_t am_sr, int am_mul,
                  void* stream);
 
+/*
+ * The same backward, restricted to the steps selected by the bit mask `parts`
+ * (1: delta = rowsum(o*do), 2: dk and dv, 4: dq), so that a caller can time or
+ * schedule the three launches separately.  Step 2 and 4 read the delta written
+ * by step 1.  bsp_attn_bwd is parts == 7.  No counterpart in the reference.
+ */
+int bsp_attn_bwd_parts(const void* q, const void* k, const void* v, const void* o,
+                       const void* dout, const float* lse, float* delta,
+                       void* dq, void* dk, void* dv,
+                       int dtype, int block, int Z, int H, int L, int D,
+                       int64_t q_sz, int64_t q_sh, int64_t q_sr,
+                       int64_t k_sz, int64_t k_sh, int64_t k_sr,
+                       int64_t v_sz, int64_t v_sh, int64_t v_sr,
+                       int64_t o_sz, int64_t o_sh, int64_t o_sr,
+                       int64_t do_sz, int64_t do_sh, int64_t do_sr,
+                       const int32_t* meta_hdr, const int32_t* meta, float scale,
+                       const void* rpe, int64_t rpe_sz, int64_t rpe_sh, int64_t rpe_sr,
+                       const void* kpm, int64_t kpm_sz, int kpm_mul,
+                       const void* am, int64_t am_sr, int am_mul,
+                       int parts, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

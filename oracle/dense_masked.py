@@ -60,8 +60,8 @@ def matmul_reference(a, b, mode, trans_a, trans_b, layout, block, dc=None,
     formats (block format for the sparse operand).  Returns (c, da, db) in the
     op's formats and in the storage dtype of `a`; da/db are None without `dc`."""
     st = a.dtype
-    x = a.to(compute_dtype)
-    w = b.to(compute_dtype)
+    x = a.detach().to(compute_dtype).clone()
+    w = b.detach().to(compute_dtype).clone()
     if mode == 'dsd':
         x = sparse_to_dense(x, layout, block)
     if mode == 'dds':
@@ -107,7 +107,7 @@ def softmax_reference(xs, layout, block, scale=1.0, rpe=None, key_padding_mask=N
     attn_mask [M,N].  Order: x*scale + rpe + kpm + attn (softmax.py:112-128).
     Returns (y, dx) in block format in xs.dtype (dx None without dy)."""
     st = xs.dtype
-    x = sparse_to_dense(xs.to(compute_dtype), layout, block, fill=float('-inf'))
+    x = sparse_to_dense(xs.detach().to(compute_dtype), layout, block, fill=float('-inf'))
     x.requires_grad_(dy is not None)
     f = x * scale
     if rpe is not None:
@@ -135,7 +135,7 @@ def attention_reference(q, k, v, layout, block, scale, rpe=None, key_padding_mas
     """deepspeedsparseselfattention.py:157-166: sdd(q, k^T) -> softmax(scale, rpe,
     masks) -> dsd(p, v), as dense-masked math.  Returns (o, dq, dk, dv)."""
     st = q.dtype
-    qq, kk, vv = (t.to(compute_dtype).clone().requires_grad_(do is not None) for t in (q, k, v))
+    qq, kk, vv = (t.detach().to(compute_dtype).clone().requires_grad_(do is not None) for t in (q, k, v))
     s = torch.matmul(qq, kk.transpose(2, 3))
     s = mask_dense(s, layout, block, fill=float('-inf'))
     f = s * scale
@@ -147,6 +147,10 @@ def attention_reference(q, k, v, layout, block, scale, rpe=None, key_padding_mas
     if attn_mask is not None:
         f = f + _mask_term(attn_mask.to(compute_dtype), attn_mask_mode)[None, None, :, :]
     p = torch.softmax(f, -1)
+    # a block-row without any nonzero block contributes nothing: the dsd product
+    # zero-fills such rows (matmul.py: zero-length segment of the DSD table)
+    valid = (layout != 0).any(-1).repeat_interleave(block, 1)[None, :, :, None]
+    p = torch.where(valid, p, torch.zeros_like(p))
     o = torch.matmul(p, vv)
     if do is None:
         return o.detach().to(st), None, None, None

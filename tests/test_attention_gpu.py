@@ -1,0 +1,124 @@
+"""GPU parity of the sparse self-attention wrapper (fused kernel and the
+three-op chain) against the dense-masked CPU oracle."""
+import pytest
+import torch
+
+import workloads
+from oracle import dense_masked as dm
+from tests.util import assert_close
+from torch_blocksparse_b200 import DeepSpeedSparseSelfAttention, SparseSelfAttention, SparsityConfig, layouts
+
+pytestmark = pytest.mark.gpu
+DEV = 'cuda'
+
+
+def run_module(mod, q, k, v, do, **kw):
+    qg, kg, vg = (t.to(DEV).requires_grad_() for t in (q, k, v))
+    gkw = {n: (t.to(DEV) if torch.is_tensor(t) else t) for n, t in kw.items()}
+    o = mod(qg, kg, vg, **gkw)
+    o.backward(do.to(DEV))
+    return o, qg.grad, kg.grad, vg.grad
+
+
+def check(layout, block, q, k, v, do, fused, kp_mode='add', am_mode='mul', **kw):
+    scale = q.size(-1) ** -0.5
+    want = dm.attention_reference(q, k, v, layout, block, scale, do=do, key_padding_mask_mode=kp_mode,
+                                  attn_mask_mode=am_mode, **kw)
+    mod = SparseSelfAttention(layout=layout, block=block, fused=fused, key_padding_mask_mode=kp_mode,
+                              attn_mask_mode=am_mode)
+    got = run_module(mod, q, k, v, do, **kw)
+    for name, g, w in zip(('o', 'dq', 'dk', 'dv'), got, want):
+        assert_close(g, w, '%s (fused=%s)' % (name, fused))
+
+
+def rand_qkv(Z, H, L, D, dtype, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    return tuple(torch.randn((Z, H, L, D), generator=g).to(dtype) for _ in range(4))
+
+
+@pytest.mark.parametrize('fused', [True, False])
+@pytest.mark.parametrize('block,D', [(16, 64), (32, 64), (64, 64), (128, 64), (32, 128), (64, 128), (128, 128)])
+@pytest.mark.parametrize('dtype', [torch.float16, torch.bfloat16])
+def test_random_layouts(block, D, dtype, fused):
+    H, nb = 2, 6
+    g = torch.Generator().manual_seed(block + D)
+    layout = (torch.rand((H, nb, nb), generator=g) > 0.5).long()
+    layout[:, :, 0] = 1
+    layout[0, 3, :] = 0                       # a block-row without any block
+    layout[1, :, 4] = 0                       # a block-column without any block
+    q, k, v, do = rand_qkv(2, H, nb * block, D, dtype, seed=block)
+    check(layout, block, q, k, v, do, fused)
+
+
+@pytest.mark.parametrize('fused', [True, False])
+@pytest.mark.parametrize('kp_mode,am_mode', [('add', 'mul'), ('mul', 'add')])
+def test_masks_and_rpe(kp_mode, am_mode, fused):
+    Z, H, L, D, block, dtype = 2, 2, 256, 64, 32, torch.float16
+    g = torch.Generator().manual_seed(17)
+    layout = (torch.rand((H, L // block, L // block), generator=g) > 0.4).long()
+    layout[:, :, 0] = 1
+    q, k, v, do = rand_qkv(Z, H, L, D, dtype, seed=3)
+    rpe = (0.5 * torch.randn((Z, H, L, L), generator=g)).to(dtype)
+    keep_k = torch.randint(0, 2, (Z, L), generator=g).bool()
+    keep_k[:, 0] = True
+    keep_a = torch.tril(torch.ones((L, L))).bool()
+    ninf = float('-inf')
+    kp = keep_k.to(dtype) if kp_mode == 'mul' else torch.where(keep_k, 0.0, ninf).to(dtype)
+    am = keep_a.to(dtype) if am_mode == 'mul' else torch.where(keep_a, 0.0, ninf).to(dtype)
+    check(layout, block, q, k, v, do, fused, kp_mode, am_mode, rpe=rpe, key_padding_mask=kp, attn_mask=am)
+
+
+def test_sparsity_config_path_and_key_transposed():
+    """The reference's constructor path: SparsityConfig 'fixed', key handed over
+    pre-transposed as [.., head_dim, L] (deepspeedsparseselfattention.py:119-123)."""
+    cfg = SparsityConfig(mode='fixed', block=16, stride=64, attention='unidirectional', numverts=2, vertsize=1)
+    Z, H, L, D = 2, 4, 256, 64
+    q, k, v, do = rand_qkv(Z, H, L, D, torch.float16, seed=5)
+    layout = layouts.fixed(H, L // 16, 4, 'unidirectional', 2, 1)
+    want = dm.attention_reference(q, k, v, layout, 16, D ** -0.5, do=do)
+    for fused in (True, False):
+        mod = DeepSpeedSparseSelfAttention(cfg, fused=fused)
+        qg, kg, vg = (t.to(DEV).requires_grad_() for t in (q, k, v))
+        o = mod(qg, kg.transpose(2, 3), vg)
+        o.backward(do.to(DEV))
+        for name, g, w in zip(('o', 'dq', 'dk', 'dv'), (o, qg.grad, kg.grad, vg.grad), want):
+            assert_close(g, w, '%s (fused=%s)' % (name, fused))
+    with pytest.raises(NotImplementedError):
+        DeepSpeedSparseSelfAttention(cfg)(q.to(DEV), k[:, :, :128].to(DEV), v.to(DEV))
+    with pytest.raises(ValueError):
+        DeepSpeedSparseSelfAttention(SparsityConfig(block=16, stride=64))(
+            torch.zeros((1, 1, 40, 64), device=DEV, dtype=torch.float16),
+            torch.zeros((1, 1, 40, 64), device=DEV, dtype=torch.float16),
+            torch.zeros((1, 1, 40, 64), device=DEV, dtype=torch.float16))
+
+
+@pytest.mark.parametrize('attention', ['unidirectional', 'bidirectional'])
+def test_config4_small(attention):
+    c = workloads.config4(attention, small=True)
+    for fused in (True, False):
+        check(c['layout'], c['block'], c['q'], c['k'], c['v'], c['do'], fused)
+
+
+def test_config5_small():
+    c = workloads.config5(small=True)
+    for fused in (True, False):
+        check(c['layout'], c['block'], c['q'], c['k'], c['v'], c['do'], fused)
+
+
+def test_config4_full_fused_matches_chain_and_oracle_slice():
+    """Full-size configuration 4 (Z reduced to 2 to bound host memory): the fused
+    kernel against the three-op chain everywhere, and against the oracle on one
+    (batch, head) slice."""
+    c = workloads.config4('unidirectional', small=False, Z=2)
+    layout, block = c['layout'], c['block']
+    outs = {}
+    for fused in (True, False):
+        mod = SparseSelfAttention(layout=layout, block=block, fused=fused)
+        outs[fused] = run_module(mod, c['q'], c['k'], c['v'], c['do'])
+    for name, a, b in zip(('o', 'dq', 'dk', 'dv'), outs[True], outs[False]):
+        assert_close(a, b, 'fused vs chain ' + name)
+    z, h = 1, 15
+    want = dm.attention_reference(c['q'][z:z + 1, h:h + 1], c['k'][z:z + 1, h:h + 1], c['v'][z:z + 1, h:h + 1],
+                                  layout[h:h + 1], block, c['scale'], do=c['do'][z:z + 1, h:h + 1])
+    for name, g, w in zip(('o', 'dq', 'dk', 'dv'), outs[True], want):
+        assert_close(g[z:z + 1, h:h + 1], w, 'oracle slice ' + name)

@@ -1,0 +1,181 @@
+"""GPU parity of the block-sparse MatMul (sdd / dsd / dds, forward and both
+gradients) against the dense-masked CPU oracle."""
+import pytest
+import torch
+
+import workloads
+from oracle import dense_masked as dm
+from tests.util import assert_close, head_blocks, load_npz
+from torch_blocksparse_b200 import MatMul
+
+pytestmark = pytest.mark.gpu
+DEV = 'cuda'
+
+
+def run_both(layout, block, mode, ta, tb, a, b, dc, what=''):
+    want_c, want_da, want_db = dm.matmul_reference(a, b, mode, ta, tb, layout, block, dc)
+    op = MatMul(layout, block, mode, trans_a=ta, trans_b=tb)
+    ag = a.to(DEV).requires_grad_()
+    bg = b.to(DEV).requires_grad_()
+    c = op(ag, bg)
+    c.backward(dc.to(DEV))
+    assert_close(c, want_c, what + ' c')
+    assert_close(ag.grad, want_da, what + ' da')
+    assert_close(bg.grad, want_db, what + ' db')
+
+
+def make_case(mode, ta, tb, block, dtype, Z=3, H=2, M=256, N=512, K=384, rho=0.5, seed=1, dist='rand'):
+    """Inputs shaped as in the reference's test (tests/test_matmul.py:44-65)."""
+    g = torch.Generator().manual_seed(seed)
+    AS = (K, M) if ta else (M, K)
+    BS = (N, K) if tb else (K, N)
+    shape = {'sdd': (M, N), 'dsd': AS, 'dds': BS}[mode]
+    layout = (torch.rand((H, shape[0] // block, shape[1] // block), generator=g) > rho).long()
+    layout[:, 0, 0] = 1
+    draw = (lambda s: torch.rand(s, generator=g)) if dist == 'rand' else (lambda s: torch.randn(s, generator=g) * 0.1)
+    x = draw((Z, H) + AS).to(dtype)
+    w = draw((Z, H) + BS).to(dtype)
+    dy = draw((Z, H, M, N)).to(dtype)
+    a = dm.dense_to_sparse(x, layout, block) if mode == 'dsd' else x
+    b = dm.dense_to_sparse(w, layout, block) if mode == 'dds' else w
+    dc = dm.dense_to_sparse(dy, layout, block) if mode == 'sdd' else dy
+    return layout, a, b, dc
+
+
+# the reference's own grid (tests/test_matmul.py:87-103): 3 modes x 4 transpose
+# combinations at block 32, and 3 modes x blocks 16/32/64, FP16, Z=3 H=2 M=256 N=512 K=384
+@pytest.mark.parametrize('mode', ['sdd', 'dsd', 'dds'])
+@pytest.mark.parametrize('ta', [False, True])
+@pytest.mark.parametrize('tb', [False, True])
+def test_reference_grid_transposes(mode, ta, tb):
+    layout, a, b, dc = make_case(mode, ta, tb, 32, torch.float16)
+    run_both(layout, 32, mode, ta, tb, a, b, dc, '%s ta=%d tb=%d' % (mode, ta, tb))
+
+
+@pytest.mark.parametrize('mode', ['sdd', 'dsd', 'dds'])
+@pytest.mark.parametrize('block', [16, 32, 64, 128])
+@pytest.mark.parametrize('dtype', [torch.float16, torch.bfloat16, torch.float32])
+def test_blocks_and_dtypes(mode, block, dtype):
+    layout, a, b, dc = make_case(mode, False, False, block, dtype, Z=2, dist='randn' if dtype != torch.float32 else 'rand')
+    run_both(layout, block, mode, False, False, a, b, dc, '%s block %d %s' % (mode, block, dtype))
+
+
+@pytest.mark.parametrize('mode', ['sdd', 'dsd', 'dds'])
+@pytest.mark.parametrize('ta', [False, True])
+@pytest.mark.parametrize('tb', [False, True])
+def test_fp32_transposes_block16(mode, ta, tb):
+    layout, a, b, dc = make_case(mode, ta, tb, 16, torch.float32, Z=2, M=64, N=96, K=48)
+    run_both(layout, 16, mode, ta, tb, a, b, dc, '%s fp32 ta=%d tb=%d' % (mode, ta, tb))
+
+
+@pytest.mark.parametrize('mode', ['sdd', 'dsd', 'dds'])
+def test_golden_reference_oracle_cases(mode):
+    """Fixtures produced by the reference's own run_mm_reference (FP32, block 16)."""
+    d = load_npz('dense_masked.npz')
+    for ta in (0, 1):
+        for tb in (0, 1):
+            key = 'mm_%s_%d%d_' % (mode, ta, tb)
+            layout = torch.from_numpy(d[key + 'layout'])
+            x, w, dy = (torch.from_numpy(d[key + n]) for n in ('x', 'w', 'dy'))
+            y, dx, dw = (torch.from_numpy(d[key + n]) for n in ('y', 'dx', 'dw'))
+            a = dm.dense_to_sparse(x, layout, 16) if mode == 'dsd' else x
+            b = dm.dense_to_sparse(w, layout, 16) if mode == 'dds' else w
+            dc = dm.dense_to_sparse(dy, layout, 16) if mode == 'sdd' else dy
+            op = MatMul(layout, 16, mode, trans_a=bool(ta), trans_b=bool(tb))
+            ag, bg = a.to(DEV).requires_grad_(), b.to(DEV).requires_grad_()
+            c = op(ag, bg)
+            c.backward(dc.to(DEV))
+            assert_close(c, y, key + 'y')
+            assert_close(ag.grad, dx, key + 'dx')
+            assert_close(bg.grad, dw, key + 'dw')
+
+
+def test_empty_rows_are_zero_filled_and_every_block_written():
+    """Dense outputs are allocated uninitialised: block-rows / columns of the
+    layout without a nonzero block must come back as zeros."""
+    block = 32
+    layout = torch.zeros((2, 4, 4), dtype=torch.long)
+    layout[0, 1, 2] = layout[0, 1, 3] = layout[1, 3, 0] = 1
+    g = torch.Generator().manual_seed(4)
+    s = torch.randn((2, 3, block, block), generator=g).half()
+    d = torch.randn((2, 2, 128, 64), generator=g).half()
+    for ta in (False, True):
+        want, _, _ = dm.matmul_reference(s, d, 'dsd', ta, False, layout, block)
+        got = MatMul(layout, block, 'dsd', trans_a=ta)(s.to(DEV), d.to(DEV))
+        assert_close(got, want, 'dsd ta=%d' % ta)
+    dd = torch.randn((2, 2, 64, 128), generator=g).half()
+    want, _, _ = dm.matmul_reference(dd, s, 'dds', False, False, layout, block)
+    assert_close(MatMul(layout, block, 'dds')(dd.to(DEV), s.to(DEV)), want, 'dds')
+
+
+def test_bogus_sdd_table_layout_still_matches_the_oracle():
+    """A layout for which the reference's 4x4 packing emits entries outside the
+    layout: the table is reproduced, the kernel must not execute from it."""
+    z = load_npz('lut_small.npz')
+    layout = torch.from_numpy(z['bogus_entries/layout'])
+    block = 16
+    g = torch.Generator().manual_seed(8)
+    a = torch.rand((1, 2, 256, 64), generator=g)
+    b = torch.rand((1, 2, 64, 512), generator=g)
+    want, _, _ = dm.matmul_reference(a, b, 'sdd', False, False, layout, block)
+    assert_close(MatMul(layout, block, 'sdd')(a.to(DEV), b.to(DEV)), want, 'sdd')
+
+
+def test_non_contiguous_and_odd_inputs():
+    """Permuted views, K not a multiple of 32, dense widths that are not tile multiples."""
+    block = 32
+    g = torch.Generator().manual_seed(6)
+    layout = (torch.rand((2, 4, 3), generator=g) > 0.3).long()
+    layout[:, 0, 0] = 1
+    a = torch.randn((2, 2, 128, 48), generator=g).half()          # K = 48
+    bt = torch.randn((2, 2, 96, 48), generator=g).half()
+    want, _, _ = dm.matmul_reference(a, bt, 'sdd', False, True, layout, block)
+    got = MatMul(layout, block, 'sdd', trans_b=True)(a.to(DEV), bt.to(DEV))
+    assert_close(got, want, 'sdd K=48')
+    # the same product with b handed over as a permuted view of a [.., K, N] tensor
+    b_kn = bt.transpose(2, 3).contiguous().to(DEV)
+    got = MatMul(layout, block, 'sdd', trans_b=True)(a.to(DEV), b_kn.transpose(2, 3))
+    assert_close(got, want, 'sdd permuted view')
+    # dsd with a dense width of 72 (not a multiple of the 64-wide tile)
+    s = torch.randn((2, int(layout.sum()), block, block), generator=g).half()
+    d = torch.randn((2, 2, 96, 72), generator=g).half()
+    want, _, _ = dm.matmul_reference(s, d, 'dsd', False, False, layout, block)
+    assert_close(MatMul(layout, block, 'dsd')(s.to(DEV), d.to(DEV)), want, 'dsd N=72')
+    with pytest.raises(ValueError):
+        MatMul(layout, block, 'sdd')(torch.zeros((1, 2, 128, 40), device=DEV), torch.zeros((1, 2, 40, 96), device=DEV))
+
+
+def test_config1():
+    c = workloads.config1()
+    want, _, _ = dm.matmul_reference(c['a'], c['b'], 'sdd', True, False, c['layout'], 16)
+    got = MatMul(c['layout'], 16, 'sdd', trans_a=True, trans_b=False)(c['a'].to(DEV), c['b'].to(DEV))
+    assert got.shape == (4, int(c['layout'].sum()), 16, 16)
+    assert_close(got, want, 'config 1')
+
+
+@pytest.mark.parametrize('mode', ['dsd', 'dds'])
+@pytest.mark.parametrize('ta', [False, True])
+@pytest.mark.parametrize('tb', [False, True])
+def test_config2_small(mode, ta, tb):
+    c = workloads.config2(mode, ta, tb, small=True)
+    run_both(c['layout'], 32, mode, ta, tb, c['a'], c['b'], c['dc'], 'config 2 small')
+
+
+@pytest.mark.parametrize('mode,ta,tb', [('dsd', False, False), ('dds', True, True)])
+def test_config2_full_slice(mode, ta, tb):
+    """Full-size configuration 2 on the GPU; the oracle checks one (batch, head)
+    slice of the result and of both gradients."""
+    c = workloads.config2(mode, ta, tb, small=False)
+    layout, block = c['layout'], 32
+    op = MatMul(layout, block, mode, trans_a=ta, trans_b=tb)
+    ag, bg = c['a'].to(DEV).requires_grad_(), c['b'].to(DEV).requires_grad_()
+    out = op(ag, bg)
+    out.backward(c['dc'].to(DEV))
+    z, h = 7, 5
+    b0, b1 = head_blocks(layout, h)
+    sl = lambda t, sparse: (t[z:z + 1, b0:b1] if sparse else t[z:z + 1, h:h + 1])
+    a_s, b_s = sl(c['a'], mode == 'dsd'), sl(c['b'], mode == 'dds')
+    want_c, want_da, want_db = dm.matmul_reference(a_s, b_s, mode, ta, tb, layout[h:h + 1], block, sl(c['dc'], False))
+    assert_close(sl(out, False), want_c, 'c')
+    assert_close(sl(ag.grad, mode == 'dsd'), want_da, 'da')
+    assert_close(sl(bg.grad, mode == 'dds'), want_db, 'db')

@@ -47,6 +47,8 @@ _SIGNATURES = {
                      + _MASKS + [c_void_p]),
     'bsp_attn_bwd': (c_int, [c_void_p] * 10 + [c_int] * 6 + [c_int64] * 15 + [c_void_p, c_void_p, c_float]
                      + _MASKS + [c_void_p]),
+    'bsp_attn_bwd_parts': (c_int, [c_void_p] * 10 + [c_int] * 6 + [c_int64] * 15 + [c_void_p, c_void_p, c_float]
+                           + _MASKS + [c_int, c_void_p]),
 }
 
 

@@ -1,0 +1,128 @@
+// C-ABI entry points of the fused block-sparse self-attention.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include "attn_impl.cuh"
+
+namespace bsp {
+namespace {
+
+bool al16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+int check_qkv(const char* name, const void* p, int64_t sz, int64_t sh, int64_t sr) {
+  if (!p) return fail(BSP_ERR_INVALID, "attention: %s is NULL", name);
+  if (!al16(p) || sz % 8 || sh % 8 || sr % 8)
+    return fail(BSP_ERR_INVALID, "attention: %s must be 16-byte aligned with strides that are multiples of 8 elements", name);
+  return BSP_OK;
+}
+
+int fill_common(AttnArgs& p, int dtype, int block, int Z, int H, int L, int D,
+                const int32_t* hdr, const int32_t* meta, float scale,
+                const void* rpe, int64_t rpe_sz, int64_t rpe_sh, int64_t rpe_sr,
+                const void* kpm, int64_t kpm_sz, int kpm_mul,
+                const void* am, int64_t am_sr, int am_mul) {
+  if (dtype != BSP_F16 && dtype != BSP_BF16)
+    return fail(BSP_ERR_UNSUPPORTED, "fused attention supports FP16 and BF16 (use the three-op chain for FP32)");
+  if (!valid_block(block)) return fail(BSP_ERR_INVALID, "attention: block must be 16, 32, 64 or 128 (got %d)", block);
+  if (D != 64 && D != 128) return fail(BSP_ERR_UNSUPPORTED, "fused attention supports head dimensions 64 and 128 (got %d)", D);
+  if (Z <= 0 || Z > 65535) return fail(BSP_ERR_INVALID, "attention: batch %d outside [1, 65535]", Z);
+  if (!hdr || !meta) return fail(BSP_ERR_INVALID, "attention: metadata pointer is NULL");
+  if (hdr[0] != BSP_META_MAGIC) return fail(BSP_ERR_INVALID, "attention: metadata header is corrupt (bad magic)");
+  if (hdr[1] != H || hdr[2] != hdr[3] || hdr[2] * block != L)
+    return fail(BSP_ERR_INVALID, "attention: layout [%d,%d,%d] with block %d does not fit %d heads of length %d",
+                hdr[1], hdr[2], hdr[3], block, H, L);
+  Meta m = meta_view(meta, hdr[1], hdr[2], hdr[3], hdr[4], hdr[5], hdr[6]);
+  p.H = H; p.L = L; p.nb = L / block; p.scale = scale;
+  p.row_ptr = m.row_ptr; p.blk_col = m.blk_col; p.row_order = m.row_order;
+  p.col_ptr = m.col_ptr; p.col_row = m.col_row; p.col_order = m.col_order;
+  p.m.rpe = rpe; p.m.rpe_sz = rpe_sz; p.m.rpe_sh = rpe_sh; p.m.rpe_sr = rpe_sr;
+  p.m.kpm = kpm; p.m.kpm_sz = kpm_sz; p.m.kpm_mul = kpm_mul;
+  p.m.am = am; p.m.am_sr = am_sr; p.m.am_mul = am_mul;
+  return BSP_OK;
+}
+
+}  // namespace
+}  // namespace bsp
+
+using namespace bsp;
+
+extern "C" int bsp_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse,
+                            int dtype, int block, int Z, int H, int L, int D,
+                            int64_t q_sz, int64_t q_sh, int64_t q_sr,
+                            int64_t k_sz, int64_t k_sh, int64_t k_sr,
+                            int64_t v_sz, int64_t v_sh, int64_t v_sr,
+                            int64_t o_sz, int64_t o_sh, int64_t o_sr,
+                            const int32_t* meta_hdr, const int32_t* meta, float scale,
+                            const void* rpe, int64_t rpe_sz, int64_t rpe_sh, int64_t rpe_sr,
+                            const void* kpm, int64_t kpm_sz, int kpm_mul,
+                            const void* am, int64_t am_sr, int am_mul, void* stream) {
+  AttnArgs p = {};
+  if (int rc = fill_common(p, dtype, block, Z, H, L, D, meta_hdr, meta, scale, rpe, rpe_sz, rpe_sh, rpe_sr,
+                           kpm, kpm_sz, kpm_mul, am, am_sr, am_mul)) return rc;
+  if (int rc = check_qkv("q", q, q_sz, q_sh, q_sr)) return rc;
+  if (int rc = check_qkv("k", k, k_sz, k_sh, k_sr)) return rc;
+  if (int rc = check_qkv("v", v, v_sz, v_sh, v_sr)) return rc;
+  if (int rc = check_qkv("o", o, o_sz, o_sh, o_sr)) return rc;
+  if (!lse) return fail(BSP_ERR_INVALID, "attention: lse is NULL");
+  p.q = q; p.k = k; p.v = v; p.o_w = o; p.lse = lse;
+  p.q_sz = q_sz; p.q_sh = q_sh; p.q_sr = q_sr; p.k_sz = k_sz; p.k_sh = k_sh; p.k_sr = k_sr;
+  p.v_sz = v_sz; p.v_sh = v_sh; p.v_sr = v_sr; p.o_sz = o_sz; p.o_sh = o_sh; p.o_sr = o_sr;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (dtype == BSP_F16) return attn_fwd_t<__half>(p, block, D, Z, st);
+  return attn_fwd_t<__nv_bfloat16>(p, block, D, Z, st);
+}
+
+extern "C" int bsp_attn_bwd_parts(const void* q, const void* k, const void* v, const void* o,
+                            const void* dout, const float* lse, float* delta,
+                            void* dq, void* dk, void* dv,
+                            int dtype, int block, int Z, int H, int L, int D,
+                            int64_t q_sz, int64_t q_sh, int64_t q_sr,
+                            int64_t k_sz, int64_t k_sh, int64_t k_sr,
+                            int64_t v_sz, int64_t v_sh, int64_t v_sr,
+                            int64_t o_sz, int64_t o_sh, int64_t o_sr,
+                            int64_t do_sz, int64_t do_sh, int64_t do_sr,
+                            const int32_t* meta_hdr, const int32_t* meta, float scale,
+                            const void* rpe, int64_t rpe_sz, int64_t rpe_sh, int64_t rpe_sr,
+                            const void* kpm, int64_t kpm_sz, int kpm_mul,
+                            const void* am, int64_t am_sr, int am_mul, int parts, void* stream) {
+  if (parts <= 0 || parts > 7) return fail(BSP_ERR_INVALID, "attention: parts must be a bit mask in [1, 7]");
+  AttnArgs p = {};
+  if (int rc = fill_common(p, dtype, block, Z, H, L, D, meta_hdr, meta, scale, rpe, rpe_sz, rpe_sh, rpe_sr,
+                           kpm, kpm_sz, kpm_mul, am, am_sr, am_mul)) return rc;
+  if (int rc = check_qkv("q", q, q_sz, q_sh, q_sr)) return rc;
+  if (int rc = check_qkv("k", k, k_sz, k_sh, k_sr)) return rc;
+  if (int rc = check_qkv("v", v, v_sz, v_sh, v_sr)) return rc;
+  if (int rc = check_qkv("o", o, o_sz, o_sh, o_sr)) return rc;
+  if (int rc = check_qkv("do", dout, do_sz, do_sh, do_sr)) return rc;
+  if (!lse || !delta) return fail(BSP_ERR_INVALID, "attention: lse or delta is NULL");
+  if (!al16(lse) || !al16(delta)) return fail(BSP_ERR_INVALID, "attention: lse and delta must be 16-byte aligned");
+  if (!dq || !dk || !dv || !al16(dq) || !al16(dk) || !al16(dv))
+    return fail(BSP_ERR_INVALID, "attention: dq, dk, dv must be non-NULL and 16-byte aligned");
+  p.q = q; p.k = k; p.v = v; p.o = o; p.dout = dout;
+  p.lse = const_cast<float*>(lse); p.delta = delta; p.dq = dq; p.dk = dk; p.dv = dv;
+  p.q_sz = q_sz; p.q_sh = q_sh; p.q_sr = q_sr; p.k_sz = k_sz; p.k_sh = k_sh; p.k_sr = k_sr;
+  p.v_sz = v_sz; p.v_sh = v_sh; p.v_sr = v_sr; p.o_sz = o_sz; p.o_sh = o_sh; p.o_sr = o_sr;
+  p.do_sz = do_sz; p.do_sh = do_sh; p.do_sr = do_sr;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (dtype == BSP_F16) return attn_bwd_t<__half>(p, block, D, Z, parts, st);
+  return attn_bwd_t<__nv_bfloat16>(p, block, D, Z, parts, st);
+}
+
+extern "C" int bsp_attn_bwd(const void* q, const void* k, const void* v, const void* o,
+                            const void* dout, const float* lse, float* delta,
+                            void* dq, void* dk, void* dv,
+                            int dtype, int block, int Z, int H, int L, int D,
+                            int64_t q_sz, int64_t q_sh, int64_t q_sr,
+                            int64_t k_sz, int64_t k_sh, int64_t k_sr,
+                            int64_t v_sz, int64_t v_sh, int64_t v_sr,
+                            int64_t o_sz, int64_t o_sh, int64_t o_sr,
+                            int64_t do_sz, int64_t do_sh, int64_t do_sr,
+                            const int32_t* meta_hdr, const int32_t* meta, float scale,
+                            const void* rpe, int64_t rpe_sz, int64_t rpe_sh, int64_t rpe_sr,
+                            const void* kpm, int64_t kpm_sz, int kpm_mul,
+                            const void* am, int64_t am_sr, int am_mul, void* stream) {
+  return bsp_attn_bwd_parts(q, k, v, o, dout, lse, delta, dq, dk, dv, dtype, block, Z, H, L, D,
+                            q_sz, q_sh, q_sr, k_sz, k_sh, k_sr, v_sz, v_sh, v_sr, o_sz, o_sh, o_sr,
+                            do_sz, do_sh, do_sr, meta_hdr, meta, scale, rpe, rpe_sz, rpe_sh, rpe_sr,
+                            kpm, kpm_sz, kpm_mul, am, am_sr, am_mul, 7, stream);
+}

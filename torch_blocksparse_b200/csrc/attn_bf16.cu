@@ -1,0 +1,6 @@
+// Fused attention kernels (mma.sync path) instantiated for __nv_bfloat16.
+#include "attn_impl.cuh"
+namespace bsp {
+template int attn_fwd_t<__nv_bfloat16>(const AttnArgs&, int, int, int, cudaStream_t);
+template int attn_bwd_t<__nv_bfloat16>(const AttnArgs&, int, int, int, int, cudaStream_t);
+}

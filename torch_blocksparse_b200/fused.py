@@ -1,0 +1,120 @@
+"""Fused sparse self-attention: scores, softmax and the product with V in one
+kernel, with a matching three-kernel backward.
+
+The reference computes the same result with three ops and keeps the score
+tensor [Z, nnz, block, block] in memory
+(torch_blocksparse/deepspeedsparseselfattention.py:157-166); this path never
+materialises it.  rpe and the masks follow the softmax op's conventions
+(torch_blocksparse/softmax.py:104-128) and receive no gradient.
+"""
+import torch
+
+from . import _lib
+from .matmul import _dtype_code, _require_cuda, _stream
+
+
+def fused_supported(q, block):
+    return q.dtype in (torch.float16, torch.bfloat16) and q.size(-1) in (64, 128) and block in (16, 32, 64, 128)
+
+
+def _rows(x):
+    """[Z,H,L,D] operand with unit stride on D and 16-byte friendly strides."""
+    if x.stride(3) != 1 or x.data_ptr() % 16 or any(s % 8 for s in x.stride()[:3]):
+        x = x.contiguous()
+    return x
+
+
+def _mask_args(Z, H, L, dtype, rpe, kpm, am, kp_mode, am_mode):
+    """Validates the optional bias / masks and flattens them to C arguments;
+    returns (args tuple, tensors to keep alive)."""
+    keep = []
+    r_ptr, rz, rh, rr = None, 0, 0, 0
+    if rpe is not None:
+        if rpe.dtype != dtype:
+            raise ValueError('relative position embedding must be %s' % dtype)
+        if rpe.dim() == 3:
+            rpe = rpe.unsqueeze(0)
+        if rpe.dim() != 4 or tuple(rpe.shape[1:]) != (H, L, L) or rpe.size(0) not in (1, Z):
+            raise ValueError('rpe must be [Z, %d, %d, %d] (got %s)' % (H, L, L, tuple(rpe.shape)))
+        if rpe.stride(3) != 1:
+            rpe = rpe.contiguous()
+        keep.append(rpe)
+        r_ptr, rz, rh, rr = rpe.data_ptr(), (0 if rpe.size(0) == 1 else rpe.stride(0)), rpe.stride(1), rpe.stride(2)
+    k_ptr, kz = None, 0
+    if kpm is not None:
+        if kpm.dtype != dtype:
+            raise ValueError('Key padding mask must be %s' % dtype)
+        if kpm.dim() != 2 or kpm.size(1) != L or kpm.size(0) not in (1, Z):
+            raise ValueError('key_padding_mask must be [Z, %d] (got %s)' % (L, tuple(kpm.shape)))
+        if kpm.stride(1) != 1:
+            kpm = kpm.contiguous()
+        keep.append(kpm)
+        k_ptr, kz = kpm.data_ptr(), (0 if kpm.size(0) == 1 else kpm.stride(0))
+    a_ptr, ar = None, 0
+    if am is not None:
+        if am.dtype != dtype:
+            raise ValueError('Attention mask must be %s' % dtype)
+        if am.dim() != 2 or tuple(am.shape) != (L, L):
+            raise ValueError('attn_mask must be [%d, %d] (got %s)' % (L, L, tuple(am.shape)))
+        if am.stride(1) != 1:
+            am = am.contiguous()
+        keep.append(am)
+        a_ptr, ar = am.data_ptr(), am.stride(0)
+    for name, mode in (('key_padding_mask_mode', kp_mode), ('attn_mask_mode', am_mode)):
+        if mode not in ('add', 'mul'):
+            raise ValueError("%s must be 'add' or 'mul'" % name)
+    return (r_ptr, rz, rh, rr, k_ptr, kz, 1 if kp_mode == 'mul' else 0, a_ptr, ar, 1 if am_mode == 'mul' else 0), keep
+
+
+class _fused_attention(torch.autograd.Function):
+
+    @staticmethod
+    def forward(ctx, q, k, v, meta, block, scale, rpe, kpm, am, kp_mode, am_mode):
+        _require_cuda(q, k, v)
+        Z, H, L, D = q.shape
+        q, k, v = _rows(q), _rows(k), _rows(v)
+        margs, keep = _mask_args(Z, H, L, q.dtype, rpe, kpm, am, kp_mode, am_mode)
+        o = torch.empty((Z, H, L, D), dtype=q.dtype, device=q.device)
+        lse = torch.empty((Z, H, L), dtype=torch.float32, device=q.device)
+        _lib.check(_lib.lib().bsp_attn_fwd(
+            q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(),
+            _dtype_code(q), block, Z, H, L, D,
+            q.stride(0), q.stride(1), q.stride(2), k.stride(0), k.stride(1), k.stride(2),
+            v.stride(0), v.stride(1), v.stride(2), o.stride(0), o.stride(1), o.stride(2),
+            meta.hdr.data_ptr(), meta.on(q.device).data_ptr(), scale, *margs, _stream(q)))
+        ctx.save_for_backward(q, k, v, o, lse, *keep)
+        ctx.meta, ctx.block, ctx.scale = meta, block, scale
+        ctx.mask_spec = (rpe is not None, kpm is not None, am is not None, kp_mode, am_mode)
+        return o
+
+    @staticmethod
+    def backward(ctx, do):
+        q, k, v, o, lse = ctx.saved_tensors[:5]
+        rest = list(ctx.saved_tensors[5:])
+        has_rpe, has_kpm, has_am, kp_mode, am_mode = ctx.mask_spec
+        rpe = rest.pop(0) if has_rpe else None
+        kpm = rest.pop(0) if has_kpm else None
+        am = rest.pop(0) if has_am else None
+        Z, H, L, D = q.shape
+        do = _rows(do)
+        margs, _ = _mask_args(Z, H, L, q.dtype, rpe, kpm, am, kp_mode, am_mode)
+        dq, dk, dv = torch.empty_like(o), torch.empty_like(o), torch.empty_like(o)
+        delta = torch.empty((Z, H, L), dtype=torch.float32, device=q.device)
+        _lib.check(_lib.lib().bsp_attn_bwd(
+            q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), do.data_ptr(), lse.data_ptr(), delta.data_ptr(),
+            dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), _dtype_code(q), ctx.block, Z, H, L, D,
+            q.stride(0), q.stride(1), q.stride(2), k.stride(0), k.stride(1), k.stride(2),
+            v.stride(0), v.stride(1), v.stride(2), o.stride(0), o.stride(1), o.stride(2),
+            do.stride(0), do.stride(1), do.stride(2),
+            ctx.meta.hdr.data_ptr(), ctx.meta.on(q.device).data_ptr(), ctx.scale, *margs, _stream(q)))
+        return (dq, dk, dv) + (None,) * 8
+
+
+def fused_attention(q, k, v, meta, block, scale, rpe=None, key_padding_mask=None, attn_mask=None,
+                    key_padding_mask_mode='add', attn_mask_mode='mul'):
+    """O = softmax(scale * Q K^T + rpe + masks, on the layout) V for [Z, H, L, D] operands."""
+    if meta.H != q.size(1) or meta.Mb != meta.Nb or meta.Mb * block != q.size(2):
+        raise ValueError('layout [%d,%d,%d] with block %d does not fit operands of shape %s'
+                         % (meta.H, meta.Mb, meta.Nb, block, tuple(q.shape)))
+    return _fused_attention.apply(q, k, v, meta, block, float(scale), rpe, key_padding_mask, attn_mask,
+                                  key_padding_mask_mode, attn_mask_mode)
