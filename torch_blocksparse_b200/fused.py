@@ -13,6 +13,28 @@ from . import _lib
 from .matmul import _dtype_code, _require_cuda, _stream
 
 
+# When set to a list, every forward / backward appends (name, start_event,
+# end_event) triples around each kernel launch (events on the current stream),
+# and the backward issues its three kernels as three calls.  Used by the
+# benchmark to time each kernel inside a full step; None costs nothing.
+PROFILE = None
+
+KERNELS_PER_FWD = 1
+KERNELS_PER_BWD = 3
+
+
+def _timed(name, fn):
+    if PROFILE is None:
+        return fn()
+    t0 = torch.cuda.Event(enable_timing=True)
+    t1 = torch.cuda.Event(enable_timing=True)
+    t0.record()
+    out = fn()
+    t1.record()
+    PROFILE.append((name, t0, t1))
+    return out
+
+
 def fused_supported(q, block):
     return q.dtype in (torch.float16, torch.bfloat16) and q.size(-1) in (64, 128) and block in (16, 32, 64, 128)
 
@@ -76,12 +98,12 @@ class _fused_attention(torch.autograd.Function):
         margs, keep = _mask_args(Z, H, L, q.dtype, rpe, kpm, am, kp_mode, am_mode)
         o = torch.empty((Z, H, L, D), dtype=q.dtype, device=q.device)
         lse = torch.empty((Z, H, L), dtype=torch.float32, device=q.device)
-        _lib.check(_lib.lib().bsp_attn_fwd(
+        _timed('attn_fwd', lambda: _lib.check(_lib.lib().bsp_attn_fwd(
             q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(),
             _dtype_code(q), block, Z, H, L, D,
             q.stride(0), q.stride(1), q.stride(2), k.stride(0), k.stride(1), k.stride(2),
             v.stride(0), v.stride(1), v.stride(2), o.stride(0), o.stride(1), o.stride(2),
-            meta.hdr.data_ptr(), meta.on(q.device).data_ptr(), scale, *margs, _stream(q)))
+            meta.hdr.data_ptr(), meta.on(q.device).data_ptr(), scale, *margs, _stream(q))))
         ctx.save_for_backward(q, k, v, o, lse, *keep)
         ctx.meta, ctx.block, ctx.scale = meta, block, scale
         ctx.mask_spec = (rpe is not None, kpm is not None, am is not None, kp_mode, am_mode)
@@ -100,13 +122,18 @@ class _fused_attention(torch.autograd.Function):
         margs, _ = _mask_args(Z, H, L, q.dtype, rpe, kpm, am, kp_mode, am_mode)
         dq, dk, dv = torch.empty_like(o), torch.empty_like(o), torch.empty_like(o)
         delta = torch.empty((Z, H, L), dtype=torch.float32, device=q.device)
-        _lib.check(_lib.lib().bsp_attn_bwd(
-            q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), do.data_ptr(), lse.data_ptr(), delta.data_ptr(),
-            dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), _dtype_code(q), ctx.block, Z, H, L, D,
-            q.stride(0), q.stride(1), q.stride(2), k.stride(0), k.stride(1), k.stride(2),
-            v.stride(0), v.stride(1), v.stride(2), o.stride(0), o.stride(1), o.stride(2),
-            do.stride(0), do.stride(1), do.stride(2),
-            ctx.meta.hdr.data_ptr(), ctx.meta.on(q.device).data_ptr(), ctx.scale, *margs, _stream(q)))
+        args = (q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), do.data_ptr(), lse.data_ptr(), delta.data_ptr(),
+                dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), _dtype_code(q), ctx.block, Z, H, L, D,
+                q.stride(0), q.stride(1), q.stride(2), k.stride(0), k.stride(1), k.stride(2),
+                v.stride(0), v.stride(1), v.stride(2), o.stride(0), o.stride(1), o.stride(2),
+                do.stride(0), do.stride(1), do.stride(2),
+                ctx.meta.hdr.data_ptr(), ctx.meta.on(q.device).data_ptr(), ctx.scale) + margs
+        L_ = _lib.lib()
+        if PROFILE is None:
+            _lib.check(L_.bsp_attn_bwd(*args, _stream(q)))
+        else:
+            for name, part in (('attn_bwd_delta', 1), ('attn_bwd_dkdv', 2), ('attn_bwd_dq', 4)):
+                _timed(name, lambda part=part: _lib.check(L_.bsp_attn_bwd_parts(*args, part, _stream(q))))
         return (dq, dk, dv) + (None,) * 8
 
 

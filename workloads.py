@@ -73,10 +73,11 @@ def config3(small=False):
                 key_padding_mask_mode='add', attn_mask_mode='mul', dy=dy, dtype=torch.float16)
 
 
-def config4(attention='unidirectional', small=False, Z=None):
+def config4(attention='unidirectional', small=False, Z=None, seed=0):
     """Sparse self-attention FP16 fwd+bwd: Z=8, H=16, L=8192, head_dim 64, block 64, fixed
-    layout with local windows of 4 blocks whose last block is global."""
-    g = _gen(0)
+    layout with local windows of 4 blocks whose last block is global.  `seed` selects
+    the shard (rank) the tensors are drawn for."""
+    g = _gen(seed)
     if small:
         z, H, L = 1, 2, 1024
     else:
