@@ -178,7 +178,7 @@ def config_dict(args, world):
             'l2': 'inputs (4 x 134 MB per GPU) exceed the 126 MB L2; no explicit flush'}
 
 
-def softmax_bench(dev, pk, iters=10):
+def softmax_bench(dev, pk, iters=20):
     """Sparse softmax (configuration 3) forward / backward bandwidth."""
     from torch_blocksparse_b200 import Softmax
     c = workloads.config3()
@@ -249,8 +249,12 @@ def run_ours(args):
         os.environ.setdefault('MASTER_ADDR', '127.0.0.1')
         dist.init_process_group('nccl', device_id=dev)
     pk = peaks()
+    if args.only_softmax:
+        if rank == 0:
+            print(json.dumps({'softmax': softmax_bench(dev, pk, iters=max(1, args.steps))}))
+        return
 
-    c = workloads.config4(args.attention, Z=8, seed=rank)
+    c = workloads.config4(args.attention, Z=args.z, seed=rank)
     layout, block, D = c['layout'], c['block'], c['q'].size(-1)
     Z = c['q'].size(0)
     flops_step = workloads.attention_flops(layout, block, Z, D)       # this rank's shard
@@ -350,7 +354,7 @@ def run_ours(args):
         parts = [torch.empty_like(digest) for _ in range(world)]
         dist.all_gather(parts, digest)
         if rank == 0:
-            other = workloads.config4(args.attention, Z=8, seed=world - 1)
+            other = workloads.config4(args.attention, Z=args.z, seed=world - 1)
             q2, k2, v2 = (other[n].to(dev).requires_grad_() for n in ('q', 'k', 'v'))
             o2 = mod(q2, k2, v2)
             o2.backward(other['do'].to(dev))
@@ -369,6 +373,8 @@ def run_ours(args):
             'frac_of_nominal_fp16_peak': value / world / 2250.0,
             'frac_of_measured_peak': value / world / peak_tf,
         }
+        if args.z != 8:
+            line['reduced_workload'] = 'Z=%d per GPU instead of 8: not the headline configuration' % args.z
         if not args.no_cpu_baseline:
             torch.set_num_threads(os.cpu_count() or 1)
             dt, fl = cpu_attention_sample(c, args.cpu_slices)
@@ -395,6 +401,9 @@ def main():
     ap.add_argument('--cpu-slices', type=int, default=16, help='(batch, head) slices timed for cpu_baseline')
     ap.add_argument('--ref-slices', type=int, default=2, help='(batch, head) slices per step of --impl reference')
     ap.add_argument('--no-softmax', action='store_true')
+    ap.add_argument('--only-softmax', action='store_true', help='run only the softmax section (profiling aid)')
+    ap.add_argument('--z', type=int, default=8, help='batch entries per GPU; anything but 8 is a reduced, '
+                    'non-headline workload (profiling aid) and is flagged in the output')
     ap.add_argument('--no-cpu-baseline', action='store_true')
     args = ap.parse_args()
     if args.impl == 'reference':

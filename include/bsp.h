@@ -220,8 +220,8 @@ int bsp_dds(const void* a, const void* s, void* c, int dtype, int block,
  * DeepSpeedSparseSelfAttention.forward
  * (torch_blocksparse/deepspeedsparseselfattention.py:157-166) without writing
  * the score tensor to memory.  q, k, v, o are [Z, H, L, D] with unit stride on
- * D and the given z / h / row strides; lse is FP32 [Z, H, L] (log-sum-exp of
- * every row, needed by the backward).  D is 64 or 128; dtype F16 or BF16.
+ * D and the given z / h / row strides; lse is FP32 [Z, H, L]: per row
+ * log2(sum_j exp(f_j)) of the pre-softmax values f, consumed by the backward.  D is 64 or 128; dtype F16 or BF16.
  */
 int bsp_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse,
                  int dtype, int block, int Z, int H, int L, int D,

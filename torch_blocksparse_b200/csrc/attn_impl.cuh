@@ -10,7 +10,7 @@
 //             blocks (CSR), S = Q K^T on tensor cores, online softmax in FP32
 //             registers (scale, rpe, key-padding and attention masks applied to
 //             S exactly as the softmax kernel applies them), O += P V.  Also
-//             writes the row-wise log-sum-exp for the backward.
+//             writes the row-wise base-2 log-sum-exp for the backward.
 //   backward  (1) delta = rowsum(O * dO);
 //             (2) one CTA per block-column (CSC): recomputes P^T from the
 //                 log-sum-exp, accumulates dV += P^T dO and dK += dS^T Q;
@@ -215,13 +215,13 @@ __global__ void __launch_bounds__(AttnCfg<B, D>::NT) attn_fwd_kernel(AttnArgs p)
       mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
       mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
       const float msafe = mx == kNegInfA ? 0.f : mx;
-      alpha[hr] = exp2f(mrow[hr] - msafe);     // 0 while the running max is still -inf
+      alpha[hr] = fast_exp2(mrow[hr] - msafe);     // 0 while the running max is still -inf
       mrow[hr] = mx;
       float rs = 0.f;
 #pragma unroll
       for (int j = 0; j < NI; ++j) {
-        s[j][2 * hr] = exp2f(s[j][2 * hr] - msafe);
-        s[j][2 * hr + 1] = exp2f(s[j][2 * hr + 1] - msafe);
+        s[j][2 * hr] = fast_exp2(s[j][2 * hr] - msafe);
+        s[j][2 * hr + 1] = fast_exp2(s[j][2 * hr + 1] - msafe);
         rs += s[j][2 * hr] + s[j][2 * hr + 1];
       }
       lsum[hr] = lsum[hr] * alpha[hr] + rs;
@@ -255,9 +255,9 @@ __global__ void __launch_bounds__(AttnCfg<B, D>::NT) attn_fwd_kernel(AttnArgs p)
     *reinterpret_cast<uint32_t*>(orow + (int64_t)(g + 8) * p.o_sr + j * 8 + 2 * t4) = pack2<T>(oacc[j][2] * inv[1], oacc[j][3] * inv[1]);
   }
   if (t4 == 0) {
-    // natural-log units: max/log2(e) + ln(l)
-    lrow[g] = mrow[0] / kLog2e + logf(lsum[0]);
-    lrow[g + 8] = mrow[1] / kLog2e + logf(lsum[1]);
+    // base-2 units, the domain the row maximum is tracked in: log2(sum_j 2^(f_j * log2 e))
+    lrow[g] = mrow[0] + log2f(lsum[0]);
+    lrow[g + 8] = mrow[1] + log2f(lsum[1]);
   }
 }
 
@@ -304,6 +304,7 @@ __global__ void __launch_bounds__(AttnCfg<B, D>::NT) attn_bwd_kv_kernel(AttnArgs
   const int h = ho / p.nb, j = ho % p.nb;
   const int first = p.col_ptr[ho], count = p.col_ptr[ho + 1] - first;
   const bool has_mask = p.m.rpe || p.m.kpm || p.m.am;
+  const float sl2 = p.scale * kLog2e;
 
   T* dkrow = reinterpret_cast<T*>(p.dk) + ((int64_t)(z * p.H + h) * p.L + (int64_t)j * B + warp * 16) * D;
   T* dvrow = reinterpret_cast<T*>(p.dv) + ((int64_t)(z * p.H + h) * p.L + (int64_t)j * B + warp * 16) * D;
@@ -366,10 +367,9 @@ __global__ void __launch_bounds__(AttnCfg<B, D>::NT) attn_bwd_kv_kernel(AttnArgs
 #pragma unroll
       for (int r = 0; r < 4; ++r) {
         const int m = c * 8 + 2 * t4 + (r & 1);            // query row inside the tile
-        float f;
-        if (has_mask) f = apply_masks<T>(st[c][r], p, z, h, grow0 + c * 8 + (r & 1), gcol0 + 8 * (r >> 1));
-        else f = st[c][r] * p.scale;
-        const float pr = __expf(f - ls[m]);
+        float pr;                                          // P = 2^(f * log2 e - lse)
+        if (has_mask) pr = fast_exp2(fmaf(apply_masks<T>(st[c][r], p, z, h, grow0 + c * 8 + (r & 1), gcol0 + 8 * (r >> 1)), kLog2e, -ls[m]));
+        else pr = fast_exp2(fmaf(st[c][r], sl2, -ls[m]));
         st[c][r] = pr;
         dp[c][r] = pr * (dp[c][r] - es[m]) * p.scale;
       }
@@ -419,6 +419,7 @@ __global__ void __launch_bounds__(AttnCfg<B, D>::NT) attn_bwd_q_kernel(AttnArgs 
   const int first = p.row_ptr[ho], count = p.row_ptr[ho + 1] - first;
   const bool has_mask = p.m.rpe || p.m.kpm || p.m.am;
 
+  const float sl2 = p.scale * kLog2e;
   T* dqrow = reinterpret_cast<T*>(p.dq) + ((int64_t)(z * p.H + h) * p.L + (int64_t)i * B + warp * 16) * D;
   if (count == 0) {
     for (int e = lane; e < 16 * D; e += 32) dqrow[e] = cvt_out<T>(0.f);
@@ -471,10 +472,9 @@ __global__ void __launch_bounds__(AttnCfg<B, D>::NT) attn_bwd_q_kernel(AttnArgs 
     for (int c = 0; c < NI; ++c)
 #pragma unroll
       for (int r = 0; r < 4; ++r) {
-        float f;
-        if (has_mask) f = apply_masks<T>(s[c][r], p, z, h, grow0 + 8 * (r >> 1), gcol0 + c * 8 + (r & 1));
-        else f = s[c][r] * p.scale;
-        const float pr = __expf(f - lse[r >> 1]);
+        float pr;                                          // P = 2^(f * log2 e - lse)
+        if (has_mask) pr = fast_exp2(fmaf(apply_masks<T>(s[c][r], p, z, h, grow0 + 8 * (r >> 1), gcol0 + c * 8 + (r & 1)), kLog2e, -lse[r >> 1]));
+        else pr = fast_exp2(fmaf(s[c][r], sl2, -lse[r >> 1]));
         dp[c][r] = pr * (dp[c][r] - dlt[r >> 1]) * p.scale;
       }
     uint32_t sf[BN / 16][4];

@@ -4,13 +4,15 @@
 // (torch_blocksparse/softmax.py:7-138, 144-194) and their launch code
 // (softmax.py:253-326).
 //
-// Work decomposition: one warp per matrix row.  A row of block-row (h, i) is
-// made of `size` chunks of `block` contiguous elements, one per nonzero block,
-// read with 16-byte vector loads; consecutive warps of a CTA take consecutive
-// rows of the same block-row, so a CTA streams whole blocks.  The row is kept
-// in registers (NV 16-byte vectors per lane, compile-time) between the
-// reduction and the write-back, so x is read once and written once; rows too
-// long for the largest NV fall back to a two-sweep loop that re-reads x.
+// A row of block-row (h, i) is made of `size` chunks of `block` contiguous
+// elements, one per nonzero block, read with 16-byte vector loads.  Three
+// work decompositions, picked by the longest row of the layout:
+//   * up to 8 blocks per row: a group of block/VEC lanes per row (see
+//     softmax_fwd_group), several rows per warp;
+//   * longer rows: one warp per row with the row held in registers (NV vectors
+//     per lane, compile-time), consecutive warps on consecutive rows;
+//   * rows beyond the largest NV: one warp per row, two sweeps, x re-read.
+// In the first two x is read once and written once.
 // The kernel is pure streaming: its roofline is HBM bandwidth.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
@@ -71,6 +73,13 @@ __device__ __forceinline__ void store_vec(T* p, const float (&f)[Vec<T>::N]) {
 #pragma unroll
   for (int i = 0; i < N; ++i) e[i] = from_f<T>(f[i]);
   __stcs(reinterpret_cast<uint4*>(p), raw);
+}
+
+// 2^x on the special-function unit (ex2.approx: about 2 ulp, denormals flushed).
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
 }
 
 __device__ __forceinline__ float warp_max(float v) {
@@ -314,6 +323,387 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32) softmax_bwd_loop(BwdArgs a)
   }
 }
 
+// ---------------------------------------------------------------------------
+// Short rows (at most 8 nonzero blocks): a group of block/VEC lanes owns one
+// row and walks its chunks, so a warp covers 32/(block/VEC) consecutive rows
+// of one block at full lane utilisation and reads 512 contiguous bytes per
+// chunk.  The batch index is the fastest grid dimension: CTAs that run
+// together read the same rpe / attention-mask rows, which then stay in L2.
+// ---------------------------------------------------------------------------
+constexpr int kGroupWarps = 4;     // warps per CTA of the short-row kernels
+
+// CTAs per SM the short-row kernels are compiled for: the register budget grows
+// with the number of vectors a thread keeps in flight.
+constexpr int fwd_ctas(int nv) { return nv <= 1 ? 12 : nv <= 2 ? 10 : nv <= 4 ? 8 : nv <= 6 ? 6 : 5; }
+constexpr int bwd_ctas(int nv) { return nv <= 1 ? 16 : nv <= 2 ? 12 : nv <= 4 ? 9 : nv <= 6 ? 8 : 6; }
+
+// Raw 16-byte vectors are kept packed while they are in flight, so that the
+// registers of a thread hold as many outstanding bytes as possible; they are
+// expanded to FP32 only when consumed.
+template <typename T>
+__device__ __forceinline__ void expand(const uint4& raw, float (&f)[Vec<T>::N]) {
+  const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+  for (int i = 0; i < Vec<T>::N; ++i) f[i] = to_f(e[i]);
+}
+
+template <typename T>
+__device__ __forceinline__ uint4 load_raw(const T* p, bool vec) {
+  if (vec) return __ldg(reinterpret_cast<const uint4*>(p));
+  uint4 raw;
+  T* e = reinterpret_cast<T*>(&raw);
+#pragma unroll
+  for (int i = 0; i < Vec<T>::N; ++i) e[i] = p[i];
+  return raw;
+}
+
+// The table lists the blocks of a block-row consecutively and numbers them in
+// the same order (block id = position in the table), so the id of the k-th
+// block of a row follows from the row's table offset: no per-block table read
+// sits between the header load and the data loads.
+__device__ __forceinline__ int first_block_of_row(int offset, int header_ints) { return (offset - header_ints) >> 2; }
+
+// Compile-time description of the optional inputs of the forward, so that no
+// per-element work depends on a run-time flag: RPE present or not; key-padding
+// and attention mask each absent (0), added (1) or in 'mul' mode (2); VEC says
+// that every optional input may be read with 16-byte loads.
+template <bool RPE_, int KPM_, int AM_, bool VEC_> struct FwdSpec {
+  static constexpr bool RPE = RPE_, VEC = VEC_;
+  static constexpr int KPM = KPM_, AM = AM_;
+};
+
+template <typename T, int NV, typename S>
+__global__ void __launch_bounds__(kGroupWarps * 32, fwd_ctas(NV))
+softmax_fwd_group(FwdArgs a, int Z, int lpr_log2, int header_ints) {
+  constexpr int N = Vec<T>::N;
+  constexpr float kLog2e = 1.4426950408889634f;
+  const int lane = threadIdx.x & 31;
+  const int z = blockIdx.x % Z;
+  const int wg = blockIdx.x / Z * kGroupWarps + (threadIdx.x >> 5);
+  const int row = (wg << (5 - lpr_log2)) + (lane >> lpr_log2);
+  if (row >= a.rows) return;
+  const int bl = a.block_log2;
+  const int rbm = row >> bl, rxm = row & ((1 << bl) - 1);
+  const int2 hdr = __ldg(reinterpret_cast<const int2*>(a.lut) + rbm);
+  const int size = hdr.x, offset = hdr.y;
+  if (size == 0) return;
+  const int c = (lane & ((1 << lpr_log2) - 1)) * N;
+  T* xp = reinterpret_cast<T*>(a.x) + z * a.x_sz + ((int64_t)first_block_of_row(offset, header_ints) << (2 * bl)) +
+          ((int64_t)rxm << bl) + c;
+  uint4 xr[NV];
+#pragma unroll
+  for (int k = 0; k < NV; ++k)
+    if (k < size) xr[k] = __ldcs(reinterpret_cast<const uint4*>(xp + ((int64_t)k << (2 * bl))));
+  float f[NV][N];
+  float m = kNegInf;
+  if constexpr (S::RPE || S::KPM != 0 || S::AM != 0) {
+    // row and head are the same for all blocks of this block-row
+    const int64_t grow = ((int64_t)__ldg(a.lut + offset + 2) << bl) + rxm;
+    const T* rpe = nullptr;
+    if constexpr (S::RPE)
+      rpe = reinterpret_cast<const T*>(a.rpe) + z * a.rpe_sz + __ldg(a.lut + offset + 3) * a.rpe_sh + grow * a.rpe_sr + c;
+    const T* kpm = reinterpret_cast<const T*>(a.kpm) + z * a.kpm_sz + c;
+    const T* am = reinterpret_cast<const T*>(a.am) + grow * a.am_sr + c;
+    int col[NV];
+#pragma unroll
+    for (int k = 0; k < NV; ++k)
+      if (k < size) col[k] = __ldg(a.lut + offset + 4 * k + 1) << bl;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      if (k < size) {
+        expand<T>(xr[k], f[k]);
+        float r[N];
+        if constexpr (S::RPE) {
+          expand<T>(load_raw(rpe + col[k], S::VEC), r);
+#pragma unroll
+          for (int i = 0; i < N; ++i) f[k][i] = fmaf(f[k][i], a.scale, r[i]);
+        } else {
+#pragma unroll
+          for (int i = 0; i < N; ++i) f[k][i] *= a.scale;
+        }
+        if constexpr (S::KPM != 0) {
+          expand<T>(load_raw(kpm + col[k], S::VEC), r);
+#pragma unroll
+          for (int i = 0; i < N; ++i) f[k][i] = S::KPM == 2 ? (r[i] == 0.f ? kNegInf : f[k][i]) : f[k][i] + r[i];
+        }
+        if constexpr (S::AM != 0) {
+          expand<T>(load_raw(am + col[k], S::VEC), r);
+#pragma unroll
+          for (int i = 0; i < N; ++i) f[k][i] = S::AM == 2 ? (r[i] == 0.f ? kNegInf : f[k][i]) : f[k][i] + r[i];
+        }
+#pragma unroll
+        for (int i = 0; i < N; ++i) m = fmaxf(m, f[k][i]);
+      }
+    }
+  } else {
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      if (k < size) {
+        expand<T>(xr[k], f[k]);
+#pragma unroll
+        for (int i = 0; i < N; ++i) { f[k][i] *= a.scale; m = fmaxf(m, f[k][i]); }
+      }
+    }
+  }
+  for (int o = (1 << lpr_log2) >> 1; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+  // exp(f - m) = 2^(f*log2(e) - m*log2(e)); a row that is masked everywhere has
+  // m = -inf and yields NaN, as the reference's kernel does
+  const float ml2 = m * kLog2e;
+  float sum = 0.f;
+#pragma unroll
+  for (int k = 0; k < NV; ++k) {
+    if (k < size) {
+#pragma unroll
+      for (int i = 0; i < N; ++i) { f[k][i] = fast_exp2(fmaf(f[k][i], kLog2e, -ml2)); sum += f[k][i]; }
+    }
+  }
+  for (int o = (1 << lpr_log2) >> 1; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+  const float inv = 1.f / sum;
+#pragma unroll
+  for (int k = 0; k < NV; ++k) {
+    if (k < size) {
+#pragma unroll
+      for (int i = 0; i < N; ++i) f[k][i] *= inv;
+      store_vec(xp + ((int64_t)k << (2 * bl)), f[k]);
+    }
+  }
+}
+
+// Same row decomposition, but the batch is walked inside the kernel: whatever
+// does not depend on the batch entry (the attention mask, an rpe that is
+// broadcast over the batch, the table look-ups) is read and converted once and
+// kept in registers as one FP32 term per element, and the x vectors of the next
+// batch entry are in flight while the current one is reduced.
+template <typename T, int NV, typename S>
+__global__ void __launch_bounds__(kGroupWarps * 32, 3)
+softmax_fwd_zloop(FwdArgs a, int Z, int lpr_log2, int header_ints) {
+  constexpr int N = Vec<T>::N;
+  constexpr float kLog2e = 1.4426950408889634f;
+  constexpr bool TERM = S::RPE || S::AM != 0;
+  const int lane = threadIdx.x & 31;
+  const int wg = blockIdx.x * kGroupWarps + (threadIdx.x >> 5);
+  const int row = (wg << (5 - lpr_log2)) + (lane >> lpr_log2);
+  if (row >= a.rows) return;
+  const int bl = a.block_log2;
+  const int rbm = row >> bl, rxm = row & ((1 << bl) - 1);
+  const int2 hdr = __ldg(reinterpret_cast<const int2*>(a.lut) + rbm);
+  const int size = hdr.x, offset = hdr.y;
+  if (size == 0) return;
+  const int c = (lane & ((1 << lpr_log2) - 1)) * N;
+  T* xp = reinterpret_cast<T*>(a.x) + ((int64_t)first_block_of_row(offset, header_ints) << (2 * bl)) + ((int64_t)rxm << bl) + c;
+  uint4 cur[NV];
+#pragma unroll
+  for (int k = 0; k < NV; ++k)
+    if (k < size) cur[k] = __ldcs(reinterpret_cast<const uint4*>(xp + ((int64_t)k << (2 * bl))));
+  int col[S::KPM != 0 ? NV : 1];
+  float term[TERM ? NV : 1][N];
+  if constexpr (TERM || S::KPM != 0) {
+    const int64_t grow = ((int64_t)__ldg(a.lut + offset + 2) << bl) + rxm;
+    const T* rpe = nullptr;
+    if constexpr (S::RPE) rpe = reinterpret_cast<const T*>(a.rpe) + __ldg(a.lut + offset + 3) * a.rpe_sh + grow * a.rpe_sr + c;
+    const T* am = reinterpret_cast<const T*>(a.am) + grow * a.am_sr + c;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      if (k < size) {
+        const int ck = __ldg(a.lut + offset + 4 * k + 1) << bl;
+        if constexpr (S::KPM != 0) col[k] = ck;
+        if constexpr (TERM) {
+          float r[N];
+#pragma unroll
+          for (int i = 0; i < N; ++i) term[k][i] = 0.f;
+          if constexpr (S::RPE) {
+            expand<T>(load_raw(rpe + ck, true), r);
+#pragma unroll
+            for (int i = 0; i < N; ++i) term[k][i] = r[i];
+          }
+          if constexpr (S::AM != 0) {
+            expand<T>(load_raw(am + ck, true), r);
+#pragma unroll
+            for (int i = 0; i < N; ++i) term[k][i] = S::AM == 2 ? (r[i] == 0.f ? kNegInf : term[k][i]) : term[k][i] + r[i];
+          }
+        }
+      }
+    }
+  }
+  const T* kpm = reinterpret_cast<const T*>(a.kpm) + c;
+  uint4 kcur[S::KPM != 0 ? NV : 1];
+  if constexpr (S::KPM != 0) {
+#pragma unroll
+    for (int k = 0; k < NV; ++k)
+      if (k < size) kcur[k] = load_raw(kpm + col[k], true);
+  }
+  for (int z = 0; z < Z; ++z) {
+    uint4 nxt[NV];
+    if (z + 1 < Z) {
+#pragma unroll
+      for (int k = 0; k < NV; ++k)
+        if (k < size) nxt[k] = __ldcs(reinterpret_cast<const uint4*>(xp + a.x_sz + ((int64_t)k << (2 * bl))));
+    }
+    float f[NV][N];
+    float m = kNegInf;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      if (k < size) {
+        expand<T>(cur[k], f[k]);
+        if constexpr (TERM) {
+#pragma unroll
+          for (int i = 0; i < N; ++i) f[k][i] = fmaf(f[k][i], a.scale, term[k][i]);
+        } else {
+#pragma unroll
+          for (int i = 0; i < N; ++i) f[k][i] *= a.scale;
+        }
+        if constexpr (S::KPM != 0) {
+          float r[N];
+          expand<T>(kcur[k], r);
+#pragma unroll
+          for (int i = 0; i < N; ++i) f[k][i] = S::KPM == 2 ? (r[i] == 0.f ? kNegInf : f[k][i]) : f[k][i] + r[i];
+        }
+#pragma unroll
+        for (int i = 0; i < N; ++i) m = fmaxf(m, f[k][i]);
+      }
+    }
+    // the key-padding vectors of the next batch entry take over the registers of
+    // the current ones as soon as those are consumed
+    kpm += a.kpm_sz;
+    if constexpr (S::KPM != 0) {
+      if (z + 1 < Z) {
+#pragma unroll
+        for (int k = 0; k < NV; ++k)
+          if (k < size) kcur[k] = load_raw(kpm + col[k], true);
+      }
+    }
+    for (int o = (1 << lpr_log2) >> 1; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    const float ml2 = m * kLog2e;
+    float sum = 0.f;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      if (k < size) {
+#pragma unroll
+        for (int i = 0; i < N; ++i) { f[k][i] = fast_exp2(fmaf(f[k][i], kLog2e, -ml2)); sum += f[k][i]; }
+      }
+    }
+    for (int o = (1 << lpr_log2) >> 1; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    const float inv = 1.f / sum;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      if (k < size) {
+#pragma unroll
+        for (int i = 0; i < N; ++i) f[k][i] *= inv;
+        store_vec(xp + ((int64_t)k << (2 * bl)), f[k]);
+      }
+    }
+    xp += a.x_sz;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) cur[k] = nxt[k];
+  }
+}
+
+template <typename T, int NV>
+__global__ void __launch_bounds__(kGroupWarps * 32, bwd_ctas(NV))
+softmax_bwd_group(BwdArgs a, int Z, int lpr_log2, int header_ints) {
+  constexpr int N = Vec<T>::N;
+  const int lane = threadIdx.x & 31;
+  const int z = blockIdx.x % Z;
+  const int wg = blockIdx.x / Z * kGroupWarps + (threadIdx.x >> 5);
+  const int row = (wg << (5 - lpr_log2)) + (lane >> lpr_log2);
+  if (row >= a.rows) return;
+  const int bl = a.block_log2;
+  const int rbm = row >> bl, rxm = row & ((1 << bl) - 1);
+  const int2 hdr = __ldg(reinterpret_cast<const int2*>(a.lut) + rbm);
+  const int size = hdr.x;
+  if (size == 0) return;
+  const int64_t off = ((int64_t)first_block_of_row(hdr.y, header_ints) << (2 * bl)) + ((int64_t)rxm << bl) +
+                      (lane & ((1 << lpr_log2) - 1)) * N;
+  const T* yp = reinterpret_cast<const T*>(a.y) + z * a.y_sz + off;
+  T* dp = reinterpret_cast<T*>(a.dy) + z * a.dy_sz + off;
+  uint4 yr[NV], dr[NV];
+#pragma unroll
+  for (int k = 0; k < NV; ++k)
+    if (k < size) {
+      yr[k] = __ldcs(reinterpret_cast<const uint4*>(yp + ((int64_t)k << (2 * bl))));
+      dr[k] = __ldcs(reinterpret_cast<const uint4*>(dp + ((int64_t)k << (2 * bl))));
+    }
+  float dot = 0.f;
+#pragma unroll
+  for (int k = 0; k < NV; ++k)
+    if (k < size) {
+      float y[N], d[N];
+      expand<T>(yr[k], y);
+      expand<T>(dr[k], d);
+#pragma unroll
+      for (int i = 0; i < N; ++i) dot += y[i] * d[i];
+    }
+  for (int o = (1 << lpr_log2) >> 1; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+#pragma unroll
+  for (int k = 0; k < NV; ++k)
+    if (k < size) {
+      float y[N], d[N];
+      expand<T>(yr[k], y);
+      expand<T>(dr[k], d);
+#pragma unroll
+      for (int i = 0; i < N; ++i) d[i] = y[i] * (d[i] - dot) * a.scale;
+      store_vec(dp + ((int64_t)k << (2 * bl)), d);
+    }
+}
+
+constexpr int kGroupMaxBlocks = 8;
+
+template <typename T, typename S>
+void launch_fwd_group(const FwdArgs& a, int maxlut, int Z, int block, int header_ints, cudaStream_t st) {
+  int lpr_log2 = 0;
+  while ((Vec<T>::N << lpr_log2) < block) ++lpr_log2;
+  const int rows_per_cta = kGroupWarps << (5 - lpr_log2);
+  if (S::RPE && Z >= 4 && a.rpe_sz == 0 && maxlut > 1) {
+    const unsigned grid = (unsigned)((a.rows + rows_per_cta - 1) / rows_per_cta);
+    if (maxlut <= 2) softmax_fwd_zloop<T, 2, S><<<grid, kGroupWarps * 32, 0, st>>>(a, Z, lpr_log2, header_ints);
+    else if (maxlut <= 4) softmax_fwd_zloop<T, 4, S><<<grid, kGroupWarps * 32, 0, st>>>(a, Z, lpr_log2, header_ints);
+    else if (maxlut <= 5) softmax_fwd_zloop<T, 5, S><<<grid, kGroupWarps * 32, 0, st>>>(a, Z, lpr_log2, header_ints);
+    else if (maxlut <= 6) softmax_fwd_zloop<T, 6, S><<<grid, kGroupWarps * 32, 0, st>>>(a, Z, lpr_log2, header_ints);
+    else softmax_fwd_zloop<T, 8, S><<<grid, kGroupWarps * 32, 0, st>>>(a, Z, lpr_log2, header_ints);
+    return;
+  }
+  const unsigned grid = (unsigned)((a.rows + rows_per_cta - 1) / rows_per_cta) * Z;
+  if (maxlut <= 1) softmax_fwd_group<T, 1, S><<<grid, kGroupWarps * 32, 0, st>>>(a, Z, lpr_log2, header_ints);
+  else if (maxlut <= 2) softmax_fwd_group<T, 2, S><<<grid, kGroupWarps * 32, 0, st>>>(a, Z, lpr_log2, header_ints);
+  else if (maxlut <= 4) softmax_fwd_group<T, 4, S><<<grid, kGroupWarps * 32, 0, st>>>(a, Z, lpr_log2, header_ints);
+  else if (maxlut <= 6) softmax_fwd_group<T, 6, S><<<grid, kGroupWarps * 32, 0, st>>>(a, Z, lpr_log2, header_ints);
+  else softmax_fwd_group<T, 8, S><<<grid, kGroupWarps * 32, 0, st>>>(a, Z, lpr_log2, header_ints);
+}
+
+// Maps the run-time description of the optional inputs onto a FwdSpec.
+template <typename T, bool RPE, int KPM>
+void pick_am(const FwdArgs& a, int maxlut, int Z, int block, int header_ints, cudaStream_t st) {
+  const int am = a.am ? (a.am_mul ? 2 : 1) : 0;
+  if (am == 0) launch_fwd_group<T, FwdSpec<RPE, KPM, 0, true>>(a, maxlut, Z, block, header_ints, st);
+  else if (am == 1) launch_fwd_group<T, FwdSpec<RPE, KPM, 1, true>>(a, maxlut, Z, block, header_ints, st);
+  else launch_fwd_group<T, FwdSpec<RPE, KPM, 2, true>>(a, maxlut, Z, block, header_ints, st);
+}
+template <typename T>
+void dispatch_fwd_group(const FwdArgs& a, int maxlut, int Z, int block, int header_ints, cudaStream_t st) {
+  const int kpm = a.kpm ? (a.kpm_mul ? 2 : 1) : 0;
+  if (a.rpe) {
+    if (kpm == 0) pick_am<T, true, 0>(a, maxlut, Z, block, header_ints, st);
+    else if (kpm == 1) pick_am<T, true, 1>(a, maxlut, Z, block, header_ints, st);
+    else pick_am<T, true, 2>(a, maxlut, Z, block, header_ints, st);
+  } else {
+    if (kpm == 0) pick_am<T, false, 0>(a, maxlut, Z, block, header_ints, st);
+    else if (kpm == 1) pick_am<T, false, 1>(a, maxlut, Z, block, header_ints, st);
+    else pick_am<T, false, 2>(a, maxlut, Z, block, header_ints, st);
+  }
+}
+template <typename T>
+void dispatch_bwd_group(const BwdArgs& a, int maxlut, int Z, int block, int header_ints, cudaStream_t st) {
+  int lpr_log2 = 0;
+  while ((Vec<T>::N << lpr_log2) < block) ++lpr_log2;
+  const int rows_per_cta = kGroupWarps << (5 - lpr_log2);
+  const unsigned grid = (unsigned)((a.rows + rows_per_cta - 1) / rows_per_cta) * Z;
+  if (maxlut <= 1) softmax_bwd_group<T, 1><<<grid, kGroupWarps * 32, 0, st>>>(a, Z, lpr_log2, header_ints);
+  else if (maxlut <= 2) softmax_bwd_group<T, 2><<<grid, kGroupWarps * 32, 0, st>>>(a, Z, lpr_log2, header_ints);
+  else if (maxlut <= 4) softmax_bwd_group<T, 4><<<grid, kGroupWarps * 32, 0, st>>>(a, Z, lpr_log2, header_ints);
+  else if (maxlut <= 6) softmax_bwd_group<T, 6><<<grid, kGroupWarps * 32, 0, st>>>(a, Z, lpr_log2, header_ints);
+  else softmax_bwd_group<T, 8><<<grid, kGroupWarps * 32, 0, st>>>(a, Z, lpr_log2, header_ints);
+}
+
 inline int log2i(int v) { int l = 0; while ((1 << l) < v) ++l; return l; }
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
@@ -398,7 +788,11 @@ extern "C" int bsp_softmax_fwd(void* x, int dtype, int Z, int64_t x_sz, int bloc
   const dim3 grid((a.rows + kWarpsPerCta - 1) / kWarpsPerCta, Z);
   const int nvec = maxlut * block / vec;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  if (dtype == BSP_F32) dispatch_fwd<float>(a, nvec, grid, st);
+  if (maxlut <= kGroupMaxBlocks && a.mask_vec) {
+    if (dtype == BSP_F32) dispatch_fwd_group<float>(a, maxlut, Z, block, 2 * H * Mb, st);
+    else if (dtype == BSP_F16) dispatch_fwd_group<__half>(a, maxlut, Z, block, 2 * H * Mb, st);
+    else dispatch_fwd_group<__nv_bfloat16>(a, maxlut, Z, block, 2 * H * Mb, st);
+  } else if (dtype == BSP_F32) dispatch_fwd<float>(a, nvec, grid, st);
   else if (dtype == BSP_F16) dispatch_fwd<__half>(a, nvec, grid, st);
   else dispatch_fwd<__nv_bfloat16>(a, nvec, grid, st);
   return finish("softmax forward");
@@ -419,7 +813,11 @@ extern "C" int bsp_softmax_bwd(const void* y, void* dy, int dtype, int Z, int64_
   const dim3 grid((a.rows + kWarpsPerCta - 1) / kWarpsPerCta, Z);
   const int nvec = maxlut * block / vec;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  if (dtype == BSP_F32) dispatch_bwd<float>(a, nvec, grid, st);
+  if (maxlut <= kGroupMaxBlocks) {
+    if (dtype == BSP_F32) dispatch_bwd_group<float>(a, maxlut, Z, block, 2 * H * Mb, st);
+    else if (dtype == BSP_F16) dispatch_bwd_group<__half>(a, maxlut, Z, block, 2 * H * Mb, st);
+    else dispatch_bwd_group<__nv_bfloat16>(a, maxlut, Z, block, 2 * H * Mb, st);
+  } else if (dtype == BSP_F32) dispatch_bwd<float>(a, nvec, grid, st);
   else if (dtype == BSP_F16) dispatch_bwd<__half>(a, nvec, grid, st);
   else dispatch_bwd<__nv_bfloat16>(a, nvec, grid, st);
   return finish("softmax backward");
