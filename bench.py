@@ -42,8 +42,10 @@ UNIT = 'TFLOP/s'
 FALLBACK_PEAKS = {'hbm_gbs': 6650.0, 'bf16_tflops': 1590.0, 'bf16_tflops_sustained': 1400.0}
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures
-# summarised under profiles/ (None until a capture of that kernel exists).
-NCU_TRAFFIC_BYTES = {'attn_bwd_dkdv': None, 'softmax_fwd': None}
+# summarised under profiles/.  The attention figure was captured at Z=2 (179.2 MB)
+# and scaled by 4 to the Z=8 launch: every (batch, head) pair is independent, so
+# traffic grows in proportion.
+NCU_TRAFFIC_BYTES = {'attn_bwd_dkdv': 4 * 179.2e6, 'softmax_fwd': 634.5e6, 'softmax_bwd': 925.0e6}
 
 
 def peaks():
@@ -229,10 +231,10 @@ def softmax_bench(dev, pk, iters=20):
         'fwd_ms': tf * 1e3, 'bwd_ms': tb * 1e3, 'fwd_bytes': fwd_bytes, 'bwd_bytes': bwd_bytes,
         'roofline': {'bound': 'hbm', 'achieved': fwd_bytes / tf / 1e9, 'peak': pk['hbm_gbs'], 'unit': 'GB/s',
                      'frac': fwd_bytes / tf / 1e9 / pk['hbm_gbs'], 'traffic': NCU_TRAFFIC_BYTES['softmax_fwd'],
-                     'kernel': 'softmax_fwd_reg', 'peak_source': pk['source']},
+                     'kernel': 'softmax_fwd_zloop', 'peak_source': pk['source']},
         'roofline_bwd': {'bound': 'hbm', 'achieved': bwd_bytes / tb / 1e9, 'peak': pk['hbm_gbs'], 'unit': 'GB/s',
-                         'frac': bwd_bytes / tb / 1e9 / pk['hbm_gbs'], 'traffic': None,
-                         'kernel': 'softmax_bwd_reg', 'peak_source': pk['source']},
+                         'frac': bwd_bytes / tb / 1e9 / pk['hbm_gbs'], 'traffic': NCU_TRAFFIC_BYTES['softmax_bwd'],
+                         'kernel': 'softmax_bwd_group', 'peak_source': pk['source']},
         'gpu_launches': 2 * (iters + 3),
     }
 
