@@ -276,6 +276,46 @@ int bsp_attn_bwd_parts(const void* q, const void* k, const void* v, const void* 
                        const void* am, int64_t am_sr, int am_mul,
                        int parts, void* stream);
 
+/*
+ * Backward of bsp_attn_fwd for callers that cannot allocate device memory.
+ * (No counterpart in the reference.)  Some hosts of this library have no
+ * allocator to hand: a runtime that pre-plans all of its device memory and
+ * forbids cudaMalloc once it is running, a plug-in that only receives the
+ * tensors of its inputs and outputs, code that runs inside a region where the
+ * driver's allocator must not be entered.  bsp_attn_bwd asks such a caller for
+ * Z*H*L floats of scratch it has no way to provide.  This variant takes the
+ * same arguments minus `delta` and keeps that scratch in an array built into
+ * the library image instead (BSP_ATTN_STATIC_ROWS floats = 4 MiB, resident on
+ * every GPU that loads the library until the process exits).  It calls no
+ * allocating routine of any kind.
+ *
+ *   limit     Z*H*L <= BSP_ATTN_STATIC_ROWS, else BSP_ERR_UNSUPPORTED.
+ *   set-up    the first call on each device looks up the device address of the
+ *             array (cudaGetSymbolAddress, with that device current) and caches
+ *             it; make that first call outside any stream capture.
+ *   sharing   every call on a device uses the same array, which keeps whatever
+ *             the previous call left in it.  Nothing in it has to start at
+ *             zero: the first kernel of the call overwrites the Z*H*L entries
+ *             the later ones read.  Two calls that overlap on the GPU (different
+ *             streams, or different threads) race on it; serialise them.
+ * Results are identical to bsp_attn_bwd.
+ */
+#define BSP_ATTN_STATIC_ROWS (1 << 20)
+int bsp_attn_bwd_static(const void* q, const void* k, const void* v, const void* o,
+                        const void* dout, const float* lse,
+                        void* dq, void* dk, void* dv,
+                        int dtype, int block, int Z, int H, int L, int D,
+                        int64_t q_sz, int64_t q_sh, int64_t q_sr,
+                        int64_t k_sz, int64_t k_sh, int64_t k_sr,
+                        int64_t v_sz, int64_t v_sh, int64_t v_sr,
+                        int64_t o_sz, int64_t o_sh, int64_t o_sr,
+                        int64_t do_sz, int64_t do_sh, int64_t do_sr,
+                        const int32_t* meta_hdr, const int32_t* meta, float scale,
+                        const void* rpe, int64_t rpe_sz, int64_t rpe_sh, int64_t rpe_sr,
+                        const void* kpm, int64_t kpm_sz, int kpm_mul,
+                        const void* am, int64_t am_sr, int am_mul,
+                        void* stream);
+
 #ifdef __cplusplus
 }
 #endif

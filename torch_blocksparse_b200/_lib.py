@@ -14,6 +14,7 @@ OK, ERR_INVALID, ERR_UNSUPPORTED, ERR_CAPACITY, ERR_CUDA, ERR_EMPTY_HEAD, ERR_TI
 F32, F16, BF16 = 0, 1, 2
 MAX_PACKS = 8
 META_HEADER = 8
+ATTN_STATIC_ROWS = 1 << 20
 
 _lib = None
 
@@ -47,6 +48,8 @@ _SIGNATURES = {
                      + _MASKS + [c_void_p]),
     'bsp_attn_bwd': (c_int, [c_void_p] * 10 + [c_int] * 6 + [c_int64] * 15 + [c_void_p, c_void_p, c_float]
                      + _MASKS + [c_void_p]),
+    'bsp_attn_bwd_static': (c_int, [c_void_p] * 9 + [c_int] * 6 + [c_int64] * 15 + [c_void_p, c_void_p, c_float]
+                            + _MASKS + [c_void_p]),
     'bsp_attn_bwd_parts': (c_int, [c_void_p] * 10 + [c_int] * 6 + [c_int64] * 15 + [c_void_p, c_void_p, c_float]
                            + _MASKS + [c_int, c_void_p]),
 }

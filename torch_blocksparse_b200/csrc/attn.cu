@@ -2,10 +2,40 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
+#include <mutex>
 #include "attn_impl.cuh"
+
+// Scratch of the allocation-free backward (bsp_attn_bwd_static): one FP32 value
+// per attention row.  It is part of the library image, so every GPU that loads
+// the library holds these 4 MiB until the process exits.
+static __device__ __align__(256) float g_static_delta[BSP_ATTN_STATIC_ROWS];
 
 namespace bsp {
 namespace {
+
+constexpr int kMaxDevices = 64;
+std::mutex g_static_mutex;
+float* g_static_delta_ptr[kMaxDevices] = {};   // device address of g_static_delta, per device
+
+// Device address of the scratch array on the current device.  In host code the
+// array's name is only a handle; the address a kernel can use comes from
+// cudaGetSymbolAddress, looked up once per device with that device current.
+int static_delta_address(float** out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return fail(BSP_ERR_CUDA, "attention (static scratch): cudaGetDevice failed: %s", cudaGetErrorString(e));
+  if (dev < 0 || dev >= kMaxDevices) return fail(BSP_ERR_UNSUPPORTED, "attention (static scratch): device index %d is outside [0, %d)", dev, kMaxDevices);
+  std::lock_guard<std::mutex> lock(g_static_mutex);
+  if (!g_static_delta_ptr[dev]) {
+    void* ptr = nullptr;
+    e = cudaGetSymbolAddress(&ptr, g_static_delta);
+    if (e != cudaSuccess || !ptr)
+      return fail(BSP_ERR_CUDA, "attention (static scratch): cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+    g_static_delta_ptr[dev] = static_cast<float*>(ptr);
+  }
+  *out = g_static_delta_ptr[dev];
+  return BSP_OK;
+}
 
 bool al16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
@@ -121,6 +151,33 @@ extern "C" int bsp_attn_bwd(const void* q, const void* k, const void* v, const v
                             const void* rpe, int64_t rpe_sz, int64_t rpe_sh, int64_t rpe_sr,
                             const void* kpm, int64_t kpm_sz, int kpm_mul,
                             const void* am, int64_t am_sr, int am_mul, void* stream) {
+  return bsp_attn_bwd_parts(q, k, v, o, dout, lse, delta, dq, dk, dv, dtype, block, Z, H, L, D,
+                            q_sz, q_sh, q_sr, k_sz, k_sh, k_sr, v_sz, v_sh, v_sr, o_sz, o_sh, o_sr,
+                            do_sz, do_sh, do_sr, meta_hdr, meta, scale, rpe, rpe_sz, rpe_sh, rpe_sr,
+                            kpm, kpm_sz, kpm_mul, am, am_sr, am_mul, 7, stream);
+}
+
+extern "C" int bsp_attn_bwd_static(const void* q, const void* k, const void* v, const void* o,
+                                   const void* dout, const float* lse,
+                                   void* dq, void* dk, void* dv,
+                                   int dtype, int block, int Z, int H, int L, int D,
+                                   int64_t q_sz, int64_t q_sh, int64_t q_sr,
+                                   int64_t k_sz, int64_t k_sh, int64_t k_sr,
+                                   int64_t v_sz, int64_t v_sh, int64_t v_sr,
+                                   int64_t o_sz, int64_t o_sh, int64_t o_sr,
+                                   int64_t do_sz, int64_t do_sh, int64_t do_sr,
+                                   const int32_t* meta_hdr, const int32_t* meta, float scale,
+                                   const void* rpe, int64_t rpe_sz, int64_t rpe_sh, int64_t rpe_sr,
+                                   const void* kpm, int64_t kpm_sz, int kpm_mul,
+                                   const void* am, int64_t am_sr, int am_mul, void* stream) {
+  if (Z <= 0 || H <= 0 || L <= 0) return fail(BSP_ERR_INVALID, "attention (static scratch): non-positive size");
+  const int64_t rows = (int64_t)Z * H * L;
+  if (rows > BSP_ATTN_STATIC_ROWS)
+    return fail(BSP_ERR_UNSUPPORTED,
+                "attention (static scratch): Z*H*L = %lld rows exceed the built-in scratch of %d rows; "
+                "use bsp_attn_bwd with caller-provided scratch", (long long)rows, BSP_ATTN_STATIC_ROWS);
+  float* delta = nullptr;
+  if (int rc = static_delta_address(&delta)) return rc;
   return bsp_attn_bwd_parts(q, k, v, o, dout, lse, delta, dq, dk, dv, dtype, block, Z, H, L, D,
                             q_sz, q_sh, q_sr, k_sz, k_sh, k_sr, v_sz, v_sh, v_sr, o_sz, o_sh, o_sr,
                             do_sz, do_sh, do_sr, meta_hdr, meta, scale, rpe, rpe_sz, rpe_sh, rpe_sr,
