@@ -129,6 +129,24 @@ int bsp_fixed_layout_build(int num_heads, int num_blocks, int mode, int block_st
 int bsp_meta_build(const int64_t* layout, int H, int Mb, int Nb,
                    int32_t* out, int64_t out_cap, int64_t* total);
 
+/*
+ * Tile lists of the tcgen05 attention kernels (no counterpart in the
+ * reference).  Those kernels work on tiles of 128 query rows (forward, dQ) or
+ * 128 key rows (dK, dV) and walk chunks of 64 rows of the other operand.  With
+ * block 64 a tile covers two block-rows (block-columns): its list is the union
+ * of their nonzero positions plus a 2-bit mask telling which half of the tile
+ * owns the block.  int32 layout of `out`:
+ *   [0] magic [1] H [2] L/block [3] block [4] tiles per head [5] row entries
+ *   [6] column entries [7] reserved
+ *   rt_ptr [H*tiles+1]  rt_chunk [E_r]  rt_mask [E_r]  rt_order [H*tiles]
+ *   ct_ptr [H*tiles+1]  ct_chunk [E_c]  ct_mask [E_c]  ct_order [H*tiles]
+ * block must be 64 or 128 and L a multiple of 128 (else BSP_ERR_UNSUPPORTED).
+ */
+#define BSP_TILES_MAGIC 0x42535054
+#define BSP_TILES_HEADER 8
+int bsp_attn_tiles_build(const int64_t* layout, int H, int nb, int block,
+                         int32_t* out, int64_t out_cap, int64_t* total);
+
 /* ------------------------------------------------------------------------ */
 /* Softmax (device)                                                         */
 /* ------------------------------------------------------------------------ */
@@ -222,6 +240,11 @@ int bsp_dds(const void* a, const void* s, void* c, int dtype, int block,
  * the score tensor to memory.  q, k, v, o are [Z, H, L, D] with unit stride on
  * D and the given z / h / row strides; lse is FP32 [Z, H, L]: per row
  * log2(sum_j exp(f_j)) of the pre-softmax values f, consumed by the backward.  D is 64 or 128; dtype F16 or BF16.
+ * tiles / tiles_hdr: optional device copy of the buffer written by
+ * bsp_attn_tiles_build and a HOST pointer to its first BSP_TILES_HEADER ints.
+ * When given (and block is 64 or 128, L a multiple of 128, no rpe / masks) the
+ * tcgen05 + tensor-memory + TMA kernels run; otherwise, or with NULL, the
+ * mma.sync kernels do.  Both give the same result within rounding.
  */
 int bsp_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse,
                  int dtype, int block, int Z, int H, int L, int D,
@@ -229,7 +252,8 @@ int bsp_attn_fwd(const void* q, const void* k, const void* v, void* o, float* ls
                  int64_t k_sz, int64_t k_sh, int64_t k_sr,
                  int64_t v_sz, int64_t v_sh, int64_t v_sr,
                  int64_t o_sz, int64_t o_sh, int64_t o_sr,
-                 const int32_t* meta_hdr, const int32_t* meta, float scale,
+                 const int32_t* meta_hdr, const int32_t* meta,
+                 const int32_t* tiles_hdr, const int32_t* tiles, float scale,
                  const void* rpe, int64_t rpe_sz, int64_t rpe_sh, int64_t rpe_sr,
                  const void* kpm, int64_t kpm_sz, int kpm_mul,
                  const void* am, int64_t am_sr, int am_mul,
@@ -249,7 +273,8 @@ int bsp_attn_bwd(const void* q, const void* k, const void* v, const void* o,
                  int64_t v_sz, int64_t v_sh, int64_t v_sr,
                  int64_t o_sz, int64_t o_sh, int64_t o_sr,
                  int64_t do_sz, int64_t do_sh, int64_t do_sr,
-                 const int32_t* meta_hdr, const int32_t* meta, float scale,
+                 const int32_t* meta_hdr, const int32_t* meta,
+                 const int32_t* tiles_hdr, const int32_t* tiles, float scale,
                  const void* rpe, int64_t rpe_sz, int64_t rpe_sh, int64_t rpe_sr,
                  const void* kpm, int64_t kpm_sz, int kpm_mul,
                  const void* am, int64_t am_sr, int am_mul,
@@ -270,7 +295,8 @@ int bsp_attn_bwd_parts(const void* q, const void* k, const void* v, const void* 
                        int64_t v_sz, int64_t v_sh, int64_t v_sr,
                        int64_t o_sz, int64_t o_sh, int64_t o_sr,
                        int64_t do_sz, int64_t do_sh, int64_t do_sr,
-                       const int32_t* meta_hdr, const int32_t* meta, float scale,
+                       const int32_t* meta_hdr, const int32_t* meta,
+                 const int32_t* tiles_hdr, const int32_t* tiles, float scale,
                        const void* rpe, int64_t rpe_sz, int64_t rpe_sh, int64_t rpe_sr,
                        const void* kpm, int64_t kpm_sz, int kpm_mul,
                        const void* am, int64_t am_sr, int am_mul,
@@ -310,11 +336,19 @@ int bsp_attn_bwd_static(const void* q, const void* k, const void* v, const void*
                         int64_t v_sz, int64_t v_sh, int64_t v_sr,
                         int64_t o_sz, int64_t o_sh, int64_t o_sr,
                         int64_t do_sz, int64_t do_sh, int64_t do_sr,
-                        const int32_t* meta_hdr, const int32_t* meta, float scale,
+                        const int32_t* meta_hdr, const int32_t* meta,
+                 const int32_t* tiles_hdr, const int32_t* tiles, float scale,
                         const void* rpe, int64_t rpe_sz, int64_t rpe_sh, int64_t rpe_sr,
                         const void* kpm, int64_t kpm_sz, int kpm_mul,
                         const void* am, int64_t am_sr, int am_mul,
                         void* stream);
+
+/*
+ * Reads the device-side status word (synchronises the device): 0, or non-zero
+ * when a bounded wait inside a tcgen05 kernel expired, in which case that
+ * launch's outputs are not valid.  No counterpart in the reference.
+ */
+int bsp_device_status(int* status);
 
 #ifdef __cplusplus
 }

@@ -61,7 +61,7 @@ def test_bad_arguments_are_rejected_with_messages():
     rc = L.bsp_softmax_fwd(None, _lib.F16, 1, 256, 16, 1, 1, 16, 1, 1.0, None, 0, 0, 0, None, 0, 0, None, 0, 0, None)
     assert rc == _lib.ERR_INVALID
     # fused attention: dtype / head-dimension limits
-    args = [16] * 4 + [16, _lib.F32, 16, 1, 1, 16, 64] + [8] * 12 + [hdr, fake_dev, 1.0] + [None, 0, 0, 0, None, 0, 0, None, 0, 0, None]
+    args = [16] * 4 + [16, _lib.F32, 16, 1, 1, 16, 64] + [8] * 12 + [hdr, fake_dev, None, None, 1.0] + [None, 0, 0, 0, None, 0, 0, None, 0, 0, None]
     assert L.bsp_attn_fwd(*args) == _lib.ERR_UNSUPPORTED
     args[5], args[10] = _lib.F16, 48
     assert L.bsp_attn_fwd(*args) == _lib.ERR_UNSUPPORTED

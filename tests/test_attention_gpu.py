@@ -12,6 +12,15 @@ pytestmark = pytest.mark.gpu
 DEV = 'cuda'
 
 
+@pytest.fixture(autouse=True)
+def no_device_side_timeout():
+    """A bounded wait that expired inside a tcgen05 kernel is reported through the
+    device status word; every test must leave it at zero."""
+    yield
+    from torch_blocksparse_b200 import fused
+    assert fused.device_status() == 0, 'a bounded device-side wait expired'
+
+
 def run_module(mod, q, k, v, do, **kw):
     qg, kg, vg = (t.to(DEV).requires_grad_() for t in (q, k, v))
     gkw = {n: (t.to(DEV) if torch.is_tensor(t) else t) for n, t in kw.items()}

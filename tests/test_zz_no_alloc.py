@@ -29,7 +29,7 @@ def _backward(entry, t, meta, block, scale, delta=None):
         head.append(delta.data_ptr())
     args = head + [g.data_ptr() for g in grads] + [_lib.F16, block, Z, H, L, D] \
         + [*st(q), *st(k), *st(v), *st(o), *st(do)] \
-        + [meta.hdr.data_ptr(), meta.on(q.device).data_ptr(), scale] \
+        + [meta.hdr.data_ptr(), meta.on(q.device).data_ptr(), None, None, scale] \
         + [None, 0, 0, 0, None, 0, 0, None, 0, 0] \
         + [torch.cuda.current_stream().cuda_stream]
     _lib.check(entry(*args))
@@ -45,7 +45,7 @@ def _forward(c, meta):
     st = lambda x: (x.stride(0), x.stride(1), x.stride(2))
     _lib.check(_lib.lib().bsp_attn_fwd(
         q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(), _lib.F16, c['block'], Z, H, L, D,
-        *st(q), *st(k), *st(v), *st(o), meta.hdr.data_ptr(), meta.on(q.device).data_ptr(), c['scale'],
+        *st(q), *st(k), *st(v), *st(o), meta.hdr.data_ptr(), meta.on(q.device).data_ptr(), None, None, c['scale'],
         None, 0, 0, 0, None, 0, 0, None, 0, 0, torch.cuda.current_stream().cuda_stream))
     return q, k, v, o, do, lse
 
@@ -74,7 +74,7 @@ def test_static_scratch_size_limit_is_reported():
     # Z * H * L one past the limit: rejected before anything is launched or dereferenced
     Z = rows // (2 * 1024) + 1
     rc = L.bsp_attn_bwd_static(16, 16, 16, 16, 16, 16, 16, 16, 16, _lib.F16, 64, Z, 2, 1024, 64,
-                               *([8] * 15), meta.hdr.data_ptr(), meta.on(torch.device(DEV)).data_ptr(), 0.125,
+                               *([8] * 15), meta.hdr.data_ptr(), meta.on(torch.device(DEV)).data_ptr(), None, None, 0.125,
                                None, 0, 0, 0, None, 0, 0, None, 0, 0, None)
     assert rc == _lib.ERR_UNSUPPORTED
     msg = L.bsp_last_error().decode()

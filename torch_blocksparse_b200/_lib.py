@@ -33,6 +33,8 @@ _SIGNATURES = {
                                   c_void_p, c_int64, _I64P, _IP, _IP]),
     'bsp_softmax_lut_build': (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, c_int64, _I64P, _IP]),
     'bsp_fixed_layout_build': (c_int, [c_int] * 7 + [c_void_p]),
+    'bsp_device_status': (c_int, [_IP]),
+    'bsp_attn_tiles_build': (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, c_int64, _I64P]),
     'bsp_meta_build': (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, c_int64, _I64P]),
     'bsp_softmax_fwd': (c_int, [c_void_p, c_int, c_int, c_int64, c_int, c_int, c_int, c_void_p, c_int, c_float]
                         + _MASKS + [c_void_p]),
@@ -44,13 +46,13 @@ _SIGNATURES = {
                 + [c_int64] * 8 + [c_void_p, c_void_p, c_void_p]),
     'bsp_dds': (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int]
                 + [c_int64] * 4 + [c_int64, c_int] + [c_int64] * 4 + [c_void_p, c_void_p, c_void_p]),
-    'bsp_attn_fwd': (c_int, [c_void_p] * 5 + [c_int] * 6 + [c_int64] * 12 + [c_void_p, c_void_p, c_float]
+    'bsp_attn_fwd': (c_int, [c_void_p] * 5 + [c_int] * 6 + [c_int64] * 12 + [c_void_p] * 4 + [c_float]
                      + _MASKS + [c_void_p]),
-    'bsp_attn_bwd': (c_int, [c_void_p] * 10 + [c_int] * 6 + [c_int64] * 15 + [c_void_p, c_void_p, c_float]
+    'bsp_attn_bwd': (c_int, [c_void_p] * 10 + [c_int] * 6 + [c_int64] * 15 + [c_void_p] * 4 + [c_float]
                      + _MASKS + [c_void_p]),
-    'bsp_attn_bwd_static': (c_int, [c_void_p] * 9 + [c_int] * 6 + [c_int64] * 15 + [c_void_p, c_void_p, c_float]
+    'bsp_attn_bwd_static': (c_int, [c_void_p] * 9 + [c_int] * 6 + [c_int64] * 15 + [c_void_p] * 4 + [c_float]
                             + _MASKS + [c_void_p]),
-    'bsp_attn_bwd_parts': (c_int, [c_void_p] * 10 + [c_int] * 6 + [c_int64] * 15 + [c_void_p, c_void_p, c_float]
+    'bsp_attn_bwd_parts': (c_int, [c_void_p] * 10 + [c_int] * 6 + [c_int64] * 15 + [c_void_p] * 4 + [c_float]
                            + _MASKS + [c_int, c_void_p]),
 }
 

@@ -63,6 +63,7 @@ class DeepSpeedSparseSelfAttention(nn.Module):
         self.attn_mask_mode = attn_mask_mode
         self.fused = fused
         self.ops = dict()
+        self.tiles = dict()
 
     def get_layout(self, H, L):
         """The [H, L/block, L/block] layout used for H heads and sequence length L."""
@@ -89,6 +90,7 @@ class DeepSpeedSparseSelfAttention(nn.Module):
             dsd_nn = MatMul(layout, self.block, 'dsd', trans_a=False, trans_b=False)
             dsd_nn._meta = sdd_nt.meta            # one metadata buffer per layout
             self.ops[key] = (sdd_nt, dsd_nn, Softmax(layout, self.block))
+            self.tiles[key] = tables.build_attn_tiles(layout, self.block) if self.fused else None
         return self.ops[key]
 
     def transpose_key_for_scores(self, x, L):
@@ -127,7 +129,8 @@ class DeepSpeedSparseSelfAttention(nn.Module):
             if fused_supported(query, self.block):
                 return fused_attention(query, key, value, sdd_nt.meta, self.block, scaling, rpe,
                                        key_padding_mask, attn_mask,
-                                       self.key_padding_mask_mode, self.attn_mask_mode)
+                                       self.key_padding_mask_mode, self.attn_mask_mode,
+                                       tiles=self.tiles[(num_heads, tgt_len)])
         w = sdd_nt(query, key)
         w = softmax(w, scale=scaling, rpe=rpe, key_padding_mask=key_padding_mask, attn_mask=attn_mask,
                     key_padding_mask_mode=self.key_padding_mask_mode, attn_mask_mode=self.attn_mask_mode)

@@ -11,7 +11,22 @@
 static __device__ __align__(256) float g_static_delta[BSP_ATTN_STATIC_ROWS];
 
 namespace bsp {
+
+int attn_fwd_tc(const void* q, const void* k, const void* v, void* o, float* lse,
+                int dtype, int Z, int H, int L, int D,
+                int64_t q_sz, int64_t q_sh, int64_t q_sr, int64_t k_sz, int64_t k_sh, int64_t k_sr,
+                int64_t v_sz, int64_t v_sh, int64_t v_sr, int64_t o_sz, int64_t o_sh, int64_t o_sr,
+                const int32_t* tiles_hdr, const int32_t* tiles, float scale, cudaStream_t st);
+int tc_device_status(int* out);
+
 namespace {
+
+// The tcgen05 kernels cover the unmasked FP16 / BF16 case on 128-row tiles.
+bool tc_eligible(const int32_t* tiles_hdr, const int32_t* tiles, int block, int L, int D,
+                 const void* rpe, const void* kpm, const void* am) {
+  return tiles_hdr && tiles && (block == 64 || block == 128) && (D == 64 || D == 128) && L % 128 == 0 &&
+         !rpe && !kpm && !am;
+}
 
 constexpr int kMaxDevices = 64;
 std::mutex g_static_mutex;
@@ -82,7 +97,8 @@ extern "C" int bsp_attn_fwd(const void* q, const void* k, const void* v, void* o
                             int64_t k_sz, int64_t k_sh, int64_t k_sr,
                             int64_t v_sz, int64_t v_sh, int64_t v_sr,
                             int64_t o_sz, int64_t o_sh, int64_t o_sr,
-                            const int32_t* meta_hdr, const int32_t* meta, float scale,
+                            const int32_t* meta_hdr, const int32_t* meta,
+                            const int32_t* tiles_hdr, const int32_t* tiles, float scale,
                             const void* rpe, int64_t rpe_sz, int64_t rpe_sh, int64_t rpe_sr,
                             const void* kpm, int64_t kpm_sz, int kpm_mul,
                             const void* am, int64_t am_sr, int am_mul, void* stream) {
@@ -98,6 +114,9 @@ extern "C" int bsp_attn_fwd(const void* q, const void* k, const void* v, void* o
   p.q_sz = q_sz; p.q_sh = q_sh; p.q_sr = q_sr; p.k_sz = k_sz; p.k_sh = k_sh; p.k_sr = k_sr;
   p.v_sz = v_sz; p.v_sh = v_sh; p.v_sr = v_sr; p.o_sz = o_sz; p.o_sh = o_sh; p.o_sr = o_sr;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (tc_eligible(tiles_hdr, tiles, block, L, D, rpe, kpm, am))
+    return attn_fwd_tc(q, k, v, o, lse, dtype, Z, H, L, D, q_sz, q_sh, q_sr, k_sz, k_sh, k_sr, v_sz, v_sh, v_sr,
+                       o_sz, o_sh, o_sr, tiles_hdr, tiles, scale, st);
   if (dtype == BSP_F16) return attn_fwd_t<__half>(p, block, D, Z, st);
   return attn_fwd_t<__nv_bfloat16>(p, block, D, Z, st);
 }
@@ -111,7 +130,8 @@ extern "C" int bsp_attn_bwd_parts(const void* q, const void* k, const void* v, c
                             int64_t v_sz, int64_t v_sh, int64_t v_sr,
                             int64_t o_sz, int64_t o_sh, int64_t o_sr,
                             int64_t do_sz, int64_t do_sh, int64_t do_sr,
-                            const int32_t* meta_hdr, const int32_t* meta, float scale,
+                            const int32_t* meta_hdr, const int32_t* meta,
+                            const int32_t* tiles_hdr, const int32_t* tiles, float scale,
                             const void* rpe, int64_t rpe_sz, int64_t rpe_sh, int64_t rpe_sr,
                             const void* kpm, int64_t kpm_sz, int kpm_mul,
                             const void* am, int64_t am_sr, int am_mul, int parts, void* stream) {
@@ -147,13 +167,14 @@ extern "C" int bsp_attn_bwd(const void* q, const void* k, const void* v, const v
                             int64_t v_sz, int64_t v_sh, int64_t v_sr,
                             int64_t o_sz, int64_t o_sh, int64_t o_sr,
                             int64_t do_sz, int64_t do_sh, int64_t do_sr,
-                            const int32_t* meta_hdr, const int32_t* meta, float scale,
+                            const int32_t* meta_hdr, const int32_t* meta,
+                            const int32_t* tiles_hdr, const int32_t* tiles, float scale,
                             const void* rpe, int64_t rpe_sz, int64_t rpe_sh, int64_t rpe_sr,
                             const void* kpm, int64_t kpm_sz, int kpm_mul,
                             const void* am, int64_t am_sr, int am_mul, void* stream) {
   return bsp_attn_bwd_parts(q, k, v, o, dout, lse, delta, dq, dk, dv, dtype, block, Z, H, L, D,
                             q_sz, q_sh, q_sr, k_sz, k_sh, k_sr, v_sz, v_sh, v_sr, o_sz, o_sh, o_sr,
-                            do_sz, do_sh, do_sr, meta_hdr, meta, scale, rpe, rpe_sz, rpe_sh, rpe_sr,
+                            do_sz, do_sh, do_sr, meta_hdr, meta, tiles_hdr, tiles, scale, rpe, rpe_sz, rpe_sh, rpe_sr,
                             kpm, kpm_sz, kpm_mul, am, am_sr, am_mul, 7, stream);
 }
 
@@ -166,7 +187,8 @@ extern "C" int bsp_attn_bwd_static(const void* q, const void* k, const void* v, 
                                    int64_t v_sz, int64_t v_sh, int64_t v_sr,
                                    int64_t o_sz, int64_t o_sh, int64_t o_sr,
                                    int64_t do_sz, int64_t do_sh, int64_t do_sr,
-                                   const int32_t* meta_hdr, const int32_t* meta, float scale,
+                                   const int32_t* meta_hdr, const int32_t* meta,
+                            const int32_t* tiles_hdr, const int32_t* tiles, float scale,
                                    const void* rpe, int64_t rpe_sz, int64_t rpe_sh, int64_t rpe_sr,
                                    const void* kpm, int64_t kpm_sz, int kpm_mul,
                                    const void* am, int64_t am_sr, int am_mul, void* stream) {
@@ -180,6 +202,11 @@ extern "C" int bsp_attn_bwd_static(const void* q, const void* k, const void* v, 
   if (int rc = static_delta_address(&delta)) return rc;
   return bsp_attn_bwd_parts(q, k, v, o, dout, lse, delta, dq, dk, dv, dtype, block, Z, H, L, D,
                             q_sz, q_sh, q_sr, k_sz, k_sh, k_sr, v_sz, v_sh, v_sr, o_sz, o_sh, o_sr,
-                            do_sz, do_sh, do_sr, meta_hdr, meta, scale, rpe, rpe_sz, rpe_sh, rpe_sr,
+                            do_sz, do_sh, do_sr, meta_hdr, meta, tiles_hdr, tiles, scale, rpe, rpe_sz, rpe_sh, rpe_sr,
                             kpm, kpm_sz, kpm_mul, am, am_sr, am_mul, 7, stream);
+}
+
+extern "C" int bsp_device_status(int* status) {
+  if (!status) return fail(BSP_ERR_INVALID, "status is NULL");
+  return tc_device_status(status);
 }

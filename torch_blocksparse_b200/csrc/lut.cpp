@@ -412,4 +412,63 @@ int bsp_meta_build(const int64_t* layout, int H, int Mb, int Nb,
   return BSP_OK;
 }
 
+
+// Tile lists of the tcgen05 attention kernels.  Those kernels work on tiles of
+// 128 query rows (forward, dQ) or 128 key rows (dK / dV) and walk chunks of 64
+// rows of the other operand.  With block 64 a tile spans two block-rows
+// (block-columns) of the layout: its list is the union of their nonzero
+// positions with a 2-bit mask saying which half of the tile really owns the
+// block.  With block 128 a tile is one block-row and every nonzero block
+// contributes two chunks.
+int bsp_attn_tiles_build(const int64_t* layout, int H, int nb, int block,
+                         int32_t* out, int64_t out_cap, int64_t* total) {
+  if (int rc = check_layout_args(layout, H, nb, nb)) return rc;
+  if (!total) return fail(BSP_ERR_INVALID, "NULL result pointer");
+  if (block != 64 && block != 128) return fail(BSP_ERR_UNSUPPORTED, "attention tiles exist for block 64 and 128 (got %d)", block);
+  if ((int64_t)nb * block % 128) return fail(BSP_ERR_UNSUPPORTED, "sequence length must be a multiple of 128");
+  const int rpt = 128 / block;                       // block-rows per tile
+  const int cpb = block / 64;                        // chunks per block
+  const int nt = nb / rpt;                           // tiles per head (rows and columns alike)
+  auto at = [&](int h, int i, int j) { return layout[(size_t(h) * nb + i) * nb + j] != 0; };
+  std::vector<int32_t> rt_ptr(1, 0), rt_chunk, rt_mask, ct_ptr(1, 0), ct_chunk, ct_mask;
+  for (int h = 0; h < H; ++h)
+    for (int t = 0; t < nt; ++t) {
+      for (int j = 0; j < nb; ++j) {
+        int mask = 0;
+        for (int r = 0; r < rpt; ++r) mask |= at(h, t * rpt + r, j) ? (1 << r) : 0;
+        if (!mask) continue;
+        for (int c = 0; c < cpb; ++c) { rt_chunk.push_back(j * cpb + c); rt_mask.push_back(rpt == 1 ? 3 : mask); }
+      }
+      rt_ptr.push_back(int32_t(rt_chunk.size()));
+    }
+  for (int h = 0; h < H; ++h)
+    for (int t = 0; t < nt; ++t) {
+      for (int i = 0; i < nb; ++i) {
+        int mask = 0;
+        for (int r = 0; r < rpt; ++r) mask |= at(h, i, t * rpt + r) ? (1 << r) : 0;
+        if (!mask) continue;
+        for (int c = 0; c < cpb; ++c) { ct_chunk.push_back(i * cpb + c); ct_mask.push_back(rpt == 1 ? 3 : mask); }
+      }
+      ct_ptr.push_back(int32_t(ct_chunk.size()));
+    }
+  const int64_t n = int64_t(H) * nt;
+  const int64_t need = BSP_TILES_HEADER + 2 * (n + 1) + 2 * int64_t(rt_chunk.size()) + 2 * int64_t(ct_chunk.size()) + 2 * n;
+  *total = need;
+  if (!out) return BSP_OK;
+  if (out_cap < need) return fail(BSP_ERR_CAPACITY, "attention tile lists need %lld ints, buffer holds %lld", (long long)need, (long long)out_cap);
+  int32_t* p = out;
+  p[0] = BSP_TILES_MAGIC; p[1] = H; p[2] = nb; p[3] = block; p[4] = nt;
+  p[5] = int32_t(rt_chunk.size()); p[6] = int32_t(ct_chunk.size()); p[7] = 0;
+  p += BSP_TILES_HEADER;
+  auto put = [&](const std::vector<int32_t>& v) { std::copy(v.begin(), v.end(), p); p += v.size(); };
+  auto put_order = [&](const std::vector<int32_t>& ptr) {
+    std::iota(p, p + n, 0);
+    std::stable_sort(p, p + n, [&](int32_t x, int32_t y) { return ptr[x + 1] - ptr[x] > ptr[y + 1] - ptr[y]; });
+    p += n;
+  };
+  put(rt_ptr); put(rt_chunk); put(rt_mask); put_order(rt_ptr);
+  put(ct_ptr); put(ct_chunk); put(ct_mask); put_order(ct_ptr);
+  return BSP_OK;
+}
+
 }  // extern "C"

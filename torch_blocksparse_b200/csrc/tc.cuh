@@ -1,0 +1,132 @@
+// Thin wrappers over the Blackwell (sm_100a) instructions the tcgen05 kernels
+// use: mbarrier, TMA tile loads (cp.async.bulk.tensor), tensor-memory
+// allocation / load / store, tcgen05.mma and its descriptors.
+//
+// Every wait is bounded: a wait that does not complete within its budget
+// returns false, the caller records the failure in a status word and keeps its
+// control flow (barriers included) intact, so a protocol error shows up as an
+// error code, never as a hung GPU.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <cstdint>
+
+namespace bsp {
+namespace tc {
+
+#define BSP_DEVI __device__ __forceinline__
+
+BSP_DEVI uint32_t saddr(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+// ---- mbarrier ---------------------------------------------------------------
+BSP_DEVI void mbar_init(uint64_t* bar, int count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(saddr(bar)), "r"(count));
+}
+BSP_DEVI void mbar_init_fence() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+BSP_DEVI void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(saddr(bar)), "r"(bytes) : "memory");
+}
+BSP_DEVI bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+               : "=r"(ok) : "r"(saddr(bar)), "r"(parity) : "memory");
+  return ok != 0;
+}
+constexpr int kWaitBudget = 1 << 21;   // try_wait attempts before a wait is declared failed
+// Returns false when the phase did not complete in time, or at once when the
+// CTA has already failed (*failed != 0), so that a failed CTA drains quickly.
+BSP_DEVI bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* failed) {
+  for (int i = 0; i < kWaitBudget; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((i & 1023) == 1023 && *failed) return false;
+  }
+  *failed = 1;
+  return false;
+}
+
+// ---- TMA ----------------------------------------------------------------------
+BSP_DEVI void tma_load_4d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1, int c2, int c3) {
+  asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+               ::"r"(saddr(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(saddr(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+               : "memory");
+}
+BSP_DEVI void prefetch_map(const CUtensorMap* map) {
+  asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
+}
+
+// ---- tensor memory ---------------------------------------------------------------
+BSP_DEVI void tmem_alloc(uint32_t* slot, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(saddr(slot)), "r"(ncols) : "memory");
+}
+BSP_DEVI void tmem_relinquish() { asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory"); }
+BSP_DEVI void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+BSP_DEVI void fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+BSP_DEVI void fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+BSP_DEVI void commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(saddr(bar)) : "memory");
+}
+// 32 lanes x 32 consecutive 32-bit columns; the warp reads its own quarter of the lanes
+BSP_DEVI void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+               "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                 "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                 "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                 "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+               : "r"(taddr) : "memory");
+}
+BSP_DEVI void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+BSP_DEVI void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+               "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+               ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+                 "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+                 "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+                 "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31]) : "memory");
+}
+BSP_DEVI void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// ---- tcgen05.mma ---------------------------------------------------------------
+// D[tmem] (+)= A[smem] * B[smem]
+BSP_DEVI void mma_ss(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+               ::"r"(d), "l"(a), "l"(b), "r"(idesc), "r"(accumulate) : "memory");
+}
+// D[tmem] (+)= A[tmem] * B[smem]; A holds two 16-bit values per 32-bit column
+BSP_DEVI void mma_ts(uint32_t d, uint32_t a, uint64_t b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+               ::"r"(d), "r"(a), "l"(b), "r"(idesc), "r"(accumulate) : "memory");
+}
+
+// Shared-memory operand descriptor for tiles in the 128-byte-swizzled layout TMA
+// writes (rows of 128 bytes, groups of 8 rows = 1024 bytes).  `sbo` is the
+// distance between consecutive 8-row groups.  For a K-major operand a row is an
+// M/N index and holds 64 K-elements: one MMA (K = 16) reads 32 bytes of each
+// row, so successive K-steps advance the start address by 32 bytes.  For an
+// MN-major operand a row is a K index and holds 64 M/N-elements: one MMA reads
+// 16 rows, successive K-steps advance the start address by 2048 bytes.
+BSP_DEVI uint64_t smem_desc(uint32_t addr, uint32_t sbo_bytes) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((addr & 0x3FFFF) >> 4);
+  d |= static_cast<uint64_t>(1) << 16;                       // leading-dimension offset: unused for these layouts
+  d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3FFF) << 32;
+  d |= static_cast<uint64_t>(1) << 46;                       // descriptor version of sm_100
+  d |= static_cast<uint64_t>(2) << 61;                       // 128-byte swizzle
+  return d;
+}
+// Instruction descriptor, kind::f16: FP16 (0) or BF16 (1) operands, FP32 accumulator.
+BSP_DEVI uint32_t instr_desc(int M, int N, int b_mn_major, int bf16) {
+  uint32_t d = 0;
+  d |= 1u << 4;                                  // accumulator format: F32
+  d |= static_cast<uint32_t>(bf16) << 7;         // A format
+  d |= static_cast<uint32_t>(bf16) << 10;        // B format
+  d |= static_cast<uint32_t>(b_mn_major) << 16;  // B is MN-major (A stays K-major)
+  d |= static_cast<uint32_t>(N >> 3) << 17;
+  d |= static_cast<uint32_t>(M >> 4) << 24;
+  return d;
+}
+
+}  // namespace tc
+}  // namespace bsp

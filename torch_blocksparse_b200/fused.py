@@ -19,6 +19,10 @@ from .matmul import _dtype_code, _require_cuda, _stream
 # benchmark to time each kernel inside a full step; None costs nothing.
 PROFILE = None
 
+# Kernel family of the unmasked FP16 / BF16 case on block 64 / 128: 'tc' (tcgen05,
+# tensor memory, TMA) or 'mma' (mma.sync).  Everything else always runs on 'mma'.
+PATH = 'tc'
+
 KERNELS_PER_FWD = 1
 KERNELS_PER_BWD = 3
 
@@ -91,7 +95,7 @@ def _mask_args(Z, H, L, dtype, rpe, kpm, am, kp_mode, am_mode):
 class _fused_attention(torch.autograd.Function):
 
     @staticmethod
-    def forward(ctx, q, k, v, meta, block, scale, rpe, kpm, am, kp_mode, am_mode):
+    def forward(ctx, q, k, v, meta, tiles, block, scale, rpe, kpm, am, kp_mode, am_mode):
         _require_cuda(q, k, v)
         Z, H, L, D = q.shape
         q, k, v = _rows(q), _rows(k), _rows(v)
@@ -103,9 +107,9 @@ class _fused_attention(torch.autograd.Function):
             _dtype_code(q), block, Z, H, L, D,
             q.stride(0), q.stride(1), q.stride(2), k.stride(0), k.stride(1), k.stride(2),
             v.stride(0), v.stride(1), v.stride(2), o.stride(0), o.stride(1), o.stride(2),
-            meta.hdr.data_ptr(), meta.on(q.device).data_ptr(), scale, *margs, _stream(q))))
+            meta.hdr.data_ptr(), meta.on(q.device).data_ptr(), *_tile_args(tiles, q.device), scale, *margs, _stream(q))))
         ctx.save_for_backward(q, k, v, o, lse, *keep)
-        ctx.meta, ctx.block, ctx.scale = meta, block, scale
+        ctx.meta, ctx.tiles, ctx.block, ctx.scale = meta, tiles, block, scale
         ctx.mask_spec = (rpe is not None, kpm is not None, am is not None, kp_mode, am_mode)
         return o
 
@@ -127,21 +131,36 @@ class _fused_attention(torch.autograd.Function):
                 q.stride(0), q.stride(1), q.stride(2), k.stride(0), k.stride(1), k.stride(2),
                 v.stride(0), v.stride(1), v.stride(2), o.stride(0), o.stride(1), o.stride(2),
                 do.stride(0), do.stride(1), do.stride(2),
-                ctx.meta.hdr.data_ptr(), ctx.meta.on(q.device).data_ptr(), ctx.scale) + margs
+                ctx.meta.hdr.data_ptr(), ctx.meta.on(q.device).data_ptr(), *_tile_args(ctx.tiles, q.device),
+                ctx.scale) + margs
         L_ = _lib.lib()
         if PROFILE is None:
             _lib.check(L_.bsp_attn_bwd(*args, _stream(q)))
         else:
             for name, part in (('attn_bwd_delta', 1), ('attn_bwd_dkdv', 2), ('attn_bwd_dq', 4)):
                 _timed(name, lambda part=part: _lib.check(L_.bsp_attn_bwd_parts(*args, part, _stream(q))))
-        return (dq, dk, dv) + (None,) * 8
+        return (dq, dk, dv) + (None,) * 9
+
+
+def _tile_args(tiles, device):
+    if tiles is None or PATH != 'tc':
+        return (None, None)
+    return (tiles.hdr.data_ptr(), tiles.on(device).data_ptr())
+
+
+def device_status():
+    """0, or non-zero when a bounded wait inside a tcgen05 kernel expired (synchronises)."""
+    import ctypes
+    out = ctypes.c_int(0)
+    _lib.check(_lib.lib().bsp_device_status(ctypes.byref(out)))
+    return out.value
 
 
 def fused_attention(q, k, v, meta, block, scale, rpe=None, key_padding_mask=None, attn_mask=None,
-                    key_padding_mask_mode='add', attn_mask_mode='mul'):
+                    key_padding_mask_mode='add', attn_mask_mode='mul', tiles=None):
     """O = softmax(scale * Q K^T + rpe + masks, on the layout) V for [Z, H, L, D] operands."""
     if meta.H != q.size(1) or meta.Mb != meta.Nb or meta.Mb * block != q.size(2):
         raise ValueError('layout [%d,%d,%d] with block %d does not fit operands of shape %s'
                          % (meta.H, meta.Mb, meta.Nb, block, tuple(q.shape)))
-    return _fused_attention.apply(q, k, v, meta, block, float(scale), rpe, key_padding_mask, attn_mask,
+    return _fused_attention.apply(q, k, v, meta, tiles, block, float(scale), rpe, key_padding_mask, attn_mask,
                                   key_padding_mask_mode, attn_mask_mode)

@@ -124,3 +124,32 @@ def build_meta(layout):
         return L.bsp_meta_build(lay.data_ptr(), H, Mb, Nb, ptr, cap, total)
 
     return Meta(_two_pass(call).clone())
+
+
+class AttnTiles:
+    """Tile lists of the tcgen05 attention kernels: host header + device buffer."""
+
+    def __init__(self, host):
+        self.host = host
+        self.hdr = host[:8].clone()
+        self._dev = {}
+
+    def on(self, device):
+        key = str(device)
+        if key not in self._dev:
+            self._dev[key] = self.host.to(device)
+        return self._dev[key]
+
+
+def build_attn_tiles(layout, block):
+    """Returns the AttnTiles of a square [H, nb, nb] layout, or None when the
+    tcgen05 kernels do not cover it (block not 64 / 128, length not a multiple of 128)."""
+    lay, H, Mb, Nb = _layout_i64(layout)
+    if Mb != Nb or block not in (64, 128) or (Mb * block) % 128:
+        return None
+    L = _lib.lib()
+
+    def call(ptr, cap, total):
+        return L.bsp_attn_tiles_build(lay.data_ptr(), H, Mb, block, ptr, cap, total)
+
+    return AttnTiles(_two_pass(call).clone())
