@@ -132,15 +132,17 @@ int bsp_meta_build(const int64_t* layout, int H, int Mb, int Nb,
 /*
  * Tile lists of the tcgen05 attention kernels (no counterpart in the
  * reference).  Those kernels work on tiles of 128 query rows (forward, dQ) or
- * 128 key rows (dK, dV) and walk chunks of 64 rows of the other operand.  With
- * block 64 a tile covers two block-rows (block-columns): its list is the union
- * of their nonzero positions plus a 2-bit mask telling which half of the tile
- * owns the block.  int32 layout of `out`:
+ * 128 key rows (dK, dV), made of two 64-row chunks, and walk 64-row chunks of
+ * the other operand.  With block 128 a tile is one block-row; with block 64 it
+ * is a pair of block-rows (block-columns) of one head, chosen by similarity of
+ * their nonzero sets: its list is the union of their positions plus a 2-bit
+ * mask telling which half of the tile owns the block.  int32 layout of `out`:
  *   [0] magic [1] H [2] L/block [3] block [4] tiles per head [5] row entries
  *   [6] column entries [7] reserved
- *   rt_ptr [H*tiles+1]  rt_chunk [E_r]  rt_mask [E_r]  rt_order [H*tiles]
- *   ct_ptr [H*tiles+1]  ct_chunk [E_c]  ct_mask [E_c]  ct_order [H*tiles]
- * block must be 64 or 128 and L a multiple of 128 (else BSP_ERR_UNSUPPORTED).
+ *   then twice (row tiles, column tiles), n = H * tiles per head:
+ *   c01 [2n] (the tile's two 64-row chunk ids, -1: none)  ptr [n+1]
+ *   chunk [E]  mask [E]  order [n] (tiles sorted longest first)
+ * block must be 64 or 128 (else BSP_ERR_UNSUPPORTED).
  */
 #define BSP_TILES_MAGIC 0x42535054
 #define BSP_TILES_HEADER 8

@@ -3,25 +3,30 @@
 //
 // Same contract as the mma.sync kernels of attn_impl.cuh (which replace the
 // sdd -> softmax -> dsd chain of
-// torch_blocksparse/deepspeedsparseselfattention.py:157-166); this path covers
-// block 64 and 128, head dimension 64 and 128, FP16 / BF16, without rpe / masks.
+// torch_blocksparse/deepspeedsparseselfattention.py:157-166 and its backward);
+// this path covers block 64 and 128, head dimension 64 and 128, FP16 / BF16,
+// without rpe / masks.
 //
-// Geometry: every MMA has M = 128.  A CTA owns a tile of 128 query rows (two
-// block-rows of the layout when block = 64, see bsp_attn_tiles_build) and walks
-// the tile's list of 64-row key chunks:
-//     S[128 x 64]  = Q . K_chunk^T          (A, B from shared memory, K-major)
-//     P            = 2^(S*c - m)            (registers; one thread per query row)
-//     O[128 x D]  += P . V_chunk            (A = P from tensor memory, B MN-major)
-// S, P and O live in tensor memory (S: 64 columns, P packed over the first 32
-// of them, O: D columns).  Because P reuses the columns of S, the next S is
-// only issued once the product that reads P has completed.  The running maximum is only raised when it grows by
-// more than 2^8 ("lazy rescale"), so O is almost never read back before the end.
-// For block = 64 a 2-bit mask per chunk says which half of the tile owns the
-// block; the other half sees -inf.
+// Geometry: every MMA has M = 128.  A CTA owns a tile of 128 rows of the
+// "outer" operand(s), resident in shared memory, made of two 64-row chunks (one
+// block-row when block = 128, a pair of block-rows when block = 64, see
+// bsp_attn_tiles_build), and walks the tile's list of 64-row "inner" chunks:
 //
-// 128 threads per CTA (thread r = query row r = TMEM lane r); thread 0 also
-// issues the TMA loads and the MMAs.  Several CTAs per SM overlap one CTA's
-// exponentials with another's MMAs.  All waits are bounded (tc.cuh).
+//   forward   outer Q            inner K, V     S = Q K^T;  P = 2^(S c - m);  O += P V
+//   dQ        outer Q, dO        inner K, V     S = Q K^T, dP = dO V^T;  dS = P (dP - delta) scale;  dQ += dS K
+//   dK / dV   outer K, V         inner Q, dO    S^T = K Q^T, dP^T = V dO^T;  dV += P^T dO,  dK += dS^T Q
+//
+// Scores live in tensor memory in two buffers, so the tensor core computes the
+// scores of chunk t+1 while the compute warps turn chunk t into P / dS; P / dS
+// are written back (16-bit, packed) over the scores they came from and feed the
+// accumulating products as the A operand straight from tensor memory.  For
+// block = 64 a 2-bit mask per chunk says which half of the tile owns the block;
+// the other half contributes zeros.
+//
+// Warp roles: compute warps (thread = one tile row, or half a row in the
+// backward), one TMA producer warp (4-stage ring of inner chunks), one MMA
+// issuer warp.  They talk through mbarriers only; every wait is bounded
+// (tc.cuh) and a wait that expires sets the device status word.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include "common.h"
@@ -39,14 +44,17 @@ using namespace tc;
 
 constexpr float kLog2eT = 1.4426950408889634f;
 constexpr float kNegInfT = -__builtin_huge_valf();
-constexpr int kStagesFwd = 3;
+constexpr int kStages = 4;
+constexpr int FWD = 0, DQ = 1, DKV = 2;
 
-struct TcFwdArgs {
-  void* o; float* lse;
-  int64_t o_sz, o_sh, o_sr;
+struct TcArgs {
+  void* out0; void* out1;             // FWD: O | DQ: dQ | DKV: dK, dV
+  float* lse_out;                     // FWD
+  const float* lse; const float* delta;   // backward
+  int64_t o_sz, o_sh, o_sr;           // strides of O (FWD); gradients are contiguous [Z, H, L, D]
   int H, L, tiles_per_head;
-  float scale_log2;
-  const int32_t *ptr, *chunk, *mask, *order;
+  float scale, scale_log2;
+  const int32_t *c01, *ptr, *chunk, *mask, *order;
 };
 
 template <typename T> BSP_DEVI uint32_t pack16(float a, float b);
@@ -61,197 +69,322 @@ template <> BSP_DEVI uint32_t pack16<__nv_bfloat16>(float a, float b) {
 template <typename T> struct IsBf16 { static constexpr int v = 0; };
 template <> struct IsBf16<__nv_bfloat16> { static constexpr int v = 1; };
 
-template <int D> struct FwdSmem {
-  static constexpr int ATOMS = D / 64;                  // 64-element (128-byte) column groups
-  static constexpr int Q_BYTES = ATOMS * 128 * 128;     // 128 rows
-  static constexpr int KV_BYTES = ATOMS * 64 * 128;     // 64 rows
-  static constexpr int TOTAL = Q_BYTES + kStagesFwd * 2 * KV_BYTES + 1024;   // + alignment slack
-  static constexpr int TMEM_COLS = D == 64 ? 128 : 256; // S (64) + O (D), rounded to a power of two
+template <int D, int MODE> struct Cfg {
+  static constexpr int ATOMS = D / 64;                         // 64-element (128-byte) column groups
+  static constexpr int NRES = MODE == FWD ? 1 : 2;             // resident 128-row operands
+  static constexpr int NC = MODE == FWD ? 4 : 8;               // compute warps
+  static constexpr int NT = (NC + 2) * 32;
+  static constexpr int RES_BYTES = ATOMS * 128 * 128;
+  static constexpr int CH_BYTES = ATOMS * 64 * 128;
+  static constexpr int STAGE = 2 * CH_BYTES + (MODE == DKV ? 1024 : 0);   // + lse / delta of the chunk
+  static constexpr int SMEM = NRES * RES_BYTES + kStages * STAGE + 1024;
+  static constexpr int SCORE_COLS = MODE == FWD ? 64 : 128;    // per buffer: S (and dP)
+  static constexpr int ACC_BASE = 2 * SCORE_COLS;
+  static constexpr int ACC_COLS = MODE == DKV ? 2 * D : D;
+  static constexpr int TMEM = ACC_BASE + ACC_COLS <= 256 ? 256 : 512;
+  static constexpr int CTAS = (MODE == FWD && D == 64) ? 2 : 1;
 };
 
-template <typename T, int D>
-__global__ void __launch_bounds__(128, 3) attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap mq,
-                                                          const __grid_constant__ CUtensorMap mk,
-                                                          const __grid_constant__ CUtensorMap mv, TcFwdArgs a) {
-  using SM = FwdSmem<D>;
-  constexpr int ATOMS = SM::ATOMS, ST = kStagesFwd;
-  extern __shared__ unsigned char smem_raw[];
-  unsigned char* smem = smem_raw + ((1024 - (saddr(smem_raw) & 1023)) & 1023);
-  unsigned char* q_s = smem;
-  unsigned char* k_s = q_s + SM::Q_BYTES;               // [ST][ATOMS][64 rows][128 B]
-  unsigned char* v_s = k_s + ST * SM::KV_BYTES;
-  __shared__ uint64_t bar_q, bar_kv[ST], bar_s, bar_pv;
-  __shared__ uint32_t tmem_slot;
-  __shared__ int failed;
-
-  const int tid = threadIdx.x, warp = tid >> 5;
-  const int z = blockIdx.y;
-  const int ti = a.order[blockIdx.x];
-  const int h = ti / a.tiles_per_head, t128 = ti % a.tiles_per_head;
-  const int first = a.ptr[ti], ntiles = a.ptr[ti + 1] - first;
-  const int row = t128 * 128 + tid;
-  T* orow = reinterpret_cast<T*>(a.o) + z * a.o_sz + h * a.o_sh + (int64_t)row * a.o_sr;
-  float* lse = a.lse + ((int64_t)(z * a.H + h) * a.L + row);
-  if (ntiles == 0) {                                    // nothing attends: zeros, as the dsd product gives
-#pragma unroll
-    for (int c = 0; c < D; c += 8) *reinterpret_cast<uint4*>(orow + c) = make_uint4(0, 0, 0, 0);
-    *lse = kNegInfT;
-    return;
-  }
-  if (tid == 0) {
-    failed = 0;
-    mbar_init(&bar_q, 1);
-    for (int s = 0; s < ST; ++s) mbar_init(&bar_kv[s], 1);
-    mbar_init(&bar_s, 1);
-    mbar_init(&bar_pv, 1);
-    mbar_init_fence();
-    prefetch_map(&mq); prefetch_map(&mk); prefetch_map(&mv);
-  }
-  if (warp == 0) { tmem_alloc(&tmem_slot, SM::TMEM_COLS); tmem_relinquish(); }
-  fence_before();
-  __syncthreads();
-  fence_after();
-  const uint32_t tmem = tmem_slot;
-  const uint32_t t_s = tmem, t_p = tmem, t_o = tmem + 64;
-  const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
-  volatile int* fl = &failed;
-
-  auto load_kv = [&](int t) {                           // thread 0 only
-    const int stage = t % ST;
-    const int krow = a.chunk[first + t] * 64;
-    mbar_expect_tx(&bar_kv[stage], 2 * SM::KV_BYTES);
-#pragma unroll
-    for (int at = 0; at < ATOMS; ++at) {
-      tma_load_4d(k_s + stage * SM::KV_BYTES + at * 8192, &mk, &bar_kv[stage], at * 64, krow, h, z);
-      tma_load_4d(v_s + stage * SM::KV_BYTES + at * 8192, &mv, &bar_kv[stage], at * 64, krow, h, z);
-    }
-  };
-  const uint32_t idesc_qk = instr_desc(128, 64, 0, IsBf16<T>::v);
-  const uint32_t idesc_pv = instr_desc(128, 64, 1, IsBf16<T>::v);
-  auto issue_qk = [&](int t) {                          // thread 0 only: S = Q . K^T
-    const int stage = t % ST;
-    mbar_wait(&bar_kv[stage], (t / ST) & 1, fl);
-    fence_after();
-#pragma unroll
-    for (int ks = 0; ks < D / 16; ++ks) {
-      const uint32_t off = (ks % 4) * 32;
-      const uint64_t da = smem_desc(saddr(q_s + (ks / 4) * 16384) + off, 1024);
-      const uint64_t db = smem_desc(saddr(k_s + stage * SM::KV_BYTES + (ks / 4) * 8192) + off, 1024);
-      mma_ss(t_s, da, db, idesc_qk, ks > 0);
-    }
-    commit(&bar_s);
-  };
-  auto issue_pv = [&](int t) {                          // thread 0 only: O += P . V
-    const int stage = t % ST;
-#pragma unroll
-    for (int at = 0; at < ATOMS; ++at)
-#pragma unroll
-      for (int ks = 0; ks < 4; ++ks) {
-        const uint64_t db = smem_desc(saddr(v_s + stage * SM::KV_BYTES + at * 8192) + ks * 2048, 1024);
-        mma_ts(t_o + at * 64, t_p + ks * 8, db, idesc_pv, (t > 0 || ks > 0) ? 1u : 0u);
-      }
-    commit(&bar_pv);
-  };
-
-  if (tid == 0) {
-    mbar_expect_tx(&bar_q, SM::Q_BYTES);
-#pragma unroll
-    for (int at = 0; at < ATOMS; ++at) tma_load_4d(q_s + at * 16384, &mq, &bar_q, at * 64, t128 * 128, h, z);
-    for (int t = 0; t < ST && t < ntiles; ++t) load_kv(t);
-    mbar_wait(&bar_q, 0, fl);
-    issue_qk(0);
-  }
-
-  float m_ref = kNegInfT, l = 0.f;
-  const int half = warp >> 1;                           // which 64 rows of the tile this warp holds
-  for (int t = 0; t < ntiles; ++t) {
-    const bool valid = (a.mask[first + t] >> half) & 1;
-    mbar_wait(&bar_s, t & 1, fl);
-    fence_after();
-    uint32_t sr[2][32];
-    tmem_ld32(t_s + lane_base, sr[0]);
-    tmem_ld32(t_s + lane_base + 32, sr[1]);
-    tmem_ld_wait();
-    float mt = kNegInfT;
-    if (valid) {
-#pragma unroll
-      for (int i = 0; i < 64; ++i) mt = fmaxf(mt, __uint_as_float(sr[i >> 5][i & 31]));
-      mt *= a.scale_log2;
-    }
-    // raise the reference maximum only when the row maximum outgrows it by 2^8
-    const bool grow = mt > m_ref + 8.f;
-    if (__any_sync(0xffffffffu, grow)) {
-      const float m_new = grow ? mt : m_ref;
-      const float alpha = grow ? fast_exp2(m_ref - m_new) : 1.f;   // 0 while m_ref is still -inf
-      l *= alpha;
-      if (t > 0) {
-        // S(t) is complete, hence so is the earlier PV(t-1): O is stable
-#pragma unroll
-        for (int c = 0; c < D; c += 32) {
-          uint32_t orr[32];
-          tmem_ld32(t_o + lane_base + c, orr);
-          tmem_ld_wait();
-#pragma unroll
-          for (int i = 0; i < 32; ++i) orr[i] = __float_as_uint(__uint_as_float(orr[i]) * alpha);
-          tmem_st32(t_o + lane_base + c, orr);
-        }
-        tmem_st_wait();
-      }
-      m_ref = m_new;
-    }
-    uint32_t pr[32];
-    if (valid) {
-      float sum = 0.f;
-#pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        const float p0 = fast_exp2(fmaf(__uint_as_float(sr[(2 * i) >> 5][(2 * i) & 31]), a.scale_log2, -m_ref));
-        const float p1 = fast_exp2(fmaf(__uint_as_float(sr[(2 * i + 1) >> 5][(2 * i + 1) & 31]), a.scale_log2, -m_ref));
-        sum += p0 + p1;
-        pr[i] = pack16<T>(p0, p1);
-      }
-      l += sum;
-    } else {
-#pragma unroll
-      for (int i = 0; i < 32; ++i) pr[i] = 0u;
-    }
-    tmem_st32(t_p + lane_base, pr);
-    tmem_st_wait();
-    fence_before();
-    __syncthreads();
-    if (tid == 0) {
-      fence_after();
-      issue_pv(t);
-      if (t + 1 < ntiles) {
-        mbar_wait(&bar_pv, t & 1, fl);                  // P(t) shares its columns with S(t+1)
-        issue_qk(t + 1);
-      }
-      // the stage of chunk t-1 is free (PV(t-1) completed before S(t) did): refill it
-      if (t >= 1 && t - 1 + ST < ntiles) load_kv(t - 1 + ST);
-    }
-  }
-  mbar_wait(&bar_pv, (ntiles - 1) & 1, fl);
-  fence_after();
-  const float inv = l > 0.f ? 1.f / l : 0.f;
-#pragma unroll
-  for (int c = 0; c < D; c += 32) {
-    uint32_t orr[32];
-    tmem_ld32(t_o + lane_base + c, orr);
+// Writes accumulator columns [c0, c0 + n) of this thread's tensor-memory lane to dst[c0 .. c0 + n) as 16-bit values.
+template <typename T>
+BSP_DEVI void store_acc(T* dst, uint32_t taddr, int c0, int n, float mul) {
+  for (int c = c0; c < c0 + n; c += 32) {
+    uint32_t r[32];
+    tmem_ld32(taddr + c, r);
     tmem_ld_wait();
 #pragma unroll
     for (int i = 0; i < 32; i += 8) {
       uint4 v;
-      v.x = pack16<T>(__uint_as_float(orr[i]) * inv, __uint_as_float(orr[i + 1]) * inv);
-      v.y = pack16<T>(__uint_as_float(orr[i + 2]) * inv, __uint_as_float(orr[i + 3]) * inv);
-      v.z = pack16<T>(__uint_as_float(orr[i + 4]) * inv, __uint_as_float(orr[i + 5]) * inv);
-      v.w = pack16<T>(__uint_as_float(orr[i + 6]) * inv, __uint_as_float(orr[i + 7]) * inv);
-      *reinterpret_cast<uint4*>(orow + c + i) = v;
+      v.x = pack16<T>(__uint_as_float(r[i]) * mul, __uint_as_float(r[i + 1]) * mul);
+      v.y = pack16<T>(__uint_as_float(r[i + 2]) * mul, __uint_as_float(r[i + 3]) * mul);
+      v.z = pack16<T>(__uint_as_float(r[i + 4]) * mul, __uint_as_float(r[i + 5]) * mul);
+      v.w = pack16<T>(__uint_as_float(r[i + 6]) * mul, __uint_as_float(r[i + 7]) * mul);
+      *reinterpret_cast<uint4*>(dst + c + i) = v;
     }
   }
-  *lse = l > 0.f ? m_ref + log2f(l) : kNegInfT;
+}
+
+template <typename T, int D, int MODE>
+__global__ void __launch_bounds__(Cfg<D, MODE>::NT, Cfg<D, MODE>::CTAS)
+attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant__ CUtensorMap m_res1,
+               const __grid_constant__ CUtensorMap m_ch0, const __grid_constant__ CUtensorMap m_ch1, TcArgs a) {
+  using C = Cfg<D, MODE>;
+  constexpr int ATOMS = C::ATOMS, ST = kStages, NC = C::NC;
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = smem_raw + ((1024 - (saddr(smem_raw) & 1023)) & 1023);
+  unsigned char* res = smem;                                   // [NRES][ATOMS][128 rows][128 B]
+  unsigned char* stg = res + C::NRES * C::RES_BYTES;           // [ST][ch0 | ch1 | lse, delta]
+  __shared__ uint64_t bar_res, bar_full[ST], bar_empty[ST], bar_s[2], bar_p[2], bar_free[2], bar_done;
+  __shared__ uint32_t tmem_slot;
+  __shared__ int failed;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int z = blockIdx.y;
+  const int ti = a.order[blockIdx.x];
+  const int h = ti / a.tiles_per_head;
+  const int first = a.ptr[ti], ntiles = a.ptr[ti + 1] - first;
+  const int c0 = a.c01[2 * ti], c1 = a.c01[2 * ti + 1];
+  const int64_t zh = (int64_t)(z * a.H + h) * a.L;
+
+  // row of the tile this thread works on (compute warps), its global row and whether it exists
+  const int quarter = warp & 3, chalf = (warp < NC) ? (warp >> 2) : 0;
+  const int trow = quarter * 32 + lane;
+  const int mychunk = trow < 64 ? c0 : c1;
+  const int64_t grow = (int64_t)(mychunk < 0 ? 0 : mychunk) * 64 + (trow & 63);
+  const bool row_ok = mychunk >= 0 && warp < NC;
+
+  if (ntiles == 0) {                                          // nothing in this tile: zeros, as the reference's products give
+    if (row_ok && chalf == 0) {
+      T* o0 = MODE == FWD ? reinterpret_cast<T*>(a.out0) + z * a.o_sz + h * a.o_sh + grow * a.o_sr
+                          : reinterpret_cast<T*>(a.out0) + (zh + grow) * D;
+      for (int c = 0; c < D; c += 8) {
+        *reinterpret_cast<uint4*>(o0 + c) = make_uint4(0, 0, 0, 0);
+        if (MODE == DKV) *reinterpret_cast<uint4*>(reinterpret_cast<T*>(a.out1) + (zh + grow) * D + c) = make_uint4(0, 0, 0, 0);
+      }
+      if (MODE == FWD) a.lse_out[zh + grow] = kNegInfT;
+    }
+    return;
+  }
+  if (tid == 0) {
+    failed = 0;
+    mbar_init(&bar_res, 1);
+    for (int s = 0; s < ST; ++s) { mbar_init(&bar_full[s], 1); mbar_init(&bar_empty[s], 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(&bar_s[b], 1); mbar_init(&bar_p[b], NC * 32); mbar_init(&bar_free[b], 1); }
+    mbar_init(&bar_done, 1);
+    mbar_init_fence();
+  }
+  if (warp == 0) { tmem_alloc(&tmem_slot, C::TMEM); tmem_relinquish(); }
   fence_before();
   __syncthreads();
-  if (warp == 0) tmem_dealloc(tmem, SM::TMEM_COLS);
-  if (tid == 0 && failed) atomicExch(&g_tc_status, 1);
+  fence_after();
+  const uint32_t tmem = tmem_slot;
+  volatile int* fl = &failed;
+
+  if (warp == NC) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      prefetch_map(&m_res0); prefetch_map(&m_ch0); prefetch_map(&m_ch1);
+      mbar_expect_tx(&bar_res, C::NRES * C::RES_BYTES);
+      for (int hf = 0; hf < 2; ++hf) {
+        const int crow = (hf == 0 || c1 < 0 ? c0 : c1) * 64;
+        for (int at = 0; at < ATOMS; ++at) {
+          tma_load_4d(res + at * 16384 + hf * 8192, &m_res0, &bar_res, at * 64, crow, h, z);
+          if (C::NRES == 2) tma_load_4d(res + C::RES_BYTES + at * 16384 + hf * 8192, &m_res1, &bar_res, at * 64, crow, h, z);
+        }
+      }
+      for (int t = 0; t < ntiles; ++t) {
+        const int stage = t % ST;
+        if (t >= ST && !mbar_wait(&bar_empty[stage], ((t / ST) - 1) & 1, fl)) break;
+        const int crow = a.chunk[first + t] * 64;
+        unsigned char* sp = stg + stage * C::STAGE;
+        mbar_expect_tx(&bar_full[stage], 2 * C::CH_BYTES + (MODE == DKV ? 512 : 0));
+        for (int at = 0; at < ATOMS; ++at) {
+          tma_load_4d(sp + at * 8192, &m_ch0, &bar_full[stage], at * 64, crow, h, z);
+          tma_load_4d(sp + C::CH_BYTES + at * 8192, &m_ch1, &bar_full[stage], at * 64, crow, h, z);
+        }
+        if (MODE == DKV) {
+          bulk_load(sp + 2 * C::CH_BYTES, a.lse + zh + crow, 256, &bar_full[stage]);
+          bulk_load(sp + 2 * C::CH_BYTES + 256, a.delta + zh + crow, 256, &bar_full[stage]);
+        }
+      }
+    }
+  } else if (warp == NC + 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc_kk = instr_desc(128, 64, 0, IsBf16<T>::v);   // A, B K-major
+      const uint32_t idesc_mn = instr_desc(128, 64, 1, IsBf16<T>::v);   // B MN-major
+      auto scores = [&](int t) {
+        unsigned char* sp = stg + (t % ST) * C::STAGE;
+        const uint32_t ts = tmem + (t & 1) * C::SCORE_COLS;
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks) {
+          const uint32_t off = (ks % 4) * 32;
+          mma_ss(ts, smem_desc(saddr(res + (ks / 4) * 16384) + off, 1024),
+                 smem_desc(saddr(sp + (ks / 4) * 8192) + off, 1024), idesc_kk, ks > 0);
+        }
+        if (MODE != FWD) {
+#pragma unroll
+          for (int ks = 0; ks < D / 16; ++ks) {
+            const uint32_t off = (ks % 4) * 32;
+            mma_ss(ts + 64, smem_desc(saddr(res + C::RES_BYTES + (ks / 4) * 16384) + off, 1024),
+                   smem_desc(saddr(sp + C::CH_BYTES + (ks / 4) * 8192) + off, 1024), idesc_kk, ks > 0);
+          }
+        }
+        commit(&bar_s[t & 1]);
+      };
+      auto accumulate = [&](int t) {
+        unsigned char* sp = stg + (t % ST) * C::STAGE;
+        const uint32_t ts = tmem + (t & 1) * C::SCORE_COLS;
+        const uint32_t ta = tmem + C::ACC_BASE;
+#pragma unroll
+        for (int at = 0; at < ATOMS; ++at)
+#pragma unroll
+          for (int ks = 0; ks < 4; ++ks) {
+            const uint32_t acc = (t > 0 || ks > 0) ? 1u : 0u;
+            // packed 16-bit operand of K-step ks: 8 columns, written by the compute warps
+            const uint32_t pa = (MODE == FWD) ? ts + ks * 8 : ts + (ks >> 1) * 32 + (ks & 1) * 8;
+            if (MODE == FWD) {          // O += P . V
+              mma_ts(ta + at * 64, pa, smem_desc(saddr(sp + C::CH_BYTES + at * 8192) + ks * 2048, 1024), idesc_mn, acc);
+            } else if (MODE == DQ) {    // dQ += dS . K
+              mma_ts(ta + at * 64, pa + 64, smem_desc(saddr(sp + at * 8192) + ks * 2048, 1024), idesc_mn, acc);
+            } else {                    // dV += P^T . dO,  dK += dS^T . Q
+              mma_ts(ta + at * 64, pa, smem_desc(saddr(sp + C::CH_BYTES + at * 8192) + ks * 2048, 1024), idesc_mn, acc);
+              mma_ts(ta + D + at * 64, pa + 64, smem_desc(saddr(sp + at * 8192) + ks * 2048, 1024), idesc_mn, acc);
+            }
+          }
+        commit(&bar_free[t & 1]);
+        commit(&bar_empty[t % ST]);
+      };
+      bool ok = mbar_wait(&bar_res, 0, fl);
+      for (int t = 0; ok && t < ntiles; ++t) {
+        ok = mbar_wait(&bar_full[t % ST], (t / ST) & 1, fl);
+        if (ok && t >= 2) ok = mbar_wait(&bar_free[t & 1], ((t / 2) - 1) & 1, fl);
+        if (!ok) break;
+        fence_after();
+        scores(t);
+        if (t >= 1) {
+          ok = mbar_wait(&bar_p[(t - 1) & 1], ((t - 1) / 2) & 1, fl);
+          if (!ok) break;
+          fence_after();
+          accumulate(t - 1);
+        }
+      }
+      if (ok && mbar_wait(&bar_p[(ntiles - 1) & 1], ((ntiles - 1) / 2) & 1, fl)) {
+        fence_after();
+        accumulate(ntiles - 1);
+        commit(&bar_done);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ compute warps
+    const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
+    const int half = trow >> 6;                               // which 64-row chunk of the tile
+    bool ok = true;
+    if (MODE == FWD) {
+      float m_ref = kNegInfT, l = 0.f;
+      for (int t = 0; ok && t < ntiles; ++t) {
+        const uint32_t ts = tmem + (t & 1) * C::SCORE_COLS + lane_base;
+        const bool valid = (a.mask[first + t] >> half) & 1;
+        ok = mbar_wait(&bar_s[t & 1], (t / 2) & 1, fl);
+        if (!ok) break;
+        fence_after();
+        uint32_t sr[2][32];
+        tmem_ld32(ts, sr[0]);
+        tmem_ld32(ts + 32, sr[1]);
+        tmem_ld_wait();
+        float mt = kNegInfT;
+        if (valid) {
+#pragma unroll
+          for (int i = 0; i < 64; ++i) mt = fmaxf(mt, __uint_as_float(sr[i >> 5][i & 31]));
+          mt *= a.scale_log2;
+        }
+        // the reference maximum is only raised when the row maximum outgrows it by 2^8
+        const bool grow_m = mt > m_ref + 8.f;
+        if (__any_sync(0xffffffffu, grow_m)) {
+          const float m_new = grow_m ? mt : m_ref;
+          const float alpha = grow_m ? fast_exp2(m_ref - m_new) : 1.f;      // 0 while m_ref is still -inf
+          l *= alpha;
+          if (t > 0) {                                      // O must be complete up to chunk t-1
+            ok = mbar_wait(&bar_free[(t - 1) & 1], ((t - 1) / 2) & 1, fl);
+            if (!ok) break;
+            fence_after();
+            for (int c = 0; c < D; c += 32) {
+              uint32_t orr[32];
+              tmem_ld32(tmem + C::ACC_BASE + lane_base + c, orr);
+              tmem_ld_wait();
+#pragma unroll
+              for (int i = 0; i < 32; ++i) orr[i] = __float_as_uint(__uint_as_float(orr[i]) * alpha);
+              tmem_st32(tmem + C::ACC_BASE + lane_base + c, orr);
+            }
+            tmem_st_wait();
+          }
+          m_ref = m_new;
+        }
+        uint32_t pr[32];
+        if (valid) {
+          float sum = 0.f;
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const float p0 = fast_exp2(fmaf(__uint_as_float(sr[(2 * i) >> 5][(2 * i) & 31]), a.scale_log2, -m_ref));
+            const float p1 = fast_exp2(fmaf(__uint_as_float(sr[(2 * i + 1) >> 5][(2 * i + 1) & 31]), a.scale_log2, -m_ref));
+            sum += p0 + p1;
+            pr[i] = pack16<T>(p0, p1);
+          }
+          l += sum;
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) pr[i] = 0u;
+        }
+        tmem_st32(ts, pr);
+        tmem_st_wait();
+        fence_before();
+        mbar_arrive(&bar_p[t & 1]);
+      }
+      if (ok && mbar_wait(&bar_done, 0, fl)) {
+        fence_after();
+        if (mychunk >= 0) {                                   // uniform per warp: a warp lies inside one chunk
+          T* orow = reinterpret_cast<T*>(a.out0) + z * a.o_sz + h * a.o_sh + grow * a.o_sr;
+          store_acc<T>(orow, tmem + C::ACC_BASE + lane_base, 0, D, l > 0.f ? 1.f / l : 0.f);
+          a.lse_out[zh + grow] = l > 0.f ? m_ref + log2f(l) : kNegInfT;
+        }
+      }
+    } else {
+      const float my_lse = (MODE == DQ && row_ok) ? a.lse[zh + grow] : 0.f;
+      const float my_delta = (MODE == DQ && row_ok) ? a.delta[zh + grow] : 0.f;
+      for (int t = 0; ok && t < ntiles; ++t) {
+        const uint32_t ts = tmem + (t & 1) * C::SCORE_COLS + lane_base + chalf * 32;
+        const bool valid = (a.mask[first + t] >> half) & 1;
+        const float* vec = reinterpret_cast<const float*>(stg + (t % ST) * C::STAGE + 2 * C::CH_BYTES) + chalf * 32;
+        ok = mbar_wait(&bar_s[t & 1], (t / 2) & 1, fl);
+        if (!ok) break;
+        fence_after();
+        uint32_t sr[32], qr[32];
+        tmem_ld32(ts, sr);
+        tmem_ld32(ts + 64, qr);
+        tmem_ld_wait();
+        uint32_t pr[16], dr[16];
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          float p0 = 0.f, p1 = 0.f, d0 = 0.f, d1 = 0.f;
+          if (valid) {
+            const float l0 = MODE == DKV ? vec[i] : my_lse, l1 = MODE == DKV ? vec[i + 1] : my_lse;
+            const float e0 = MODE == DKV ? vec[64 + i] : my_delta, e1 = MODE == DKV ? vec[64 + i + 1] : my_delta;
+            p0 = fast_exp2(fmaf(__uint_as_float(sr[i]), a.scale_log2, -l0));
+            p1 = fast_exp2(fmaf(__uint_as_float(sr[i + 1]), a.scale_log2, -l1));
+            d0 = p0 * (__uint_as_float(qr[i]) - e0) * a.scale;
+            d1 = p1 * (__uint_as_float(qr[i + 1]) - e1) * a.scale;
+          }
+          pr[i / 2] = pack16<T>(p0, p1);
+          dr[i / 2] = pack16<T>(d0, d1);
+        }
+        // packed values go over the first 16 columns of this thread's own 32-column slice
+        if (MODE == DKV) tmem_st16(ts, pr);
+        tmem_st16(ts + 64, dr);
+        tmem_st_wait();
+        fence_before();
+        mbar_arrive(&bar_p[t & 1]);
+      }
+      if (ok && mbar_wait(&bar_done, 0, fl)) {
+        fence_after();
+        if (mychunk >= 0) {                                   // uniform per warp
+          // the two threads of a row split the D output columns
+          const uint32_t ta = tmem + C::ACC_BASE + lane_base;
+          T* o0 = reinterpret_cast<T*>(a.out0) + (zh + grow) * D;
+          if (MODE == DQ) {
+            store_acc<T>(o0, ta, chalf * (D / 2), D / 2, 1.f);
+          } else {
+            T* o1 = reinterpret_cast<T*>(a.out1) + (zh + grow) * D;
+            store_acc<T>(o1, ta, chalf * (D / 2), D / 2, 1.f);            // dV: accumulator columns [0, D)
+            store_acc<T>(o0 - D, ta, D + chalf * (D / 2), D / 2, 1.f);    // dK: accumulator columns [D, 2D)
+          }
+        }
+      }
+    }
+  }
+  fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem, C::TMEM);
+  if (tid == 0 && failed) atomicExch(&g_tc_status, 1 + MODE);
 }
 
 // ---------------------------------------------------------------------------
@@ -271,15 +404,15 @@ EncodeTiledFn encode_fn() {
   return fn;
 }
 
-// [Z, H, L, D] operand with unit stride on D: box of 64 columns x `rows` rows.
-int make_map_4d(CUtensorMap* m, const void* ptr, int dtype, int Z, int H, int L, int D,
-                int64_t sz, int64_t sh, int64_t sr, int rows) {
+// [Z, H, L, D] operand with unit stride on D: boxes of 64 columns x 64 rows, 128-byte swizzle.
+int make_map(CUtensorMap* m, const void* ptr, int dtype, int Z, int H, int L, int D,
+             int64_t sz, int64_t sh, int64_t sr) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return fail(BSP_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
   cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)L, (cuuint64_t)H, (cuuint64_t)Z};
   cuuint64_t strides[3] = {(cuuint64_t)sr * 2, (cuuint64_t)(H > 1 ? sh : (int64_t)L * sr) * 2,
                            (cuuint64_t)(Z > 1 ? sz : (int64_t)H * L * sr) * 2};
-  cuuint32_t box[4] = {64, (cuuint32_t)rows, 1, 1};
+  cuuint32_t box[4] = {64, 64, 1, 1};
   cuuint32_t es[4] = {1, 1, 1, 1};
   CUresult r = fn(m, dtype == BSP_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4,
                   const_cast<void*>(ptr), dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
@@ -288,37 +421,55 @@ int make_map_4d(CUtensorMap* m, const void* ptr, int dtype, int Z, int H, int L,
   return BSP_OK;
 }
 
-struct TilesView {
-  int H, nb, block, tiles_per_head;
-  const int32_t *rt_ptr, *rt_chunk, *rt_mask, *rt_order, *ct_ptr, *ct_chunk, *ct_mask, *ct_order;
-};
+struct TileSet { const int32_t *c01, *ptr, *chunk, *mask, *order; };
+struct TilesView { int H, nb, block, tiles_per_head; TileSet rt, ct; };
 
 int decode_tiles(const int32_t* hdr, const int32_t* dev, TilesView& v) {
   if (hdr[0] != BSP_TILES_MAGIC) return fail(BSP_ERR_INVALID, "attention tile lists: bad magic");
   v.H = hdr[1]; v.nb = hdr[2]; v.block = hdr[3]; v.tiles_per_head = hdr[4];
-  const int64_t n = (int64_t)v.H * v.tiles_per_head, er = hdr[5], ec = hdr[6];
+  const int64_t n = (int64_t)v.H * v.tiles_per_head;
   const int32_t* p = dev + BSP_TILES_HEADER;
-  v.rt_ptr = p; p += n + 1; v.rt_chunk = p; p += er; v.rt_mask = p; p += er; v.rt_order = p; p += n;
-  v.ct_ptr = p; p += n + 1; v.ct_chunk = p; p += ec; v.ct_mask = p; p += ec; v.ct_order = p;
+  auto take = [&](TileSet& s, int64_t entries) {
+    s.c01 = p; p += 2 * n; s.ptr = p; p += n + 1; s.chunk = p; p += entries; s.mask = p; p += entries; s.order = p; p += n;
+  };
+  take(v.rt, hdr[5]);
+  take(v.ct, hdr[6]);
   return BSP_OK;
 }
 
-template <typename T, int D>
-int launch_fwd(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const TcFwdArgs& a,
-               int n_tiles, int Z, cudaStream_t st) {
-  auto kern = attn_fwd_tc_kernel<T, D>;
-  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, FwdSmem<D>::TOTAL);
-  if (e != cudaSuccess) return fail(BSP_ERR_CUDA, "attention (tcgen05 forward): cannot reserve shared memory: %s", cudaGetErrorString(e));
-  kern<<<dim3(n_tiles, Z), 128, FwdSmem<D>::TOTAL, st>>>(mq, mk, mv, a);
+template <typename T, int D, int MODE>
+int launch(const CUtensorMap& r0, const CUtensorMap& r1, const CUtensorMap& c0, const CUtensorMap& c1,
+           const TcArgs& a, int n_tiles, int Z, cudaStream_t st, const char* what) {
+  using C = Cfg<D, MODE>;
+  auto kern = attn_tc_kernel<T, D, MODE>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM);
+  if (e != cudaSuccess) return fail(BSP_ERR_CUDA, "attention (tcgen05 %s): cannot reserve shared memory: %s", what, cudaGetErrorString(e));
+  kern<<<dim3(n_tiles, Z), C::NT, C::SMEM, st>>>(r0, r1, c0, c1, a);
   e = cudaGetLastError();
-  if (e != cudaSuccess) return fail(BSP_ERR_CUDA, "attention (tcgen05 forward) launch failed: %s", cudaGetErrorString(e));
+  if (e != cudaSuccess) return fail(BSP_ERR_CUDA, "attention (tcgen05 %s) launch failed: %s", what, cudaGetErrorString(e));
   return BSP_OK;
+}
+
+template <int MODE>
+int launch_any(int dtype, int D, const CUtensorMap& r0, const CUtensorMap& r1, const CUtensorMap& c0,
+               const CUtensorMap& c1, const TcArgs& a, int n_tiles, int Z, cudaStream_t st, const char* what) {
+  if (dtype == BSP_F16) {
+    if (D == 64) return launch<__half, 64, MODE>(r0, r1, c0, c1, a, n_tiles, Z, st, what);
+    return launch<__half, 128, MODE>(r0, r1, c0, c1, a, n_tiles, Z, st, what);
+  }
+  if (D == 64) return launch<__nv_bfloat16, 64, MODE>(r0, r1, c0, c1, a, n_tiles, Z, st, what);
+  return launch<__nv_bfloat16, 128, MODE>(r0, r1, c0, c1, a, n_tiles, Z, st, what);
+}
+
+void fill_tiles(TcArgs& a, const TilesView& tv, const TileSet& s) {
+  a.tiles_per_head = tv.tiles_per_head;
+  a.c01 = s.c01; a.ptr = s.ptr; a.chunk = s.chunk; a.mask = s.mask; a.order = s.order;
 }
 
 }  // namespace
 
 // Forward on the tcgen05 path.  Preconditions (checked by the caller): dtype F16 / BF16,
-// D in {64, 128}, block in {64, 128}, L multiple of 128, no rpe / masks, unit stride on D.
+// D in {64, 128}, block in {64, 128}, no rpe / masks, unit stride on D.
 int attn_fwd_tc(const void* q, const void* k, const void* v, void* o, float* lse,
                 int dtype, int Z, int H, int L, int D,
                 int64_t q_sz, int64_t q_sh, int64_t q_sr, int64_t k_sz, int64_t k_sh, int64_t k_sr,
@@ -328,20 +479,44 @@ int attn_fwd_tc(const void* q, const void* k, const void* v, void* o, float* lse
   if (int rc = decode_tiles(tiles_hdr, tiles, tv)) return rc;
   if (tv.H != H || tv.nb * tv.block != L) return fail(BSP_ERR_INVALID, "attention tile lists do not fit %d heads of length %d", H, L);
   CUtensorMap mq, mk, mv;
-  if (int rc = make_map_4d(&mq, q, dtype, Z, H, L, D, q_sz, q_sh, q_sr, 128)) return rc;
-  if (int rc = make_map_4d(&mk, k, dtype, Z, H, L, D, k_sz, k_sh, k_sr, 64)) return rc;
-  if (int rc = make_map_4d(&mv, v, dtype, Z, H, L, D, v_sz, v_sh, v_sr, 64)) return rc;
-  TcFwdArgs a;
-  a.o = o; a.lse = lse; a.o_sz = o_sz; a.o_sh = o_sh; a.o_sr = o_sr;
-  a.H = H; a.L = L; a.tiles_per_head = tv.tiles_per_head; a.scale_log2 = scale * kLog2eT;
-  a.ptr = tv.rt_ptr; a.chunk = tv.rt_chunk; a.mask = tv.rt_mask; a.order = tv.rt_order;
+  if (int rc = make_map(&mq, q, dtype, Z, H, L, D, q_sz, q_sh, q_sr)) return rc;
+  if (int rc = make_map(&mk, k, dtype, Z, H, L, D, k_sz, k_sh, k_sr)) return rc;
+  if (int rc = make_map(&mv, v, dtype, Z, H, L, D, v_sz, v_sh, v_sr)) return rc;
+  TcArgs a = {};
+  a.out0 = o; a.lse_out = lse; a.o_sz = o_sz; a.o_sh = o_sh; a.o_sr = o_sr;
+  a.H = H; a.L = L; a.scale = scale; a.scale_log2 = scale * kLog2eT;
+  fill_tiles(a, tv, tv.rt);
+  return launch_any<FWD>(dtype, D, mq, mq, mk, mv, a, H * tv.tiles_per_head, Z, st, "forward");
+}
+
+// dK/dV (parts & 2) and dQ (parts & 4) on the tcgen05 path; `delta` must already hold rowsum(o * do).
+int attn_bwd_tc(const void* q, const void* k, const void* v, const void* dout, const float* lse, const float* delta,
+                void* dq, void* dk, void* dv, int dtype, int Z, int H, int L, int D,
+                int64_t q_sz, int64_t q_sh, int64_t q_sr, int64_t k_sz, int64_t k_sh, int64_t k_sr,
+                int64_t v_sz, int64_t v_sh, int64_t v_sr, int64_t do_sz, int64_t do_sh, int64_t do_sr,
+                const int32_t* tiles_hdr, const int32_t* tiles, float scale, int parts, cudaStream_t st) {
+  TilesView tv;
+  if (int rc = decode_tiles(tiles_hdr, tiles, tv)) return rc;
+  if (tv.H != H || tv.nb * tv.block != L) return fail(BSP_ERR_INVALID, "attention tile lists do not fit %d heads of length %d", H, L);
+  CUtensorMap mq, mk, mv, md;
+  if (int rc = make_map(&mq, q, dtype, Z, H, L, D, q_sz, q_sh, q_sr)) return rc;
+  if (int rc = make_map(&mk, k, dtype, Z, H, L, D, k_sz, k_sh, k_sr)) return rc;
+  if (int rc = make_map(&mv, v, dtype, Z, H, L, D, v_sz, v_sh, v_sr)) return rc;
+  if (int rc = make_map(&md, dout, dtype, Z, H, L, D, do_sz, do_sh, do_sr)) return rc;
+  TcArgs a = {};
+  a.lse = lse; a.delta = delta; a.H = H; a.L = L; a.scale = scale; a.scale_log2 = scale * kLog2eT;
   const int n_tiles = H * tv.tiles_per_head;
-  if (dtype == BSP_F16) {
-    if (D == 64) return launch_fwd<__half, 64>(mq, mk, mv, a, n_tiles, Z, st);
-    return launch_fwd<__half, 128>(mq, mk, mv, a, n_tiles, Z, st);
+  if (parts & 2) {
+    a.out0 = dk; a.out1 = dv;
+    fill_tiles(a, tv, tv.ct);
+    if (int rc = launch_any<DKV>(dtype, D, mk, mv, mq, md, a, n_tiles, Z, st, "dK/dV")) return rc;
   }
-  if (D == 64) return launch_fwd<__nv_bfloat16, 64>(mq, mk, mv, a, n_tiles, Z, st);
-  return launch_fwd<__nv_bfloat16, 128>(mq, mk, mv, a, n_tiles, Z, st);
+  if (parts & 4) {
+    a.out0 = dq; a.out1 = nullptr;
+    fill_tiles(a, tv, tv.rt);
+    if (int rc = launch_any<DQ>(dtype, D, mq, md, mk, mv, a, n_tiles, Z, st, "dQ")) return rc;
+  }
+  return BSP_OK;
 }
 
 int tc_device_status(int* out) {

@@ -12,6 +12,7 @@
 // Heads are independent in every builder; the SDD packer (the only one with a
 // sequential scan) runs its heads on a small pool of std::threads.
 #include <algorithm>
+#include <climits>
 #include <cstring>
 #include <numeric>
 #include <thread>
@@ -414,60 +415,129 @@ int bsp_meta_build(const int64_t* layout, int H, int Mb, int Nb,
 
 
 // Tile lists of the tcgen05 attention kernels.  Those kernels work on tiles of
-// 128 query rows (forward, dQ) or 128 key rows (dK / dV) and walk chunks of 64
-// rows of the other operand.  With block 64 a tile spans two block-rows
-// (block-columns) of the layout: its list is the union of their nonzero
-// positions with a 2-bit mask saying which half of the tile really owns the
-// block.  With block 128 a tile is one block-row and every nonzero block
-// contributes two chunks.
+// 128 query rows (forward, dQ) or 128 key rows (dK / dV), made of two 64-row
+// chunks, and walk 64-row chunks of the other operand.  With block 128 a tile
+// is one block-row and every nonzero block contributes two chunks.  With block
+// 64 a tile is a PAIR of block-rows (block-columns) of one head, not
+// necessarily adjacent: the list is the union of their nonzero positions with a
+// 2-bit mask saying which half owns the block.  Pairs are chosen greedily by
+// similarity of their nonzero sets, since every position only one of the two
+// owns is computed for nothing in the other half.
+namespace {
+
+struct TileLists {
+  std::vector<int32_t> c01, ptr{0}, chunk, mask;   // c01: two outer chunk ids per tile (-1: none)
+};
+
+// rows[i] = sorted nonzero positions of block-row (or block-column) i of one head
+void pair_blocks(const std::vector<std::vector<int>>& sets, int nb, std::vector<std::pair<int, int>>& pairs) {
+  const int words = (nb + 63) / 64;
+  std::vector<std::vector<uint64_t>> bits(sets.size(), std::vector<uint64_t>(words, 0));
+  for (size_t i = 0; i < sets.size(); ++i)
+    for (int j : sets[i]) bits[i][j >> 6] |= uint64_t(1) << (j & 63);
+  std::vector<int> order(sets.size());
+  std::iota(order.begin(), order.end(), 0);
+  std::stable_sort(order.begin(), order.end(), [&](int x, int y) { return sets[x].size() > sets[y].size(); });
+  std::vector<char> used(sets.size(), 0);
+  for (size_t oi = 0; oi < order.size(); ++oi) {
+    const int u = order[oi];
+    if (used[u]) continue;
+    used[u] = 1;
+    int best = -1;
+    double best_score = -1.0;
+    for (size_t oj = oi + 1; oj < order.size(); ++oj) {
+      const int v = order[oj];
+      if (used[v]) continue;
+      int inter = 0, uni = 0;
+      for (int w = 0; w < words; ++w) {
+        inter += __builtin_popcountll(bits[u][w] & bits[v][w]);
+        uni += __builtin_popcountll(bits[u][w] | bits[v][w]);
+      }
+      const double score = uni ? double(inter) / uni : 1.0;
+      if (score > best_score) { best_score = score; best = v; }
+      if (inter == uni) break;                      // cannot do better than identical sets
+    }
+    if (best >= 0) used[best] = 1;
+    pairs.push_back({std::min(u, best < 0 ? u : best), best < 0 ? -1 : std::max(u, best)});
+  }
+}
+
+void build_lists(const std::vector<std::vector<int>>& sets, int nb, int block, TileLists& out) {
+  if (block == 128) {
+    for (size_t i = 0; i < sets.size(); ++i) {
+      out.c01.push_back(int32_t(2 * i)); out.c01.push_back(int32_t(2 * i + 1));
+      for (int j : sets[i]) { out.chunk.push_back(2 * j); out.mask.push_back(3); out.chunk.push_back(2 * j + 1); out.mask.push_back(3); }
+      out.ptr.push_back(int32_t(out.chunk.size()));
+    }
+    return;
+  }
+  std::vector<std::pair<int, int>> pairs;
+  pair_blocks(sets, nb, pairs);
+  for (auto& pr : pairs) {
+    out.c01.push_back(pr.first); out.c01.push_back(pr.second);
+    const std::vector<int>& A = sets[pr.first];
+    static const std::vector<int> none;
+    const std::vector<int>& B = pr.second >= 0 ? sets[pr.second] : none;
+    size_t ia = 0, ib = 0;
+    while (ia < A.size() || ib < B.size()) {
+      const int ja = ia < A.size() ? A[ia] : INT32_MAX, jb = ib < B.size() ? B[ib] : INT32_MAX;
+      const int j = std::min(ja, jb);
+      int m = 0;
+      if (ja == j) { m |= 1; ++ia; }
+      if (jb == j) { m |= 2; ++ib; }
+      out.chunk.push_back(j); out.mask.push_back(m);
+    }
+    out.ptr.push_back(int32_t(out.chunk.size()));
+  }
+}
+
+}  // namespace
+
 int bsp_attn_tiles_build(const int64_t* layout, int H, int nb, int block,
                          int32_t* out, int64_t out_cap, int64_t* total) {
   if (int rc = check_layout_args(layout, H, nb, nb)) return rc;
   if (!total) return fail(BSP_ERR_INVALID, "NULL result pointer");
   if (block != 64 && block != 128) return fail(BSP_ERR_UNSUPPORTED, "attention tiles exist for block 64 and 128 (got %d)", block);
-  if ((int64_t)nb * block % 128) return fail(BSP_ERR_UNSUPPORTED, "sequence length must be a multiple of 128");
-  const int rpt = 128 / block;                       // block-rows per tile
-  const int cpb = block / 64;                        // chunks per block
-  const int nt = nb / rpt;                           // tiles per head (rows and columns alike)
-  auto at = [&](int h, int i, int j) { return layout[(size_t(h) * nb + i) * nb + j] != 0; };
-  std::vector<int32_t> rt_ptr(1, 0), rt_chunk, rt_mask, ct_ptr(1, 0), ct_chunk, ct_mask;
-  for (int h = 0; h < H; ++h)
-    for (int t = 0; t < nt; ++t) {
-      for (int j = 0; j < nb; ++j) {
-        int mask = 0;
-        for (int r = 0; r < rpt; ++r) mask |= at(h, t * rpt + r, j) ? (1 << r) : 0;
-        if (!mask) continue;
-        for (int c = 0; c < cpb; ++c) { rt_chunk.push_back(j * cpb + c); rt_mask.push_back(rpt == 1 ? 3 : mask); }
-      }
-      rt_ptr.push_back(int32_t(rt_chunk.size()));
-    }
-  for (int h = 0; h < H; ++h)
-    for (int t = 0; t < nt; ++t) {
-      for (int i = 0; i < nb; ++i) {
-        int mask = 0;
-        for (int r = 0; r < rpt; ++r) mask |= at(h, i, t * rpt + r) ? (1 << r) : 0;
-        if (!mask) continue;
-        for (int c = 0; c < cpb; ++c) { ct_chunk.push_back(i * cpb + c); ct_mask.push_back(rpt == 1 ? 3 : mask); }
-      }
-      ct_ptr.push_back(int32_t(ct_chunk.size()));
-    }
+  const int nt = block == 128 ? nb : (nb + 1) / 2;   // tiles per head
+  std::vector<TileLists> rt(H), ct(H);
+  parallel_heads(H, [&](int h) {
+    std::vector<std::vector<int>> rows(nb), cols(nb);
+    for (int i = 0; i < nb; ++i)
+      for (int j = 0; j < nb; ++j)
+        if (layout[(size_t(h) * nb + i) * nb + j] != 0) { rows[i].push_back(j); cols[j].push_back(i); }
+    build_lists(rows, nb, block, rt[h]);
+    build_lists(cols, nb, block, ct[h]);
+  });
+  int64_t er = 0, ec = 0;
+  for (int h = 0; h < H; ++h) { er += int64_t(rt[h].chunk.size()); ec += int64_t(ct[h].chunk.size()); }
   const int64_t n = int64_t(H) * nt;
-  const int64_t need = BSP_TILES_HEADER + 2 * (n + 1) + 2 * int64_t(rt_chunk.size()) + 2 * int64_t(ct_chunk.size()) + 2 * n;
+  const int64_t need = BSP_TILES_HEADER + 2 * (2 * n + (n + 1) + n) + 2 * er + 2 * ec;
   *total = need;
   if (!out) return BSP_OK;
   if (out_cap < need) return fail(BSP_ERR_CAPACITY, "attention tile lists need %lld ints, buffer holds %lld", (long long)need, (long long)out_cap);
   int32_t* p = out;
-  p[0] = BSP_TILES_MAGIC; p[1] = H; p[2] = nb; p[3] = block; p[4] = nt;
-  p[5] = int32_t(rt_chunk.size()); p[6] = int32_t(ct_chunk.size()); p[7] = 0;
+  p[0] = BSP_TILES_MAGIC; p[1] = H; p[2] = nb; p[3] = block; p[4] = nt; p[5] = int32_t(er); p[6] = int32_t(ec); p[7] = 0;
   p += BSP_TILES_HEADER;
-  auto put = [&](const std::vector<int32_t>& v) { std::copy(v.begin(), v.end(), p); p += v.size(); };
-  auto put_order = [&](const std::vector<int32_t>& ptr) {
-    std::iota(p, p + n, 0);
-    std::stable_sort(p, p + n, [&](int32_t x, int32_t y) { return ptr[x + 1] - ptr[x] > ptr[y + 1] - ptr[y]; });
-    p += n;
+  auto emit = [&](std::vector<TileLists>& v, int64_t entries) {
+    int32_t* c01 = p; p += 2 * n;
+    int32_t* ptr = p; p += n + 1;
+    int32_t* chunk = p; p += entries;
+    int32_t* mask = p; p += entries;
+    int32_t* order = p; p += n;
+    int32_t base = 0;
+    ptr[0] = 0;
+    for (int h = 0; h < H; ++h) {
+      std::copy(v[h].c01.begin(), v[h].c01.end(), c01 + size_t(h) * nt * 2);
+      for (int t = 0; t < nt; ++t) ptr[size_t(h) * nt + t + 1] = base + v[h].ptr[t + 1];
+      std::copy(v[h].chunk.begin(), v[h].chunk.end(), chunk + base);
+      std::copy(v[h].mask.begin(), v[h].mask.end(), mask + base);
+      base += int32_t(v[h].chunk.size());
+    }
+    std::iota(order, order + n, 0);
+    std::stable_sort(order, order + n, [&](int32_t x, int32_t y) { return ptr[x + 1] - ptr[x] > ptr[y + 1] - ptr[y]; });
   };
-  put(rt_ptr); put(rt_chunk); put(rt_mask); put_order(rt_ptr);
-  put(ct_ptr); put(ct_chunk); put(ct_mask); put_order(ct_ptr);
+  emit(rt, er);
+  emit(ct, ec);
   return BSP_OK;
 }
 

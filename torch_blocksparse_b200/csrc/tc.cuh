@@ -32,6 +32,9 @@ BSP_DEVI bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
                : "=r"(ok) : "r"(saddr(bar)), "r"(parity) : "memory");
   return ok != 0;
 }
+BSP_DEVI void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(saddr(bar)) : "memory");
+}
 constexpr int kWaitBudget = 1 << 21;   // try_wait attempts before a wait is declared failed
 // Returns false when the phase did not complete in time, or at once when the
 // CTA has already failed (*failed != 0), so that a failed CTA drains quickly.
@@ -49,6 +52,11 @@ BSP_DEVI void tma_load_4d(void* dst, const CUtensorMap* map, uint64_t* bar, int 
   asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
                ::"r"(saddr(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(saddr(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
                : "memory");
+}
+// Plain (untiled) bulk copy global -> shared; both addresses 16-byte aligned, size a multiple of 16.
+BSP_DEVI void bulk_load(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(saddr(dst)), "l"(reinterpret_cast<uint64_t>(src)), "r"(bytes), "r"(saddr(bar)) : "memory");
 }
 BSP_DEVI void prefetch_map(const CUtensorMap* map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
@@ -76,6 +84,12 @@ BSP_DEVI void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
                  "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
                  "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
                : "r"(taddr) : "memory");
+}
+BSP_DEVI void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+               "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+               ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+                 "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]) : "memory");
 }
 BSP_DEVI void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 BSP_DEVI void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {

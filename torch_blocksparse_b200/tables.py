@@ -143,9 +143,9 @@ class AttnTiles:
 
 def build_attn_tiles(layout, block):
     """Returns the AttnTiles of a square [H, nb, nb] layout, or None when the
-    tcgen05 kernels do not cover it (block not 64 / 128, length not a multiple of 128)."""
+    tcgen05 kernels do not cover it (block other than 64 / 128)."""
     lay, H, Mb, Nb = _layout_i64(layout)
-    if Mb != Nb or block not in (64, 128) or (Mb * block) % 128:
+    if Mb != Nb or block not in (64, 128):
         return None
     L = _lib.lib()
 
