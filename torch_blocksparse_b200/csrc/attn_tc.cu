@@ -16,16 +16,19 @@
 //   dQ        outer Q, dO        inner K, V     S = Q K^T, dP = dO V^T;  dS = P (dP - delta) scale;  dQ += dS K
 //   dK / dV   outer K, V         inner Q, dO    S^T = K Q^T, dP^T = V dO^T;  dV += P^T dO,  dK += dS^T Q
 //
-// Scores live in tensor memory in two buffers, so the tensor core computes the
-// scores of chunk t+1 while the compute warps turn chunk t into P / dS; P / dS
-// are written back (16-bit, packed) over the scores they came from and feed the
-// accumulating products as the A operand straight from tensor memory.  For
+// Scores live in tensor memory, in two buffers where the columns allow it (the
+// tensor core then computes the scores of chunk t+1 while the compute warps turn
+// chunk t into P / dS); P / dS are written back (16-bit, packed) over the scores
+// they came from and feed the accumulating products as the A operand straight
+// from tensor memory.  Two threads share a tile row, 32 columns of a chunk each;
+// in the forward each keeps its own running maximum, sum and O accumulator (the
+// two halves of a chunk are two K-slices of the P V product) and the halves are
+// merged when the tile is done.  For
 // block = 64 a 2-bit mask per chunk says which half of the tile owns the block;
 // the other half contributes zeros.
 //
-// Warp roles: compute warps (thread = one tile row, or half a row in the
-// backward), one TMA producer warp (4-stage ring of inner chunks), one MMA
-// issuer warp.  They talk through mbarriers only; every wait is bounded
+// Warp roles: eight compute warps, one TMA producer warp (ring of inner chunks),
+// one MMA issuer warp.  They talk through mbarriers only; every wait is bounded
 // (tc.cuh) and a wait that expires sets the device status word.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
@@ -38,13 +41,20 @@ namespace bsp {
 // Set by a kernel whose bounded wait expired; read by bsp_device_status().
 static __device__ int g_tc_status;
 
+#ifdef BSP_TC_TRACE
+// Development aid, compiled out of the library: timestamps of the first CTA's pipeline events.
+__device__ long long g_tc_trace[3][64][6];
+#define TC_TRACE(role, t, k) do { if (blockIdx.x == 0 && blockIdx.y == 0 && (t) < 64) g_tc_trace[role][t][k] = clock64(); } while (0)
+#else
+#define TC_TRACE(role, t, k) do { } while (0)
+#endif
+
 namespace {
 
 using namespace tc;
 
 constexpr float kLog2eT = 1.4426950408889634f;
 constexpr float kNegInfT = -__builtin_huge_valf();
-constexpr int kStages = 4;
 constexpr int FWD = 0, DQ = 1, DKV = 2;
 
 struct TcArgs {
@@ -72,17 +82,23 @@ template <> struct IsBf16<__nv_bfloat16> { static constexpr int v = 1; };
 template <int D, int MODE> struct Cfg {
   static constexpr int ATOMS = D / 64;                         // 64-element (128-byte) column groups
   static constexpr int NRES = MODE == FWD ? 1 : 2;             // resident 128-row operands
-  static constexpr int NC = MODE == FWD ? 4 : 8;               // compute warps
+  static constexpr int NC = 8;                                 // compute warps: two threads per tile row
   static constexpr int NT = (NC + 2) * 32;
   static constexpr int RES_BYTES = ATOMS * 128 * 128;
   static constexpr int CH_BYTES = ATOMS * 64 * 128;
   static constexpr int STAGE = 2 * CH_BYTES + (MODE == DKV ? 1024 : 0);   // + lse / delta of the chunk
-  static constexpr int SMEM = NRES * RES_BYTES + kStages * STAGE + 1024;
+  // score buffers in tensor memory: two (scores of the next chunk are computed while this
+  // one is consumed) where the columns allow it with two CTAs per SM, else one
+  static constexpr int NBUF = MODE == FWD ? 2 : (D == 64 ? 1 : 2);
+  static constexpr int NSTAGE = (MODE != FWD && D == 128) ? 3 : 4;
+  static constexpr int SMEM = NRES * RES_BYTES + NSTAGE * STAGE + 1024;
   static constexpr int SCORE_COLS = MODE == FWD ? 64 : 128;    // per buffer: S (and dP)
-  static constexpr int ACC_BASE = 2 * SCORE_COLS;
-  static constexpr int ACC_COLS = MODE == DKV ? 2 * D : D;
+  static constexpr int ACC_BASE = NBUF * SCORE_COLS;
+  // forward: one O accumulator per half of the key chunk (the two threads of a row keep
+  // independent running maxima); dK/dV: dV and dK
+  static constexpr int ACC_COLS = MODE == DQ ? D : 2 * D;
   static constexpr int TMEM = ACC_BASE + ACC_COLS <= 256 ? 256 : 512;
-  static constexpr int CTAS = (MODE == FWD && D == 64) ? 2 : 1;
+  static constexpr int CTAS = D == 64 ? 2 : 1;
 };
 
 // Writes accumulator columns [c0, c0 + n) of this thread's tensor-memory lane to dst[c0 .. c0 + n) as 16-bit values.
@@ -109,12 +125,13 @@ __global__ void __launch_bounds__(Cfg<D, MODE>::NT, Cfg<D, MODE>::CTAS)
 attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant__ CUtensorMap m_res1,
                const __grid_constant__ CUtensorMap m_ch0, const __grid_constant__ CUtensorMap m_ch1, TcArgs a) {
   using C = Cfg<D, MODE>;
-  constexpr int ATOMS = C::ATOMS, ST = kStages, NC = C::NC;
+  constexpr int ATOMS = C::ATOMS, ST = C::NSTAGE, NC = C::NC, NBUF = C::NBUF;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = smem_raw + ((1024 - (saddr(smem_raw) & 1023)) & 1023);
   unsigned char* res = smem;                                   // [NRES][ATOMS][128 rows][128 B]
   unsigned char* stg = res + C::NRES * C::RES_BYTES;           // [ST][ch0 | ch1 | lse, delta]
-  __shared__ uint64_t bar_res, bar_full[ST], bar_empty[ST], bar_s[2], bar_p[2], bar_free[2], bar_done;
+  __shared__ uint64_t bar_res, bar_full[ST], bar_s[4], bar_p[4], bar_acc[4], bar_done;
+  __shared__ float xch[2][2][128];                           // forward: (max, sum) of the two halves of every row
   __shared__ uint32_t tmem_slot;
   __shared__ int failed;
 
@@ -127,7 +144,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
   const int64_t zh = (int64_t)(z * a.H + h) * a.L;
 
   // row of the tile this thread works on (compute warps), its global row and whether it exists
-  const int quarter = warp & 3, chalf = (warp < NC) ? (warp >> 2) : 0;
+  const int quarter = warp & 3, chalf = (warp < NC) ? (warp >> 2) : 0;   // chalf: which 32 columns of a chunk
   const int trow = quarter * 32 + lane;
   const int mychunk = trow < 64 ? c0 : c1;
   const int64_t grow = (int64_t)(mychunk < 0 ? 0 : mychunk) * 64 + (trow & 63);
@@ -148,8 +165,9 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
   if (tid == 0) {
     failed = 0;
     mbar_init(&bar_res, 1);
-    for (int s = 0; s < ST; ++s) { mbar_init(&bar_full[s], 1); mbar_init(&bar_empty[s], 1); }
-    for (int b = 0; b < 2; ++b) { mbar_init(&bar_s[b], 1); mbar_init(&bar_p[b], NC * 32); mbar_init(&bar_free[b], 1); }
+    for (int s = 0; s < ST; ++s) mbar_init(&bar_full[s], 1);
+    for (int b = 0; b < 4; ++b) mbar_init(&bar_acc[b], 1);
+    for (int b = 0; b < NBUF; ++b) { mbar_init(&bar_s[b], 1); mbar_init(&bar_p[b], NC * 32); }
     mbar_init(&bar_done, 1);
     mbar_init_fence();
   }
@@ -174,9 +192,10 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
       }
       for (int t = 0; t < ntiles; ++t) {
         const int stage = t % ST;
-        if (t >= ST && !mbar_wait(&bar_empty[stage], ((t / ST) - 1) & 1, fl)) break;
+        if (t >= ST && !mbar_wait(&bar_acc[(t - ST) & 3], ((t - ST) >> 2) & 1, fl)) break;
         const int crow = a.chunk[first + t] * 64;
         unsigned char* sp = stg + stage * C::STAGE;
+        TC_TRACE(0, t, 0);
         mbar_expect_tx(&bar_full[stage], 2 * C::CH_BYTES + (MODE == DKV ? 512 : 0));
         for (int at = 0; at < ATOMS; ++at) {
           tma_load_4d(sp + at * 8192, &m_ch0, &bar_full[stage], at * 64, crow, h, z);
@@ -193,63 +212,116 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
     if (lane == 0) {
       const uint32_t idesc_kk = instr_desc(128, 64, 0, IsBf16<T>::v);   // A, B K-major
       const uint32_t idesc_mn = instr_desc(128, 64, 1, IsBf16<T>::v);   // B MN-major
-      auto scores = [&](int t) {
-        unsigned char* sp = stg + (t % ST) * C::STAGE;
-        const uint32_t ts = tmem + (t & 1) * C::SCORE_COLS;
+      // Descriptor low words: a K-step advances a K-major operand by 32 bytes (2 units of 16
+      // bytes) inside a 64-column group and an MN-major operand by 16 rows (128 units); the
+      // next group of 64 columns lies 128 rows (resident) or 64 rows (chunk) further.
+      // The issuing thread executes its instructions one after the other, and every
+      // instruction between two MMAs delays the tensor core: all descriptors of a chunk are
+      // therefore built first (while the barriers are still pending) and the MMAs of a
+      // product are issued back to back.  A K-step advances a K-major operand by 32 bytes (2
+      // units of 16 bytes) inside a 64-column group and an MN-major operand by 16 rows (128
+      // units); the next group of 64 columns lies 128 rows (resident) or 64 rows (chunk) on.
+      constexpr int KS = D / 16;
+      const uint32_t res_lo = desc_lo(saddr(res));
+      const uint32_t stg_lo = desc_lo(saddr(stg));
+      uint64_t a0[KS], a1[MODE == FWD ? 1 : KS];            // resident operands: the same for every chunk
 #pragma unroll
-        for (int ks = 0; ks < D / 16; ++ks) {
-          const uint32_t off = (ks % 4) * 32;
-          mma_ss(ts, smem_desc(saddr(res + (ks / 4) * 16384) + off, 1024),
-                 smem_desc(saddr(sp + (ks / 4) * 8192) + off, 1024), idesc_kk, ks > 0);
-        }
-        if (MODE != FWD) {
+      for (int ks = 0; ks < KS; ++ks) {
+        a0[ks] = desc_from_lo(res_lo + (ks / 4) * 1024 + (ks % 4) * 2);
+        if (MODE != FWD) a1[ks] = desc_from_lo(res_lo + C::RES_BYTES / 16 + (ks / 4) * 1024 + (ks % 4) * 2);
+      }
+      uint64_t sb0[KS], sb1[MODE == FWD ? 1 : KS];          // chunk operands of the scores being prepared
+      auto prep_scores = [&](int t) {
+        const uint32_t sp_lo = stg_lo + (t % ST) * (C::STAGE / 16);
 #pragma unroll
-          for (int ks = 0; ks < D / 16; ++ks) {
-            const uint32_t off = (ks % 4) * 32;
-            mma_ss(ts + 64, smem_desc(saddr(res + C::RES_BYTES + (ks / 4) * 16384) + off, 1024),
-                   smem_desc(saddr(sp + C::CH_BYTES + (ks / 4) * 8192) + off, 1024), idesc_kk, ks > 0);
-          }
+        for (int ks = 0; ks < KS; ++ks) {
+          sb0[ks] = desc_from_lo(sp_lo + (ks / 4) * 512 + (ks % 4) * 2);
+          if (MODE != FWD) sb1[ks] = desc_from_lo(sp_lo + C::CH_BYTES / 16 + (ks / 4) * 512 + (ks % 4) * 2);
         }
-        commit(&bar_s[t & 1]);
       };
-      auto accumulate = [&](int t) {
-        unsigned char* sp = stg + (t % ST) * C::STAGE;
-        const uint32_t ts = tmem + (t & 1) * C::SCORE_COLS;
-        const uint32_t ta = tmem + C::ACC_BASE;
+      auto scores = [&](int t) {
+        const uint32_t ts = tmem + (t % NBUF) * C::SCORE_COLS;
+        mma_ss(ts, a0[0], sb0[0], idesc_kk, 0u);
+#pragma unroll
+        for (int ks = 1; ks < KS; ++ks) mma_ss_acc(ts, a0[ks], sb0[ks], idesc_kk);
+        if (MODE != FWD) {
+          mma_ss(ts + 64, a1[0], sb1[0], idesc_kk, 0u);
+#pragma unroll
+          for (int ks = 1; ks < KS; ++ks) mma_ss_acc(ts + 64, a1[ks], sb1[ks], idesc_kk);
+        }
+        TC_TRACE(1, t, 5);
+        commit(&bar_s[t % NBUF]);
+      };
+      uint64_t vb0[ATOMS * 4], vb1[ATOMS * 4];              // chunk operands of the accumulation being prepared
+      auto prep_acc = [&](int t) {
+        const uint32_t sp_lo = stg_lo + (t % ST) * (C::STAGE / 16);
 #pragma unroll
         for (int at = 0; at < ATOMS; ++at)
 #pragma unroll
           for (int ks = 0; ks < 4; ++ks) {
-            const uint32_t acc = (t > 0 || ks > 0) ? 1u : 0u;
-            // packed 16-bit operand of K-step ks: 8 columns, written by the compute warps
-            const uint32_t pa = (MODE == FWD) ? ts + ks * 8 : ts + (ks >> 1) * 32 + (ks & 1) * 8;
-            if (MODE == FWD) {          // O += P . V
-              mma_ts(ta + at * 64, pa, smem_desc(saddr(sp + C::CH_BYTES + at * 8192) + ks * 2048, 1024), idesc_mn, acc);
+            vb0[at * 4 + ks] = desc_from_lo(sp_lo + at * 512 + ks * 128);
+            vb1[at * 4 + ks] = desc_from_lo(sp_lo + C::CH_BYTES / 16 + at * 512 + ks * 128);
+          }
+      };
+      auto accumulate = [&](int t) {
+        const uint32_t ts = tmem + (t % NBUF) * C::SCORE_COLS;
+        const uint32_t ta = tmem + C::ACC_BASE;
+        const uint32_t later = t > 0 ? 1u : 0u;
+#pragma unroll
+        for (int at = 0; at < ATOMS; ++at)
+#pragma unroll
+          for (int ks = 0; ks < 4; ++ks) {
+            // packed 16-bit operand of K-step ks (16 rows of the chunk): 8 columns inside the
+            // 32-column slice of the compute thread that produced it
+            const uint32_t pa = ts + (ks >> 1) * 32 + (ks & 1) * 8;
+            if (MODE == FWD) {          // O_half += P_half . V_half: one accumulator per half of the chunk
+              if (ks & 1) mma_ts_acc(ta + (ks >> 1) * D + at * 64, pa, vb1[at * 4 + ks], idesc_mn);
+              else mma_ts(ta + (ks >> 1) * D + at * 64, pa, vb1[at * 4 + ks], idesc_mn, later);
             } else if (MODE == DQ) {    // dQ += dS . K
-              mma_ts(ta + at * 64, pa + 64, smem_desc(saddr(sp + at * 8192) + ks * 2048, 1024), idesc_mn, acc);
+              if (ks > 0) mma_ts_acc(ta + at * 64, pa + 64, vb0[at * 4 + ks], idesc_mn);
+              else mma_ts(ta + at * 64, pa + 64, vb0[at * 4 + ks], idesc_mn, later);
             } else {                    // dV += P^T . dO,  dK += dS^T . Q
-              mma_ts(ta + at * 64, pa, smem_desc(saddr(sp + C::CH_BYTES + at * 8192) + ks * 2048, 1024), idesc_mn, acc);
-              mma_ts(ta + D + at * 64, pa + 64, smem_desc(saddr(sp + at * 8192) + ks * 2048, 1024), idesc_mn, acc);
+              if (ks > 0) {
+                mma_ts_acc(ta + at * 64, pa, vb1[at * 4 + ks], idesc_mn);
+                mma_ts_acc(ta + D + at * 64, pa + 64, vb0[at * 4 + ks], idesc_mn);
+              } else {
+                mma_ts(ta + at * 64, pa, vb1[at * 4 + ks], idesc_mn, later);
+                mma_ts(ta + D + at * 64, pa + 64, vb0[at * 4 + ks], idesc_mn, later);
+              }
             }
           }
-        commit(&bar_free[t & 1]);
-        commit(&bar_empty[t % ST]);
+        commit(&bar_acc[t & 3]);      // chunk t fully consumed: its score buffer and its stage are free
       };
       bool ok = mbar_wait(&bar_res, 0, fl);
       for (int t = 0; ok && t < ntiles; ++t) {
-        ok = mbar_wait(&bar_full[t % ST], (t / ST) & 1, fl);
-        if (ok && t >= 2) ok = mbar_wait(&bar_free[t & 1], ((t / 2) - 1) & 1, fl);
-        if (!ok) break;
-        fence_after();
-        scores(t);
-        if (t >= 1) {
-          ok = mbar_wait(&bar_p[(t - 1) & 1], ((t - 1) / 2) & 1, fl);
+        if (NBUF == 1 && t >= 1) {                          // one buffer: finish chunk t-1 before its scores are overwritten
+          prep_acc(t - 1);
+          ok = mbar_wait(&bar_p[0], (t - 1) & 1, fl);
           if (!ok) break;
           fence_after();
           accumulate(t - 1);
         }
+        prep_scores(t);
+        ok = mbar_wait(&bar_full[t % ST], (t / ST) & 1, fl);
+        TC_TRACE(1, t, 0);
+        if (ok && t >= NBUF) ok = mbar_wait(&bar_acc[(t - NBUF) & 3], ((t - NBUF) >> 2) & 1, fl);
+        TC_TRACE(1, t, 1);
+        if (!ok) break;
+        fence_after();
+        scores(t);
+        TC_TRACE(1, t, 2);
+        if (NBUF >= 2 && t >= 1) {
+          prep_acc(t - 1);
+          ok = mbar_wait(&bar_p[(t - 1) % NBUF], ((t - 1) / NBUF) & 1, fl);
+          TC_TRACE(1, t, 3);
+          if (!ok) break;
+          fence_after();
+          accumulate(t - 1);
+          TC_TRACE(1, t, 4);
+        }
       }
-      if (ok && mbar_wait(&bar_p[(ntiles - 1) & 1], ((ntiles - 1) / 2) & 1, fl)) {
+      if (ok) prep_acc(ntiles - 1);
+      if (ok && mbar_wait(&bar_p[(ntiles - 1) % NBUF], ((ntiles - 1) / NBUF) & 1, fl)) {
         fence_after();
         accumulate(ntiles - 1);
         commit(&bar_done);
@@ -261,22 +333,28 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
     const int half = trow >> 6;                               // which 64-row chunk of the tile
     bool ok = true;
     if (MODE == FWD) {
+      // this thread owns 32 of the 64 key columns of its row, with its own running
+      // maximum, sum and O accumulator; the two halves are merged at the end
+      const uint32_t t_acc = tmem + C::ACC_BASE + chalf * D + lane_base;
       float m_ref = kNegInfT, l = 0.f;
       for (int t = 0; ok && t < ntiles; ++t) {
-        const uint32_t ts = tmem + (t & 1) * C::SCORE_COLS + lane_base;
+        const uint32_t ts = tmem + (t % NBUF) * C::SCORE_COLS + lane_base + chalf * 32;
         const bool valid = (a.mask[first + t] >> half) & 1;
-        ok = mbar_wait(&bar_s[t & 1], (t / 2) & 1, fl);
+        TC_TRACE(2, t, 0);
+        ok = mbar_wait(&bar_s[t % NBUF], (t / NBUF) & 1, fl);
+        TC_TRACE(2, t, 1);
         if (!ok) break;
         fence_after();
-        uint32_t sr[2][32];
-        tmem_ld32(ts, sr[0]);
-        tmem_ld32(ts + 32, sr[1]);
+        uint32_t sr[32];
+        tmem_ld32(ts, sr);
         tmem_ld_wait();
+        TC_TRACE(2, t, 2);
         float mt = kNegInfT;
         if (valid) {
+          float m4[4] = {kNegInfT, kNegInfT, kNegInfT, kNegInfT};
 #pragma unroll
-          for (int i = 0; i < 64; ++i) mt = fmaxf(mt, __uint_as_float(sr[i >> 5][i & 31]));
-          mt *= a.scale_log2;
+          for (int i = 0; i < 32; ++i) m4[i & 3] = fmaxf(m4[i & 3], __uint_as_float(sr[i]));
+          mt = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])) * a.scale_log2;
         }
         // the reference maximum is only raised when the row maximum outgrows it by 2^8
         const bool grow_m = mt > m_ref + 8.f;
@@ -284,58 +362,86 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
           const float m_new = grow_m ? mt : m_ref;
           const float alpha = grow_m ? fast_exp2(m_ref - m_new) : 1.f;      // 0 while m_ref is still -inf
           l *= alpha;
-          if (t > 0) {                                      // O must be complete up to chunk t-1
-            ok = mbar_wait(&bar_free[(t - 1) & 1], ((t - 1) / 2) & 1, fl);
+          if (t > 0) {                                      // the accumulator must be complete up to chunk t-1
+            ok = mbar_wait(&bar_acc[(t - 1) & 3], ((t - 1) >> 2) & 1, fl);
             if (!ok) break;
             fence_after();
             for (int c = 0; c < D; c += 32) {
               uint32_t orr[32];
-              tmem_ld32(tmem + C::ACC_BASE + lane_base + c, orr);
+              tmem_ld32(t_acc + c, orr);
               tmem_ld_wait();
 #pragma unroll
               for (int i = 0; i < 32; ++i) orr[i] = __float_as_uint(__uint_as_float(orr[i]) * alpha);
-              tmem_st32(tmem + C::ACC_BASE + lane_base + c, orr);
+              tmem_st32(t_acc + c, orr);
             }
             tmem_st_wait();
           }
           m_ref = m_new;
         }
-        uint32_t pr[32];
+        uint32_t pr[16];
         if (valid) {
-          float sum = 0.f;
+          float s4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const float p0 = fast_exp2(fmaf(__uint_as_float(sr[(2 * i) >> 5][(2 * i) & 31]), a.scale_log2, -m_ref));
-            const float p1 = fast_exp2(fmaf(__uint_as_float(sr[(2 * i + 1) >> 5][(2 * i + 1) & 31]), a.scale_log2, -m_ref));
-            sum += p0 + p1;
+          for (int i = 0; i < 16; ++i) {
+            const float p0 = fast_exp2(fmaf(__uint_as_float(sr[2 * i]), a.scale_log2, -m_ref));
+            const float p1 = fast_exp2(fmaf(__uint_as_float(sr[2 * i + 1]), a.scale_log2, -m_ref));
+            s4[i & 3] += p0 + p1;
             pr[i] = pack16<T>(p0, p1);
           }
-          l += sum;
+          l += (s4[0] + s4[1]) + (s4[2] + s4[3]);
         } else {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) pr[i] = 0u;
+          for (int i = 0; i < 16; ++i) pr[i] = 0u;
         }
-        tmem_st32(ts, pr);
+        TC_TRACE(2, t, 3);
+        tmem_st16(ts, pr);
         tmem_st_wait();
         fence_before();
-        mbar_arrive(&bar_p[t & 1]);
+        mbar_arrive(&bar_p[t % NBUF]);
+        TC_TRACE(2, t, 4);
       }
+      // merge the two halves of every row: O = (O_a 2^(m_a - m) + O_b 2^(m_b - m)) / l
+      xch[chalf][0][trow] = m_ref;
+      xch[chalf][1][trow] = l;
+      asm volatile("bar.sync 1, 256;" ::: "memory");          // the eight compute warps, always executed
       if (ok && mbar_wait(&bar_done, 0, fl)) {
         fence_after();
         if (mychunk >= 0) {                                   // uniform per warp: a warp lies inside one chunk
+          const float ma = xch[0][0][trow], mb = xch[1][0][trow], la = xch[0][1][trow], lb = xch[1][1][trow];
+          const float m = fmaxf(ma, mb);
+          const float wa = ma == kNegInfT ? 0.f : fast_exp2(ma - m), wb = mb == kNegInfT ? 0.f : fast_exp2(mb - m);
+          const float lsum = la * wa + lb * wb;
+          const float inv = lsum > 0.f ? 1.f / lsum : 0.f;
           T* orow = reinterpret_cast<T*>(a.out0) + z * a.o_sz + h * a.o_sh + grow * a.o_sr;
-          store_acc<T>(orow, tmem + C::ACC_BASE + lane_base, 0, D, l > 0.f ? 1.f / l : 0.f);
-          a.lse_out[zh + grow] = l > 0.f ? m_ref + log2f(l) : kNegInfT;
+          const uint32_t ta = tmem + C::ACC_BASE + lane_base;
+          for (int c = chalf * (D / 2); c < (chalf + 1) * (D / 2); c += 32) {
+            uint32_t ra[32], rb[32];
+            tmem_ld32(ta + c, ra);
+            tmem_ld32(ta + D + c, rb);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; i += 8) {
+              float o[8];
+#pragma unroll
+              for (int j = 0; j < 8; ++j)
+                o[j] = (__uint_as_float(ra[i + j]) * wa + __uint_as_float(rb[i + j]) * wb) * inv;
+              uint4 v;
+              v.x = pack16<T>(o[0], o[1]); v.y = pack16<T>(o[2], o[3]);
+              v.z = pack16<T>(o[4], o[5]); v.w = pack16<T>(o[6], o[7]);
+              *reinterpret_cast<uint4*>(orow + c + i) = v;
+            }
+          }
+          if (chalf == 0) a.lse_out[zh + grow] = lsum > 0.f ? m + log2f(lsum) : kNegInfT;
         }
       }
     } else {
       const float my_lse = (MODE == DQ && row_ok) ? a.lse[zh + grow] : 0.f;
-      const float my_delta = (MODE == DQ && row_ok) ? a.delta[zh + grow] : 0.f;
+      const float my_ds = (MODE == DQ && row_ok) ? a.delta[zh + grow] * a.scale : 0.f;
       for (int t = 0; ok && t < ntiles; ++t) {
-        const uint32_t ts = tmem + (t & 1) * C::SCORE_COLS + lane_base + chalf * 32;
+        const uint32_t ts = tmem + (t % NBUF) * C::SCORE_COLS + lane_base + chalf * 32;
         const bool valid = (a.mask[first + t] >> half) & 1;
-        const float* vec = reinterpret_cast<const float*>(stg + (t % ST) * C::STAGE + 2 * C::CH_BYTES) + chalf * 32;
-        ok = mbar_wait(&bar_s[t & 1], (t / 2) & 1, fl);
+        const float4* vec = reinterpret_cast<const float4*>(stg + (t % ST) * C::STAGE + 2 * C::CH_BYTES) + chalf * 8;
+        ok = mbar_wait(&bar_s[t % NBUF], (t / NBUF) & 1, fl);
         if (!ok) break;
         fence_after();
         uint32_t sr[32], qr[32];
@@ -343,26 +449,37 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
         tmem_ld32(ts + 64, qr);
         tmem_ld_wait();
         uint32_t pr[16], dr[16];
+        if (valid) {
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          float p0 = 0.f, p1 = 0.f, d0 = 0.f, d1 = 0.f;
-          if (valid) {
-            const float l0 = MODE == DKV ? vec[i] : my_lse, l1 = MODE == DKV ? vec[i + 1] : my_lse;
-            const float e0 = MODE == DKV ? vec[64 + i] : my_delta, e1 = MODE == DKV ? vec[64 + i + 1] : my_delta;
-            p0 = fast_exp2(fmaf(__uint_as_float(sr[i]), a.scale_log2, -l0));
-            p1 = fast_exp2(fmaf(__uint_as_float(sr[i + 1]), a.scale_log2, -l1));
-            d0 = p0 * (__uint_as_float(qr[i]) - e0) * a.scale;
-            d1 = p1 * (__uint_as_float(qr[i + 1]) - e1) * a.scale;
+          for (int i = 0; i < 32; i += 4) {
+            float ls[4], es[4];
+            if (MODE == DKV) {                              // per-query lse and delta of this chunk
+              const float4 lv = vec[i / 4], ev = vec[16 + i / 4];
+              ls[0] = lv.x; ls[1] = lv.y; ls[2] = lv.z; ls[3] = lv.w;
+              es[0] = ev.x * a.scale; es[1] = ev.y * a.scale; es[2] = ev.z * a.scale; es[3] = ev.w * a.scale;
+            } else {
+#pragma unroll
+              for (int j = 0; j < 4; ++j) { ls[j] = my_lse; es[j] = my_ds; }
+            }
+            float pv[4], dv[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              pv[j] = fast_exp2(fmaf(__uint_as_float(sr[i + j]), a.scale_log2, -ls[j]));
+              dv[j] = pv[j] * fmaf(__uint_as_float(qr[i + j]), a.scale, -es[j]);     // P (dP - delta) scale
+            }
+            pr[i / 2] = pack16<T>(pv[0], pv[1]); pr[i / 2 + 1] = pack16<T>(pv[2], pv[3]);
+            dr[i / 2] = pack16<T>(dv[0], dv[1]); dr[i / 2 + 1] = pack16<T>(dv[2], dv[3]);
           }
-          pr[i / 2] = pack16<T>(p0, p1);
-          dr[i / 2] = pack16<T>(d0, d1);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) { pr[i] = 0u; dr[i] = 0u; }
         }
         // packed values go over the first 16 columns of this thread's own 32-column slice
         if (MODE == DKV) tmem_st16(ts, pr);
         tmem_st16(ts + 64, dr);
         tmem_st_wait();
         fence_before();
-        mbar_arrive(&bar_p[t & 1]);
+        mbar_arrive(&bar_p[t % NBUF]);
       }
       if (ok && mbar_wait(&bar_done, 0, fl)) {
         fence_after();
@@ -518,6 +635,12 @@ int attn_bwd_tc(const void* q, const void* k, const void* v, const void* dout, c
   }
   return BSP_OK;
 }
+
+#ifdef BSP_TC_TRACE
+extern "C" int bsp_tc_trace_read(long long* out) {
+  return (int)cudaMemcpyFromSymbol(out, g_tc_trace, sizeof(long long) * 3 * 64 * 6);
+}
+#endif
 
 int tc_device_status(int* out) {
   int v = 0;

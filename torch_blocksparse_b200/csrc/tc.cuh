@@ -103,6 +103,12 @@ BSP_DEVI void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
 BSP_DEVI void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 // ---- tcgen05.mma ---------------------------------------------------------------
+// High word of every shared-memory descriptor used here: 1024 bytes between 8-row
+// groups (bits 32-45), descriptor version 1 (bit 46), 128-byte swizzle (bits 61-63).
+constexpr uint32_t kDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);
+// Low word: start address (bits 0-13, in 16-byte units) and the unused leading offset.
+BSP_DEVI uint32_t desc_lo(uint32_t addr) { return ((addr & 0x3FFFF) >> 4) | (1u << 16); }
+
 // D[tmem] (+)= A[smem] * B[smem]
 BSP_DEVI void mma_ss(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t accumulate) {
   asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
@@ -112,6 +118,48 @@ BSP_DEVI void mma_ss(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_
 BSP_DEVI void mma_ts(uint32_t d, uint32_t a, uint64_t b, uint32_t idesc, uint32_t accumulate) {
   asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
                ::"r"(d), "r"(a), "l"(b), "r"(idesc), "r"(accumulate) : "memory");
+}
+
+// The same two products with the operand descriptors given as their low 32-bit
+// words (see desc_lo): the high word is the same for every descriptor of these
+// kernels, so an issue costs one add per operand instead of a 64-bit rebuild.
+BSP_DEVI void mma_ss_lo(uint32_t d, uint32_t a_lo, uint32_t b_lo, uint32_t idesc, uint32_t accumulate) {
+  asm volatile("{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+               "mov.b64 da, {%1, %5};\n\tmov.b64 db, {%2, %5};\n\t"
+               "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %3, p;\n\t}"
+               ::"r"(d), "r"(a_lo), "r"(b_lo), "r"(idesc), "r"(accumulate), "r"(kDescHi) : "memory");
+}
+BSP_DEVI void mma_ts_lo(uint32_t d, uint32_t a, uint32_t b_lo, uint32_t idesc, uint32_t accumulate) {
+  asm volatile("{\n\t.reg .pred p;\n\t.reg .b64 db;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+               "mov.b64 db, {%2, %5};\n\t"
+               "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %3, p;\n\t}"
+               ::"r"(d), "r"(a), "r"(b_lo), "r"(idesc), "r"(accumulate), "r"(kDescHi) : "memory");
+}
+
+// Issue forms for back-to-back issue with descriptors prepared in advance: nothing
+// but the MMA itself sits between two issues.
+BSP_DEVI void mma_ss_acc(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc) {
+  asm volatile("{\n\t.reg .pred p;\n\tsetp.eq.b32 p, 0, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+               ::"r"(d), "l"(a), "l"(b), "r"(idesc) : "memory");
+}
+BSP_DEVI void mma_ts_acc(uint32_t d, uint32_t a, uint64_t b, uint32_t idesc) {
+  asm volatile("{\n\t.reg .pred p;\n\tsetp.eq.b32 p, 0, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+               ::"r"(d), "r"(a), "l"(b), "r"(idesc) : "memory");
+}
+BSP_DEVI uint64_t desc_from_lo(uint32_t lo) { return (static_cast<uint64_t>(kDescHi) << 32) | lo; }
+
+// Variants that always accumulate (no predicate set-up between back-to-back issues).
+BSP_DEVI void mma_ss_lo_acc(uint32_t d, uint32_t a_lo, uint32_t b_lo, uint32_t idesc) {
+  asm volatile("{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\tsetp.eq.b32 p, 0, 0;\n\t"
+               "mov.b64 da, {%1, %4};\n\tmov.b64 db, {%2, %4};\n\t"
+               "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %3, p;\n\t}"
+               ::"r"(d), "r"(a_lo), "r"(b_lo), "r"(idesc), "r"(kDescHi) : "memory");
+}
+BSP_DEVI void mma_ts_lo_acc(uint32_t d, uint32_t a, uint32_t b_lo, uint32_t idesc) {
+  asm volatile("{\n\t.reg .pred p;\n\t.reg .b64 db;\n\tsetp.eq.b32 p, 0, 0;\n\t"
+               "mov.b64 db, {%2, %4};\n\t"
+               "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %3, p;\n\t}"
+               ::"r"(d), "r"(a), "r"(b_lo), "r"(idesc), "r"(kDescHi) : "memory");
 }
 
 // Shared-memory operand descriptor for tiles in the 128-byte-swizzled layout TMA
