@@ -131,3 +131,50 @@ def test_config4_full_fused_matches_chain_and_oracle_slice():
                                   layout[h:h + 1], block, c['scale'], do=c['do'][z:z + 1, h:h + 1])
     for name, g, w in zip(('o', 'dq', 'dk', 'dv'), outs[True], want):
         assert_close(g[z:z + 1, h:h + 1], w, 'oracle slice ' + name)
+
+
+@pytest.mark.parametrize('block,nb', [(64, 5), (64, 8), (128, 3)])
+@pytest.mark.parametrize('dtype,D', [(torch.float16, 64), (torch.bfloat16, 128)])
+def test_tcgen05_and_mma_sync_paths_agree(block, nb, dtype, D):
+    """The same call on both kernel families (odd block counts leave a tile with a
+    single block-row), each against the oracle, and against each other."""
+    from torch_blocksparse_b200 import fused
+    H = 3
+    g = torch.Generator().manual_seed(block * nb + D)
+    layout = (torch.rand((H, nb, nb), generator=g) > 0.45).long()
+    layout[:, :, 0] = 1
+    layout[2, 1, :] = 0
+    q, k, v, do = rand_qkv(2, H, nb * block, D, dtype, seed=nb)
+    want = dm.attention_reference(q, k, v, layout, block, D ** -0.5, do=do)
+    outs = {}
+    try:
+        for path in ('tc', 'mma'):
+            fused.PATH = path
+            mod = SparseSelfAttention(layout=layout, block=block, fused=True)
+            outs[path] = run_module(mod, q, k, v, do)
+            for name, got, w in zip(('o', 'dq', 'dk', 'dv'), outs[path], want):
+                assert_close(got, w, '%s on path %s' % (name, path))
+    finally:
+        fused.PATH = 'tc'
+    for name, a, b in zip(('o', 'dq', 'dk', 'dv'), outs['tc'], outs['mma']):
+        assert_close(a, b, 'tc vs mma ' + name)
+
+
+def test_config5_full_layout_slice():
+    """Benchmark configuration 5 at its full layout and length (L = 16384, block 128,
+    head_dim 128, BF16), batch reduced to 1: oracle on one head, both kernel families."""
+    from torch_blocksparse_b200 import fused
+    c = workloads.config5(small=False, Z=1)
+    layout, block = c['layout'], c['block']
+    h = 7
+    want = dm.attention_reference(c['q'][:, h:h + 1], c['k'][:, h:h + 1], c['v'][:, h:h + 1], layout[h:h + 1], block,
+                                  c['scale'], do=c['do'][:, h:h + 1])
+    try:
+        for path in ('tc', 'mma'):
+            fused.PATH = path
+            mod = SparseSelfAttention(layout=layout, block=block, fused=True)
+            got = run_module(mod, c['q'], c['k'], c['v'], c['do'])
+            for name, g_, w in zip(('o', 'dq', 'dk', 'dv'), got, want):
+                assert_close(g_[:, h:h + 1], w, 'config 5 %s on path %s' % (name, path))
+    finally:
+        fused.PATH = 'tc'
