@@ -178,3 +178,31 @@ def test_config5_full_layout_slice():
                 assert_close(g_[:, h:h + 1], w, 'config 5 %s on path %s' % (name, path))
     finally:
         fused.PATH = 'tc'
+
+
+def test_multihead_attention_matches_torch_dense():
+    """The reference's own test (tests/test_attention.py:13-49): all-ones layout against
+    torch.nn.MultiheadAttention, FP16, block 16, B=2, H=2, L=128, E=128, key-padding mask
+    given additively (-inf) to the sparse module and as bool to the dense one."""
+    from torch_blocksparse_b200 import MultiheadAttention, replace_mha
+    torch.manual_seed(0)
+    block, B, H, L, E = 16, 2, 2, 128, 128
+    layout = torch.ones(H, L // block, L // block).long()
+    sparse = MultiheadAttention(E, H, layout, block).to(DEV).half()
+    torch.manual_seed(0)
+    dense = torch.nn.MultiheadAttention(E, H).to(DEV).half()
+    for ps, pd in zip(sparse.parameters(), dense.parameters()):
+        ps.data.copy_(pd.data)
+    x = torch.rand(L, B, E, device=DEV).half()
+    mul_mask = torch.randint(0, 2, (B, L), dtype=torch.bool, device=DEV)
+    mul_mask[:, 0] = False
+    add_mask = torch.zeros((B, L), device=DEV).half()
+    add_mask[mul_mask] = float('-inf')
+    got, _ = sparse(x, x, x, key_padding_mask=add_mask, need_weights=False)
+    want, _ = dense(x, x, x, key_padding_mask=mul_mask, need_weights=False)
+    assert_close(got, want, 'MultiheadAttention')
+    # model surgery keeps the parameters
+    model = torch.nn.Sequential(torch.nn.MultiheadAttention(E, H)).to(DEV).half()
+    ref_w = model[0].in_proj_weight.detach().clone()
+    replace_mha(model, (layout, block))
+    assert isinstance(model[0], MultiheadAttention) and torch.equal(model[0].in_proj_weight, ref_w)

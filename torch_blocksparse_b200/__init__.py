@@ -7,7 +7,8 @@ deepspeedsparseselfattention.py, also exported as SparseSelfAttention).
 from .softmax import Softmax
 from .matmul import MatMul
 from .attention import DeepSpeedSparseSelfAttention, SparseSelfAttention, SparsityConfig
+from .mha import MultiheadAttention, replace_mha, make_layout
 from . import layouts
 
 __all__ = ['Softmax', 'MatMul', 'DeepSpeedSparseSelfAttention', 'SparseSelfAttention',
-           'SparsityConfig', 'layouts']
+           'SparsityConfig', 'MultiheadAttention', 'replace_mha', 'make_layout', 'layouts']

@@ -122,8 +122,17 @@ class DeepSpeedSparseSelfAttention(nn.Module):
                 key_padding_mask = key_padding_mask.unsqueeze(0)
         if attn_mask is not None:
             attn_mask = self.transpose_mask_for_sparse(query.dtype, attn_mask)
+        return self.attend(query, key, value, float(head_dim) ** -0.5, rpe, key_padding_mask, attn_mask)
+
+    def attend(self, query, key, value, scaling, rpe=None, key_padding_mask=None, attn_mask=None):
+        """The attention core on [bsz, heads, L, head_dim] operands with an explicit score scale
+        (masks already in the dtype of the operands)."""
+        bsz, num_heads, tgt_len, head_dim = query.size()
+        if key_padding_mask is not None and key_padding_mask.dtype != query.dtype:
+            key_padding_mask = key_padding_mask.to(query.dtype)
+        if attn_mask is not None and attn_mask.dtype != query.dtype:
+            attn_mask = attn_mask.to(query.dtype)
         sdd_nt, dsd_nn, softmax = self.get_ops(num_heads, tgt_len)
-        scaling = float(head_dim) ** -0.5
         if self.fused:
             from .fused import fused_attention, fused_supported
             if fused_supported(query, self.block):

@@ -27,9 +27,9 @@
 // block = 64 a 2-bit mask per chunk says which half of the tile owns the block;
 // the other half contributes zeros.
 //
-// Warp roles: eight compute warps, one TMA producer warp (ring of inner chunks),
-// one MMA issuer warp.  They talk through mbarriers only; every wait is bounded
-// (tc.cuh) and a wait that expires sets the device status word.
+// Warp roles: eight compute warps and two issuing warps (one thread each): one issues the
+// score products and the TMA loads of the ring of inner chunks, the other the accumulating
+// products.  They talk through mbarriers only; every wait is bounded (tc.cuh) and a wait that expires sets the device status word.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include "common.h"
@@ -83,7 +83,7 @@ template <int D, int MODE> struct Cfg {
   static constexpr int ATOMS = D / 64;                         // 64-element (128-byte) column groups
   static constexpr int NRES = MODE == FWD ? 1 : 2;             // resident 128-row operands
   static constexpr int NC = 8;                                 // compute warps: two threads per tile row
-  static constexpr int NT = (NC + 2) * 32;
+  static constexpr int NT = (NC + 2) * 32;                     // + loader / score issuer, accumulate issuer
   static constexpr int RES_BYTES = ATOMS * 128 * 128;
   static constexpr int CH_BYTES = ATOMS * 64 * 128;
   static constexpr int STAGE = 2 * CH_BYTES + (MODE == DKV ? 1024 : 0);   // + lse / delta of the chunk
@@ -178,37 +178,8 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
   const uint32_t tmem = tmem_slot;
   volatile int* fl = &failed;
 
-  if (warp == NC) {
-    // ------------------------------------------------------------------ TMA producer
-    if (lane == 0) {
-      prefetch_map(&m_res0); prefetch_map(&m_ch0); prefetch_map(&m_ch1);
-      mbar_expect_tx(&bar_res, C::NRES * C::RES_BYTES);
-      for (int hf = 0; hf < 2; ++hf) {
-        const int crow = (hf == 0 || c1 < 0 ? c0 : c1) * 64;
-        for (int at = 0; at < ATOMS; ++at) {
-          tma_load_4d(res + at * 16384 + hf * 8192, &m_res0, &bar_res, at * 64, crow, h, z);
-          if (C::NRES == 2) tma_load_4d(res + C::RES_BYTES + at * 16384 + hf * 8192, &m_res1, &bar_res, at * 64, crow, h, z);
-        }
-      }
-      for (int t = 0; t < ntiles; ++t) {
-        const int stage = t % ST;
-        if (t >= ST && !mbar_wait(&bar_acc[(t - ST) & 3], ((t - ST) >> 2) & 1, fl)) break;
-        const int crow = a.chunk[first + t] * 64;
-        unsigned char* sp = stg + stage * C::STAGE;
-        TC_TRACE(0, t, 0);
-        mbar_expect_tx(&bar_full[stage], 2 * C::CH_BYTES + (MODE == DKV ? 512 : 0));
-        for (int at = 0; at < ATOMS; ++at) {
-          tma_load_4d(sp + at * 8192, &m_ch0, &bar_full[stage], at * 64, crow, h, z);
-          tma_load_4d(sp + C::CH_BYTES + at * 8192, &m_ch1, &bar_full[stage], at * 64, crow, h, z);
-        }
-        if (MODE == DKV) {
-          bulk_load(sp + 2 * C::CH_BYTES, a.lse + zh + crow, 256, &bar_full[stage]);
-          bulk_load(sp + 2 * C::CH_BYTES + 256, a.delta + zh + crow, 256, &bar_full[stage]);
-        }
-      }
-    }
-  } else if (warp == NC + 1) {
-    // ------------------------------------------------------------------ MMA issuer
+  if (warp >= NC) {
+    // ------------------------------------------------------------------ loader and MMA issuers
     if (lane == 0) {
       const uint32_t idesc_kk = instr_desc(128, 64, 0, IsBf16<T>::v);   // A, B K-major
       const uint32_t idesc_mn = instr_desc(128, 64, 1, IsBf16<T>::v);   // B MN-major
@@ -292,39 +263,64 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
           }
         commit(&bar_acc[t & 3]);      // chunk t fully consumed: its score buffer and its stage are free
       };
-      bool ok = mbar_wait(&bar_res, 0, fl);
-      for (int t = 0; ok && t < ntiles; ++t) {
-        if (NBUF == 1 && t >= 1) {                          // one buffer: finish chunk t-1 before its scores are overwritten
-          prep_acc(t - 1);
-          ok = mbar_wait(&bar_p[0], (t - 1) & 1, fl);
+      // Two issuing threads, one per kind of product, each in its own warp: the scores of chunk
+      // t only wait for their operands and for the score buffer, the accumulation of chunk t
+      // only for the compute warps; neither queues behind the other's barrier.  The score
+      // issuer also feeds the ring of chunk operands: the wait that frees a score buffer
+      // frees a stage as well, which it refills right after its MMAs.
+      if (warp == NC) {
+        auto load_chunk = [&](int t, int crow) {
+          const int stage = t % ST;
+          unsigned char* sp = stg + stage * C::STAGE;
+          TC_TRACE(0, t, 0);
+          mbar_expect_tx(&bar_full[stage], 2 * C::CH_BYTES + (MODE == DKV ? 512 : 0));
+          for (int at = 0; at < ATOMS; ++at) {
+            tma_load_4d(sp + at * 8192, &m_ch0, &bar_full[stage], at * 64, crow, h, z);
+            tma_load_4d(sp + C::CH_BYTES + at * 8192, &m_ch1, &bar_full[stage], at * 64, crow, h, z);
+          }
+          if (MODE == DKV) {
+            bulk_load(sp + 2 * C::CH_BYTES, a.lse + zh + crow, 256, &bar_full[stage]);
+            bulk_load(sp + 2 * C::CH_BYTES + 256, a.delta + zh + crow, 256, &bar_full[stage]);
+          }
+        };
+        prefetch_map(&m_res0); prefetch_map(&m_ch0); prefetch_map(&m_ch1);
+        mbar_expect_tx(&bar_res, C::NRES * C::RES_BYTES);
+        for (int hf = 0; hf < 2; ++hf) {
+          const int crow = (hf == 0 || c1 < 0 ? c0 : c1) * 64;
+          for (int at = 0; at < ATOMS; ++at) {
+            tma_load_4d(res + at * 16384 + hf * 8192, &m_res0, &bar_res, at * 64, crow, h, z);
+            if (C::NRES == 2) tma_load_4d(res + C::RES_BYTES + at * 16384 + hf * 8192, &m_res1, &bar_res, at * 64, crow, h, z);
+          }
+        }
+        for (int t = 0; t < ST && t < ntiles; ++t) load_chunk(t, a.chunk[first + t] * 64);
+        bool ok = mbar_wait(&bar_res, 0, fl);
+        for (int t = 0; ok && t < ntiles; ++t) {
+          // chunk whose stage the wait below frees; its index is fetched ahead of its use
+          const int tn = t - NBUF + ST;
+          const int crow_n = (t >= NBUF && tn < ntiles) ? a.chunk[first + tn] * 64 : -1;
+          prep_scores(t);
+          ok = mbar_wait(&bar_full[t % ST], (t / ST) & 1, fl);
+          TC_TRACE(1, t, 0);
+          if (ok && t >= NBUF) ok = mbar_wait(&bar_acc[(t - NBUF) & 3], ((t - NBUF) >> 2) & 1, fl);
+          TC_TRACE(1, t, 1);
           if (!ok) break;
           fence_after();
-          accumulate(t - 1);
+          scores(t);
+          TC_TRACE(1, t, 2);
+          if (crow_n >= 0) load_chunk(tn, crow_n);
         }
-        prep_scores(t);
-        ok = mbar_wait(&bar_full[t % ST], (t / ST) & 1, fl);
-        TC_TRACE(1, t, 0);
-        if (ok && t >= NBUF) ok = mbar_wait(&bar_acc[(t - NBUF) & 3], ((t - NBUF) >> 2) & 1, fl);
-        TC_TRACE(1, t, 1);
-        if (!ok) break;
-        fence_after();
-        scores(t);
-        TC_TRACE(1, t, 2);
-        if (NBUF >= 2 && t >= 1) {
-          prep_acc(t - 1);
-          ok = mbar_wait(&bar_p[(t - 1) % NBUF], ((t - 1) / NBUF) & 1, fl);
+      } else {
+        bool ok = true;
+        for (int t = 0; ok && t < ntiles; ++t) {
+          prep_acc(t);
+          ok = mbar_wait(&bar_full[t % ST], (t / ST) & 1, fl) && mbar_wait(&bar_p[t % NBUF], (t / NBUF) & 1, fl);
           TC_TRACE(1, t, 3);
           if (!ok) break;
           fence_after();
-          accumulate(t - 1);
+          accumulate(t);
           TC_TRACE(1, t, 4);
         }
-      }
-      if (ok) prep_acc(ntiles - 1);
-      if (ok && mbar_wait(&bar_p[(ntiles - 1) % NBUF], ((ntiles - 1) / NBUF) & 1, fl)) {
-        fence_after();
-        accumulate(ntiles - 1);
-        commit(&bar_done);
+        if (ok) commit(&bar_done);
       }
     }
   } else {
@@ -441,13 +437,16 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
         const uint32_t ts = tmem + (t % NBUF) * C::SCORE_COLS + lane_base + chalf * 32;
         const bool valid = (a.mask[first + t] >> half) & 1;
         const float4* vec = reinterpret_cast<const float4*>(stg + (t % ST) * C::STAGE + 2 * C::CH_BYTES) + chalf * 8;
+        TC_TRACE(2, t, 0);
         ok = mbar_wait(&bar_s[t % NBUF], (t / NBUF) & 1, fl);
+        TC_TRACE(2, t, 1);
         if (!ok) break;
         fence_after();
         uint32_t sr[32], qr[32];
         tmem_ld32(ts, sr);
         tmem_ld32(ts + 64, qr);
         tmem_ld_wait();
+        TC_TRACE(2, t, 2);
         uint32_t pr[16], dr[16];
         if (valid) {
 #pragma unroll
@@ -475,11 +474,13 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
           for (int i = 0; i < 16; ++i) { pr[i] = 0u; dr[i] = 0u; }
         }
         // packed values go over the first 16 columns of this thread's own 32-column slice
+        TC_TRACE(2, t, 3);
         if (MODE == DKV) tmem_st16(ts, pr);
         tmem_st16(ts + 64, dr);
         tmem_st_wait();
         fence_before();
         mbar_arrive(&bar_p[t % NBUF]);
+        TC_TRACE(2, t, 4);
       }
       if (ok && mbar_wait(&bar_done, 0, fl)) {
         fence_after();
