@@ -442,41 +442,45 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
         TC_TRACE(2, t, 1);
         if (!ok) break;
         fence_after();
-        uint32_t sr[32], qr[32];
-        tmem_ld32(ts, sr);
-        tmem_ld32(ts + 64, qr);
-        tmem_ld_wait();
-        TC_TRACE(2, t, 2);
-        uint32_t pr[16], dr[16];
-        if (valid) {
+        // Two passes of 16 columns keep the live registers of a pass at 48.  The packed
+        // 16-bit results of pass hv go to columns [8 hv, 8 hv + 8) of this thread's own
+        // 32-column slice: pass 0 only overwrites columns it has already read.
 #pragma unroll
-          for (int i = 0; i < 32; i += 4) {
-            float ls[4], es[4];
-            if (MODE == DKV) {                              // per-query lse and delta of this chunk
-              const float4 lv = vec[i / 4], ev = vec[16 + i / 4];
-              ls[0] = lv.x; ls[1] = lv.y; ls[2] = lv.z; ls[3] = lv.w;
-              es[0] = ev.x * a.scale; es[1] = ev.y * a.scale; es[2] = ev.z * a.scale; es[3] = ev.w * a.scale;
-            } else {
+        for (int hv = 0; hv < 2; ++hv) {
+          uint32_t sr[16], qr[16], pr[8], dr[8];
+          if (valid) {
+            tmem_ld16(ts + hv * 16, sr);
+            tmem_ld16(ts + 64 + hv * 16, qr);
+            tmem_ld_wait();
+            if (hv == 0) TC_TRACE(2, t, 2);
 #pragma unroll
-              for (int j = 0; j < 4; ++j) { ls[j] = my_lse; es[j] = my_ds; }
+            for (int i = 0; i < 16; i += 4) {
+              float ls[4], es[4];
+              if (MODE == DKV) {                            // per-query lse and delta * scale of this chunk
+                const float4 lv = vec[hv * 4 + i / 4], ev = vec[16 + hv * 4 + i / 4];
+                ls[0] = lv.x; ls[1] = lv.y; ls[2] = lv.z; ls[3] = lv.w;
+                es[0] = ev.x * a.scale; es[1] = ev.y * a.scale; es[2] = ev.z * a.scale; es[3] = ev.w * a.scale;
+              } else {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) { ls[j] = my_lse; es[j] = my_ds; }
+              }
+              float pv[4], dv[4];
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                pv[j] = fast_exp2(fmaf(__uint_as_float(sr[i + j]), a.scale_log2, -ls[j]));
+                dv[j] = pv[j] * fmaf(__uint_as_float(qr[i + j]), a.scale, -es[j]);     // P (dP - delta) scale
+              }
+              pr[i / 2] = pack16<T>(pv[0], pv[1]); pr[i / 2 + 1] = pack16<T>(pv[2], pv[3]);
+              dr[i / 2] = pack16<T>(dv[0], dv[1]); dr[i / 2 + 1] = pack16<T>(dv[2], dv[3]);
             }
-            float pv[4], dv[4];
+          } else {
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              pv[j] = fast_exp2(fmaf(__uint_as_float(sr[i + j]), a.scale_log2, -ls[j]));
-              dv[j] = pv[j] * fmaf(__uint_as_float(qr[i + j]), a.scale, -es[j]);     // P (dP - delta) scale
-            }
-            pr[i / 2] = pack16<T>(pv[0], pv[1]); pr[i / 2 + 1] = pack16<T>(pv[2], pv[3]);
-            dr[i / 2] = pack16<T>(dv[0], dv[1]); dr[i / 2 + 1] = pack16<T>(dv[2], dv[3]);
+            for (int i = 0; i < 8; ++i) { pr[i] = 0u; dr[i] = 0u; }
           }
-        } else {
-#pragma unroll
-          for (int i = 0; i < 16; ++i) { pr[i] = 0u; dr[i] = 0u; }
+          if (MODE == DKV) tmem_st8(ts + hv * 8, pr);
+          tmem_st8(ts + 64 + hv * 8, dr);
         }
-        // packed values go over the first 16 columns of this thread's own 32-column slice
         TC_TRACE(2, t, 3);
-        if (MODE == DKV) tmem_st16(ts, pr);
-        tmem_st16(ts + 64, dr);
         tmem_st_wait();
         fence_before();
         mbar_arrive(&bar_p[t % NBUF]);
