@@ -97,7 +97,14 @@ template <int D, int MODE> struct Cfg {
   // forward: one O accumulator per half of the key chunk (the two threads of a row keep
   // independent running maxima); dK/dV: dV and dK
   static constexpr int ACC_COLS = MODE == DQ ? D : 2 * D;
-  static constexpr int TMEM = ACC_BASE + ACC_COLS <= 256 ? 256 : 512;
+  // Resident operands that are the A side of the score products are copied to tensor memory
+  // once per tile where the columns allow it: an MMA whose A comes from shared memory reads
+  // 4 KB of A and 2 KB of B per K-step and is bound by that traffic (48 cycles at N = 64
+  // instead of 32).
+  static constexpr bool RES_T = MODE == DQ || (MODE == FWD && D == 128);
+  static constexpr int RES_BASE = ACC_BASE + ACC_COLS;
+  static constexpr int RES_COLS = RES_T ? NRES * (D / 2) : 0;
+  static constexpr int TMEM = RES_BASE + RES_COLS <= 256 ? 256 : 512;
   static constexpr int CTAS = D == 64 ? 2 : 1;
 };
 
@@ -130,7 +137,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
   unsigned char* smem = smem_raw + ((1024 - (saddr(smem_raw) & 1023)) & 1023);
   unsigned char* res = smem;                                   // [NRES][ATOMS][128 rows][128 B]
   unsigned char* stg = res + C::NRES * C::RES_BYTES;           // [ST][ch0 | ch1 | lse, delta]
-  __shared__ uint64_t bar_res, bar_full[ST], bar_s[4], bar_p[4], bar_acc[4], bar_done;
+  __shared__ uint64_t bar_res, bar_rt, bar_full[ST], bar_s[4], bar_p[4], bar_acc[4], bar_done;
   __shared__ float xch[2][2][128];                           // forward: (max, sum) of the two halves of every row
   __shared__ uint32_t tmem_slot;
   __shared__ int failed;
@@ -165,6 +172,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
   if (tid == 0) {
     failed = 0;
     mbar_init(&bar_res, 1);
+    mbar_init(&bar_rt, NC * 32);
     for (int s = 0; s < ST; ++s) mbar_init(&bar_full[s], 1);
     for (int b = 0; b < 4; ++b) mbar_init(&bar_acc[b], 1);
     for (int b = 0; b < NBUF; ++b) { mbar_init(&bar_s[b], 1); mbar_init(&bar_p[b], NC * 32); }
@@ -212,13 +220,25 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
       };
       auto scores = [&](int t) {
         const uint32_t ts = tmem + (t % NBUF) * C::SCORE_COLS;
-        mma_ss(ts, a0[0], sb0[0], idesc_kk, 0u);
+        if (C::RES_T) {
+          const uint32_t tq = tmem + C::RES_BASE;
+          mma_ts(ts, tq, sb0[0], idesc_kk, 0u);
 #pragma unroll
-        for (int ks = 1; ks < KS; ++ks) mma_ss_acc(ts, a0[ks], sb0[ks], idesc_kk);
-        if (MODE != FWD) {
-          mma_ss(ts + 64, a1[0], sb1[0], idesc_kk, 0u);
+          for (int ks = 1; ks < KS; ++ks) mma_ts_acc(ts, tq + ks * 8, sb0[ks], idesc_kk);
+          if (MODE != FWD) {
+            mma_ts(ts + 64, tq + D / 2, sb1[0], idesc_kk, 0u);
 #pragma unroll
-          for (int ks = 1; ks < KS; ++ks) mma_ss_acc(ts + 64, a1[ks], sb1[ks], idesc_kk);
+            for (int ks = 1; ks < KS; ++ks) mma_ts_acc(ts + 64, tq + D / 2 + ks * 8, sb1[ks], idesc_kk);
+          }
+        } else {
+          mma_ss(ts, a0[0], sb0[0], idesc_kk, 0u);
+#pragma unroll
+          for (int ks = 1; ks < KS; ++ks) mma_ss_acc(ts, a0[ks], sb0[ks], idesc_kk);
+          if (MODE != FWD) {
+            mma_ss(ts + 64, a1[0], sb1[0], idesc_kk, 0u);
+#pragma unroll
+            for (int ks = 1; ks < KS; ++ks) mma_ss_acc(ts + 64, a1[ks], sb1[ks], idesc_kk);
+          }
         }
         TC_TRACE(1, t, 5);
         commit(&bar_s[t % NBUF]);
@@ -293,7 +313,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
           }
         }
         for (int t = 0; t < ST && t < ntiles; ++t) load_chunk(t, a.chunk[first + t] * 64);
-        bool ok = mbar_wait(&bar_res, 0, fl);
+        bool ok = mbar_wait(C::RES_T ? &bar_rt : &bar_res, 0, fl);
         for (int t = 0; ok && t < ntiles; ++t) {
           // chunk whose stage the wait below frees; its index is fetched ahead of its use
           const int tn = t - NBUF + ST;
@@ -328,6 +348,30 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
     const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
     const int half = trow >> 6;                               // which 64-row chunk of the tile
     bool ok = true;
+    if (C::RES_T) {
+      // this thread's share of its row of the resident operands: shared memory (128-byte
+      // rows, 16-byte units swizzled by the row) -> tensor memory, two 16-bit values per column
+      ok = mbar_wait(&bar_res, 0, fl);
+      if (ok) {
+        constexpr int UNITS = D / 16;                            // 16-byte units per thread and operand
+#pragma unroll
+        for (int r = 0; r < C::NRES; ++r) {
+          const unsigned char* row = res + r * C::RES_BYTES + (D == 128 ? chalf * 16384 : 0) + trow * 128;
+          uint32_t w[UNITS * 4];
+#pragma unroll
+          for (int u = 0; u < UNITS; ++u) {
+            const int unit = (D == 128 ? u : chalf * UNITS + u) ^ (trow & 7);
+            const uint4 v = *reinterpret_cast<const uint4*>(row + unit * 16);
+            w[4 * u] = v.x; w[4 * u + 1] = v.y; w[4 * u + 2] = v.z; w[4 * u + 3] = v.w;
+          }
+          const uint32_t tq = tmem + C::RES_BASE + r * (D / 2) + chalf * (D / 4) + lane_base;
+          if constexpr (D == 128) tmem_st32(tq, w); else tmem_st16(tq, w);
+        }
+        tmem_st_wait();
+        fence_before();
+        mbar_arrive(&bar_rt);
+      }
+    }
     if (MODE == FWD) {
       // this thread owns 32 of the 64 key columns of its row, with its own running
       // maximum, sum and O accumulator; the two halves are merged at the end
