@@ -28,8 +28,8 @@
 // the other half contributes zeros.
 //
 // Warp roles: eight compute warps and two issuing warps (one thread each): one issues the
-// score products and the TMA loads of the ring of inner chunks, the other the accumulating
-// products.  They talk through mbarriers only; every wait is bounded (tc.cuh) and a wait that expires sets the device status word.
+// score products, the other the accumulating products and the TMA loads of the ring of inner
+// chunks.  They talk through mbarriers only; every wait is bounded (tc.cuh) and a wait that expires sets the device status word.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include "common.h"
@@ -93,15 +93,21 @@ template <int D, int MODE> struct Cfg {
   static constexpr int NSTAGE = (MODE != FWD && D == 128) ? 3 : 4;
   static constexpr int SMEM = NRES * RES_BYTES + NSTAGE * STAGE + 1024;
   static constexpr int SCORE_COLS = MODE == FWD ? 64 : 128;    // per buffer: S (and dP)
-  static constexpr int ACC_BASE = NBUF * SCORE_COLS;
+  // Early release (dQ at head_dim 64): the packed dS operand of the accumulating product gets
+  // its own double-buffered columns instead of overwriting the scores, so the score buffer is
+  // free as soon as the compute threads have read it and the scores of the next chunk are
+  // computed during the exponentials of this one.
+  static constexpr bool ER = MODE == DQ && D == 64;
+  static constexpr int PK_BASE = NBUF * SCORE_COLS;
+  static constexpr int ACC_BASE = PK_BASE + (ER ? 64 : 0);
   // forward: one O accumulator per half of the key chunk (the two threads of a row keep
   // independent running maxima); dK/dV: dV and dK
   static constexpr int ACC_COLS = MODE == DQ ? D : 2 * D;
   // Resident operands that are the A side of the score products are copied to tensor memory
   // once per tile where the columns allow it: an MMA whose A comes from shared memory reads
   // 4 KB of A and 2 KB of B per K-step and is bound by that traffic (48 cycles at N = 64
-  // instead of 32).
-  static constexpr bool RES_T = MODE == DQ || (MODE == FWD && D == 128);
+  // instead of 32 with two CTAs issuing).
+  static constexpr bool RES_T = (MODE == DQ || MODE == FWD) && D == 128;
   static constexpr int RES_BASE = ACC_BASE + ACC_COLS;
   static constexpr int RES_COLS = RES_T ? NRES * (D / 2) : 0;
   static constexpr int TMEM = RES_BASE + RES_COLS <= 256 ? 256 : 512;
@@ -137,7 +143,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
   unsigned char* smem = smem_raw + ((1024 - (saddr(smem_raw) & 1023)) & 1023);
   unsigned char* res = smem;                                   // [NRES][ATOMS][128 rows][128 B]
   unsigned char* stg = res + C::NRES * C::RES_BYTES;           // [ST][ch0 | ch1 | lse, delta]
-  __shared__ uint64_t bar_res, bar_rt, bar_full[ST], bar_s[4], bar_p[4], bar_acc[4], bar_done;
+  __shared__ uint64_t bar_res, bar_rt, bar_rd, bar_full[ST], bar_s[4], bar_p[4], bar_acc[4], bar_done;
   __shared__ float xch[2][2][128];                           // forward: (max, sum) of the two halves of every row
   __shared__ uint32_t tmem_slot;
   __shared__ int failed;
@@ -172,10 +178,12 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
   if (tid == 0) {
     failed = 0;
     mbar_init(&bar_res, 1);
-    mbar_init(&bar_rt, NC * 32);
+    mbar_init(&bar_rt, NC);
+    mbar_init(&bar_rd, NC);
+    if (C::ER) mbar_init(&bar_p[1], NC);
     for (int s = 0; s < ST; ++s) mbar_init(&bar_full[s], 1);
     for (int b = 0; b < 4; ++b) mbar_init(&bar_acc[b], 1);
-    for (int b = 0; b < NBUF; ++b) { mbar_init(&bar_s[b], 1); mbar_init(&bar_p[b], NC * 32); }
+    for (int b = 0; b < NBUF; ++b) { mbar_init(&bar_s[b], 1); mbar_init(&bar_p[b], NC); }
     mbar_init(&bar_done, 1);
     mbar_init_fence();
   }
@@ -269,8 +277,9 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
               if (ks & 1) mma_ts_acc(ta + (ks >> 1) * D + at * 64, pa, vb1[at * 4 + ks], idesc_mn);
               else mma_ts(ta + (ks >> 1) * D + at * 64, pa, vb1[at * 4 + ks], idesc_mn, later);
             } else if (MODE == DQ) {    // dQ += dS . K
-              if (ks > 0) mma_ts_acc(ta + at * 64, pa + 64, vb0[at * 4 + ks], idesc_mn);
-              else mma_ts(ta + at * 64, pa + 64, vb0[at * 4 + ks], idesc_mn, later);
+              const uint32_t da = C::ER ? tmem + C::PK_BASE + (t & 1) * 32 + ks * 8 : pa + 64;
+              if (ks > 0) mma_ts_acc(ta + at * 64, da, vb0[at * 4 + ks], idesc_mn);
+              else mma_ts(ta + at * 64, da, vb0[at * 4 + ks], idesc_mn, later);
             } else {                    // dV += P^T . dO,  dK += dS^T . Q
               if (ks > 0) {
                 mma_ts_acc(ta + at * 64, pa, vb1[at * 4 + ks], idesc_mn);
@@ -285,24 +294,23 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
       };
       // Two issuing threads, one per kind of product, each in its own warp: the scores of chunk
       // t only wait for their operands and for the score buffer, the accumulation of chunk t
-      // only for the compute warps; neither queues behind the other's barrier.  The score
-      // issuer also feeds the ring of chunk operands: the wait that frees a score buffer
-      // frees a stage as well, which it refills right after its MMAs.
+      // only for the compute warps; neither queues behind the other's barrier.  The accumulate
+      // issuer, which has the shorter list of MMAs, also refills the ring of chunk operands.
+      auto load_chunk = [&](int t, int crow) {
+        const int stage = t % ST;
+        unsigned char* sp = stg + stage * C::STAGE;
+        TC_TRACE(0, t, 0);
+        mbar_expect_tx(&bar_full[stage], 2 * C::CH_BYTES + (MODE == DKV ? 512 : 0));
+        for (int at = 0; at < ATOMS; ++at) {
+          tma_load_4d(sp + at * 8192, &m_ch0, &bar_full[stage], at * 64, crow, h, z);
+          tma_load_4d(sp + C::CH_BYTES + at * 8192, &m_ch1, &bar_full[stage], at * 64, crow, h, z);
+        }
+        if (MODE == DKV) {
+          bulk_load(sp + 2 * C::CH_BYTES, a.lse + zh + crow, 256, &bar_full[stage]);
+          bulk_load(sp + 2 * C::CH_BYTES + 256, a.delta + zh + crow, 256, &bar_full[stage]);
+        }
+      };
       if (warp == NC) {
-        auto load_chunk = [&](int t, int crow) {
-          const int stage = t % ST;
-          unsigned char* sp = stg + stage * C::STAGE;
-          TC_TRACE(0, t, 0);
-          mbar_expect_tx(&bar_full[stage], 2 * C::CH_BYTES + (MODE == DKV ? 512 : 0));
-          for (int at = 0; at < ATOMS; ++at) {
-            tma_load_4d(sp + at * 8192, &m_ch0, &bar_full[stage], at * 64, crow, h, z);
-            tma_load_4d(sp + C::CH_BYTES + at * 8192, &m_ch1, &bar_full[stage], at * 64, crow, h, z);
-          }
-          if (MODE == DKV) {
-            bulk_load(sp + 2 * C::CH_BYTES, a.lse + zh + crow, 256, &bar_full[stage]);
-            bulk_load(sp + 2 * C::CH_BYTES + 256, a.delta + zh + crow, 256, &bar_full[stage]);
-          }
-        };
         prefetch_map(&m_res0); prefetch_map(&m_ch0); prefetch_map(&m_ch1);
         mbar_expect_tx(&bar_res, C::NRES * C::RES_BYTES);
         for (int hf = 0; hf < 2; ++hf) {
@@ -315,34 +323,51 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
         for (int t = 0; t < ST && t < ntiles; ++t) load_chunk(t, a.chunk[first + t] * 64);
         bool ok = mbar_wait(C::RES_T ? &bar_rt : &bar_res, 0, fl);
         for (int t = 0; ok && t < ntiles; ++t) {
-          // chunk whose stage the wait below frees; its index is fetched ahead of its use
-          const int tn = t - NBUF + ST;
-          const int crow_n = (t >= NBUF && tn < ntiles) ? a.chunk[first + tn] * 64 : -1;
           prep_scores(t);
+          TC_TRACE(0, t, 5);
           ok = mbar_wait(&bar_full[t % ST], (t / ST) & 1, fl);
           TC_TRACE(1, t, 0);
-          if (ok && t >= NBUF) ok = mbar_wait(&bar_acc[(t - NBUF) & 3], ((t - NBUF) >> 2) & 1, fl);
+          if (C::ER) {
+            if (ok && t >= 1) ok = mbar_wait(&bar_rd, (t - 1) & 1, fl);     // scores of chunk t - 1 are in registers
+          } else {
+            if (ok && t >= NBUF) ok = mbar_wait(&bar_acc[(t - NBUF) & 3], ((t - NBUF) >> 2) & 1, fl);
+          }
           TC_TRACE(1, t, 1);
           if (!ok) break;
           fence_after();
           scores(t);
           TC_TRACE(1, t, 2);
-          if (crow_n >= 0) load_chunk(tn, crow_n);
         }
       } else {
         bool ok = true;
         for (int t = 0; ok && t < ntiles; ++t) {
+          // the stage of chunk t - 1 is refilled once its accumulation, issued one iteration
+          // ago, is complete; the index of the new chunk is fetched ahead of its use
+          const int tn = t - 1 + ST;
+          const int crow_n = (t >= 1 && tn < ntiles) ? a.chunk[first + tn] * 64 : -1;
           prep_acc(t);
-          ok = mbar_wait(&bar_full[t % ST], (t / ST) & 1, fl) && mbar_wait(&bar_p[t % NBUF], (t / NBUF) & 1, fl);
+          ok = mbar_wait(&bar_full[t % ST], (t / ST) & 1, fl) &&
+               (C::ER ? mbar_wait(&bar_p[t & 1], (t >> 1) & 1, fl) : mbar_wait(&bar_p[t % NBUF], (t / NBUF) & 1, fl));
           TC_TRACE(1, t, 3);
           if (!ok) break;
           fence_after();
           accumulate(t);
           TC_TRACE(1, t, 4);
+          if (crow_n >= 0) {
+            ok = mbar_wait(&bar_acc[(t - 1) & 3], ((t - 1) >> 2) & 1, fl);
+            if (!ok) break;
+            load_chunk(tn, crow_n);
+          }
         }
         if (ok) commit(&bar_done);
       }
     }
+#ifdef BSP_TC_TRACE
+    else if (lane == 1 && warp == NC + 1) {                     // arrival times of the chunk loads
+      bool ok = true;
+      for (int t = 0; ok && t < ntiles; ++t) { ok = mbar_wait(&bar_full[t % ST], (t / ST) & 1, fl); TC_TRACE(0, t, 1); }
+    }
+#endif
   } else {
     // ------------------------------------------------------------------ compute warps
     const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
@@ -351,7 +376,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
     if (C::RES_T) {
       // this thread's share of its row of the resident operands: shared memory (128-byte
       // rows, 16-byte units swizzled by the row) -> tensor memory, two 16-bit values per column
-      ok = mbar_wait(&bar_res, 0, fl);
+      ok = mbar_wait_warp(&bar_res, 0, fl);
       if (ok) {
         constexpr int UNITS = D / 16;                            // 16-byte units per thread and operand
 #pragma unroll
@@ -369,7 +394,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
         }
         tmem_st_wait();
         fence_before();
-        mbar_arrive(&bar_rt);
+        warp_arrive(&bar_rt, lane);
       }
     }
     if (MODE == FWD) {
@@ -381,7 +406,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
         const uint32_t ts = tmem + (t % NBUF) * C::SCORE_COLS + lane_base + chalf * 32;
         const bool valid = (a.mask[first + t] >> half) & 1;
         TC_TRACE(2, t, 0);
-        ok = mbar_wait(&bar_s[t % NBUF], (t / NBUF) & 1, fl);
+        ok = mbar_wait_warp(&bar_s[t % NBUF], (t / NBUF) & 1, fl);
         TC_TRACE(2, t, 1);
         if (!ok) break;
         fence_after();
@@ -403,7 +428,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
           const float alpha = grow_m ? fast_exp2(m_ref - m_new) : 1.f;      // 0 while m_ref is still -inf
           l *= alpha;
           if (t > 0) {                                      // the accumulator must be complete up to chunk t-1
-            ok = mbar_wait(&bar_acc[(t - 1) & 3], ((t - 1) >> 2) & 1, fl);
+            ok = mbar_wait_warp(&bar_acc[(t - 1) & 3], ((t - 1) >> 2) & 1, fl);
             if (!ok) break;
             fence_after();
             for (int c = 0; c < D; c += 32) {
@@ -437,14 +462,14 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
         tmem_st16(ts, pr);
         tmem_st_wait();
         fence_before();
-        mbar_arrive(&bar_p[t % NBUF]);
+        warp_arrive(&bar_p[t % NBUF], lane);
         TC_TRACE(2, t, 4);
       }
       // merge the two halves of every row: O = (O_a 2^(m_a - m) + O_b 2^(m_b - m)) / l
       xch[chalf][0][trow] = m_ref;
       xch[chalf][1][trow] = l;
       asm volatile("bar.sync 1, 256;" ::: "memory");          // the eight compute warps, always executed
-      if (ok && mbar_wait(&bar_done, 0, fl)) {
+      if (ok && mbar_wait_warp(&bar_done, 0, fl)) {
         fence_after();
         if (mychunk >= 0) {                                   // uniform per warp: a warp lies inside one chunk
           const float ma = xch[0][0][trow], mb = xch[1][0][trow], la = xch[0][1][trow], lb = xch[1][1][trow];
@@ -482,10 +507,45 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
         const bool valid = (a.mask[first + t] >> half) & 1;
         const float4* vec = reinterpret_cast<const float4*>(stg + (t % ST) * C::STAGE + 2 * C::CH_BYTES) + chalf * 8;
         TC_TRACE(2, t, 0);
-        ok = mbar_wait(&bar_s[t % NBUF], (t / NBUF) & 1, fl);
+        ok = mbar_wait_warp(&bar_s[t % NBUF], (t / NBUF) & 1, fl);
         TC_TRACE(2, t, 1);
         if (!ok) break;
         fence_after();
+        if constexpr (C::ER) {
+          // S and dP of this thread's 32 columns go to registers at once; the score buffer is
+          // then handed back, and the next scores are computed during the arithmetic below
+          uint32_t sr[32], qr[32], dr[16];
+          tmem_ld32(ts, sr);
+          tmem_ld32(ts + 64, qr);
+          tmem_ld_wait();
+          TC_TRACE(2, t, 2);
+          fence_before();
+          warp_arrive(&bar_rd, lane);
+          if (valid) {
+#pragma unroll
+            for (int i = 0; i < 32; i += 2) {
+              const float p0 = fast_exp2(fmaf(__uint_as_float(sr[i]), a.scale_log2, -my_lse));
+              const float p1 = fast_exp2(fmaf(__uint_as_float(sr[i + 1]), a.scale_log2, -my_lse));
+              dr[i / 2] = pack16<T>(p0 * fmaf(__uint_as_float(qr[i]), a.scale, -my_ds),
+                                    p1 * fmaf(__uint_as_float(qr[i + 1]), a.scale, -my_ds));   // P (dP - delta) scale
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) dr[i] = 0u;
+          }
+          TC_TRACE(2, t, 3);
+          if (t >= 2) {                                     // the accumulation of chunk t - 2 has read its operand
+            ok = mbar_wait_warp(&bar_acc[(t - 2) & 3], ((t - 2) >> 2) & 1, fl);
+            if (!ok) break;
+            fence_after();
+          }
+          tmem_st16(tmem + C::PK_BASE + (t & 1) * 32 + chalf * 16 + lane_base, dr);
+          tmem_st_wait();
+          fence_before();
+          warp_arrive(&bar_p[t & 1], lane);
+          TC_TRACE(2, t, 4);
+          continue;
+        }
         // Two passes of 16 columns keep the live registers of a pass at 48.  The packed
         // 16-bit results of pass hv go to columns [8 hv, 8 hv + 8) of this thread's own
         // 32-column slice: pass 0 only overwrites columns it has already read.
@@ -527,10 +587,10 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
         TC_TRACE(2, t, 3);
         tmem_st_wait();
         fence_before();
-        mbar_arrive(&bar_p[t % NBUF]);
+        warp_arrive(&bar_p[t % NBUF], lane);
         TC_TRACE(2, t, 4);
       }
-      if (ok && mbar_wait(&bar_done, 0, fl)) {
+      if (ok && mbar_wait_warp(&bar_done, 0, fl)) {
         fence_after();
         if (mychunk >= 0) {                                   // uniform per warp
           // the two threads of a row split the D output columns

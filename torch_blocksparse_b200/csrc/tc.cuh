@@ -35,6 +35,12 @@ BSP_DEVI bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 BSP_DEVI void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(saddr(bar)) : "memory");
 }
+// One arrival per warp, after all its lanes have finished (and fenced) their part: 32 lanes
+// arriving on one barrier serialise in the shared-memory atomic unit.  The whole warp must call it.
+BSP_DEVI void warp_arrive(uint64_t* bar, int lane) {
+  __syncwarp();
+  if (lane == 0) mbar_arrive(bar);
+}
 constexpr int kWaitBudget = 1 << 21;   // try_wait attempts before a wait is declared failed
 // Returns false when the phase did not complete in time, or at once when the
 // CTA has already failed (*failed != 0), so that a failed CTA drains quickly.
@@ -45,6 +51,11 @@ BSP_DEVI bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* failed) {
   }
   *failed = 1;
   return false;
+}
+
+// mbar_wait for a whole warp: the outcome is made uniform, so that a warp leaves its loop as one.
+BSP_DEVI bool mbar_wait_warp(uint64_t* bar, uint32_t parity, volatile int* failed) {
+  return __all_sync(0xffffffffu, mbar_wait(bar, parity, failed));
 }
 
 // ---- TMA ----------------------------------------------------------------------
