@@ -472,8 +472,8 @@ softmax_fwd_group(FwdArgs a, int Z, int lpr_log2, int header_ints) {
 // Same row decomposition, but the batch is walked inside the kernel: whatever
 // does not depend on the batch entry (the attention mask, an rpe that is
 // broadcast over the batch, the table look-ups) is read and converted once and
-// kept in registers as one FP32 term per element, and the x vectors of the next
-// batch entry are in flight while the current one is reduced.
+// kept in registers as one term per element, and the x vectors of the next two
+// batch entries are in flight while the current one is reduced.
 template <typename T, int NV, typename S>
 __global__ void __launch_bounds__(kGroupWarps * 32, 3)
 softmax_fwd_zloop(FwdArgs a, int Z, int lpr_log2, int header_ints) {
@@ -491,33 +491,81 @@ softmax_fwd_zloop(FwdArgs a, int Z, int lpr_log2, int header_ints) {
   if (size == 0) return;
   const int c = (lane & ((1 << lpr_log2) - 1)) * N;
   T* xp = reinterpret_cast<T*>(a.x) + ((int64_t)first_block_of_row(offset, header_ints) << (2 * bl)) + ((int64_t)rxm << bl) + c;
-  uint4 cur[NV];
+  // Loads are issued in the order of their dependences and none is consumed before all
+  // independent ones are in flight: table entries of the row, then x of the first two batch
+  // entries, then the optional inputs.
+  int ck[NV];
+  int hb[2] = {0, 0};
+  if constexpr (TERM || S::KPM != 0) {
+#pragma unroll
+    for (int k = 0; k < NV; ++k)
+      if (k < size) ck[k] = __ldg(a.lut + offset + 4 * k + 1);
+    if constexpr (TERM) { hb[0] = __ldg(a.lut + offset + 2); hb[1] = __ldg(a.lut + offset + 3); }
+  }
+  uint4 cur[NV], nxt[NV];
 #pragma unroll
   for (int k = 0; k < NV; ++k)
     if (k < size) cur[k] = __ldcs(reinterpret_cast<const uint4*>(xp + ((int64_t)k << (2 * bl))));
+  if (Z > 1) {
+#pragma unroll
+    for (int k = 0; k < NV; ++k)
+      if (k < size) nxt[k] = __ldcs(reinterpret_cast<const uint4*>(xp + a.x_sz + ((int64_t)k << (2 * bl))));
+  }
   int col[S::KPM != 0 ? NV : 1];
-  float term[TERM ? NV : 1][N];
+  // The batch-independent term stays in registers.  It is kept in the storage type, which
+  // is exact, unless rpe and an additive attention mask are both present: their sum is an
+  // FP32 value.  (A 'mul' mask only turns elements of the term into -inf.)
+  constexpr bool PACKED = TERM && !(S::RPE && S::AM == 1) && N == 8;
+  float term[TERM && !PACKED ? NV : 1][N];
+  uint4 pterm[PACKED ? NV : 1];
+  const T* kpm = reinterpret_cast<const T*>(a.kpm) + c;
+  uint4 kcur[S::KPM != 0 ? NV : 1];
   if constexpr (TERM || S::KPM != 0) {
-    const int64_t grow = ((int64_t)__ldg(a.lut + offset + 2) << bl) + rxm;
+    const int64_t grow = ((int64_t)hb[0] << bl) + rxm;
     const T* rpe = nullptr;
-    if constexpr (S::RPE) rpe = reinterpret_cast<const T*>(a.rpe) + __ldg(a.lut + offset + 3) * a.rpe_sh + grow * a.rpe_sr + c;
+    if constexpr (S::RPE) rpe = reinterpret_cast<const T*>(a.rpe) + hb[1] * a.rpe_sh + grow * a.rpe_sr + c;
     const T* am = reinterpret_cast<const T*>(a.am) + grow * a.am_sr + c;
+    uint4 rraw[S::RPE ? NV : 1], mraw[S::AM != 0 ? NV : 1];
 #pragma unroll
     for (int k = 0; k < NV; ++k) {
       if (k < size) {
-        const int ck = __ldg(a.lut + offset + 4 * k + 1) << bl;
-        if constexpr (S::KPM != 0) col[k] = ck;
-        if constexpr (TERM) {
+        const int cc = ck[k] << bl;
+        if constexpr (S::KPM != 0) { col[k] = cc; kcur[k] = load_raw(kpm + cc, true); }
+        if constexpr (S::RPE) rraw[k] = load_raw(rpe + cc, true);
+        if constexpr (S::AM != 0) mraw[k] = load_raw(am + cc, true);
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      if (k < size) {
+        if constexpr (PACKED) {
+          if constexpr (S::RPE) {
+            pterm[k] = rraw[k];
+            if constexpr (S::AM == 2) {
+              const T* me = reinterpret_cast<const T*>(&mraw[k]);
+              T* te = reinterpret_cast<T*>(&pterm[k]);
+#pragma unroll
+              for (int i = 0; i < N; ++i) if (to_f(me[i]) == 0.f) te[i] = from_f<T>(kNegInf);
+            }
+          } else {                                           // the attention mask alone
+            pterm[k] = mraw[k];
+            if constexpr (S::AM == 2) {
+              T* te = reinterpret_cast<T*>(&pterm[k]);
+#pragma unroll
+              for (int i = 0; i < N; ++i) te[i] = from_f<T>(to_f(te[i]) == 0.f ? kNegInf : 0.f);
+            }
+          }
+        } else if constexpr (TERM) {
           float r[N];
 #pragma unroll
           for (int i = 0; i < N; ++i) term[k][i] = 0.f;
           if constexpr (S::RPE) {
-            expand<T>(load_raw(rpe + ck, true), r);
+            expand<T>(rraw[k], r);
 #pragma unroll
             for (int i = 0; i < N; ++i) term[k][i] = r[i];
           }
           if constexpr (S::AM != 0) {
-            expand<T>(load_raw(am + ck, true), r);
+            expand<T>(mraw[k], r);
 #pragma unroll
             for (int i = 0; i < N; ++i) term[k][i] = S::AM == 2 ? (r[i] == 0.f ? kNegInf : term[k][i]) : term[k][i] + r[i];
           }
@@ -525,19 +573,13 @@ softmax_fwd_zloop(FwdArgs a, int Z, int lpr_log2, int header_ints) {
       }
     }
   }
-  const T* kpm = reinterpret_cast<const T*>(a.kpm) + c;
-  uint4 kcur[S::KPM != 0 ? NV : 1];
-  if constexpr (S::KPM != 0) {
-#pragma unroll
-    for (int k = 0; k < NV; ++k)
-      if (k < size) kcur[k] = load_raw(kpm + col[k], true);
-  }
+  // x of the next two batch entries is in flight while this one is reduced
   for (int z = 0; z < Z; ++z) {
-    uint4 nxt[NV];
-    if (z + 1 < Z) {
+    uint4 nx2[NV];
+    if (z + 2 < Z) {
 #pragma unroll
       for (int k = 0; k < NV; ++k)
-        if (k < size) nxt[k] = __ldcs(reinterpret_cast<const uint4*>(xp + a.x_sz + ((int64_t)k << (2 * bl))));
+        if (k < size) nx2[k] = __ldcs(reinterpret_cast<const uint4*>(xp + 2 * a.x_sz + ((int64_t)k << (2 * bl))));
     }
     float f[NV][N];
     float m = kNegInf;
@@ -545,7 +587,12 @@ softmax_fwd_zloop(FwdArgs a, int Z, int lpr_log2, int header_ints) {
     for (int k = 0; k < NV; ++k) {
       if (k < size) {
         expand<T>(cur[k], f[k]);
-        if constexpr (TERM) {
+        if constexpr (PACKED) {
+          float r[N];
+          expand<T>(pterm[k], r);
+#pragma unroll
+          for (int i = 0; i < N; ++i) f[k][i] = fmaf(f[k][i], a.scale, r[i]);
+        } else if constexpr (TERM) {
 #pragma unroll
           for (int i = 0; i < N; ++i) f[k][i] = fmaf(f[k][i], a.scale, term[k][i]);
         } else {
@@ -594,7 +641,7 @@ softmax_fwd_zloop(FwdArgs a, int Z, int lpr_log2, int header_ints) {
     }
     xp += a.x_sz;
 #pragma unroll
-    for (int k = 0; k < NV; ++k) cur[k] = nxt[k];
+    for (int k = 0; k < NV; ++k) { cur[k] = nxt[k]; nxt[k] = nx2[k]; }
   }
 }
 
