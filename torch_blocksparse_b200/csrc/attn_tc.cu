@@ -98,6 +98,10 @@ template <int D, int MODE> struct Cfg {
   // free as soon as the compute threads have read it and the scores of the next chunk are
   // computed during the exponentials of this one.
   static constexpr bool ER = MODE == DQ && D == 64;
+  // dK/dV at head_dim 64 has no spare columns.  There the packed P^T and dS^T both go over
+  // dP^T's columns (a thread's 32 columns of dP^T hold its 16 + 16 packed columns), so S^T's
+  // columns are released after the read and only dP^T waits for the accumulation.
+  static constexpr bool ER2 = MODE == DKV && D == 64;
   static constexpr int PK_BASE = NBUF * SCORE_COLS;
   static constexpr int ACC_BASE = PK_BASE + (ER ? 64 : 0);
   // forward: one O accumulator per half of the key chunk (the two threads of a row keep
@@ -183,6 +187,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
     mbar_init(&bar_rt, NC);
     mbar_init(&bar_rd, NC);
     if (C::ER) mbar_init(&bar_p[1], NC);
+    if (C::ER2) mbar_init(&bar_s[2], 1);
     for (int s = 0; s < ST; ++s) mbar_init(&bar_full[s], 1);
     for (int b = 0; b < 4; ++b) mbar_init(&bar_acc[b], 1);
     for (int b = 0; b < NBUF; ++b) { mbar_init(&bar_s[b], 1); mbar_init(&bar_p[b], NC); }
@@ -228,30 +233,35 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
           if (MODE != FWD) sb1[ks] = desc_from_lo(sp_lo + C::CH_BYTES / 16 + (ks / 4) * 512 + (ks % 4) * 2);
         }
       };
-      auto scores = [&](int t) {
+      // part: 1 = first product (S), 2 = second (dP), 3 = both, one commit each call
+      auto scores = [&](int t, int part, uint64_t* bar) {
         const uint32_t ts = tmem + (t % NBUF) * C::SCORE_COLS;
         if (C::RES_T) {
           const uint32_t tq = tmem + C::RES_BASE;
-          mma_ts(ts, tq, sb0[0], idesc_kk, 0u);
+          if (part & 1) {
+            mma_ts(ts, tq, sb0[0], idesc_kk, 0u);
 #pragma unroll
-          for (int ks = 1; ks < KS; ++ks) mma_ts_acc(ts, tq + ks * 8, sb0[ks], idesc_kk);
-          if (MODE != FWD) {
+            for (int ks = 1; ks < KS; ++ks) mma_ts_acc(ts, tq + ks * 8, sb0[ks], idesc_kk);
+          }
+          if (MODE != FWD && (part & 2)) {
             mma_ts(ts + 64, tq + D / 2, sb1[0], idesc_kk, 0u);
 #pragma unroll
             for (int ks = 1; ks < KS; ++ks) mma_ts_acc(ts + 64, tq + D / 2 + ks * 8, sb1[ks], idesc_kk);
           }
         } else {
-          mma_ss(ts, a0[0], sb0[0], idesc_kk, 0u);
+          if (part & 1) {
+            mma_ss(ts, a0[0], sb0[0], idesc_kk, 0u);
 #pragma unroll
-          for (int ks = 1; ks < KS; ++ks) mma_ss_acc(ts, a0[ks], sb0[ks], idesc_kk);
-          if (MODE != FWD) {
+            for (int ks = 1; ks < KS; ++ks) mma_ss_acc(ts, a0[ks], sb0[ks], idesc_kk);
+          }
+          if (MODE != FWD && (part & 2)) {
             mma_ss(ts + 64, a1[0], sb1[0], idesc_kk, 0u);
 #pragma unroll
             for (int ks = 1; ks < KS; ++ks) mma_ss_acc(ts + 64, a1[ks], sb1[ks], idesc_kk);
           }
         }
         TC_TRACE(1, t, 5);
-        commit(&bar_s[t % NBUF]);
+        commit(bar);
       };
       uint64_t vb0[ATOMS * 4], vb1[ATOMS * 4];              // chunk operands of the accumulation being prepared
       auto prep_acc = [&](int t) {
@@ -283,12 +293,14 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
               if (ks > 0) mma_ts_acc(ta + at * 64, da, vb0[at * 4 + ks], idesc_mn);
               else mma_ts(ta + at * 64, da, vb0[at * 4 + ks], idesc_mn, later);
             } else {                    // dV += P^T . dO,  dK += dS^T . Q
+              const uint32_t pp = C::ER2 ? ts + 64 + (ks >> 1) * 32 + (ks & 1) * 16 : pa;
+              const uint32_t pd = C::ER2 ? pp + 8 : pa + 64;
               if (ks > 0) {
-                mma_ts_acc(ta + at * 64, pa, vb1[at * 4 + ks], idesc_mn);
-                mma_ts_acc(ta + D + at * 64, pa + 64, vb0[at * 4 + ks], idesc_mn);
+                mma_ts_acc(ta + at * 64, pp, vb1[at * 4 + ks], idesc_mn);
+                mma_ts_acc(ta + D + at * 64, pd, vb0[at * 4 + ks], idesc_mn);
               } else {
-                mma_ts(ta + at * 64, pa, vb1[at * 4 + ks], idesc_mn, later);
-                mma_ts(ta + D + at * 64, pa + 64, vb0[at * 4 + ks], idesc_mn, later);
+                mma_ts(ta + at * 64, pp, vb1[at * 4 + ks], idesc_mn, later);
+                mma_ts(ta + D + at * 64, pd, vb0[at * 4 + ks], idesc_mn, later);
               }
             }
           }
@@ -331,7 +343,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
           TC_TRACE(0, t, 5);
           ok = mbar_wait(&bar_full[t % ST], (t / ST) & 1, fl);
           TC_TRACE(1, t, 0);
-          if (C::ER) {
+          if (C::ER || C::ER2) {
             if (ok && t >= 1) ok = mbar_wait(&bar_rd, (t - 1) & 1, fl);     // scores of chunk t - 1 are in registers
           } else {
             if (ok && t >= NBUF) ok = mbar_wait(&bar_acc[(t - NBUF) & 3], ((t - NBUF) >> 2) & 1, fl);
@@ -339,7 +351,17 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
           TC_TRACE(1, t, 1);
           if (!ok) break;
           fence_after();
-          scores(t);
+          if (C::ER2) {
+            scores(t, 1, &bar_s[0]);
+            if (t >= 1) {                                   // dP^T's columns still hold the operands of chunk t - 1
+              ok = mbar_wait(&bar_acc[(t - 1) & 3], ((t - 1) >> 2) & 1, fl);
+              if (!ok) break;
+              fence_after();
+            }
+            scores(t, 2, &bar_s[2]);
+          } else {
+            scores(t, 3, &bar_s[t % NBUF]);
+          }
           TC_TRACE(1, t, 2);
           if (crow_n >= 0) load_chunk(tn, crow_n);
         }
@@ -542,6 +564,64 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
           tmem_st_wait();
           fence_before();
           warp_arrive(&bar_p[t & 1], lane);
+          TC_TRACE(2, t, 4);
+          continue;
+        }
+        if constexpr (C::ER2) {
+          // Two passes of 16 columns.  Pass hv leaves its packed P^T in columns [16 hv, 16 hv + 8)
+          // and its packed dS^T in the next 8 columns of this thread's 32 columns of dP^T, all
+          // read before.  S^T is handed back after its last read; the exponentials of pass 0
+          // run while dP^T is still being computed.
+#pragma unroll
+          for (int hv = 0; hv < 2; ++hv) {
+            uint32_t sr[16], qr[16], pr[8], dr[8];
+            float pv[16];
+            if (valid) {
+              tmem_ld16(ts + hv * 16, sr);
+              tmem_ld_wait();
+            }
+            if (hv == 1) { fence_before(); warp_arrive(&bar_rd, lane); }
+            if (valid) {
+#pragma unroll
+              for (int i = 0; i < 16; i += 4) {
+                const float4 lv = vec[hv * 4 + i / 4];          // per-query lse of this chunk
+                pv[i] = fast_exp2(fmaf(__uint_as_float(sr[i]), a.scale_log2, -lv.x));
+                pv[i + 1] = fast_exp2(fmaf(__uint_as_float(sr[i + 1]), a.scale_log2, -lv.y));
+                pv[i + 2] = fast_exp2(fmaf(__uint_as_float(sr[i + 2]), a.scale_log2, -lv.z));
+                pv[i + 3] = fast_exp2(fmaf(__uint_as_float(sr[i + 3]), a.scale_log2, -lv.w));
+                pr[i / 2] = pack16<T>(pv[i], pv[i + 1]); pr[i / 2 + 1] = pack16<T>(pv[i + 2], pv[i + 3]);
+              }
+            }
+            if (hv == 0) {
+              ok = mbar_wait_warp(&bar_s[2], t & 1, fl);
+              if (!ok) break;
+              fence_after();
+              TC_TRACE(2, t, 2);
+            }
+            if (valid) {
+              tmem_ld16(ts + 64 + hv * 16, qr);
+              tmem_ld_wait();
+#pragma unroll
+              for (int i = 0; i < 16; i += 4) {
+                const float4 ev = vec[16 + hv * 4 + i / 4];     // per-query delta of this chunk
+                const float d0 = pv[i] * fmaf(__uint_as_float(qr[i]), a.scale, -ev.x * a.scale);
+                const float d1 = pv[i + 1] * fmaf(__uint_as_float(qr[i + 1]), a.scale, -ev.y * a.scale);
+                const float d2 = pv[i + 2] * fmaf(__uint_as_float(qr[i + 2]), a.scale, -ev.z * a.scale);
+                const float d3 = pv[i + 3] * fmaf(__uint_as_float(qr[i + 3]), a.scale, -ev.w * a.scale);
+                dr[i / 2] = pack16<T>(d0, d1); dr[i / 2 + 1] = pack16<T>(d2, d3);
+              }
+            } else {
+#pragma unroll
+              for (int i = 0; i < 8; ++i) { pr[i] = 0u; dr[i] = 0u; }
+            }
+            tmem_st8(ts + 64 + hv * 16, pr);
+            tmem_st8(ts + 64 + hv * 16 + 8, dr);
+            if (hv == 0) TC_TRACE(2, t, 3);
+          }
+          if (!ok) break;
+          tmem_st_wait();
+          fence_before();
+          warp_arrive(&bar_p[0], lane);
           TC_TRACE(2, t, 4);
           continue;
         }
