@@ -76,6 +76,11 @@ template <> BSP_DEVI uint32_t pack16<__nv_bfloat16>(float a, float b) {
   __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
   return *reinterpret_cast<uint32_t*>(&h);
 }
+template <typename T> BSP_DEVI float2 unpack16(uint32_t v);
+template <> BSP_DEVI float2 unpack16<__half>(uint32_t v) { return __half22float2(*reinterpret_cast<__half2*>(&v)); }
+template <> BSP_DEVI float2 unpack16<__nv_bfloat16>(uint32_t v) {
+  return make_float2(__uint_as_float(v << 16), __uint_as_float(v & 0xffff0000u));
+}
 template <typename T> struct IsBf16 { static constexpr int v = 0; };
 template <> struct IsBf16<__nv_bfloat16> { static constexpr int v = 1; };
 
@@ -568,57 +573,64 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
           continue;
         }
         if constexpr (C::ER2) {
-          // Two passes of 16 columns.  Pass hv leaves its packed P^T in columns [16 hv, 16 hv + 8)
-          // and its packed dS^T in the next 8 columns of this thread's 32 columns of dP^T, all
-          // read before.  S^T is handed back after its last read; the exponentials of pass 0
-          // run while dP^T is still being computed.
+          // First all of S^T: read, handed back, exponentials, P^T packed to 16 bits; this runs
+          // while dP^T is still being computed.  Then dP^T in two passes of 16 columns; pass
+          // hv leaves its part of the packed P^T in columns [16 hv, 16 hv + 8) and its packed
+          // dS^T in the next 8 columns of this thread's 32 columns of dP^T, all read before.
+          // dS is formed with P as the accumulating product sees it (rounded to 16 bits),
+          // which is also how a stored softmax output would enter the product.
+          uint32_t pr[16];
+          if (valid) {
+            uint32_t sr[32];
+            tmem_ld32(ts, sr);
+            tmem_ld_wait();
+            fence_before();
+            warp_arrive(&bar_rd, lane);
+#pragma unroll
+            for (int i = 0; i < 32; i += 4) {
+              const float4 lv = vec[i / 4];                     // per-query lse of this chunk
+              pr[i / 2] = pack16<T>(fast_exp2(fmaf(__uint_as_float(sr[i]), a.scale_log2, -lv.x)),
+                                    fast_exp2(fmaf(__uint_as_float(sr[i + 1]), a.scale_log2, -lv.y)));
+              pr[i / 2 + 1] = pack16<T>(fast_exp2(fmaf(__uint_as_float(sr[i + 2]), a.scale_log2, -lv.z)),
+                                        fast_exp2(fmaf(__uint_as_float(sr[i + 3]), a.scale_log2, -lv.w)));
+            }
+          } else {
+            fence_before();
+            warp_arrive(&bar_rd, lane);
+#pragma unroll
+            for (int i = 0; i < 16; ++i) pr[i] = 0u;
+          }
+          ok = mbar_wait_warp(&bar_s[2], t & 1, fl);
+          if (!ok) break;
+          fence_after();
+          TC_TRACE(2, t, 2);
 #pragma unroll
           for (int hv = 0; hv < 2; ++hv) {
-            uint32_t sr[16], qr[16], pr[8], dr[8];
-            float pv[16];
-            if (valid) {
-              tmem_ld16(ts + hv * 16, sr);
-              tmem_ld_wait();
-            }
-            if (hv == 1) { fence_before(); warp_arrive(&bar_rd, lane); }
-            if (valid) {
-#pragma unroll
-              for (int i = 0; i < 16; i += 4) {
-                const float4 lv = vec[hv * 4 + i / 4];          // per-query lse of this chunk
-                pv[i] = fast_exp2(fmaf(__uint_as_float(sr[i]), a.scale_log2, -lv.x));
-                pv[i + 1] = fast_exp2(fmaf(__uint_as_float(sr[i + 1]), a.scale_log2, -lv.y));
-                pv[i + 2] = fast_exp2(fmaf(__uint_as_float(sr[i + 2]), a.scale_log2, -lv.z));
-                pv[i + 3] = fast_exp2(fmaf(__uint_as_float(sr[i + 3]), a.scale_log2, -lv.w));
-                pr[i / 2] = pack16<T>(pv[i], pv[i + 1]); pr[i / 2 + 1] = pack16<T>(pv[i + 2], pv[i + 3]);
-              }
-            }
-            if (hv == 0) {
-              ok = mbar_wait_warp(&bar_s[2], t & 1, fl);
-              if (!ok) break;
-              fence_after();
-              TC_TRACE(2, t, 2);
-            }
+            uint32_t qr[16], dr[8];
             if (valid) {
               tmem_ld16(ts + 64 + hv * 16, qr);
               tmem_ld_wait();
 #pragma unroll
               for (int i = 0; i < 16; i += 4) {
                 const float4 ev = vec[16 + hv * 4 + i / 4];     // per-query delta of this chunk
-                const float d0 = pv[i] * fmaf(__uint_as_float(qr[i]), a.scale, -ev.x * a.scale);
-                const float d1 = pv[i + 1] * fmaf(__uint_as_float(qr[i + 1]), a.scale, -ev.y * a.scale);
-                const float d2 = pv[i + 2] * fmaf(__uint_as_float(qr[i + 2]), a.scale, -ev.z * a.scale);
-                const float d3 = pv[i + 3] * fmaf(__uint_as_float(qr[i + 3]), a.scale, -ev.w * a.scale);
+                const float2 p01 = unpack16<T>(pr[hv * 8 + i / 2]), p23 = unpack16<T>(pr[hv * 8 + i / 2 + 1]);
+                const float d0 = p01.x * fmaf(__uint_as_float(qr[i]), a.scale, -ev.x * a.scale);
+                const float d1 = p01.y * fmaf(__uint_as_float(qr[i + 1]), a.scale, -ev.y * a.scale);
+                const float d2 = p23.x * fmaf(__uint_as_float(qr[i + 2]), a.scale, -ev.z * a.scale);
+                const float d3 = p23.y * fmaf(__uint_as_float(qr[i + 3]), a.scale, -ev.w * a.scale);
                 dr[i / 2] = pack16<T>(d0, d1); dr[i / 2 + 1] = pack16<T>(d2, d3);
               }
             } else {
 #pragma unroll
-              for (int i = 0; i < 8; ++i) { pr[i] = 0u; dr[i] = 0u; }
+              for (int i = 0; i < 8; ++i) dr[i] = 0u;
             }
-            tmem_st8(ts + 64 + hv * 16, pr);
+            uint32_t ph[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) ph[i] = pr[hv * 8 + i];
+            tmem_st8(ts + 64 + hv * 16, ph);
             tmem_st8(ts + 64 + hv * 16 + 8, dr);
             if (hv == 0) TC_TRACE(2, t, 3);
           }
-          if (!ok) break;
           tmem_st_wait();
           fence_before();
           warp_arrive(&bar_p[0], lane);
