@@ -206,3 +206,26 @@ def test_multihead_attention_matches_torch_dense():
     ref_w = model[0].in_proj_weight.detach().clone()
     replace_mha(model, (layout, block))
     assert isinstance(model[0], MultiheadAttention) and torch.equal(model[0].in_proj_weight, ref_w)
+
+
+def test_host_pipeline_matches_device_path():
+    """HostAttention (pinned host operands streamed by batch slices over three streams) gives
+    bit for bit what the module gives on device tensors, on two runs in a row (the second one
+    reuses the slice buffers while the first is still draining)."""
+    from torch_blocksparse_b200 import HostAttention
+    c = workloads.config4('unidirectional', small=True, Z=5)
+    Z, H, L, D = c['q'].shape
+    mod = SparseSelfAttention(layout=c['layout'], block=c['block'], fused=True)
+    q, k, v = (c[n].cuda().requires_grad_() for n in ('q', 'k', 'v'))
+    o = mod(q, k, v)
+    o.backward(c['do'].cuda())
+    want = [o.detach().cpu(), q.grad.cpu(), k.grad.cpu(), v.grad.cpu()]
+    pipe = HostAttention(mod, H, L, D, torch.float16, 'cuda', slice_batch=2, depth=2)
+    host = [c[n].pin_memory() for n in ('q', 'k', 'v', 'do')]
+    for attempt in range(2):
+        outs = [torch.zeros_like(host[0]).pin_memory() for _ in range(4)]
+        pipe.run(*host, *outs).synchronize()
+        for name, got, ref in zip(('o', 'dq', 'dk', 'dv'), outs, want):
+            assert torch.equal(got, ref), '%s differs on run %d' % (name, attempt)
+    with pytest.raises(ValueError):
+        pipe.run(*[t.clone() for t in host], *outs)          # unpinned operands

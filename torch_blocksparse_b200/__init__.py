@@ -8,7 +8,8 @@ from .softmax import Softmax
 from .matmul import MatMul
 from .attention import DeepSpeedSparseSelfAttention, SparseSelfAttention, SparsityConfig
 from .mha import MultiheadAttention, replace_mha, make_layout
+from .host import HostAttention
 from . import layouts
 
 __all__ = ['Softmax', 'MatMul', 'DeepSpeedSparseSelfAttention', 'SparseSelfAttention',
-           'SparsityConfig', 'MultiheadAttention', 'replace_mha', 'make_layout', 'layouts']
+           'SparsityConfig', 'MultiheadAttention', 'replace_mha', 'make_layout', 'HostAttention', 'layouts']
