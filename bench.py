@@ -258,6 +258,8 @@ def run_ours(args):
             print(json.dumps({'softmax': softmax_bench(dev, pk, iters=max(1, args.steps))}))
         return
 
+    from torch_blocksparse_b200.host import bind_near_gpu
+    numa_node = bind_near_gpu(dev)          # before any pinned allocation: host buffers local to the GPU
     c = workloads.config4(args.attention, Z=args.z, seed=rank)
     layout, block, D = c['layout'], c['block'], c['q'].size(-1)
     Z = c['q'].size(0)
@@ -361,7 +363,7 @@ def run_ours(args):
     tensor_bytes = host['q'].numel() * host['q'].element_size()
     e2e = {'value': flops_step * world * e2e_steps / float(e2e_t) / 1e12, 'unit': UNIT,
            'h2d_bytes_per_step': 4 * tensor_bytes, 'd2h_bytes_per_step': 4 * tensor_bytes,
-           'ms_per_step': float(e2e_t) / e2e_steps * 1e3, 'steps': e2e_steps}
+           'ms_per_step': float(e2e_t) / e2e_steps * 1e3, 'steps': e2e_steps, 'numa_node': numa_node}
 
     # verification off the clock: all-gather a digest of every rank's outputs, and
     # have rank 0 recompute the last rank's shard and compare bit for bit

@@ -23,6 +23,34 @@ from . import _lib
 from .matmul import _dtype_code
 
 
+def bind_near_gpu(device):
+    """Restricts the calling process to the CPU cores of the NUMA node the GPU hangs off, so
+    that pinned buffers allocated afterwards (first touch) are local to the GPU's PCIe root.
+    With one process per GPU this keeps the host side of several concurrent pipelines off the
+    inter-socket link.  Returns the node, or None when the topology cannot be read (then
+    nothing is changed).  Linux only."""
+    import os
+    try:
+        p = torch.cuda.get_device_properties(device)
+        bdf = '%04x:%02x:%02x.0' % (p.pci_domain_id, p.pci_bus_id, p.pci_device_id)
+        with open('/sys/bus/pci/devices/%s/numa_node' % bdf) as f:
+            node = int(f.read())
+        if node < 0:
+            return None
+        with open('/sys/devices/system/node/node%d/cpulist' % node) as f:
+            cpus = set()
+            for part in f.read().strip().split(','):
+                lo, _, hi = part.partition('-')
+                cpus.update(range(int(lo), int(hi or lo) + 1))
+        allowed = cpus & os.sched_getaffinity(0)
+        if not allowed:
+            return None
+        os.sched_setaffinity(0, allowed)
+        return node
+    except (OSError, ValueError, AttributeError):
+        return None
+
+
 class HostAttention:
 
     def __init__(self, module, heads, length, head_dim, dtype=torch.float16, device='cuda',
