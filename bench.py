@@ -182,6 +182,49 @@ def config_dict(args, world):
             'l2': 'inputs (4 x 134 MB per GPU) exceed the 126 MB L2; no explicit flush'}
 
 
+def matmul_bench(dev, pk, iters=10, z=8):
+    """Block-sparse MatMul (configuration 2: dsd / dds, FP16, block 32, Z=8, H=8, 2048^3, layout
+    Bernoulli(0.25)), forward and forward + backward, TFLOP/s on nonzero-block FLOPs."""
+    from torch_blocksparse_b200 import MatMul
+    out = {'workload': 'config2: dsd / dds FP16, block 32, Z=%d, H=8, M=N=K=2048, Bernoulli(0.25) layout' % z, 'cases': []}
+    peak_tf = pk.get('bf16_tflops_sustained', pk['bf16_tflops'])
+
+    def timed(fn):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(iters):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / iters * 1e-3
+
+    for mode in ('dsd', 'dds'):
+        for ta in (False, True):
+            for tb in (False, True):
+                c = workloads.config2(mode, ta, tb)
+                op = MatMul(c['layout'], c['block'], mode, trans_a=ta, trans_b=tb)
+                a = c['a'][:z].to(dev).requires_grad_()
+                b = c['b'][:z].to(dev).requires_grad_()
+                dc = c['dc'][:z].to(dev)
+                flops = 2 * z * int(c['layout'].sum()) * c['block'] ** 2 * 2048
+
+                def fwd_bwd():
+                    a.grad = b.grad = None
+                    op(a, b).backward(dc)
+
+                tf, tfb = timed(lambda: op(a, b)), timed(fwd_bwd)
+                out['cases'].append({'mode': mode, 'trans_a': ta, 'trans_b': tb, 'fwd_ms': tf * 1e3,
+                                     'fwd_tflops': flops / tf / 1e12, 'fwd_bwd_ms': tfb * 1e3,
+                                     'fwd_bwd_tflops': 3 * flops / tfb / 1e12,
+                                     'fwd_frac_of_measured_peak': flops / tf / 1e12 / peak_tf})
+                del a, b, dc, c
+                torch.cuda.empty_cache()
+    return out
+
+
 def softmax_bench(dev, pk, iters=20):
     """Sparse softmax (configuration 3) forward / backward bandwidth."""
     from torch_blocksparse_b200 import Softmax
@@ -253,6 +296,10 @@ def run_ours(args):
         os.environ.setdefault('MASTER_ADDR', '127.0.0.1')
         dist.init_process_group('nccl', device_id=dev)
     pk = peaks()
+    if args.only_matmul:
+        if rank == 0:
+            print(json.dumps({'matmul': matmul_bench(dev, pk, iters=max(1, args.steps), z=args.z)}))
+        return
     if args.only_softmax:
         if rank == 0:
             print(json.dumps({'softmax': softmax_bench(dev, pk, iters=max(1, args.steps))}))
@@ -422,6 +469,7 @@ def main():
     ap.add_argument('--ref-slices', type=int, default=2, help='(batch, head) slices per step of --impl reference')
     ap.add_argument('--no-softmax', action='store_true')
     ap.add_argument('--only-softmax', action='store_true', help='run only the softmax section (profiling aid)')
+    ap.add_argument('--only-matmul', action='store_true', help='run only the MatMul section (configuration 2)')
     ap.add_argument('--z', type=int, default=8, help='batch entries per GPU; anything but 8 is a reduced, '
                     'non-headline workload (profiling aid) and is flagged in the output')
     ap.add_argument('--no-cpu-baseline', action='store_true')

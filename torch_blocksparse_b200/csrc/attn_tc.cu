@@ -121,8 +121,6 @@ template <int D, int MODE> struct Cfg {
   static constexpr int RES_COLS = RES_T ? NRES * (D / 2) : 0;
   static constexpr int TMEM = RES_BASE + RES_COLS <= 256 ? 256 : 512;
   static constexpr int CTAS = D == 64 ? 2 : 1;
-  // which issuing thread refills the ring of chunk operands: the one with less to issue
-  static constexpr bool ACC_LOADS = MODE != FWD;
 };
 
 // Writes accumulator columns [c0, c0 + n) of this thread's tensor-memory lane to dst[c0 .. c0 + n) as 16-bit values.
@@ -313,8 +311,8 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
       };
       // Two issuing threads, one per kind of product, each in its own warp: the scores of chunk
       // t only wait for their operands and for the score buffer, the accumulation of chunk t
-      // only for the compute warps; neither queues behind the other's barrier.  One of them
-      // (Cfg::ACC_LOADS) also refills the ring of chunk operands.
+      // only for the compute warps; neither queues behind the other's barrier.  The accumulate
+      // issuer, which has less to issue, also refills the ring of chunk operands.
       auto load_chunk = [&](int t, int crow) {
         const int stage = t % ST;
         unsigned char* sp = stg + stage * C::STAGE;
@@ -342,8 +340,6 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
         for (int t = 0; t < ST && t < ntiles; ++t) load_chunk(t, a.chunk[first + t] * 64);
         bool ok = mbar_wait(C::RES_T ? &bar_rt : &bar_res, 0, fl);
         for (int t = 0; ok && t < ntiles; ++t) {
-          const int tn = t - NBUF + ST;     // chunk for the stage that the buffer wait below also frees
-          const int crow_n = (!C::ACC_LOADS && t >= NBUF && tn < ntiles) ? a.chunk[first + tn] * 64 : -1;
           prep_scores(t);
           TC_TRACE(0, t, 5);
           ok = mbar_wait(&bar_full[t % ST], (t / ST) & 1, fl);
@@ -368,7 +364,6 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
             scores(t, 3, &bar_s[t % NBUF]);
           }
           TC_TRACE(1, t, 2);
-          if (crow_n >= 0) load_chunk(tn, crow_n);
         }
       } else {
         bool ok = true;
@@ -376,7 +371,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
           // first the stage of chunk t - 1 is refilled: its accumulation, issued one iteration
           // ago, completes while the compute warps are still busy with chunk t
           const int tn = t - 1 + ST;
-          if (C::ACC_LOADS && t >= 1 && tn < ntiles) {
+          if (t >= 1 && tn < ntiles) {
             const int crow_n = a.chunk[first + tn] * 64;
             ok = mbar_wait(&bar_acc[(t - 1) & 3], ((t - 1) >> 2) & 1, fl);
             if (!ok) break;
