@@ -77,6 +77,41 @@ def test_masks_and_rpe(kp_mode, am_mode, fused):
     check(layout, block, q, k, v, do, fused, kp_mode, am_mode, rpe=rpe, key_padding_mask=kp, attn_mask=am)
 
 
+@pytest.mark.parametrize('kp_mode', ['add', 'mul'])
+@pytest.mark.parametrize('block,D', [(64, 64), (128, 64), (64, 128), (128, 128)])
+@pytest.mark.parametrize('dtype', [torch.float16, torch.bfloat16])
+def test_key_padding_mask_on_tcgen05_path(block, D, dtype, kp_mode):
+    """A key-padding mask alone (the BERT-style call of the reference's wrapper) stays on the
+    tcgen05 kernels at block 64 / 128.  Checked against the dense-masked definition and against
+    the mma.sync kernels; the first column block is kept and never masked, so that no row is
+    masked out entirely (the reference's softmax gives NaN there)."""
+    from torch_blocksparse_b200 import fused as F
+    Z, H, nb = 3, 2, 6
+    L = nb * block
+    g = torch.Generator().manual_seed(block * 3 + D)
+    layout = (torch.rand((H, nb, nb), generator=g) > 0.5).long()
+    layout[:, :, 0] = 1
+    layout[0, 2, 1:] = 0
+    q, k, v, do = rand_qkv(Z, H, L, D, dtype, seed=block + 1)
+    keep = torch.rand((Z, L), generator=g) > 0.3
+    keep[:, :block] = True
+    keep[1, L // 2:] = False                      # a padded tail, as with variable-length batches
+    if kp_mode == 'mul':
+        kp = keep.to(dtype)
+    else:
+        kp = torch.where(keep, 0.25 * torch.randn((Z, L), generator=g), torch.tensor(float('-inf'))).to(dtype)
+    check(layout, block, q, k, v, do, True, kp_mode, 'mul', key_padding_mask=kp)
+    mod = SparseSelfAttention(layout=layout, block=block, fused=True, key_padding_mask_mode=kp_mode)
+    try:
+        tc = run_module(mod, q, k, v, do, key_padding_mask=kp)
+        F.PATH = 'mma'
+        mma = run_module(mod, q, k, v, do, key_padding_mask=kp)
+    finally:
+        F.PATH = 'tc'
+    for name, a, b in zip(('o', 'dq', 'dk', 'dv'), tc, mma):
+        assert_close(a.cpu(), b.cpu(), name + ' tcgen05 vs mma.sync')
+
+
 def test_sparsity_config_path_and_key_transposed():
     """The reference's constructor path: SparsityConfig 'fixed', key handed over
     pre-transposed as [.., head_dim, L] (deepspeedsparseselfattention.py:119-123)."""

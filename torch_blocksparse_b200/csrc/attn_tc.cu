@@ -65,6 +65,7 @@ struct TcArgs {
   int H, L, tiles_per_head;
   float scale, scale_log2;
   const int32_t *c01, *ptr, *chunk, *mask, *order;
+  const void* kpm; int64_t kpm_sz; int kpm_mul;   // key-padding mask [Z, L] (KPM variants), 'mul' mode flag
 };
 
 template <typename T> BSP_DEVI uint32_t pack16(float a, float b);
@@ -81,17 +82,35 @@ template <> BSP_DEVI float2 unpack16<__half>(uint32_t v) { return __half22float2
 template <> BSP_DEVI float2 unpack16<__nv_bfloat16>(uint32_t v) {
   return make_float2(__uint_as_float(v << 16), __uint_as_float(v & 0xffff0000u));
 }
+// Key-padding mask values -> additive terms in the base-2 domain: 'add' mode adds the value,
+// 'mul' mode turns a zero into -inf and anything else into 0 (softmax.py:104-110 of the reference).
+BSP_DEVI float kpm_term(float v, int mul) { return mul ? (v == 0.f ? kNegInfT : 0.f) : v * kLog2eT; }
+template <typename T>
+BSP_DEVI void kpm_terms8(const unsigned char* p, int mul, float (&b)[8]) {
+  const uint4 raw = *reinterpret_cast<const uint4*>(p);
+  const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 f = unpack16<T>(w[i]);
+    b[2 * i] = kpm_term(f.x, mul);
+    b[2 * i + 1] = kpm_term(f.y, mul);
+  }
+}
 template <typename T> struct IsBf16 { static constexpr int v = 0; };
 template <> struct IsBf16<__nv_bfloat16> { static constexpr int v = 1; };
 
-template <int D, int MODE> struct Cfg {
+template <int D, int MODE, bool KPM = false> struct Cfg {
   static constexpr int ATOMS = D / 64;                         // 64-element (128-byte) column groups
   static constexpr int NRES = MODE == FWD ? 1 : 2;             // resident 128-row operands
   static constexpr int NC = 8;                                 // compute warps: two threads per tile row
   static constexpr int NT = (NC + 2) * 32;                     // + loader / score issuer, accumulate issuer
   static constexpr int RES_BYTES = ATOMS * 128 * 128;
   static constexpr int CH_BYTES = ATOMS * 64 * 128;
-  static constexpr int STAGE = 2 * CH_BYTES + (MODE == DKV ? 1024 : 0);   // + lse / delta of the chunk
+  // A key-padding mask is a bias per key: per column of the scores in the forward and in dQ
+  // (64 values travel with every chunk), per row in dK/dV (read once per tile).
+  static constexpr bool BIAS = KPM && MODE != DKV;
+  static constexpr int STAGE = 2 * CH_BYTES + ((MODE == DKV || BIAS) ? 1024 : 0);   // + lse / delta, or the bias, of the chunk
+  static constexpr int TAIL_BYTES = MODE == DKV ? 512 : (BIAS ? 128 : 0);
   // score buffers in tensor memory: two (scores of the next chunk are computed while this
   // one is consumed) where the columns allow it with two CTAs per SM, else one
   static constexpr int NBUF = MODE == FWD ? 2 : (D == 64 ? 1 : 2);
@@ -142,11 +161,11 @@ BSP_DEVI void store_acc(T* dst, uint32_t taddr, int c0, int n, float mul) {
   }
 }
 
-template <typename T, int D, int MODE>
-__global__ void __launch_bounds__(Cfg<D, MODE>::NT, Cfg<D, MODE>::CTAS)
+template <typename T, int D, int MODE, bool KPM>
+__global__ void __launch_bounds__(Cfg<D, MODE, KPM>::NT, Cfg<D, MODE, KPM>::CTAS)
 attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant__ CUtensorMap m_res1,
                const __grid_constant__ CUtensorMap m_ch0, const __grid_constant__ CUtensorMap m_ch1, TcArgs a) {
-  using C = Cfg<D, MODE>;
+  using C = Cfg<D, MODE, KPM>;
   constexpr int ATOMS = C::ATOMS, ST = C::NSTAGE, NC = C::NC, NBUF = C::NBUF;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = smem_raw + ((1024 - (saddr(smem_raw) & 1023)) & 1023);
@@ -317,7 +336,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
         const int stage = t % ST;
         unsigned char* sp = stg + stage * C::STAGE;
         TC_TRACE(0, t, 0);
-        mbar_expect_tx(&bar_full[stage], 2 * C::CH_BYTES + (MODE == DKV ? 512 : 0));
+        mbar_expect_tx(&bar_full[stage], 2 * C::CH_BYTES + C::TAIL_BYTES);
         for (int at = 0; at < ATOMS; ++at) {
           tma_load_4d(sp + at * 8192, &m_ch0, &bar_full[stage], at * 64, crow, h, z);
           tma_load_4d(sp + C::CH_BYTES + at * 8192, &m_ch1, &bar_full[stage], at * 64, crow, h, z);
@@ -326,6 +345,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
           bulk_load(sp + 2 * C::CH_BYTES, a.lse + zh + crow, 256, &bar_full[stage]);
           bulk_load(sp + 2 * C::CH_BYTES + 256, a.delta + zh + crow, 256, &bar_full[stage]);
         }
+        if (C::BIAS) bulk_load(sp + 2 * C::CH_BYTES, reinterpret_cast<const T*>(a.kpm) + z * a.kpm_sz + crow, 128, &bar_full[stage]);
       };
       if (warp == NC) {
         prefetch_map(&m_res0); prefetch_map(&m_ch0); prefetch_map(&m_ch1);
@@ -437,10 +457,20 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
         TC_TRACE(2, t, 2);
         float mt = kNegInfT;
         if (valid) {
+          if constexpr (KPM) {                               // scores become s * scale + bias (base 2) in place
+            const unsigned char* bp = stg + (t % ST) * C::STAGE + 2 * C::CH_BYTES + chalf * 64;
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              float b[8];
+              kpm_terms8<T>(bp + g * 16, a.kpm_mul, b);
+#pragma unroll
+              for (int i = 0; i < 8; ++i) sr[8 * g + i] = __float_as_uint(fmaf(__uint_as_float(sr[8 * g + i]), a.scale_log2, b[i]));
+            }
+          }
           float m4[4] = {kNegInfT, kNegInfT, kNegInfT, kNegInfT};
 #pragma unroll
           for (int i = 0; i < 32; ++i) m4[i & 3] = fmaxf(m4[i & 3], __uint_as_float(sr[i]));
-          mt = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])) * a.scale_log2;
+          mt = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])) * (KPM ? 1.f : a.scale_log2);
         }
         // the reference maximum is only raised when the row maximum outgrows it by 2^8
         const bool grow_m = mt > m_ref + 8.f;
@@ -452,35 +482,44 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
             ok = mbar_wait_warp(&bar_acc[(t - 1) & 3], ((t - 1) >> 2) & 1, fl);
             if (!ok) break;
             fence_after();
-            for (int c = 0; c < D; c += 32) {
-              uint32_t orr[32];
-              tmem_ld32(t_acc + c, orr);
+            for (int c = 0; c < D; c += 16) {               // (16 at a time: the scores stay in registers)
+              uint32_t orr[16];
+              tmem_ld16(t_acc + c, orr);
               tmem_ld_wait();
 #pragma unroll
-              for (int i = 0; i < 32; ++i) orr[i] = __float_as_uint(__uint_as_float(orr[i]) * alpha);
-              tmem_st32(t_acc + c, orr);
+              for (int i = 0; i < 16; ++i) orr[i] = __float_as_uint(__uint_as_float(orr[i]) * alpha);
+              tmem_st16(t_acc + c, orr);
             }
             tmem_st_wait();
           }
           m_ref = m_new;
         }
-        uint32_t pr[16];
+        // exponentials in two halves of 16 columns: eight packed registers live at a time
         if (valid) {
           float s4[4] = {0.f, 0.f, 0.f, 0.f};
+          // (with a mask a row may still have seen -inf only: its reference stays 0 then)
+          const float m_use = (KPM && m_ref == kNegInfT) ? 0.f : m_ref;
 #pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            const float p0 = fast_exp2(fmaf(__uint_as_float(sr[2 * i]), a.scale_log2, -m_ref));
-            const float p1 = fast_exp2(fmaf(__uint_as_float(sr[2 * i + 1]), a.scale_log2, -m_ref));
-            s4[i & 3] += p0 + p1;
-            pr[i] = pack16<T>(p0, p1);
+          for (int hp = 0; hp < 2; ++hp) {
+            uint32_t ph[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const float s0 = __uint_as_float(sr[16 * hp + 2 * i]), s1 = __uint_as_float(sr[16 * hp + 2 * i + 1]);
+              const float p0 = KPM ? fast_exp2(s0 - m_use) : fast_exp2(fmaf(s0, a.scale_log2, -m_ref));
+              const float p1 = KPM ? fast_exp2(s1 - m_use) : fast_exp2(fmaf(s1, a.scale_log2, -m_ref));
+              s4[i & 3] += p0 + p1;
+              ph[i] = pack16<T>(p0, p1);
+            }
+            tmem_st8(ts + hp * 8, ph);
           }
           l += (s4[0] + s4[1]) + (s4[2] + s4[3]);
         } else {
+          uint32_t pz[16];
 #pragma unroll
-          for (int i = 0; i < 16; ++i) pr[i] = 0u;
+          for (int i = 0; i < 16; ++i) pz[i] = 0u;
+          tmem_st16(ts, pz);
         }
         TC_TRACE(2, t, 3);
-        tmem_st16(ts, pr);
         tmem_st_wait();
         fence_before();
         warp_arrive(&bar_p[t % NBUF], lane);
@@ -521,7 +560,12 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
         }
       }
     } else {
-      const float my_lse = (MODE == DQ && row_ok) ? a.lse[zh + grow] : 0.f;
+      // (a fully masked query row has lse = -inf: +inf makes its probabilities 0, not NaN)
+      float my_lse = (MODE == DQ && row_ok) ? a.lse[zh + grow] : 0.f;
+      if (KPM && my_lse == kNegInfT) my_lse = -kNegInfT;
+      // dK/dV: the bias of this thread's key row
+      const float my_b = (KPM && MODE == DKV && row_ok)
+          ? kpm_term(static_cast<float>(reinterpret_cast<const T*>(a.kpm)[z * a.kpm_sz + grow]), a.kpm_mul) : 0.f;
       const float my_ds = (MODE == DQ && row_ok) ? a.delta[zh + grow] * a.scale : 0.f;
       for (int t = 0; ok && t < ntiles; ++t) {
         const uint32_t ts = tmem + (t % NBUF) * C::SCORE_COLS + lane_base + chalf * 32;
@@ -543,12 +587,25 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
           fence_before();
           warp_arrive(&bar_rd, lane);
           if (valid) {
+            const unsigned char* bp = stg + (t % ST) * C::STAGE + 2 * C::CH_BYTES + chalf * 64;
 #pragma unroll
-            for (int i = 0; i < 32; i += 2) {
-              const float p0 = fast_exp2(fmaf(__uint_as_float(sr[i]), a.scale_log2, -my_lse));
-              const float p1 = fast_exp2(fmaf(__uint_as_float(sr[i + 1]), a.scale_log2, -my_lse));
-              dr[i / 2] = pack16<T>(p0 * fmaf(__uint_as_float(qr[i]), a.scale, -my_ds),
-                                    p1 * fmaf(__uint_as_float(qr[i + 1]), a.scale, -my_ds));   // P (dP - delta) scale
+            for (int g = 0; g < 4; ++g) {
+              float b[8];
+              if constexpr (KPM) {
+                kpm_terms8<T>(bp + g * 16, a.kpm_mul, b);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) b[i] -= my_lse;
+              } else {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) b[i] = -my_lse;
+              }
+#pragma unroll
+              for (int i = 8 * g; i < 8 * g + 8; i += 2) {
+                const float p0 = fast_exp2(fmaf(__uint_as_float(sr[i]), a.scale_log2, b[i - 8 * g]));
+                const float p1 = fast_exp2(fmaf(__uint_as_float(sr[i + 1]), a.scale_log2, b[i + 1 - 8 * g]));
+                dr[i / 2] = pack16<T>(p0 * fmaf(__uint_as_float(qr[i]), a.scale, -my_ds),
+                                      p1 * fmaf(__uint_as_float(qr[i + 1]), a.scale, -my_ds));   // P (dP - delta) scale
+              }
             }
           } else {
 #pragma unroll
@@ -583,7 +640,11 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
             warp_arrive(&bar_rd, lane);
 #pragma unroll
             for (int i = 0; i < 32; i += 4) {
-              const float4 lv = vec[i / 4];                     // per-query lse of this chunk
+              float4 lv = vec[i / 4];                           // per-query lse of this chunk
+              if constexpr (KPM) {                              // own bias; a masked-out query row counts as +inf
+                lv.x = lv.x == kNegInfT ? -kNegInfT : lv.x - my_b; lv.y = lv.y == kNegInfT ? -kNegInfT : lv.y - my_b;
+                lv.z = lv.z == kNegInfT ? -kNegInfT : lv.z - my_b; lv.w = lv.w == kNegInfT ? -kNegInfT : lv.w - my_b;
+              }
               pr[i / 2] = pack16<T>(fast_exp2(fmaf(__uint_as_float(sr[i]), a.scale_log2, -lv.x)),
                                     fast_exp2(fmaf(__uint_as_float(sr[i + 1]), a.scale_log2, -lv.y)));
               pr[i / 2 + 1] = pack16<T>(fast_exp2(fmaf(__uint_as_float(sr[i + 2]), a.scale_log2, -lv.z)),
@@ -650,9 +711,19 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
                 const float4 lv = vec[hv * 4 + i / 4], ev = vec[16 + hv * 4 + i / 4];
                 ls[0] = lv.x; ls[1] = lv.y; ls[2] = lv.z; ls[3] = lv.w;
                 es[0] = ev.x * a.scale; es[1] = ev.y * a.scale; es[2] = ev.z * a.scale; es[3] = ev.w * a.scale;
+                if constexpr (KPM) {
+#pragma unroll
+                  for (int j = 0; j < 4; ++j) ls[j] = ls[j] == kNegInfT ? -kNegInfT : ls[j] - my_b;
+                }
               } else {
 #pragma unroll
                 for (int j = 0; j < 4; ++j) { ls[j] = my_lse; es[j] = my_ds; }
+                if constexpr (KPM) {                        // bias of the four keys
+                  const uint2 raw = *reinterpret_cast<const uint2*>(stg + (t % ST) * C::STAGE + 2 * C::CH_BYTES + chalf * 64 + (hv * 16 + i) * 2);
+                  const float2 b01 = unpack16<T>(raw.x), b23 = unpack16<T>(raw.y);
+                  ls[0] -= kpm_term(b01.x, a.kpm_mul); ls[1] -= kpm_term(b01.y, a.kpm_mul);
+                  ls[2] -= kpm_term(b23.x, a.kpm_mul); ls[3] -= kpm_term(b23.y, a.kpm_mul);
+                }
               }
               float pv[4], dv[4];
 #pragma unroll
@@ -749,11 +820,11 @@ int decode_tiles(const int32_t* hdr, const int32_t* dev, TilesView& v) {
   return BSP_OK;
 }
 
-template <typename T, int D, int MODE>
+template <typename T, int D, int MODE, bool KPM>
 int launch(const CUtensorMap& r0, const CUtensorMap& r1, const CUtensorMap& c0, const CUtensorMap& c1,
            const TcArgs& a, int n_tiles, int Z, cudaStream_t st, const char* what) {
-  using C = Cfg<D, MODE>;
-  auto kern = attn_tc_kernel<T, D, MODE>;
+  using C = Cfg<D, MODE, KPM>;
+  auto kern = attn_tc_kernel<T, D, MODE, KPM>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM);
   if (e != cudaSuccess) return fail(BSP_ERR_CUDA, "attention (tcgen05 %s): cannot reserve shared memory: %s", what, cudaGetErrorString(e));
   kern<<<dim3(n_tiles, Z), C::NT, C::SMEM, st>>>(r0, r1, c0, c1, a);
@@ -762,15 +833,21 @@ int launch(const CUtensorMap& r0, const CUtensorMap& r1, const CUtensorMap& c0, 
   return BSP_OK;
 }
 
+template <int MODE, bool KPM>
+int launch_kpm(int dtype, int D, const CUtensorMap& r0, const CUtensorMap& r1, const CUtensorMap& c0,
+               const CUtensorMap& c1, const TcArgs& a, int n_tiles, int Z, cudaStream_t st, const char* what) {
+  if (dtype == BSP_F16) {
+    if (D == 64) return launch<__half, 64, MODE, KPM>(r0, r1, c0, c1, a, n_tiles, Z, st, what);
+    return launch<__half, 128, MODE, KPM>(r0, r1, c0, c1, a, n_tiles, Z, st, what);
+  }
+  if (D == 64) return launch<__nv_bfloat16, 64, MODE, KPM>(r0, r1, c0, c1, a, n_tiles, Z, st, what);
+  return launch<__nv_bfloat16, 128, MODE, KPM>(r0, r1, c0, c1, a, n_tiles, Z, st, what);
+}
 template <int MODE>
 int launch_any(int dtype, int D, const CUtensorMap& r0, const CUtensorMap& r1, const CUtensorMap& c0,
                const CUtensorMap& c1, const TcArgs& a, int n_tiles, int Z, cudaStream_t st, const char* what) {
-  if (dtype == BSP_F16) {
-    if (D == 64) return launch<__half, 64, MODE>(r0, r1, c0, c1, a, n_tiles, Z, st, what);
-    return launch<__half, 128, MODE>(r0, r1, c0, c1, a, n_tiles, Z, st, what);
-  }
-  if (D == 64) return launch<__nv_bfloat16, 64, MODE>(r0, r1, c0, c1, a, n_tiles, Z, st, what);
-  return launch<__nv_bfloat16, 128, MODE>(r0, r1, c0, c1, a, n_tiles, Z, st, what);
+  if (a.kpm) return launch_kpm<MODE, true>(dtype, D, r0, r1, c0, c1, a, n_tiles, Z, st, what);
+  return launch_kpm<MODE, false>(dtype, D, r0, r1, c0, c1, a, n_tiles, Z, st, what);
 }
 
 void fill_tiles(TcArgs& a, const TilesView& tv, const TileSet& s) {
@@ -781,12 +858,14 @@ void fill_tiles(TcArgs& a, const TilesView& tv, const TileSet& s) {
 }  // namespace
 
 // Forward on the tcgen05 path.  Preconditions (checked by the caller): dtype F16 / BF16,
-// D in {64, 128}, block in {64, 128}, no rpe / masks, unit stride on D.
+// D in {64, 128}, block in {64, 128}, no rpe / attention mask, unit stride on D; kpm (optional)
+// is the key-padding mask [Z, L] in the operands' type with 16-byte aligned rows.
 int attn_fwd_tc(const void* q, const void* k, const void* v, void* o, float* lse,
                 int dtype, int Z, int H, int L, int D,
                 int64_t q_sz, int64_t q_sh, int64_t q_sr, int64_t k_sz, int64_t k_sh, int64_t k_sr,
                 int64_t v_sz, int64_t v_sh, int64_t v_sr, int64_t o_sz, int64_t o_sh, int64_t o_sr,
-                const int32_t* tiles_hdr, const int32_t* tiles, float scale, cudaStream_t st) {
+                const int32_t* tiles_hdr, const int32_t* tiles, float scale,
+                const void* kpm, int64_t kpm_sz, int kpm_mul, cudaStream_t st) {
   TilesView tv;
   if (int rc = decode_tiles(tiles_hdr, tiles, tv)) return rc;
   if (tv.H != H || tv.nb * tv.block != L) return fail(BSP_ERR_INVALID, "attention tile lists do not fit %d heads of length %d", H, L);
@@ -797,6 +876,7 @@ int attn_fwd_tc(const void* q, const void* k, const void* v, void* o, float* lse
   TcArgs a = {};
   a.out0 = o; a.lse_out = lse; a.o_sz = o_sz; a.o_sh = o_sh; a.o_sr = o_sr;
   a.H = H; a.L = L; a.scale = scale; a.scale_log2 = scale * kLog2eT;
+  a.kpm = kpm; a.kpm_sz = kpm_sz; a.kpm_mul = kpm_mul;
   fill_tiles(a, tv, tv.rt);
   return launch_any<FWD>(dtype, D, mq, mq, mk, mv, a, H * tv.tiles_per_head, Z, st, "forward");
 }
@@ -806,7 +886,8 @@ int attn_bwd_tc(const void* q, const void* k, const void* v, const void* dout, c
                 void* dq, void* dk, void* dv, int dtype, int Z, int H, int L, int D,
                 int64_t q_sz, int64_t q_sh, int64_t q_sr, int64_t k_sz, int64_t k_sh, int64_t k_sr,
                 int64_t v_sz, int64_t v_sh, int64_t v_sr, int64_t do_sz, int64_t do_sh, int64_t do_sr,
-                const int32_t* tiles_hdr, const int32_t* tiles, float scale, int parts, cudaStream_t st) {
+                const int32_t* tiles_hdr, const int32_t* tiles, float scale,
+                const void* kpm, int64_t kpm_sz, int kpm_mul, int parts, cudaStream_t st) {
   TilesView tv;
   if (int rc = decode_tiles(tiles_hdr, tiles, tv)) return rc;
   if (tv.H != H || tv.nb * tv.block != L) return fail(BSP_ERR_INVALID, "attention tile lists do not fit %d heads of length %d", H, L);
@@ -817,6 +898,7 @@ int attn_bwd_tc(const void* q, const void* k, const void* v, const void* dout, c
   if (int rc = make_map(&md, dout, dtype, Z, H, L, D, do_sz, do_sh, do_sr)) return rc;
   TcArgs a = {};
   a.lse = lse; a.delta = delta; a.H = H; a.L = L; a.scale = scale; a.scale_log2 = scale * kLog2eT;
+  a.kpm = kpm; a.kpm_sz = kpm_sz; a.kpm_mul = kpm_mul;
   const int n_tiles = H * tv.tiles_per_head;
   if (parts & 2) {
     a.out0 = dk; a.out1 = dv;
