@@ -62,7 +62,7 @@ struct TcArgs {
   float* lse_out;                     // FWD
   const float* lse; const float* delta;   // backward
   int64_t o_sz, o_sh, o_sr;           // strides of O (FWD); gradients are contiguous [Z, H, L, D]
-  int H, L, tiles_per_head;
+  int Z, H, L, tiles_per_head;
   float scale, scale_log2;
   const int32_t *c01, *ptr, *chunk, *mask, *order;
   const void* kpm; int64_t kpm_sz; int kpm_mul;   // key-padding mask [Z, L] (KPM variants), 'mul' mode flag
@@ -177,8 +177,10 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
   __shared__ int failed;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int z = blockIdx.y;
-  const int ti = a.order[blockIdx.x];
+  // One-dimensional grid, batch entries of a tile adjacent: CTAs start in the order of the
+  // tiles' lengths (longest first) over the whole launch, not per batch entry.
+  const int z = blockIdx.x % a.Z;
+  const int ti = a.order[blockIdx.x / a.Z];
   const int h = ti / a.tiles_per_head;
   const int first = a.ptr[ti], ntiles = a.ptr[ti + 1] - first;
   const int c0 = a.c01[2 * ti], c1 = a.c01[2 * ti + 1];
@@ -827,7 +829,9 @@ int launch(const CUtensorMap& r0, const CUtensorMap& r1, const CUtensorMap& c0, 
   auto kern = attn_tc_kernel<T, D, MODE, KPM>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM);
   if (e != cudaSuccess) return fail(BSP_ERR_CUDA, "attention (tcgen05 %s): cannot reserve shared memory: %s", what, cudaGetErrorString(e));
-  kern<<<dim3(n_tiles, Z), C::NT, C::SMEM, st>>>(r0, r1, c0, c1, a);
+  TcArgs b = a;
+  b.Z = Z;
+  kern<<<(unsigned)((int64_t)n_tiles * Z), C::NT, C::SMEM, st>>>(r0, r1, c0, c1, b);
   e = cudaGetLastError();
   if (e != cudaSuccess) return fail(BSP_ERR_CUDA, "attention (tcgen05 %s) launch failed: %s", what, cudaGetErrorString(e));
   return BSP_OK;
