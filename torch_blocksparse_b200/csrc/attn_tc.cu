@@ -177,6 +177,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
   __shared__ int failed;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (tid == 0) TC_TRACE(0, 60, 0);
   // One-dimensional grid, batch entries of a tile adjacent: CTAs start in the order of the
   // tiles' lengths (longest first) over the whole launch, not per batch entry.
   const int z = blockIdx.x % a.Z;
@@ -205,25 +206,58 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
     }
     return;
   }
+  // One chunk of the other operand (and what travels with it) into its stage of the ring.
+  auto load_chunk = [&](int t, int crow) {
+    const int stage = t % ST;
+    unsigned char* sp = stg + stage * C::STAGE;
+    TC_TRACE(0, t, 0);
+    mbar_expect_tx(&bar_full[stage], 2 * C::CH_BYTES + C::TAIL_BYTES);
+    for (int at = 0; at < ATOMS; ++at) {
+      tma_load_4d(sp + at * 8192, &m_ch0, &bar_full[stage], at * 64, crow, h, z);
+      tma_load_4d(sp + C::CH_BYTES + at * 8192, &m_ch1, &bar_full[stage], at * 64, crow, h, z);
+    }
+    if (MODE == DKV) {
+      bulk_load(sp + 2 * C::CH_BYTES, a.lse + zh + crow, 256, &bar_full[stage]);
+      bulk_load(sp + 2 * C::CH_BYTES + 256, a.delta + zh + crow, 256, &bar_full[stage]);
+    }
+    if (C::BIAS) bulk_load(sp + 2 * C::CH_BYTES, reinterpret_cast<const T*>(a.kpm) + z * a.kpm_sz + crow, 128, &bar_full[stage]);
+  };
+  // The thread that issues the loads sets up their barriers itself and starts the resident
+  // operands and the first chunks at once: their latency overlaps the rest of the set-up
+  // (other barriers, tensor-memory allocation, the block-wide synchronisation).
+  if (tid == NC * 32) {
+    mbar_init(&bar_res, 1);
+    for (int s = 0; s < ST; ++s) mbar_init(&bar_full[s], 1);
+    mbar_init_fence();
+    prefetch_map(&m_res0); prefetch_map(&m_ch0); prefetch_map(&m_ch1);
+    mbar_expect_tx(&bar_res, C::NRES * C::RES_BYTES);
+    for (int hf = 0; hf < 2; ++hf) {
+      const int crow = (hf == 0 || c1 < 0 ? c0 : c1) * 64;
+      for (int at = 0; at < ATOMS; ++at) {
+        tma_load_4d(res + at * 16384 + hf * 8192, &m_res0, &bar_res, at * 64, crow, h, z);
+        if (C::NRES == 2) tma_load_4d(res + C::RES_BYTES + at * 16384 + hf * 8192, &m_res1, &bar_res, at * 64, crow, h, z);
+      }
+    }
+    for (int t = 0; t < ST && t < ntiles; ++t) load_chunk(t, a.chunk[first + t] * 64);
+  }
   if (tid == 0) {
     failed = 0;
-    mbar_init(&bar_res, 1);
     mbar_init(&bar_rt, NC);
     mbar_init(&bar_rd, NC);
     if (C::ER) mbar_init(&bar_p[1], NC);
     if (C::ER2) mbar_init(&bar_s[2], 1);
-    for (int s = 0; s < ST; ++s) mbar_init(&bar_full[s], 1);
     for (int b = 0; b < 4; ++b) mbar_init(&bar_acc[b], 1);
     for (int b = 0; b < NBUF; ++b) { mbar_init(&bar_s[b], 1); mbar_init(&bar_p[b], NC); }
     mbar_init(&bar_done, 1);
     mbar_init_fence();
   }
-  if (warp == 0) { tmem_alloc(&tmem_slot, C::TMEM); tmem_relinquish(); }
+  if (warp == 1) { tmem_alloc(&tmem_slot, C::TMEM); tmem_relinquish(); }
   fence_before();
   __syncthreads();
   fence_after();
   const uint32_t tmem = tmem_slot;
   volatile int* fl = &failed;
+  if (tid == 0) TC_TRACE(0, 60, 1);
 
   if (warp >= NC) {
     // ------------------------------------------------------------------ loader and MMA issuers
@@ -334,33 +368,9 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
       // t only wait for their operands and for the score buffer, the accumulation of chunk t
       // only for the compute warps; neither queues behind the other's barrier.  The accumulate
       // issuer, which has less to issue, also refills the ring of chunk operands.
-      auto load_chunk = [&](int t, int crow) {
-        const int stage = t % ST;
-        unsigned char* sp = stg + stage * C::STAGE;
-        TC_TRACE(0, t, 0);
-        mbar_expect_tx(&bar_full[stage], 2 * C::CH_BYTES + C::TAIL_BYTES);
-        for (int at = 0; at < ATOMS; ++at) {
-          tma_load_4d(sp + at * 8192, &m_ch0, &bar_full[stage], at * 64, crow, h, z);
-          tma_load_4d(sp + C::CH_BYTES + at * 8192, &m_ch1, &bar_full[stage], at * 64, crow, h, z);
-        }
-        if (MODE == DKV) {
-          bulk_load(sp + 2 * C::CH_BYTES, a.lse + zh + crow, 256, &bar_full[stage]);
-          bulk_load(sp + 2 * C::CH_BYTES + 256, a.delta + zh + crow, 256, &bar_full[stage]);
-        }
-        if (C::BIAS) bulk_load(sp + 2 * C::CH_BYTES, reinterpret_cast<const T*>(a.kpm) + z * a.kpm_sz + crow, 128, &bar_full[stage]);
-      };
       if (warp == NC) {
-        prefetch_map(&m_res0); prefetch_map(&m_ch0); prefetch_map(&m_ch1);
-        mbar_expect_tx(&bar_res, C::NRES * C::RES_BYTES);
-        for (int hf = 0; hf < 2; ++hf) {
-          const int crow = (hf == 0 || c1 < 0 ? c0 : c1) * 64;
-          for (int at = 0; at < ATOMS; ++at) {
-            tma_load_4d(res + at * 16384 + hf * 8192, &m_res0, &bar_res, at * 64, crow, h, z);
-            if (C::NRES == 2) tma_load_4d(res + C::RES_BYTES + at * 16384 + hf * 8192, &m_res1, &bar_res, at * 64, crow, h, z);
-          }
-        }
-        for (int t = 0; t < ST && t < ntiles; ++t) load_chunk(t, a.chunk[first + t] * 64);
         bool ok = mbar_wait(C::RES_T ? &bar_rt : &bar_res, 0, fl);
+        TC_TRACE(0, 60, 2);
         for (int t = 0; ok && t < ntiles; ++t) {
           prep_scores(t);
           TC_TRACE(0, t, 5);
@@ -532,6 +542,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
       xch[chalf][1][trow] = l;
       asm volatile("bar.sync 1, 256;" ::: "memory");          // the eight compute warps, always executed
       if (ok && mbar_wait_warp(&bar_done, 0, fl)) {
+        if (tid == 0) TC_TRACE(0, 60, 3);
         fence_after();
         if (mychunk >= 0) {                                   // uniform per warp: a warp lies inside one chunk
           const float ma = xch[0][0][trow], mb = xch[1][0][trow], la = xch[0][1][trow], lb = xch[1][1][trow];
@@ -750,6 +761,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
         TC_TRACE(2, t, 4);
       }
       if (ok && mbar_wait_warp(&bar_done, 0, fl)) {
+        if (tid == 0) TC_TRACE(0, 60, 3);
         fence_after();
         if (mychunk >= 0) {                                   // uniform per warp
           // the two threads of a row split the D output columns
@@ -766,9 +778,11 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
       }
     }
   }
+  if (tid == 0) TC_TRACE(0, 60, 4);
   fence_before();
   __syncthreads();
-  if (warp == 0) tmem_dealloc(tmem, C::TMEM);
+  if (tid == 0) TC_TRACE(0, 60, 5);
+  if (warp == 1) tmem_dealloc(tmem, C::TMEM);
   if (tid == 0 && failed) atomicExch(&g_tc_status, 1 + MODE);
 }
 
