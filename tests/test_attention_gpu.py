@@ -112,6 +112,30 @@ def test_key_padding_mask_on_tcgen05_path(block, D, dtype, kp_mode):
         assert_close(a.cpu(), b.cpu(), name + ' tcgen05 vs mma.sync')
 
 
+@pytest.mark.parametrize('D', [64, 128])
+@pytest.mark.parametrize('with_kpm', [False, True])
+def test_odd_number_of_block_rows_on_tcgen05_path(D, with_kpm):
+    """Block 64 with an odd number of block-rows: one 128-row tile of every head has a single
+    64-row chunk; heads with one-block and empty rows / columns; chunk lists of one to five."""
+    block, H, nb, Z = 64, 3, 5, 2
+    g = torch.Generator().manual_seed(D)
+    layout = (torch.rand((H, nb, nb), generator=g) > 0.4).long()
+    layout[:, :, 0] = 1
+    layout[1] = torch.eye(nb, dtype=torch.long)
+    layout[2, 4, :] = 0
+    layout[2, :, 3] = 0
+    q, k, v, do = rand_qkv(Z, H, nb * block, D, torch.float16, seed=D + 7)
+    kw = {}
+    if with_kpm:
+        keep = torch.ones((Z, nb * block), dtype=torch.bool)
+        keep[0, 70:90] = False
+        keep[1, 200:] = False
+        keep[1, 256:264] = True                   # the diagonal block of head 1 keeps one key per row block
+        keep[:, ::64] = True
+        kw['key_padding_mask'] = torch.where(keep, 0.0, float('-inf')).to(torch.float16)
+    check(layout, block, q, k, v, do, True, **kw)
+
+
 def test_sparsity_config_path_and_key_transposed():
     """The reference's constructor path: SparsityConfig 'fixed', key handed over
     pre-transposed as [.., head_dim, L] (deepspeedsparseselfattention.py:119-123)."""
