@@ -12,7 +12,7 @@ table builders (MatMul.make_lut, _sparse_matmul.make_sdd_lut / make_dxx_lut /
 load_balance, _sparse_softmax.make_lut, _make_layout) run without a GPU.
 
 The reference checkout is located through the environment variable
-BSP_REFERENCE_ROOT (default: /root/reference).  When it is absent every entry
+BSP_REFERENCE_ROOT (default: REFERENCE_ROOT below).  When it is absent every entry
 point here returns None / False; callers then fall back to the committed
 fixtures.
 """

@@ -2,7 +2,7 @@
 
     python tests/golden/make_golden.py
 
-Needs the reference checkout (BSP_REFERENCE_ROOT, default /root/reference); the
+Needs the reference checkout (BSP_REFERENCE_ROOT, see oracle/build_ref.py for the default); the
 fixtures it writes are committed so that the tests run without it.
 
   lut_small.npz       tables produced by the reference's own builders

@@ -5,7 +5,7 @@
 // sdd -> softmax -> dsd chain of
 // torch_blocksparse/deepspeedsparseselfattention.py:157-166 and its backward);
 // this path covers block 64 and 128, head dimension 64 and 128, FP16 / BF16,
-// without rpe / masks.
+// without rpe and attention mask; a key-padding mask is a per-key bias here.
 //
 // Geometry: every MMA has M = 128.  A CTA owns a tile of 128 rows of the
 // "outer" operand(s), resident in shared memory, made of two 64-row chunks (one
@@ -23,13 +23,17 @@
 // from tensor memory.  Two threads share a tile row, 32 columns of a chunk each;
 // in the forward each keeps its own running maximum, sum and O accumulator (the
 // two halves of a chunk are two K-slices of the P V product) and the halves are
-// merged when the tile is done.  For
-// block = 64 a 2-bit mask per chunk says which half of the tile owns the block;
-// the other half contributes zeros.
+// merged when the tile is done.  For block = 64 a 2-bit mask per chunk says
+// which half of the tile owns the block; the other half contributes zeros.
+// Where tensor memory has columns to spare the packed operands get columns of
+// their own, so that the score columns are free again as soon as they have been
+// read (Cfg::ER, Cfg::ER2).
 //
-// Warp roles: eight compute warps and two issuing warps (one thread each): one issues the
-// score products, the other the accumulating products and the TMA loads of the ring of inner
-// chunks.  They talk through mbarriers only; every wait is bounded (tc.cuh) and a wait that expires sets the device status word.
+// Warp roles: eight compute warps and two issuing warps (one thread each): one
+// issues the score products, the other the accumulating products and the TMA
+// loads of the ring of inner chunks.  They talk through mbarriers only (one
+// arrival per warp); every wait is bounded (tc.cuh) and a wait that expires
+// sets the device status word.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include "common.h"
