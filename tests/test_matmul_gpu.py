@@ -179,3 +179,43 @@ def test_config2_full_slice(mode, ta, tb):
     assert_close(sl(out, False), want_c, 'c')
     assert_close(sl(ag.grad, mode == 'dsd'), want_da, 'da')
     assert_close(sl(bg.grad, mode == 'dds'), want_db, 'db')
+
+
+@pytest.mark.parametrize('mode', ['dsd', 'dds'])
+@pytest.mark.parametrize('ta', [False, True])
+@pytest.mark.parametrize('tb', [False, True])
+@pytest.mark.parametrize('block', [64, 128])
+@pytest.mark.parametrize('dtype', [torch.float16, torch.bfloat16])
+def test_dsd_dds_tcgen05_kernel(mode, ta, tb, block, dtype):
+    """Block 64 / 128: the products whose sparse operand is taken untransposed run on the
+    tcgen05 kernel, the others on mma.sync.  An odd number of block-rows at block 64 (a tile
+    with one block-row only), a block-row and a block-column without blocks; checked against
+    the dense-masked oracle and against the mma.sync kernels on the same inputs."""
+    from torch_blocksparse_b200 import _lib, fused
+    Z, H, K = 2, 2, 384
+    big = 5 * 64 if block == 64 else 384                      # extent of the sparse operand's non-K side
+    M, N = (big, 256) if mode == 'dsd' else (256, big)
+    g = torch.Generator().manual_seed(block + 3)
+    AS = (K, M) if ta else (M, K)
+    BS = (N, K) if tb else (K, N)
+    sshape = AS if mode == 'dsd' else BS
+    layout = (torch.rand((H, sshape[0] // block, sshape[1] // block), generator=g) > 0.5).long()
+    layout[1, 1, :] = 0
+    layout[0, :, 2] = 0
+    layout[:, 0, 0] = 1
+    x = (torch.randn((Z, H) + AS, generator=g) * 0.1).to(dtype)
+    w = (torch.randn((Z, H) + BS, generator=g) * 0.1).to(dtype)
+    dc = (torch.randn((Z, H, M, N), generator=g) * 0.1).to(dtype)
+    a = dm.dense_to_sparse(x, layout, block) if mode == 'dsd' else x
+    b = dm.dense_to_sparse(w, layout, block) if mode == 'dds' else w
+    run_both(layout, block, mode, ta, tb, a, b, dc, '%s ta=%d tb=%d block %d' % (mode, ta, tb, block))
+    op = MatMul(layout, block, mode, trans_a=ta, trans_b=tb)
+    L = _lib.lib()
+    try:
+        c_tc = op(a.to(DEV), b.to(DEV))
+        _lib.check(L.bsp_matmul_use_tcgen05(0))
+        c_mma = op(a.to(DEV), b.to(DEV))
+    finally:
+        _lib.check(L.bsp_matmul_use_tcgen05(1))
+    assert_close(c_tc.cpu(), c_mma.cpu(), 'tcgen05 vs mma.sync')
+    assert fused.device_status() == 0

@@ -25,6 +25,7 @@ int attn_bwd_tc(const void* q, const void* k, const void* v, const void* dout, c
                 const int32_t* tiles_hdr, const int32_t* tiles, float scale,
                 const void* kpm, int64_t kpm_sz, int kpm_mul, int parts, cudaStream_t st);
 int tc_device_status(int* out);
+int dsd_tc_device_status(int* out);
 
 namespace {
 
@@ -227,5 +228,9 @@ extern "C" int bsp_attn_bwd_static(const void* q, const void* k, const void* v, 
 
 extern "C" int bsp_device_status(int* status) {
   if (!status) return fail(BSP_ERR_INVALID, "status is NULL");
-  return tc_device_status(status);
+  int attn = 0, dsd = 0;
+  if (int rc = tc_device_status(&attn)) return rc;
+  if (int rc = dsd_tc_device_status(&dsd)) return rc;
+  *status = attn ? attn : dsd;
+  return BSP_OK;
 }

@@ -3,6 +3,7 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
+#include <atomic>
 #include "common.h"
 
 namespace bsp {
@@ -18,6 +19,13 @@ int dsd_mma_t(const void* s, const void* b, void* c, int block, int Z, int N,
               int64_t b_sz, int64_t b_sh, int64_t b_sk, int64_t b_sn,
               int64_t c_sz, int64_t c_sh, int64_t c_sm, int64_t c_sn,
               const Meta& m, cudaStream_t st);
+
+bool dsd_tc_eligible(const void* s, const void* b, const void* c, int dtype, int block, int N, int trans_s, int64_t s_sz,
+                     int64_t b_sz, int64_t b_sh, int64_t b_sk, int64_t b_sn,
+                     int64_t c_sz, int64_t c_sh, int64_t c_sm, int64_t c_sn);
+int dsd_tc(const void* s, const void* b, void* c, int dtype, int block, int Z, int N, int64_t s_sz,
+           int64_t b_sz, int64_t b_sh, int64_t b_sk, int64_t b_sn,
+           int64_t c_sz, int64_t c_sh, int64_t c_sm, int64_t c_sn, const Meta& m, cudaStream_t st);
 
 namespace {
 
@@ -61,11 +69,17 @@ int check_sparse(const char* op, const char* name, const void* p, int dtype, int
   return BSP_OK;
 }
 
+// Switch of the tcgen05 kernels for MatMul (on by default); see bsp_matmul_use_tcgen05.
+std::atomic<int> g_matmul_tc{1};
+
 int run_dsd(const void* s, const void* b, void* c, int dtype, int block, int Z, int N,
             int64_t s_sz, int trans_s,
             int64_t b_sz, int64_t b_sh, int64_t b_sk, int64_t b_sn,
             int64_t c_sz, int64_t c_sh, int64_t c_sm, int64_t c_sn,
             const Meta& m, cudaStream_t st) {
+  if (g_matmul_tc.load() && Z <= 65535 &&
+      dsd_tc_eligible(s, b, c, dtype, block, N, trans_s, s_sz, b_sz, b_sh, b_sk, b_sn, c_sz, c_sh, c_sm, c_sn))
+    return dsd_tc(s, b, c, dtype, block, Z, N, s_sz, b_sz, b_sh, b_sk, b_sn, c_sz, c_sh, c_sm, c_sn, m, st);
   if (dtype == BSP_F32)
     return dsd_mma_t<float>(s, b, c, block, Z, N, s_sz, trans_s, b_sz, b_sh, b_sk, b_sn, c_sz, c_sh, c_sm, c_sn, m, st);
   if (dtype == BSP_F16)
@@ -135,4 +149,12 @@ extern "C" int bsp_dds(const void* a, const void* s, void* c, int dtype, int blo
   if (!c) return fail(BSP_ERR_INVALID, "dds: c is NULL");
   return run_dsd(s, a, c, dtype, block, Z, M, s_sz, !trans_s, a_sz, a_sh, a_sk, a_sm, c_sz, c_sh, c_sn, c_sm, m,
                  reinterpret_cast<cudaStream_t>(stream));
+}
+
+// Chooses the kernel family of MatMul for block 64 / 128 with FP16 / BF16 operands: non-zero
+// (default) lets the eligible cases run on the tcgen05 kernels, zero keeps everything on the
+// mma.sync kernels.  Process-wide; meant for comparisons and tests.
+extern "C" int bsp_matmul_use_tcgen05(int enable) {
+  g_matmul_tc.store(enable ? 1 : 0);
+  return BSP_OK;
 }
