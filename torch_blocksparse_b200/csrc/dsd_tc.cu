@@ -4,8 +4,9 @@
 //
 // Same contract as the mma.sync kernel of dsd_impl.cuh (which replaces the launch of
 // torch_blocksparse/matmul.py:498-504, 545-551): C[rows of a block-row] = sum over the
-// nonzero blocks (i, j) of that block-row of S(i, j) . B[rows of block j].  This kernel
-// takes the sparse operand untransposed; the transposed use stays on the mma.sync kernel.
+// nonzero blocks (i, j) of that block-row of op(S)(i, j) . B[rows of block j].  The sparse
+// operand is used as stored (K-major A tiles) or transposed (MN-major A tiles, lists from the
+// CSC side of the metadata).
 //
 // Geometry: every MMA has M = 128.  A CTA owns 128 rows of C (one block-row for block 128,
 // block-rows 2i and 2i + 1 for block 64) and 128 columns, and walks "stages" of K = 64:
@@ -45,7 +46,8 @@ struct DsdTcArgs {
   int64_t c_sz, c_sh, c_sm, c_sn;
   int H, Mb, block, rows_total, nnz_rows;   // rows_total = Mb * block; nnz_rows = nnz * block (first out-of-range row of S)
   int tiles_per_head;
-  const int32_t *row_ptr, *blk_col;
+  const int32_t *row_ptr, *blk_col;          // lists of a block-row of op(S): CSR of the layout, or (transposed use) its CSC
+  const int32_t* blk_id;                     // storage index of every list entry (NULL: the entry's own position)
 };
 
 template <typename T> __device__ __forceinline__ uint32_t pack2(float a, float b);
@@ -72,7 +74,9 @@ BSP_DEVI void tma_load_3d(void* dst, const CUtensorMap* map, uint64_t* bar, int 
 // B_KMAJOR: the dense operand has k contiguous ([n][k] in memory); else n contiguous ([k][n]).
 // C_ROWS: the result has unit stride along n (a thread writes its row with 16-byte stores);
 // else unit stride along m (the transposed problem of dds: lanes write neighbouring addresses).
-template <typename T, bool B_KMAJOR, bool C_ROWS>
+// A_MN: the sparse operand is used transposed: a stored block [k][m] is an MN-major A tile, two
+// groups of 64 m each holding 64 k-rows of 128 bytes (the second group 8 KB after the first).
+template <typename T, bool A_MN, bool B_KMAJOR, bool C_ROWS>
 __global__ void __launch_bounds__(kThreads, 2)
 dsd_tc_kernel(const __grid_constant__ CUtensorMap m_s, const __grid_constant__ CUtensorMap m_b, DsdTcArgs a) {
   extern __shared__ unsigned char smem_raw[];
@@ -131,14 +135,20 @@ dsd_tc_kernel(const __grid_constant__ CUtensorMap m_s, const __grid_constant__ C
         mbar_expect_tx(&bar_full[s], kStageBytes);
         if (block == 128) {
           const int e = p0 + (it >> 1), kh = it & 1;
-          tma_load_3d(sp, &m_s, &bar_full[s], kh * 64, e * 128, z);
+          const int bid = a.blk_id ? a.blk_id[e] : e;
+          if (A_MN) {                               // rows kh * 64 .. of the stored block, its two halves of 64 columns
+            tma_load_3d(sp, &m_s, &bar_full[s], 0, bid * 128 + kh * 64, z);
+            tma_load_3d(sp + 8192, &m_s, &bar_full[s], 64, bid * 128 + kh * 64, z);
+          } else {
+            tma_load_3d(sp, &m_s, &bar_full[s], kh * 64, bid * 128, z);
+          }
           krow = a.blk_col[e] * 128 + kh * 64;
         } else {
           const int ci = i < e0 ? a.blk_col[i] : 0x7fffffff, cj = j < e1 ? a.blk_col[j] : 0x7fffffff;
           const int col = ci < cj ? ci : cj;
           // a row without a block in this column gets zeros: the box lies past the last block
-          tma_load_3d(sp, &m_s, &bar_full[s], 0, ci == col ? i * 64 : a.nnz_rows, z);
-          tma_load_3d(sp + 8192, &m_s, &bar_full[s], 0, cj == col ? j * 64 : a.nnz_rows, z);
+          tma_load_3d(sp, &m_s, &bar_full[s], 0, ci == col ? (a.blk_id ? a.blk_id[i] : i) * 64 : a.nnz_rows, z);
+          tma_load_3d(sp + 8192, &m_s, &bar_full[s], 0, cj == col ? (a.blk_id ? a.blk_id[j] : j) * 64 : a.nnz_rows, z);
           if (ci == col) ++i;
           if (cj == col) ++j;
           krow = col * 64;
@@ -154,11 +164,13 @@ dsd_tc_kernel(const __grid_constant__ CUtensorMap m_s, const __grid_constant__ C
   } else if (warp == 5) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0 && ns > 0) {
-      const uint32_t idesc = instr_desc(128, B_KMAJOR ? 128 : 64, B_KMAJOR ? 0 : 1, Bf<T>::v);
+      const uint32_t idesc = instr_desc(128, B_KMAJOR ? 128 : 64, B_KMAJOR ? 0 : 1, Bf<T>::v) | (A_MN ? 1u << 15 : 0u);
       bool ok = true;
       for (int it = 0; ok && it < ns; ++it) {
         const int s = it % kStages;
-        const uint32_t a_lo = desc_lo(saddr(smem + s * kStageBytes));
+        // (MN-major A: 8 KB between its two groups of 64 rows, in the leading-offset field)
+        const uint32_t a_lo = A_MN ? (((saddr(smem + s * kStageBytes) & 0x3FFFF) >> 4) | (512u << 16))
+                                   : desc_lo(saddr(smem + s * kStageBytes));
         const uint32_t b_lo = desc_lo(saddr(smem + s * kStageBytes + 16384));
         ok = mbar_wait(&bar_full[s], (it / kStages) & 1, fl);
         if (!ok) break;
@@ -166,7 +178,7 @@ dsd_tc_kernel(const __grid_constant__ CUtensorMap m_s, const __grid_constant__ C
 #pragma unroll
         for (int ks = 0; ks < 4; ++ks) {
           const uint32_t acc = (it > 0 || ks > 0) ? 1u : 0u;
-          const uint64_t da = desc_from_lo(a_lo + ks * 2);          // K-major: 32 bytes per K-step
+          const uint64_t da = desc_from_lo(a_lo + ks * (A_MN ? 128 : 2));   // per K-step: 32 bytes (K-major), 16 rows (MN-major)
           if (B_KMAJOR) {
             mma_ss(tmem, da, desc_from_lo(b_lo + ks * 2), idesc, acc);
           } else {                                                  // MN-major: 16 rows (2048 bytes) per K-step, 8 KB per 64 columns
@@ -250,9 +262,9 @@ int encode(CUtensorMap* m, const void* ptr, int dtype, int rank, const cuuint64_
   return BSP_OK;
 }
 
-template <typename T, bool BK, bool CR>
+template <typename T, bool AM, bool BK, bool CR>
 int launch(const CUtensorMap& ms, const CUtensorMap& mb, const DsdTcArgs& a, dim3 grid, cudaStream_t st) {
-  auto kern = dsd_tc_kernel<T, BK, CR>;
+  auto kern = dsd_tc_kernel<T, AM, BK, CR>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
   if (e != cudaSuccess) return fail(BSP_ERR_CUDA, "dsd (tcgen05): cannot reserve shared memory: %s", cudaGetErrorString(e));
   kern<<<grid, kThreads, kSmem, st>>>(ms, mb, a);
@@ -261,22 +273,26 @@ int launch(const CUtensorMap& ms, const CUtensorMap& mb, const DsdTcArgs& a, dim
   return BSP_OK;
 }
 
+template <typename T, bool AM>
+int launch_a(bool bk, bool cr, const CUtensorMap& ms, const CUtensorMap& mb, const DsdTcArgs& a, dim3 grid, cudaStream_t st) {
+  if (bk) return cr ? launch<T, AM, true, true>(ms, mb, a, grid, st) : launch<T, AM, true, false>(ms, mb, a, grid, st);
+  return cr ? launch<T, AM, false, true>(ms, mb, a, grid, st) : launch<T, AM, false, false>(ms, mb, a, grid, st);
+}
+
 template <typename T>
-int launch_t(bool bk, bool cr, const CUtensorMap& ms, const CUtensorMap& mb, const DsdTcArgs& a, dim3 grid, cudaStream_t st) {
-  if (bk) return cr ? launch<T, true, true>(ms, mb, a, grid, st) : launch<T, true, false>(ms, mb, a, grid, st);
-  return cr ? launch<T, false, true>(ms, mb, a, grid, st) : launch<T, false, false>(ms, mb, a, grid, st);
+int launch_t(bool am, bool bk, bool cr, const CUtensorMap& ms, const CUtensorMap& mb, const DsdTcArgs& a, dim3 grid, cudaStream_t st) {
+  return am ? launch_a<T, true>(bk, cr, ms, mb, a, grid, st) : launch_a<T, false>(bk, cr, ms, mb, a, grid, st);
 }
 
 }  // namespace
 
-// True when dsd_tc covers the case: FP16 / BF16, block 64 / 128, sparse operand untransposed,
-// N a multiple of 128, both dense tensors with one unit inner stride and 16-byte friendly
+// True when dsd_tc covers the case: FP16 / BF16, block 64 / 128, N a multiple of 128, both dense tensors with one unit inner stride and 16-byte friendly
 // addresses and strides.
 bool dsd_tc_eligible(const void* s, const void* b, const void* c, int dtype, int block, int N, int trans_s, int64_t s_sz,
                      int64_t b_sz, int64_t b_sh, int64_t b_sk, int64_t b_sn,
                      int64_t c_sz, int64_t c_sh, int64_t c_sm, int64_t c_sn) {
   if (dtype != BSP_F16 && dtype != BSP_BF16) return false;
-  if ((block != 64 && block != 128) || trans_s || N % kTN) return false;
+  if ((block != 64 && block != 128) || N % kTN) return false;
   if ((b_sk != 1) == (b_sn != 1) || (c_sm != 1) == (c_sn != 1)) return false;
   const int64_t b_outer = b_sk == 1 ? b_sn : b_sk;
   if ((reinterpret_cast<uintptr_t>(s) | reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(c)) & 15) return false;
@@ -286,16 +302,18 @@ bool dsd_tc_eligible(const void* s, const void* b, const void* c, int dtype, int
   return true;
 }
 
-int dsd_tc(const void* s, const void* b, void* c, int dtype, int block, int Z, int N, int64_t s_sz,
+int dsd_tc(const void* s, const void* b, void* c, int dtype, int block, int Z, int N, int64_t s_sz, int trans_s,
            int64_t b_sz, int64_t b_sh, int64_t b_sk, int64_t b_sn,
            int64_t c_sz, int64_t c_sh, int64_t c_sm, int64_t c_sn, const Meta& m, cudaStream_t st) {
   const bool bk = b_sk == 1, cr = c_sn == 1;
-  const int64_t ktot = (int64_t)m.Nb * block;
+  // op(S) has the layout's rows (and walks its CSR) or, transposed, its columns (CSC)
+  const int out_b = trans_s ? m.Nb : m.Mb, red_b = trans_s ? m.Mb : m.Nb;
+  const int64_t ktot = (int64_t)red_b * block;
   CUtensorMap ms, mb;
   {
     cuuint64_t dims[3] = {(cuuint64_t)block, (cuuint64_t)m.nnz * block, (cuuint64_t)Z};
     cuuint64_t strides[2] = {(cuuint64_t)block * 2, (cuuint64_t)(Z > 1 ? s_sz : (int64_t)m.nnz * block * block) * 2};
-    cuuint32_t box[3] = {64, (cuuint32_t)(block == 128 ? 128 : 64), 1};
+    cuuint32_t box[3] = {64, (cuuint32_t)((block == 128 && !trans_s) ? 128 : 64), 1};
     if (int rc = encode(&ms, s, dtype, 3, dims, strides, box)) return rc;
   }
   {
@@ -308,12 +326,13 @@ int dsd_tc(const void* s, const void* b, void* c, int dtype, int block, int Z, i
   }
   DsdTcArgs a = {};
   a.c = c; a.c_sz = c_sz; a.c_sh = c_sh; a.c_sm = c_sm; a.c_sn = c_sn;
-  a.H = m.H; a.Mb = m.Mb; a.block = block; a.rows_total = m.Mb * block; a.nnz_rows = m.nnz * block;
-  a.tiles_per_head = (m.Mb * block + 127) / 128;
-  a.row_ptr = m.row_ptr; a.blk_col = m.blk_col;
+  a.H = m.H; a.Mb = out_b; a.block = block; a.rows_total = out_b * block; a.nnz_rows = m.nnz * block;
+  a.tiles_per_head = (out_b * block + 127) / 128;
+  if (trans_s) { a.row_ptr = m.col_ptr; a.blk_col = m.col_row; a.blk_id = m.col_bid; }
+  else { a.row_ptr = m.row_ptr; a.blk_col = m.blk_col; a.blk_id = nullptr; }
   dim3 grid(m.H * a.tiles_per_head, N / kTN, Z);
-  if (dtype == BSP_F16) return launch_t<__half>(bk, cr, ms, mb, a, grid, st);
-  return launch_t<__nv_bfloat16>(bk, cr, ms, mb, a, grid, st);
+  if (dtype == BSP_F16) return launch_t<__half>(trans_s != 0, bk, cr, ms, mb, a, grid, st);
+  return launch_t<__nv_bfloat16>(trans_s != 0, bk, cr, ms, mb, a, grid, st);
 }
 
 // 0, or non-zero when a bounded wait inside the kernel above expired (synchronises the device).

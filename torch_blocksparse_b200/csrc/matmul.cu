@@ -23,7 +23,7 @@ int dsd_mma_t(const void* s, const void* b, void* c, int block, int Z, int N,
 bool dsd_tc_eligible(const void* s, const void* b, const void* c, int dtype, int block, int N, int trans_s, int64_t s_sz,
                      int64_t b_sz, int64_t b_sh, int64_t b_sk, int64_t b_sn,
                      int64_t c_sz, int64_t c_sh, int64_t c_sm, int64_t c_sn);
-int dsd_tc(const void* s, const void* b, void* c, int dtype, int block, int Z, int N, int64_t s_sz,
+int dsd_tc(const void* s, const void* b, void* c, int dtype, int block, int Z, int N, int64_t s_sz, int trans_s,
            int64_t b_sz, int64_t b_sh, int64_t b_sk, int64_t b_sn,
            int64_t c_sz, int64_t c_sh, int64_t c_sm, int64_t c_sn, const Meta& m, cudaStream_t st);
 
@@ -79,7 +79,7 @@ int run_dsd(const void* s, const void* b, void* c, int dtype, int block, int Z, 
             const Meta& m, cudaStream_t st) {
   if (g_matmul_tc.load() && Z <= 65535 &&
       dsd_tc_eligible(s, b, c, dtype, block, N, trans_s, s_sz, b_sz, b_sh, b_sk, b_sn, c_sz, c_sh, c_sm, c_sn))
-    return dsd_tc(s, b, c, dtype, block, Z, N, s_sz, b_sz, b_sh, b_sk, b_sn, c_sz, c_sh, c_sm, c_sn, m, st);
+    return dsd_tc(s, b, c, dtype, block, Z, N, s_sz, trans_s, b_sz, b_sh, b_sk, b_sn, c_sz, c_sh, c_sm, c_sn, m, st);
   if (dtype == BSP_F32)
     return dsd_mma_t<float>(s, b, c, block, Z, N, s_sz, trans_s, b_sz, b_sh, b_sk, b_sn, c_sz, c_sh, c_sm, c_sn, m, st);
   if (dtype == BSP_F16)
