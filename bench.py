@@ -222,6 +222,30 @@ def matmul_bench(dev, pk, iters=10, z=8):
                                      'fwd_frac_of_measured_peak': flops / tf / 1e12 / peak_tf})
                 del a, b, dc, c
                 torch.cuda.empty_cache()
+
+    # blocks 64 and 128 (the tcgen05 kernels) on a compute-bound shape: Z=2, H=8, M=N=K=4096,
+    # layout Bernoulli(0.25), forward only, every mode, plain and one transposed variant
+    out['large_blocks'] = {'workload': 'sdd / dsd / dds FP16, block 64 and 128, Z=2, H=8, M=N=K=4096, Bernoulli(0.25) layout, forward',
+                           'cases': []}
+    S, zz, hh = 4096, 2, 8
+    g = torch.Generator().manual_seed(0)
+    for block in (64, 128):
+        nb = S // block
+        layout = (torch.rand((hh, nb, nb), generator=g) < 0.25).long()
+        nnz = int(layout.sum())
+        d1 = (torch.randn((zz, hh, S, S), generator=g) * S ** -0.5).half().to(dev)
+        d2 = (torch.randn((zz, hh, S, S), generator=g) * S ** -0.5).half().to(dev)
+        sp = (torch.randn((zz, nnz, block, block), generator=g) * S ** -0.5).half().to(dev)
+        flops = 2 * zz * nnz * block * block * S
+        for mode, a, b in (('sdd', d1, d2), ('dsd', sp, d1), ('dds', d1, sp)):
+            for ta, tb in ((False, False), (True, False), (False, True)):
+                op = MatMul(layout, block, mode, trans_a=ta, trans_b=tb)
+                t = timed(lambda: op(a, b))
+                out['large_blocks']['cases'].append({'block': block, 'mode': mode, 'trans_a': ta, 'trans_b': tb, 'fwd_ms': t * 1e3,
+                                                     'fwd_tflops': flops / t / 1e12,
+                                                     'fwd_frac_of_measured_peak': flops / t / 1e12 / peak_tf})
+        del d1, d2, sp
+        torch.cuda.empty_cache()
     return out
 
 

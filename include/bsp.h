@@ -356,11 +356,11 @@ int bsp_attn_bwd_static(const void* q, const void* k, const void* v, const void*
 int bsp_device_status(int* status);
 
 /*
- * Kernel family of bsp_dsd / bsp_dds for block 64 / 128 with FP16 / BF16
- * operands (no counterpart in the reference): non-zero (the default) lets the
- * cases the tcgen05 kernel covers (sparse operand untransposed after the dds
- * mapping, dense width a multiple of 128, TMA-friendly strides) run on it; zero
- * keeps every product on the mma.sync kernels.  Process-wide.
+ * Kernel family of bsp_sdd / bsp_dsd / bsp_dds for block 64 / 128 with FP16 /
+ * BF16 operands (no counterpart in the reference): non-zero (the default) lets
+ * the cases the tcgen05 kernels cover (sdd: K a multiple of 64; dsd / dds: dense
+ * width a multiple of 128; TMA-friendly strides) run on them; zero keeps every
+ * product on the mma.sync kernels.  Process-wide.
  */
 int bsp_matmul_use_tcgen05(int enable);
 

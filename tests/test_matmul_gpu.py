@@ -219,3 +219,38 @@ def test_dsd_dds_tcgen05_kernel(mode, ta, tb, block, dtype):
         _lib.check(L.bsp_matmul_use_tcgen05(1))
     assert_close(c_tc.cpu(), c_mma.cpu(), 'tcgen05 vs mma.sync')
     assert fused.device_status() == 0
+
+
+@pytest.mark.parametrize('ta', [False, True])
+@pytest.mark.parametrize('tb', [False, True])
+@pytest.mark.parametrize('block', [64, 128])
+@pytest.mark.parametrize('dtype', [torch.float16, torch.bfloat16])
+def test_sdd_tcgen05_kernel(ta, tb, block, dtype):
+    """Block 64 / 128 with K a multiple of 64: sdd on the tcgen05 kernel, every transpose (K- and
+    MN-major tiles of both operands).  An odd number of block-rows and of block-columns at block
+    64, a block-row and a block-column without blocks, rows with one block; checked against the
+    dense-masked oracle and against the mma.sync kernel on the same inputs."""
+    from torch_blocksparse_b200 import _lib, fused
+    Z, H, K = 2, 2, 192
+    M, N = (5 * 64, 7 * 64) if block == 64 else (384, 256)
+    g = torch.Generator().manual_seed(block + 11)
+    layout = (torch.rand((H, M // block, N // block), generator=g) > 0.5).long()
+    layout[1, 1, :] = 0
+    layout[0, :, 1] = 0
+    layout[0, 2, :] = 0
+    layout[0, 2, 0] = 1
+    layout[:, 0, 0] = 1
+    x = (torch.randn((Z, H) + ((K, M) if ta else (M, K)), generator=g) * 0.1).to(dtype)
+    w = (torch.randn((Z, H) + ((N, K) if tb else (K, N)), generator=g) * 0.1).to(dtype)
+    dc = dm.dense_to_sparse((torch.randn((Z, H, M, N), generator=g) * 0.1).to(dtype), layout, block)
+    run_both(layout, block, 'sdd', ta, tb, x, w, dc, 'sdd ta=%d tb=%d block %d' % (ta, tb, block))
+    op = MatMul(layout, block, 'sdd', trans_a=ta, trans_b=tb)
+    L = _lib.lib()
+    try:
+        c_tc = op(x.to(DEV), w.to(DEV))
+        _lib.check(L.bsp_matmul_use_tcgen05(0))
+        c_mma = op(x.to(DEV), w.to(DEV))
+    finally:
+        _lib.check(L.bsp_matmul_use_tcgen05(1))
+    assert_close(c_tc.cpu(), c_mma.cpu(), 'tcgen05 vs mma.sync')
+    assert fused.device_status() == 0

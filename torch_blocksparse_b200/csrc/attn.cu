@@ -26,6 +26,7 @@ int attn_bwd_tc(const void* q, const void* k, const void* v, const void* dout, c
                 const void* kpm, int64_t kpm_sz, int kpm_mul, int parts, cudaStream_t st);
 int tc_device_status(int* out);
 int dsd_tc_device_status(int* out);
+int sdd_tc_device_status(int* out);
 
 namespace {
 
@@ -228,9 +229,10 @@ extern "C" int bsp_attn_bwd_static(const void* q, const void* k, const void* v, 
 
 extern "C" int bsp_device_status(int* status) {
   if (!status) return fail(BSP_ERR_INVALID, "status is NULL");
-  int attn = 0, dsd = 0;
+  int attn = 0, dsd = 0, sdd = 0;
   if (int rc = tc_device_status(&attn)) return rc;
   if (int rc = dsd_tc_device_status(&dsd)) return rc;
-  *status = attn ? attn : dsd;
+  if (int rc = sdd_tc_device_status(&sdd)) return rc;
+  *status = attn ? attn : (dsd ? dsd : sdd);
   return BSP_OK;
 }

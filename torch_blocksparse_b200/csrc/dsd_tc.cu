@@ -25,6 +25,7 @@
 #include <cuda_fp16.h>
 #include "common.h"
 #include "tc.cuh"
+#include "mm_tc.cuh"
 
 namespace bsp {
 
@@ -34,6 +35,7 @@ static __device__ int g_dsd_status;
 namespace {
 
 using namespace tc;
+using namespace mmtc;
 
 constexpr int kTN = 128;          // columns of C per CTA
 constexpr int kStages = 3;
@@ -49,27 +51,6 @@ struct DsdTcArgs {
   const int32_t *row_ptr, *blk_col;          // lists of a block-row of op(S): CSR of the layout, or (transposed use) its CSC
   const int32_t* blk_id;                     // storage index of every list entry (NULL: the entry's own position)
 };
-
-template <typename T> __device__ __forceinline__ uint32_t pack2(float a, float b);
-template <> __device__ __forceinline__ uint32_t pack2<__half>(float a, float b) {
-  __half2 h = __floats2half2_rn(a, b);
-  return *reinterpret_cast<uint32_t*>(&h);
-}
-template <> __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float a, float b) {
-  __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
-  return *reinterpret_cast<uint32_t*>(&h);
-}
-template <typename T> __device__ __forceinline__ T cvt1(float a);
-template <> __device__ __forceinline__ __half cvt1<__half>(float a) { return __float2half_rn(a); }
-template <> __device__ __forceinline__ __nv_bfloat16 cvt1<__nv_bfloat16>(float a) { return __float2bfloat16_rn(a); }
-template <typename T> struct Bf { static constexpr int v = 0; };
-template <> struct Bf<__nv_bfloat16> { static constexpr int v = 1; };
-
-BSP_DEVI void tma_load_3d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1, int c2) {
-  asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
-               ::"r"(saddr(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(saddr(bar)), "r"(c0), "r"(c1), "r"(c2)
-               : "memory");
-}
 
 // B_KMAJOR: the dense operand has k contiguous ([n][k] in memory); else n contiguous ([k][n]).
 // C_ROWS: the result has unit stride along n (a thread writes its row with 16-byte stores);
@@ -234,32 +215,6 @@ dsd_tc_kernel(const __grid_constant__ CUtensorMap m_s, const __grid_constant__ C
   __syncthreads();
   if (warp == 1) tmem_dealloc(tmem, kTN);
   if (tid == 0 && failed) atomicExch(&g_dsd_status, 4);
-}
-
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  if (!fn) {
-    cudaDriverEntryPointQueryResult q;
-    void* p = nullptr;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess) fn = (EncodeTiledFn)p;
-  }
-  return fn;
-}
-
-int encode(CUtensorMap* m, const void* ptr, int dtype, int rank, const cuuint64_t* dims, const cuuint64_t* strides_bytes,
-           const cuuint32_t* box) {
-  EncodeTiledFn fn = encode_fn();
-  if (!fn) return fail(BSP_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
-  cuuint32_t es[5] = {1, 1, 1, 1, 1};
-  CUresult r = fn(m, dtype == BSP_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, rank,
-                  const_cast<void*>(ptr), dims, strides_bytes, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) return fail(BSP_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d", (int)r);
-  return BSP_OK;
 }
 
 template <typename T, bool AM, bool BK, bool CR>

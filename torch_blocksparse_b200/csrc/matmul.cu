@@ -27,6 +27,13 @@ int dsd_tc(const void* s, const void* b, void* c, int dtype, int block, int Z, i
            int64_t b_sz, int64_t b_sh, int64_t b_sk, int64_t b_sn,
            int64_t c_sz, int64_t c_sh, int64_t c_sm, int64_t c_sn, const Meta& m, cudaStream_t st);
 
+bool sdd_tc_eligible(const void* a, const void* b, const void* c, int dtype, int block, int K,
+                     int64_t a_sz, int64_t a_sh, int64_t a_sm, int64_t a_sk,
+                     int64_t b_sz, int64_t b_sh, int64_t b_sk, int64_t b_sn, int64_t c_sz);
+int sdd_tc(const void* a, const void* b, void* c, int dtype, int block, int Z, int K,
+           int64_t a_sz, int64_t a_sh, int64_t a_sm, int64_t a_sk,
+           int64_t b_sz, int64_t b_sh, int64_t b_sk, int64_t b_sn, int64_t c_sz, const Meta& m, cudaStream_t st);
+
 namespace {
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
@@ -106,6 +113,8 @@ extern "C" int bsp_sdd(const void* a, const void* b, void* c, int dtype, int blo
   if (int rc = check_sparse("sdd", "c", c, dtype, c_sz)) return rc;
   if (m.nnz == 0) return BSP_OK;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (g_matmul_tc.load() && sdd_tc_eligible(a, b, c, dtype, block, K, a_sz, a_sh, a_sm, a_sk, b_sz, b_sh, b_sk, b_sn, c_sz))
+    return sdd_tc(a, b, c, dtype, block, Z, K, a_sz, a_sh, a_sm, a_sk, b_sz, b_sh, b_sk, b_sn, c_sz, m, st);
   if (dtype == BSP_F32)
     return sdd_mma_t<float>(a, b, c, block, Z, K, a_sz, a_sh, a_sm, a_sk, b_sz, b_sh, b_sk, b_sn, c_sz, m, st);
   if (dtype == BSP_F16)
