@@ -812,6 +812,10 @@ int make_map(CUtensorMap* m, const void* ptr, int dtype, int Z, int H, int L, in
              int64_t sz, int64_t sh, int64_t sr) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return fail(BSP_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+  // The encoder is a driver call and needs the primary context bound to this thread; a thread
+  // that has made no runtime call yet (a worker thread of the caller) has none.
+  static thread_local bool bound = false;
+  if (!bound) { cudaFree(nullptr); bound = true; }
   cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)L, (cuuint64_t)H, (cuuint64_t)Z};
   cuuint64_t strides[3] = {(cuuint64_t)sr * 2, (cuuint64_t)(H > 1 ? sh : (int64_t)L * sr) * 2,
                            (cuuint64_t)(Z > 1 ? sz : (int64_t)H * L * sr) * 2};

@@ -113,7 +113,8 @@ extern "C" int bsp_sdd(const void* a, const void* b, void* c, int dtype, int blo
   if (int rc = check_sparse("sdd", "c", c, dtype, c_sz)) return rc;
   if (m.nnz == 0) return BSP_OK;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  if (g_matmul_tc.load() && sdd_tc_eligible(a, b, c, dtype, block, K, a_sz, a_sh, a_sm, a_sk, b_sz, b_sh, b_sk, b_sn, c_sz))
+  if (g_matmul_tc.load() && (int64_t)m.H * ((m.Mb + 1) / 2) <= 65535 &&
+      sdd_tc_eligible(a, b, c, dtype, block, K, a_sz, a_sh, a_sm, a_sk, b_sz, b_sh, b_sk, b_sn, c_sz))
     return sdd_tc(a, b, c, dtype, block, Z, K, a_sz, a_sh, a_sm, a_sk, b_sz, b_sh, b_sk, b_sn, c_sz, m, st);
   if (dtype == BSP_F32)
     return sdd_mma_t<float>(a, b, c, block, Z, K, a_sz, a_sh, a_sm, a_sk, b_sz, b_sh, b_sk, b_sn, c_sz, m, st);

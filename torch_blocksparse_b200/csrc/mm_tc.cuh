@@ -55,6 +55,10 @@ inline int encode(CUtensorMap* m, const void* ptr, int dtype, int rank, const cu
            const cuuint32_t* box) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return fail(BSP_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+  // The encoder is a driver call and needs the primary context bound to this thread; a thread
+  // that has made no runtime call yet (a worker thread of the caller) has none.
+  static thread_local bool bound = false;
+  if (!bound) { cudaFree(nullptr); bound = true; }
   cuuint32_t es[5] = {1, 1, 1, 1, 1};
   CUresult r = fn(m, dtype == BSP_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, rank,
                   const_cast<void*>(ptr), dims, strides_bytes, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,

@@ -71,7 +71,7 @@ sdd_tc_kernel(const __grid_constant__ CUtensorMap m_a, const __grid_constant__ C
       w_n[1] = w_n[0] + 64;
       w_id[0][0] = e;
     } else {
-      const int tile = blockIdx.x, g = blockIdx.y;
+      const int tile = blockIdx.y, g = blockIdx.x;   // the groups of a tile are neighbours in the launch: they share A in L2
       const int h = tile / a.tiles_per_head, r0 = 2 * (tile % a.tiles_per_head), r1 = r0 + 1 < a.Mb ? r0 + 1 : -1;
       w_h = h;
       w_m0 = r0 * 64;
@@ -260,8 +260,7 @@ int sdd_tc(const void* a, const void* b, void* c, int dtype, int block, int Z, i
   } else {
     // the union of two column lists has at most 2 * max_row entries, and never more than Nb
     const int groups = std::min((m.Nb + 1) / 2, std::max(m.max_row, 1));
-    if (groups > 65535) return fail(BSP_ERR_UNSUPPORTED, "sdd (tcgen05): more than 65535 column groups per row");
-    grid = dim3(m.H * p.tiles_per_head, groups, Z);
+    grid = dim3(groups, m.H * p.tiles_per_head, Z);
   }
   if (dtype == BSP_F16) return launch_t<__half>(am, bm, ma, mb, p, grid, st);
   return launch_t<__nv_bfloat16>(am, bm, ma, mb, p, grid, st);
