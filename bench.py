@@ -466,7 +466,7 @@ def run_ours(args):
         }
         if args.z != 8:
             line['reduced_workload'] = 'Z=%d per GPU instead of 8: not the headline configuration' % args.z
-        if not args.no_cpu_baseline:
+        if not args.no_cpu_baseline and world == 1:          # the host cores are timed on one rank at N = 1 only
             torch.set_num_threads(os.cpu_count() or 1)
             dt, fl = cpu_attention_sample(c, args.cpu_slices)
             line['cpu_baseline'] = {'value': fl / dt / 1e12, 'unit': UNIT, 'cores': torch.get_num_threads(), 'kind': 'port',
