@@ -336,33 +336,39 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
             vb1[at * 4 + ks] = desc_from_lo(sp_lo + C::CH_BYTES / 16 + at * 512 + ks * 128);
           }
       };
+      // head_dim 128: the chunk operand of an accumulating product has two groups of 64 columns,
+      // 8 KB apart; with that distance in the leading-offset field one N = 128 MMA covers both
+      // (64 cycles instead of 2 x 48)
+      constexpr bool WIDE = ATOMS == 2;
+      const uint32_t idesc_acc = WIDE ? instr_desc(128, 128, 1, IsBf16<T>::v) : idesc_mn;
+      auto wide = [](uint64_t d) { return WIDE ? ((d & ~0x3FFF0000ull) | (512ull << 16)) : d; };
       auto accumulate = [&](int t) {
         const uint32_t ts = tmem + (t % NBUF) * C::SCORE_COLS;
         const uint32_t ta = tmem + C::ACC_BASE;
         const uint32_t later = t > 0 ? 1u : 0u;
 #pragma unroll
-        for (int at = 0; at < ATOMS; ++at)
+        for (int at = 0; at < (WIDE ? 1 : ATOMS); ++at)
 #pragma unroll
           for (int ks = 0; ks < 4; ++ks) {
             // packed 16-bit operand of K-step ks (16 rows of the chunk): 8 columns inside the
             // 32-column slice of the compute thread that produced it
             const uint32_t pa = ts + (ks >> 1) * 32 + (ks & 1) * 8;
             if (MODE == FWD) {          // O_half += P_half . V_half: one accumulator per half of the chunk
-              if (ks & 1) mma_ts_acc(ta + (ks >> 1) * D + at * 64, pa, vb1[at * 4 + ks], idesc_mn);
-              else mma_ts(ta + (ks >> 1) * D + at * 64, pa, vb1[at * 4 + ks], idesc_mn, later);
+              if (ks & 1) mma_ts_acc(ta + (ks >> 1) * D + at * 64, pa, wide(vb1[at * 4 + ks]), idesc_acc);
+              else mma_ts(ta + (ks >> 1) * D + at * 64, pa, wide(vb1[at * 4 + ks]), idesc_acc, later);
             } else if (MODE == DQ) {    // dQ += dS . K
               const uint32_t da = C::ER ? tmem + C::PK_BASE + (t & 1) * 32 + ks * 8 : pa + 64;
-              if (ks > 0) mma_ts_acc(ta + at * 64, da, vb0[at * 4 + ks], idesc_mn);
-              else mma_ts(ta + at * 64, da, vb0[at * 4 + ks], idesc_mn, later);
+              if (ks > 0) mma_ts_acc(ta + at * 64, da, wide(vb0[at * 4 + ks]), idesc_acc);
+              else mma_ts(ta + at * 64, da, wide(vb0[at * 4 + ks]), idesc_acc, later);
             } else {                    // dV += P^T . dO,  dK += dS^T . Q
               const uint32_t pp = C::ER2 ? ts + 64 + (ks >> 1) * 32 + (ks & 1) * 16 : pa;
               const uint32_t pd = C::ER2 ? pp + 8 : pa + 64;
               if (ks > 0) {
-                mma_ts_acc(ta + at * 64, pp, vb1[at * 4 + ks], idesc_mn);
-                mma_ts_acc(ta + D + at * 64, pd, vb0[at * 4 + ks], idesc_mn);
+                mma_ts_acc(ta + at * 64, pp, wide(vb1[at * 4 + ks]), idesc_acc);
+                mma_ts_acc(ta + D + at * 64, pd, wide(vb0[at * 4 + ks]), idesc_acc);
               } else {
-                mma_ts(ta + at * 64, pp, vb1[at * 4 + ks], idesc_mn, later);
-                mma_ts(ta + D + at * 64, pd, vb0[at * 4 + ks], idesc_mn, later);
+                mma_ts(ta + at * 64, pp, wide(vb1[at * 4 + ks]), idesc_acc, later);
+                mma_ts(ta + D + at * 64, pd, wide(vb0[at * 4 + ks]), idesc_acc, later);
               }
             }
           }
