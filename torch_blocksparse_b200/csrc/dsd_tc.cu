@@ -15,8 +15,8 @@
 //              A tile whose row has no block there is filled with zeros by an out-of-range
 //              TMA box.
 // A stage is 16 KB of A (128 rows x 64 k, K-major) and 16 KB of the dense operand (64 k x
-// 128 n): n contiguous -> two 64-wide groups, one N = 64 MMA each per K-step (MN-major B);
-// k contiguous -> one N = 128 MMA per K-step (K-major B).
+// 128 n), one N = 128 MMA per K-step: n contiguous -> MN-major B (two 64-wide groups, 8 KB
+// apart, in one descriptor); k contiguous -> K-major B.
 //
 // Warps: 0-3 write the result back (tensor memory -> registers -> global), 4 issues the TMA
 // loads (one thread), 5 issues the MMAs (one thread).  mbarriers only; every wait is bounded
@@ -145,14 +145,16 @@ dsd_tc_kernel(const __grid_constant__ CUtensorMap m_s, const __grid_constant__ C
   } else if (warp == 5) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0 && ns > 0) {
-      const uint32_t idesc = instr_desc(128, B_KMAJOR ? 128 : 64, B_KMAJOR ? 0 : 1, Bf<T>::v) | (A_MN ? 1u << 15 : 0u);
+      const uint32_t idesc = instr_desc(128, 128, B_KMAJOR ? 0 : 1, Bf<T>::v) | (A_MN ? 1u << 15 : 0u);
       bool ok = true;
       for (int it = 0; ok && it < ns; ++it) {
         const int s = it % kStages;
         // (MN-major A: 8 KB between its two groups of 64 rows, in the leading-offset field)
         const uint32_t a_lo = A_MN ? (((saddr(smem + s * kStageBytes) & 0x3FFFF) >> 4) | (512u << 16))
                                    : desc_lo(saddr(smem + s * kStageBytes));
-        const uint32_t b_lo = desc_lo(saddr(smem + s * kStageBytes + 16384));
+        // (MN-major B: 8 KB between its two groups of 64 columns, in the leading-offset field)
+        const uint32_t b_lo = B_KMAJOR ? desc_lo(saddr(smem + s * kStageBytes + 16384))
+                                       : (((saddr(smem + s * kStageBytes + 16384) & 0x3FFFF) >> 4) | (512u << 16));
         ok = mbar_wait(&bar_full[s], (it / kStages) & 1, fl);
         if (!ok) break;
         fence_after();
@@ -160,12 +162,8 @@ dsd_tc_kernel(const __grid_constant__ CUtensorMap m_s, const __grid_constant__ C
         for (int ks = 0; ks < 4; ++ks) {
           const uint32_t acc = (it > 0 || ks > 0) ? 1u : 0u;
           const uint64_t da = desc_from_lo(a_lo + ks * (A_MN ? 128 : 2));   // per K-step: 32 bytes (K-major), 16 rows (MN-major)
-          if (B_KMAJOR) {
-            mma_ss(tmem, da, desc_from_lo(b_lo + ks * 2), idesc, acc);
-          } else {                                                  // MN-major: 16 rows (2048 bytes) per K-step, 8 KB per 64 columns
-            mma_ss(tmem, da, desc_from_lo(b_lo + ks * 128), idesc, acc);
-            mma_ss(tmem + 64, da, desc_from_lo(b_lo + 512 + ks * 128), idesc, acc);
-          }
+          // per K-step: 32 bytes (K-major) or 16 rows = 2048 bytes (MN-major)
+          mma_ss(tmem, da, desc_from_lo(b_lo + ks * (B_KMAJOR ? 2 : 128)), idesc, acc);
         }
         commit(&bar_empty[s]);                                      // the stage is free once these MMAs have read it
       }

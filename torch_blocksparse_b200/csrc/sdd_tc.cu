@@ -11,9 +11,8 @@
 //              of their column lists: four blocks, of which those the layout holds are stored.
 // The reduction runs over K in stages of 64: 16 KB of A (128 m x 64 k) and 16 KB of B (64 k x
 // 128 n), each as two TMA boxes of 64 x 64.  Either operand may have k or its other dimension
-// contiguous: k contiguous gives K-major tiles (one N = 128 MMA per K-step for B), the other
-// case MN-major tiles (A: two groups of 64 rows, 8 KB apart, one descriptor; B: one N = 64 MMA
-// per group).  A box that lies outside the tensor (odd number of block-rows, missing second
+// contiguous: k contiguous gives K-major tiles, the other case MN-major tiles (two groups of 64
+// rows or columns, 8 KB apart, in one descriptor); every K-step is one 128 x 128 x 16 MMA.  A box that lies outside the tensor (odd number of block-rows, missing second
 // column) is filled with zeros.
 //
 // Warps: 0-3 write the blocks back, 4 issues the TMA loads, 5 the MMAs (one thread each).
@@ -137,14 +136,15 @@ sdd_tc_kernel(const __grid_constant__ CUtensorMap m_a, const __grid_constant__ C
   } else if (warp == 5) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
-      const uint32_t idesc = instr_desc(128, B_MN ? 64 : 128, B_MN ? 1 : 0, Bf<T>::v) | (A_MN ? 1u << 15 : 0u);
+      const uint32_t idesc = instr_desc(128, 128, B_MN ? 1 : 0, Bf<T>::v) | (A_MN ? 1u << 15 : 0u);
       bool ok = true;
       for (int it = 0; ok && it < ns; ++it) {
         const int s = it % kStages;
         // (MN-major A: 8 KB between its two groups of 64 rows, in the leading-offset field)
         const uint32_t a_lo = A_MN ? (((saddr(smem + s * kStageBytes) & 0x3FFFF) >> 4) | (512u << 16))
                                    : desc_lo(saddr(smem + s * kStageBytes));
-        const uint32_t b_lo = desc_lo(saddr(smem + s * kStageBytes + 16384));
+        const uint32_t b_lo = B_MN ? (((saddr(smem + s * kStageBytes + 16384) & 0x3FFFF) >> 4) | (512u << 16))
+                                   : desc_lo(saddr(smem + s * kStageBytes + 16384));
         ok = mbar_wait(&bar_full[s], (it / kStages) & 1, fl);
         if (!ok) break;
         fence_after();
@@ -152,12 +152,7 @@ sdd_tc_kernel(const __grid_constant__ CUtensorMap m_a, const __grid_constant__ C
         for (int ks = 0; ks < 4; ++ks) {
           const uint32_t acc = (it > 0 || ks > 0) ? 1u : 0u;
           const uint64_t da = desc_from_lo(a_lo + ks * (A_MN ? 128 : 2));   // per K-step: 16 rows (MN-major), 32 bytes (K-major)
-          if (B_MN) {
-            mma_ss(tmem, da, desc_from_lo(b_lo + ks * 128), idesc, acc);
-            mma_ss(tmem + 64, da, desc_from_lo(b_lo + 512 + ks * 128), idesc, acc);
-          } else {
-            mma_ss(tmem, da, desc_from_lo(b_lo + ks * 2), idesc, acc);
-          }
+          mma_ss(tmem, da, desc_from_lo(b_lo + ks * (B_MN ? 128 : 2)), idesc, acc);
         }
         commit(&bar_empty[s]);
       }
