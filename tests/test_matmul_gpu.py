@@ -254,3 +254,34 @@ def test_sdd_tcgen05_kernel(ta, tb, block, dtype):
         _lib.check(L.bsp_matmul_use_tcgen05(1))
     assert_close(c_tc.cpu(), c_mma.cpu(), 'tcgen05 vs mma.sync')
     assert fused.device_status() == 0
+
+
+@pytest.mark.parametrize('block,dtype', [(16, torch.float32), (32, torch.float16), (64, torch.float16), (128, torch.bfloat16)])
+def test_linear_layer(block, dtype):
+    """Linear (the layer torch_blocksparse/matmul.py:693-709 describes): forward and gradients
+    against a dense layer whose weight is the sparse weight scattered into zeros; inputs of
+    rank 3 with a row count that is not a multiple of 8."""
+    from torch_blocksparse_b200 import Linear
+    fin, fout = 3 * block if block >= 64 else 256, 2 * block if block >= 64 else 128
+    g = torch.Generator().manual_seed(block)
+    layout = (torch.rand((fin // block, fout // block), generator=g) > 0.4).long()
+    layout[0, 0] = 1
+    lin = Linear(fin, fout, block, layout).to(DEV)
+    x = (torch.randn((3, 7, fin), generator=g) * 0.5).to(dtype)
+    dy = (torch.randn((3, 7, fout), generator=g) * 0.5).to(dtype)
+    xg = x.to(DEV).requires_grad_()
+    y = lin(xg)
+    assert y.shape == (3, 7, fout) and y.dtype == dtype
+    y.backward(dy.to(DEV))
+    w = lin.weight.detach().cpu().float()
+    wd = dm.sparse_to_dense(w[None].to(dtype), layout[None], block)[0, 0].float()      # [fin, fout]
+    xr = x.float().requires_grad_()
+    yr = xr @ wd
+    yr.backward(dy.float())
+    assert_close(y, yr.to(dtype), 'linear y')
+    assert_close(xg.grad, xr.grad.to(dtype), 'linear dx')
+    dwd = x.float().reshape(-1, fin).t() @ dy.float().reshape(-1, fout)
+    want_dw = dm.dense_to_sparse(dwd[None, None], layout[None], block)[0]
+    assert_close(lin.weight.grad.to(dtype), want_dw.to(dtype), 'linear dw')
+    with pytest.raises(ValueError):
+        Linear(fin, fout + 1, block, layout)

@@ -12,6 +12,8 @@ sparse ones [Z, nnz, block, block] in layout.nonzero() order.
 
 All arithmetic runs in the native CUDA library; there is no other code path.
 """
+import math
+
 import torch
 
 from . import _lib, tables
@@ -275,3 +277,53 @@ class MatMul:
         self.time_da = time_da[0]
         self.time_db = time_db[0]
         return c
+
+
+class Linear(torch.nn.Module):
+    """y = x . W with a block-sparse weight (torch_blocksparse/matmul.py:693-709).
+
+    The reference's class cannot be constructed: it calls MatMul with its
+    arguments in the wrong order (matmul.py:702).  This is the layer it
+    describes: `weight` holds the nonzero blocks of an [in_features,
+    out_features] matrix as [nnz, block, block] (Kaiming-uniform, as the
+    reference initialises it), `layout` is [in_features / block, out_features /
+    block] (a leading singleton head dimension is accepted), and forward is the
+    'dds' product.  Inputs of any rank [..., in_features] are flattened to rows.
+    There is no bias, as in the reference.
+    """
+
+    def __init__(self, in_features, out_features, block, layout, bench=False):
+        super().__init__()
+        if layout.dim() == 2:
+            layout = layout.unsqueeze(0)
+        if layout.dim() != 3 or layout.size(0) != 1:
+            raise ValueError('Linear: layout must be [in_features / block, out_features / block]')
+        if in_features % block or out_features % block:
+            raise ValueError('Linear: in_features and out_features must be multiples of block %d' % block)
+        if tuple(layout.shape[1:]) != (in_features // block, out_features // block):
+            raise ValueError('Linear: layout %s does not fit %d x %d features with block %d'
+                             % (tuple(layout.shape[1:]), in_features, out_features, block))
+        self.in_features = in_features
+        self.out_features = out_features
+        self.block = block
+        self.weight = torch.nn.Parameter(torch.empty(int(layout.sum()), block, block))
+        self.reset_parameters()
+        self.matmul = MatMul(layout, block, 'dds', trans_a=False, trans_b=False, bench=bench)
+
+    def reset_parameters(self):
+        torch.nn.init.kaiming_uniform_(self.weight, a=math.sqrt(5))
+
+    def forward(self, input):
+        if input.size(-1) != self.in_features:
+            raise ValueError('Linear: expected %d input features, got %d' % (self.in_features, input.size(-1)))
+        lead = input.shape[:-1]
+        x = input.reshape(1, 1, -1, self.in_features)
+        # rows are the reduction dimension of the weight gradient (an sdd product), which must be
+        # a multiple of 16 (matmul.py:318-319); zero rows change nothing
+        pad = (-x.size(2)) % 16
+        if pad:
+            x = torch.nn.functional.pad(x, (0, 0, 0, pad))
+        y = self.matmul(x, self.weight.to(x.dtype))
+        if pad:
+            y = y[:, :, :y.size(2) - pad]
+        return y.reshape(*lead, self.out_features)
