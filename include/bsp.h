@@ -138,11 +138,13 @@ int bsp_meta_build(const int64_t* layout, int H, int Mb, int Nb,
  * their nonzero sets: its list is the union of their positions plus a 2-bit
  * mask telling which half of the tile owns the block.  int32 layout of `out`:
  *   [0] magic [1] H [2] L/block [3] block [4] tiles per head [5] row entries
- *   [6] column entries [7] reserved
+ *   [6] column entries [7] block of the layout the lists were built from
+ *   (block 32 is turned into 64-wide lists, [2] and [3] then describe those,
+ *   and bits 8-15 of every mask word say which 32 x 32 blocks exist)
  *   then twice (row tiles, column tiles), n = H * tiles per head:
  *   c01 [2n] (the tile's two 64-row chunk ids, -1: none)  ptr [n+1]
  *   chunk [E]  mask [E]  order [n] (tiles sorted longest first)
- * block must be 64 or 128 (else BSP_ERR_UNSUPPORTED).
+ * block must be 32 (even block count), 64 or 128 (else BSP_ERR_UNSUPPORTED).
  */
 #define BSP_TILES_MAGIC 0x42535054
 #define BSP_TILES_HEADER 8

@@ -78,11 +78,11 @@ def test_masks_and_rpe(kp_mode, am_mode, fused):
 
 
 @pytest.mark.parametrize('kp_mode', ['add', 'mul'])
-@pytest.mark.parametrize('block,D', [(64, 64), (128, 64), (64, 128), (128, 128)])
+@pytest.mark.parametrize('block,D', [(32, 64), (64, 64), (128, 64), (32, 128), (64, 128), (128, 128)])
 @pytest.mark.parametrize('dtype', [torch.float16, torch.bfloat16])
 def test_key_padding_mask_on_tcgen05_path(block, D, dtype, kp_mode):
     """A key-padding mask alone (the BERT-style call of the reference's wrapper) stays on the
-    tcgen05 kernels at block 64 / 128.  Checked against the dense-masked definition and against
+    tcgen05 kernels at block 32 / 64 / 128.  Checked against the dense-masked definition and against
     the mma.sync kernels; the first column block is kept and never masked, so that no row is
     masked out entirely (the reference's softmax gives NaN there)."""
     from torch_blocksparse_b200 import fused as F

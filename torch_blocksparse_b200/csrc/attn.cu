@@ -34,7 +34,9 @@ namespace {
 // key-padding mask is taken when its rows can be fetched in 16-byte pieces.
 bool tc_eligible(const int32_t* tiles_hdr, const int32_t* tiles, int block, int L, int D,
                  const void* rpe, const void* kpm, int64_t kpm_sz, const void* am) {
-  if (!(tiles_hdr && tiles && (block == 64 || block == 128) && (D == 64 || D == 128)) || rpe || am) return false;
+  if (!(tiles_hdr && tiles && (D == 64 || D == 128)) || rpe || am) return false;
+  // the lists were built for this block size (block 32 runs on 64-wide lists with sub-block masks)
+  if (!((block == 64 || block == 128 || block == 32) && tiles_hdr[7] == block)) return false;
   if (kpm && ((reinterpret_cast<uintptr_t>(kpm) & 15) || (kpm_sz & 7))) return false;
   return true;
 }

@@ -100,6 +100,13 @@ BSP_DEVI void kpm_terms8(const unsigned char* p, int mul, float (&b)[8]) {
     b[2 * i + 1] = kpm_term(f.y, mul);
   }
 }
+// Does this thread's part of a chunk exist?  Bit `half` of the mask word: the block of its
+// half of the tile; bits 8-15: with block 32, the four 32 x 32 blocks inside each half's 64 x
+// 64 position (bit 8 + 4 half + 2 a + b for row group a and column group b of 32): a thread's
+// 32 columns are one such group.  All ones for blocks 64 and 128.  Uniform per warp.
+BSP_DEVI bool chunk_valid(int mask, int half, int trow, int chalf) {
+  return ((mask >> half) & 1) && ((mask >> (8 + 4 * half + 2 * ((trow & 63) >> 5) + chalf)) & 1);
+}
 template <typename T> struct IsBf16 { static constexpr int v = 0; };
 template <> struct IsBf16<__nv_bfloat16> { static constexpr int v = 1; };
 
@@ -467,7 +474,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
       float m_ref = kNegInfT, l = 0.f;
       for (int t = 0; ok && t < ntiles; ++t) {
         const uint32_t ts = tmem + (t % NBUF) * C::SCORE_COLS + lane_base + chalf * 32;
-        const bool valid = (a.mask[first + t] >> half) & 1;
+        const bool valid = chunk_valid(a.mask[first + t], half, trow, chalf);
         TC_TRACE(2, t, 0);
         ok = mbar_wait_warp(&bar_s[t % NBUF], (t / NBUF) & 1, fl);
         TC_TRACE(2, t, 1);
@@ -592,7 +599,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
       const float my_ds = (MODE == DQ && row_ok) ? a.delta[zh + grow] * a.scale : 0.f;
       for (int t = 0; ok && t < ntiles; ++t) {
         const uint32_t ts = tmem + (t % NBUF) * C::SCORE_COLS + lane_base + chalf * 32;
-        const bool valid = (a.mask[first + t] >> half) & 1;
+        const bool valid = chunk_valid(a.mask[first + t], half, trow, chalf);
         const float4* vec = reinterpret_cast<const float4*>(stg + (t % ST) * C::STAGE + 2 * C::CH_BYTES) + chalf * 8;
         TC_TRACE(2, t, 0);
         ok = mbar_wait_warp(&bar_s[t % NBUF], (t / NBUF) & 1, fl);

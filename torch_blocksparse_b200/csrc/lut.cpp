@@ -16,6 +16,7 @@
 #include <cstring>
 #include <numeric>
 #include <thread>
+#include <functional>
 #include <vector>
 #include "common.h"
 
@@ -462,11 +463,16 @@ void pair_blocks(const std::vector<std::vector<int>>& sets, int nb, std::vector<
   }
 }
 
-void build_lists(const std::vector<std::vector<int>>& sets, int nb, int block, TileLists& out) {
+// `fine(outer, inner)`: for block 32, the 2 x 2 presence bits of the 32-blocks inside the coarse
+// 64 x 64 position (outer block of this side, inner block of the other side), bit a * 2 + b for
+// outer sub-block a and inner sub-block b; NULL: every sub-block present.  The bits of the two
+// halves of a tile go to bits 8-11 and 12-15 of the entry's mask word.
+void build_lists(const std::vector<std::vector<int>>& sets, int nb, int block, TileLists& out,
+                 const std::function<int(int, int)>* fine = nullptr) {
   if (block == 128) {
     for (size_t i = 0; i < sets.size(); ++i) {
       out.c01.push_back(int32_t(2 * i)); out.c01.push_back(int32_t(2 * i + 1));
-      for (int j : sets[i]) { out.chunk.push_back(2 * j); out.mask.push_back(3); out.chunk.push_back(2 * j + 1); out.mask.push_back(3); }
+      for (int j : sets[i]) { out.chunk.push_back(2 * j); out.mask.push_back(3 | 0xFF00); out.chunk.push_back(2 * j + 1); out.mask.push_back(3 | 0xFF00); }
       out.ptr.push_back(int32_t(out.chunk.size()));
     }
     return;
@@ -485,7 +491,9 @@ void build_lists(const std::vector<std::vector<int>>& sets, int nb, int block, T
       int m = 0;
       if (ja == j) { m |= 1; ++ia; }
       if (jb == j) { m |= 2; ++ib; }
-      out.chunk.push_back(j); out.mask.push_back(m);
+      int sub = 0xFF;
+      if (fine) sub = ((m & 1) ? (*fine)(pr.first, j) : 0) | (((m & 2) ? (*fine)(pr.second, j) : 0) << 4);
+      out.chunk.push_back(j); out.mask.push_back(m | (sub << 8));
     }
     out.ptr.push_back(int32_t(out.chunk.size()));
   }
@@ -497,16 +505,38 @@ int bsp_attn_tiles_build(const int64_t* layout, int H, int nb, int block,
                          int32_t* out, int64_t out_cap, int64_t* total) {
   if (int rc = check_layout_args(layout, H, nb, nb)) return rc;
   if (!total) return fail(BSP_ERR_INVALID, "NULL result pointer");
-  if (block != 64 && block != 128) return fail(BSP_ERR_UNSUPPORTED, "attention tiles exist for block 64 and 128 (got %d)", block);
+  if (block != 32 && block != 64 && block != 128) return fail(BSP_ERR_UNSUPPORTED, "attention tiles exist for block 32, 64 and 128 (got %d)", block);
+  if (block == 32 && (nb & 1)) return fail(BSP_ERR_UNSUPPORTED, "attention tiles for block 32 need an even number of blocks per side (got %d)", nb);
+  // block 32 is handled as block 64 on the coarsened layout, with the presence of the four
+  // 32-blocks of every position in the mask words
+  const int fine_nb = nb, fine_block = block;
+  if (block == 32) { nb /= 2; block = 64; }
   const int nt = block == 128 ? nb : (nb + 1) / 2;   // tiles per head
   std::vector<TileLists> rt(H), ct(H);
   parallel_heads(H, [&](int h) {
     std::vector<std::vector<int>> rows(nb), cols(nb);
-    for (int i = 0; i < nb; ++i)
-      for (int j = 0; j < nb; ++j)
-        if (layout[(size_t(h) * nb + i) * nb + j] != 0) { rows[i].push_back(j); cols[j].push_back(i); }
-    build_lists(rows, nb, block, rt[h]);
-    build_lists(cols, nb, block, ct[h]);
+    const int64_t* lay = layout + size_t(h) * fine_nb * fine_nb;
+    if (fine_block != 32) {
+      for (int i = 0; i < nb; ++i)
+        for (int j = 0; j < nb; ++j)
+          if (lay[size_t(i) * nb + j] != 0) { rows[i].push_back(j); cols[j].push_back(i); }
+      build_lists(rows, nb, block, rt[h]);
+      build_lists(cols, nb, block, ct[h]);
+    } else {
+      auto at = [&](int i, int j) { return lay[size_t(i) * fine_nb + j] != 0 ? 1 : 0; };
+      for (int i = 0; i < nb; ++i)
+        for (int j = 0; j < nb; ++j)
+          if (at(2 * i, 2 * j) | at(2 * i, 2 * j + 1) | at(2 * i + 1, 2 * j) | at(2 * i + 1, 2 * j + 1)) { rows[i].push_back(j); cols[j].push_back(i); }
+      // row tiles: outer = query block, inner = key block; column tiles: outer = key block, inner = query block
+      const std::function<int(int, int)> by_row = [&](int i, int j) {
+        return at(2 * i, 2 * j) | (at(2 * i, 2 * j + 1) << 1) | (at(2 * i + 1, 2 * j) << 2) | (at(2 * i + 1, 2 * j + 1) << 3);
+      };
+      const std::function<int(int, int)> by_col = [&](int j, int i) {
+        return at(2 * i, 2 * j) | (at(2 * i + 1, 2 * j) << 1) | (at(2 * i, 2 * j + 1) << 2) | (at(2 * i + 1, 2 * j + 1) << 3);
+      };
+      build_lists(rows, nb, block, rt[h], &by_row);
+      build_lists(cols, nb, block, ct[h], &by_col);
+    }
   });
   int64_t er = 0, ec = 0;
   for (int h = 0; h < H; ++h) { er += int64_t(rt[h].chunk.size()); ec += int64_t(ct[h].chunk.size()); }
@@ -516,7 +546,7 @@ int bsp_attn_tiles_build(const int64_t* layout, int H, int nb, int block,
   if (!out) return BSP_OK;
   if (out_cap < need) return fail(BSP_ERR_CAPACITY, "attention tile lists need %lld ints, buffer holds %lld", (long long)need, (long long)out_cap);
   int32_t* p = out;
-  p[0] = BSP_TILES_MAGIC; p[1] = H; p[2] = nb; p[3] = block; p[4] = nt; p[5] = int32_t(er); p[6] = int32_t(ec); p[7] = 0;
+  p[0] = BSP_TILES_MAGIC; p[1] = H; p[2] = nb; p[3] = block; p[4] = nt; p[5] = int32_t(er); p[6] = int32_t(ec); p[7] = fine_block;
   p += BSP_TILES_HEADER;
   auto emit = [&](std::vector<TileLists>& v, int64_t entries) {
     int32_t* c01 = p; p += 2 * n;

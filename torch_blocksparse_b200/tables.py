@@ -143,9 +143,9 @@ class AttnTiles:
 
 def build_attn_tiles(layout, block):
     """Returns the AttnTiles of a square [H, nb, nb] layout, or None when the
-    tcgen05 kernels do not cover it (block other than 64 / 128)."""
+    tcgen05 kernels do not cover it (blocks 32 with an even block count, 64, 128 are covered)."""
     lay, H, Mb, Nb = _layout_i64(layout)
-    if Mb != Nb or block not in (64, 128):
+    if Mb != Nb or block not in (32, 64, 128) or (block == 32 and Mb % 2):
         return None
     L = _lib.lib()
 
