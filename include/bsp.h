@@ -139,12 +139,15 @@ int bsp_meta_build(const int64_t* layout, int H, int Mb, int Nb,
  * mask telling which half of the tile owns the block.  int32 layout of `out`:
  *   [0] magic [1] H [2] L/block [3] block [4] tiles per head [5] row entries
  *   [6] column entries [7] block of the layout the lists were built from
- *   (block 32 is turned into 64-wide lists, [2] and [3] then describe those,
- *   and bits 8-15 of every mask word say which 32 x 32 blocks exist)
+ *   (blocks 16 and 32 are turned into 64-wide lists on the coarsened layout:
+ *   [2] and [3] then describe those)
  *   then twice (row tiles, column tiles), n = H * tiles per head:
  *   c01 [2n] (the tile's two 64-row chunk ids, -1: none)  ptr [n+1]
- *   chunk [E]  mask [E]  order [n] (tiles sorted longest first)
- * block must be 32 (even block count), 64 or 128 (else BSP_ERR_UNSUPPORTED).
+ *   chunk [E]  mask [E]  sub [E]  order [n] (tiles sorted longest first)
+ *   sub: per half of the tile 16 bits saying which 16 x 16 pieces of the 64 x
+ *   64 position lie in a nonzero block (all ones for blocks 64 and 128).
+ * block must be 16, 32, 64 or 128, and L a multiple of 64 (else
+ * BSP_ERR_UNSUPPORTED).
  */
 #define BSP_TILES_MAGIC 0x42535054
 #define BSP_TILES_HEADER 8

@@ -78,15 +78,15 @@ def test_masks_and_rpe(kp_mode, am_mode, fused):
 
 
 @pytest.mark.parametrize('kp_mode', ['add', 'mul'])
-@pytest.mark.parametrize('block,D', [(32, 64), (64, 64), (128, 64), (32, 128), (64, 128), (128, 128)])
+@pytest.mark.parametrize('block,D', [(16, 64), (32, 64), (64, 64), (128, 64), (16, 128), (32, 128), (64, 128), (128, 128)])
 @pytest.mark.parametrize('dtype', [torch.float16, torch.bfloat16])
 def test_key_padding_mask_on_tcgen05_path(block, D, dtype, kp_mode):
     """A key-padding mask alone (the BERT-style call of the reference's wrapper) stays on the
-    tcgen05 kernels at block 32 / 64 / 128.  Checked against the dense-masked definition and against
+    tcgen05 kernels at every block size.  Checked against the dense-masked definition and against
     the mma.sync kernels; the first column block is kept and never masked, so that no row is
     masked out entirely (the reference's softmax gives NaN there)."""
     from torch_blocksparse_b200 import fused as F
-    Z, H, nb = 3, 2, 6
+    Z, H, nb = 3, 2, 8
     L = nb * block
     g = torch.Generator().manual_seed(block * 3 + D)
     layout = (torch.rand((H, nb, nb), generator=g) > 0.5).long()
@@ -134,6 +134,40 @@ def test_odd_number_of_block_rows_on_tcgen05_path(D, with_kpm):
         keep[:, ::64] = True
         kw['key_padding_mask'] = torch.where(keep, 0.0, float('-inf')).to(torch.float16)
     check(layout, block, q, k, v, do, True, **kw)
+
+
+@pytest.mark.parametrize('block', [16, 32])
+@pytest.mark.parametrize('D', [64, 128])
+@pytest.mark.parametrize('dtype', [torch.float16, torch.bfloat16])
+def test_small_blocks_on_tcgen05_path(block, D, dtype):
+    """Blocks 16 and 32 run on the tcgen05 kernels through 64-wide lists of the coarsened layout,
+    with absent 16 x 16 pieces masked out.  Random fine layout; a fine block-row without any
+    block inside a coarse row that has some; a coarse position with a single fine block; a
+    whole coarse row and column without blocks.  Against the oracle and the mma.sync kernels."""
+    from torch_blocksparse_b200 import fused as F
+    f = 64 // block
+    H, nbc, Z = 2, 5, 2
+    nb = nbc * f
+    g = torch.Generator().manual_seed(block + D)
+    layout = (torch.rand((H, nb, nb), generator=g) > 0.55).long()
+    layout[:, :, 0] = 1
+    layout[0, 1, :] = 0                                      # a fine row without blocks, neighbours have some
+    layout[1, 2 * f:3 * f, :] = 0                            # a coarse row without blocks
+    layout[1, :, 3 * f:4 * f] = 0                            # a coarse column without blocks
+    layout[0, 3 * f:4 * f, f:2 * f] = 0
+    layout[0, 3 * f, f + 1 if f > 1 else f] = 1              # a coarse position with one fine block
+    q, k, v, do = rand_qkv(Z, H, nb * block, D, dtype, seed=block + D)
+    check(layout, block, q, k, v, do, True)
+    mod = SparseSelfAttention(layout=layout, block=block, fused=True)
+    assert mod.get_ops(H, nb * block) and mod.tiles[(H, nb * block)] is not None
+    try:
+        tc = run_module(mod, q, k, v, do)
+        F.PATH = 'mma'
+        mma = run_module(mod, q, k, v, do)
+    finally:
+        F.PATH = 'tc'
+    for name, a, b in zip(('o', 'dq', 'dk', 'dv'), tc, mma):
+        assert_close(a.cpu(), b.cpu(), name + ' tcgen05 vs mma.sync')
 
 
 def test_sparsity_config_path_and_key_transposed():

@@ -35,8 +35,8 @@ namespace {
 bool tc_eligible(const int32_t* tiles_hdr, const int32_t* tiles, int block, int L, int D,
                  const void* rpe, const void* kpm, int64_t kpm_sz, const void* am) {
   if (!(tiles_hdr && tiles && (D == 64 || D == 128)) || rpe || am) return false;
-  // the lists were built for this block size (block 32 runs on 64-wide lists with sub-block masks)
-  if (!((block == 64 || block == 128 || block == 32) && tiles_hdr[7] == block)) return false;
+  // the lists were built for this block size (blocks 16 and 32 run on 64-wide lists with masks of 16 x 16 pieces)
+  if (!((block == 16 || block == 32 || block == 64 || block == 128) && tiles_hdr[7] == block)) return false;
   if (kpm && ((reinterpret_cast<uintptr_t>(kpm) & 15) || (kpm_sz & 7))) return false;
   return true;
 }

@@ -4,8 +4,11 @@
 // Same contract as the mma.sync kernels of attn_impl.cuh (which replace the
 // sdd -> softmax -> dsd chain of
 // torch_blocksparse/deepspeedsparseselfattention.py:157-166 and its backward);
-// this path covers block 64 and 128, head dimension 64 and 128, FP16 / BF16,
-// without rpe and attention mask; a key-padding mask is a per-key bias here.
+// this path covers head dimension 64 and 128, FP16 / BF16, without rpe and
+// attention mask; a key-padding mask is a per-key bias here.  Blocks 64 and
+// 128 map onto its tiles directly; blocks 16 and 32 run on the lists of the
+// layout coarsened to 64, with the 16 x 16 pieces that no block covers masked
+// out of the scores.
 //
 // Geometry: every MMA has M = 128.  A CTA owns a tile of 128 rows of the
 // "outer" operand(s), resident in shared memory, made of two 64-row chunks (one
@@ -68,7 +71,8 @@ struct TcArgs {
   int64_t o_sz, o_sh, o_sr;           // strides of O (FWD); gradients are contiguous [Z, H, L, D]
   int Z, H, L, tiles_per_head;
   float scale, scale_log2;
-  const int32_t *c01, *ptr, *chunk, *mask, *order;
+  const int32_t *c01, *ptr, *chunk, *mask, *sub, *order;
+  int fine;                            // the layout's blocks are smaller than 64: pieces of a position may be absent
   const void* kpm; int64_t kpm_sz; int kpm_mul;   // key-padding mask [Z, L] (KPM variants), 'mul' mode flag
 };
 
@@ -100,12 +104,25 @@ BSP_DEVI void kpm_terms8(const unsigned char* p, int mul, float (&b)[8]) {
     b[2 * i + 1] = kpm_term(f.y, mul);
   }
 }
-// Does this thread's part of a chunk exist?  Bit `half` of the mask word: the block of its
-// half of the tile; bits 8-15: with block 32, the four 32 x 32 blocks inside each half's 64 x
-// 64 position (bit 8 + 4 half + 2 a + b for row group a and column group b of 32): a thread's
-// 32 columns are one such group.  All ones for blocks 64 and 128.  Uniform per warp.
-BSP_DEVI bool chunk_valid(int mask, int half, int trow, int chalf) {
-  return ((mask >> half) & 1) && ((mask >> (8 + 4 * half + 2 * ((trow & 63) >> 5) + chalf)) & 1);
+// Which of this thread's two groups of 16 columns of a chunk exist (bit 0, bit 1)?  `sub` holds,
+// per half of the tile, 16 bits: bit 4 a + b for the piece of row group a and column group b (of
+// 16 each) of the 64 x 64 position; all ones for blocks 64 and 128, partly zero for smaller
+// blocks.  0 when the half's block is absent.
+BSP_DEVI int chunk_pieces(int mask, int sub, int half, int trow, int chalf) {
+  if (!((mask >> half) & 1)) return 0;
+  return (sub >> (16 * half + 4 * ((trow & 63) >> 4) + 2 * chalf)) & 3;
+}
+constexpr uint32_t kNegInfBits = 0xff800000u;
+// Scores of absent pieces become -inf: their probabilities are exactly zero.
+BSP_DEVI void mask_pieces(uint32_t (&s)[32], int pieces) {
+  if (!(pieces & 1)) {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) s[i] = kNegInfBits;
+  }
+  if (!(pieces & 2)) {
+#pragma unroll
+    for (int i = 16; i < 32; ++i) s[i] = kNegInfBits;
+  }
 }
 template <typename T> struct IsBf16 { static constexpr int v = 0; };
 template <> struct IsBf16<__nv_bfloat16> { static constexpr int v = 1; };
@@ -172,7 +189,9 @@ BSP_DEVI void store_acc(T* dst, uint32_t taddr, int c0, int n, float mul) {
   }
 }
 
-template <typename T, int D, int MODE, bool KPM>
+// FINE: the lists come from a layout with blocks smaller than 64 (pieces of a position may be
+// absent); a separate instantiation keeps the other case free of that bookkeeping.
+template <typename T, int D, int MODE, bool KPM, bool FINE>
 __global__ void __launch_bounds__(Cfg<D, MODE, KPM>::NT, Cfg<D, MODE, KPM>::CTAS)
 attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant__ CUtensorMap m_res1,
                const __grid_constant__ CUtensorMap m_ch0, const __grid_constant__ CUtensorMap m_ch1, TcArgs a) {
@@ -474,7 +493,15 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
       float m_ref = kNegInfT, l = 0.f;
       for (int t = 0; ok && t < ntiles; ++t) {
         const uint32_t ts = tmem + (t % NBUF) * C::SCORE_COLS + lane_base + chalf * 32;
-        const bool valid = chunk_valid(a.mask[first + t], half, trow, chalf);
+        int pieces = 3;
+        bool valid, partial = false;
+        if constexpr (FINE) {
+          pieces = chunk_pieces(a.mask[first + t], a.sub[first + t], half, trow, chalf);
+          valid = __any_sync(0xffffffffu, pieces != 0);               // per warp: something to compute
+          partial = __any_sync(0xffffffffu, pieces != 3);
+        } else {
+          valid = (a.mask[first + t] >> half) & 1;                    // uniform per warp
+        }
         TC_TRACE(2, t, 0);
         ok = mbar_wait_warp(&bar_s[t % NBUF], (t / NBUF) & 1, fl);
         TC_TRACE(2, t, 1);
@@ -484,6 +511,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
         tmem_ld32(ts, sr);
         tmem_ld_wait();
         TC_TRACE(2, t, 2);
+        if (partial) mask_pieces(sr, pieces);
         float mt = kNegInfT;
         if (valid) {
           if constexpr (KPM) {                               // scores become s * scale + bias (base 2) in place
@@ -526,16 +554,16 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
         // exponentials in two halves of 16 columns: eight packed registers live at a time
         if (valid) {
           float s4[4] = {0.f, 0.f, 0.f, 0.f};
-          // (with a mask a row may still have seen -inf only: its reference stays 0 then)
-          const float m_use = (KPM && m_ref == kNegInfT) ? 0.f : m_ref;
+          // (with a mask or absent pieces a row may still have seen -inf only: its reference stays 0 then)
+          const float m_use = ((KPM || FINE) && m_ref == kNegInfT) ? 0.f : m_ref;
 #pragma unroll
           for (int hp = 0; hp < 2; ++hp) {
             uint32_t ph[8];
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
               const float s0 = __uint_as_float(sr[16 * hp + 2 * i]), s1 = __uint_as_float(sr[16 * hp + 2 * i + 1]);
-              const float p0 = KPM ? fast_exp2(s0 - m_use) : fast_exp2(fmaf(s0, a.scale_log2, -m_ref));
-              const float p1 = KPM ? fast_exp2(s1 - m_use) : fast_exp2(fmaf(s1, a.scale_log2, -m_ref));
+              const float p0 = KPM ? fast_exp2(s0 - m_use) : fast_exp2(fmaf(s0, a.scale_log2, -m_use));
+              const float p1 = KPM ? fast_exp2(s1 - m_use) : fast_exp2(fmaf(s1, a.scale_log2, -m_use));
               s4[i & 3] += p0 + p1;
               ph[i] = pack16<T>(p0, p1);
             }
@@ -592,14 +620,22 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
     } else {
       // (a fully masked query row has lse = -inf: +inf makes its probabilities 0, not NaN)
       float my_lse = (MODE == DQ && row_ok) ? a.lse[zh + grow] : 0.f;
-      if (KPM && my_lse == kNegInfT) my_lse = -kNegInfT;
+      if ((KPM || FINE) && my_lse == kNegInfT) my_lse = -kNegInfT;
       // dK/dV: the bias of this thread's key row
       const float my_b = (KPM && MODE == DKV && row_ok)
           ? kpm_term(static_cast<float>(reinterpret_cast<const T*>(a.kpm)[z * a.kpm_sz + grow]), a.kpm_mul) : 0.f;
       const float my_ds = (MODE == DQ && row_ok) ? a.delta[zh + grow] * a.scale : 0.f;
       for (int t = 0; ok && t < ntiles; ++t) {
         const uint32_t ts = tmem + (t % NBUF) * C::SCORE_COLS + lane_base + chalf * 32;
-        const bool valid = chunk_valid(a.mask[first + t], half, trow, chalf);
+        int pieces = 3;
+        bool valid, partial = false;
+        if constexpr (FINE) {
+          pieces = chunk_pieces(a.mask[first + t], a.sub[first + t], half, trow, chalf);
+          valid = __any_sync(0xffffffffu, pieces != 0);               // per warp: something to compute
+          partial = __any_sync(0xffffffffu, pieces != 3);
+        } else {
+          valid = (a.mask[first + t] >> half) & 1;                    // uniform per warp
+        }
         const float4* vec = reinterpret_cast<const float4*>(stg + (t % ST) * C::STAGE + 2 * C::CH_BYTES) + chalf * 8;
         TC_TRACE(2, t, 0);
         ok = mbar_wait_warp(&bar_s[t % NBUF], (t / NBUF) & 1, fl);
@@ -616,6 +652,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
           TC_TRACE(2, t, 2);
           fence_before();
           warp_arrive(&bar_rd, lane);
+          if (partial) mask_pieces(sr, pieces);
           if (valid) {
             const unsigned char* bp = stg + (t % ST) * C::STAGE + 2 * C::CH_BYTES + chalf * 64;
 #pragma unroll
@@ -668,10 +705,11 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
             tmem_ld_wait();
             fence_before();
             warp_arrive(&bar_rd, lane);
+            if (partial) mask_pieces(sr, pieces);
 #pragma unroll
             for (int i = 0; i < 32; i += 4) {
               float4 lv = vec[i / 4];                           // per-query lse of this chunk
-              if constexpr (KPM) {                              // own bias; a masked-out query row counts as +inf
+              if (KPM || FINE) {                              // own bias; a query row without any key counts as +inf
                 lv.x = lv.x == kNegInfT ? -kNegInfT : lv.x - my_b; lv.y = lv.y == kNegInfT ? -kNegInfT : lv.y - my_b;
                 lv.z = lv.z == kNegInfT ? -kNegInfT : lv.z - my_b; lv.w = lv.w == kNegInfT ? -kNegInfT : lv.w - my_b;
               }
@@ -734,6 +772,10 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
             tmem_ld16(ts + 64 + hv * 16, qr);
             tmem_ld_wait();
             if (hv == 0) TC_TRACE(2, t, 2);
+            if (partial && !((pieces >> hv) & 1)) {             // this pass is one group of 16 columns
+#pragma unroll
+              for (int i = 0; i < 16; ++i) sr[i] = kNegInfBits;
+            }
 #pragma unroll
             for (int i = 0; i < 16; i += 4) {
               float ls[4], es[4];
@@ -741,7 +783,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
                 const float4 lv = vec[hv * 4 + i / 4], ev = vec[16 + hv * 4 + i / 4];
                 ls[0] = lv.x; ls[1] = lv.y; ls[2] = lv.z; ls[3] = lv.w;
                 es[0] = ev.x * a.scale; es[1] = ev.y * a.scale; es[2] = ev.z * a.scale; es[3] = ev.w * a.scale;
-                if constexpr (KPM) {
+                if (KPM || FINE) {
 #pragma unroll
                   for (int j = 0; j < 4; ++j) ls[j] = ls[j] == kNegInfT ? -kNegInfT : ls[j] - my_b;
                 }
@@ -841,27 +883,27 @@ int make_map(CUtensorMap* m, const void* ptr, int dtype, int Z, int H, int L, in
   return BSP_OK;
 }
 
-struct TileSet { const int32_t *c01, *ptr, *chunk, *mask, *order; };
-struct TilesView { int H, nb, block, tiles_per_head; TileSet rt, ct; };
+struct TileSet { const int32_t *c01, *ptr, *chunk, *mask, *sub, *order; };
+struct TilesView { int H, nb, block, tiles_per_head, fine; TileSet rt, ct; };
 
 int decode_tiles(const int32_t* hdr, const int32_t* dev, TilesView& v) {
   if (hdr[0] != BSP_TILES_MAGIC) return fail(BSP_ERR_INVALID, "attention tile lists: bad magic");
-  v.H = hdr[1]; v.nb = hdr[2]; v.block = hdr[3]; v.tiles_per_head = hdr[4];
+  v.H = hdr[1]; v.nb = hdr[2]; v.block = hdr[3]; v.tiles_per_head = hdr[4]; v.fine = hdr[7] < 64 ? 1 : 0;
   const int64_t n = (int64_t)v.H * v.tiles_per_head;
   const int32_t* p = dev + BSP_TILES_HEADER;
   auto take = [&](TileSet& s, int64_t entries) {
-    s.c01 = p; p += 2 * n; s.ptr = p; p += n + 1; s.chunk = p; p += entries; s.mask = p; p += entries; s.order = p; p += n;
+    s.c01 = p; p += 2 * n; s.ptr = p; p += n + 1; s.chunk = p; p += entries; s.mask = p; p += entries; s.sub = p; p += entries; s.order = p; p += n;
   };
   take(v.rt, hdr[5]);
   take(v.ct, hdr[6]);
   return BSP_OK;
 }
 
-template <typename T, int D, int MODE, bool KPM>
+template <typename T, int D, int MODE, bool KPM, bool FINE>
 int launch(const CUtensorMap& r0, const CUtensorMap& r1, const CUtensorMap& c0, const CUtensorMap& c1,
            const TcArgs& a, int n_tiles, int Z, cudaStream_t st, const char* what) {
   using C = Cfg<D, MODE, KPM>;
-  auto kern = attn_tc_kernel<T, D, MODE, KPM>;
+  auto kern = attn_tc_kernel<T, D, MODE, KPM, FINE>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM);
   if (e != cudaSuccess) return fail(BSP_ERR_CUDA, "attention (tcgen05 %s): cannot reserve shared memory: %s", what, cudaGetErrorString(e));
   TcArgs b = a;
@@ -872,26 +914,31 @@ int launch(const CUtensorMap& r0, const CUtensorMap& r1, const CUtensorMap& c0, 
   return BSP_OK;
 }
 
-template <int MODE, bool KPM>
-int launch_kpm(int dtype, int D, const CUtensorMap& r0, const CUtensorMap& r1, const CUtensorMap& c0,
-               const CUtensorMap& c1, const TcArgs& a, int n_tiles, int Z, cudaStream_t st, const char* what) {
+template <int MODE, bool KPM, bool FINE>
+int launch_dt(int dtype, int D, const CUtensorMap& r0, const CUtensorMap& r1, const CUtensorMap& c0,
+              const CUtensorMap& c1, const TcArgs& a, int n_tiles, int Z, cudaStream_t st, const char* what) {
   if (dtype == BSP_F16) {
-    if (D == 64) return launch<__half, 64, MODE, KPM>(r0, r1, c0, c1, a, n_tiles, Z, st, what);
-    return launch<__half, 128, MODE, KPM>(r0, r1, c0, c1, a, n_tiles, Z, st, what);
+    if (D == 64) return launch<__half, 64, MODE, KPM, FINE>(r0, r1, c0, c1, a, n_tiles, Z, st, what);
+    return launch<__half, 128, MODE, KPM, FINE>(r0, r1, c0, c1, a, n_tiles, Z, st, what);
   }
-  if (D == 64) return launch<__nv_bfloat16, 64, MODE, KPM>(r0, r1, c0, c1, a, n_tiles, Z, st, what);
-  return launch<__nv_bfloat16, 128, MODE, KPM>(r0, r1, c0, c1, a, n_tiles, Z, st, what);
+  if (D == 64) return launch<__nv_bfloat16, 64, MODE, KPM, FINE>(r0, r1, c0, c1, a, n_tiles, Z, st, what);
+  return launch<__nv_bfloat16, 128, MODE, KPM, FINE>(r0, r1, c0, c1, a, n_tiles, Z, st, what);
 }
 template <int MODE>
 int launch_any(int dtype, int D, const CUtensorMap& r0, const CUtensorMap& r1, const CUtensorMap& c0,
                const CUtensorMap& c1, const TcArgs& a, int n_tiles, int Z, cudaStream_t st, const char* what) {
-  if (a.kpm) return launch_kpm<MODE, true>(dtype, D, r0, r1, c0, c1, a, n_tiles, Z, st, what);
-  return launch_kpm<MODE, false>(dtype, D, r0, r1, c0, c1, a, n_tiles, Z, st, what);
+  if (a.kpm) {
+    if (a.fine) return launch_dt<MODE, true, true>(dtype, D, r0, r1, c0, c1, a, n_tiles, Z, st, what);
+    return launch_dt<MODE, true, false>(dtype, D, r0, r1, c0, c1, a, n_tiles, Z, st, what);
+  }
+  if (a.fine) return launch_dt<MODE, false, true>(dtype, D, r0, r1, c0, c1, a, n_tiles, Z, st, what);
+  return launch_dt<MODE, false, false>(dtype, D, r0, r1, c0, c1, a, n_tiles, Z, st, what);
 }
 
 void fill_tiles(TcArgs& a, const TilesView& tv, const TileSet& s) {
   a.tiles_per_head = tv.tiles_per_head;
-  a.c01 = s.c01; a.ptr = s.ptr; a.chunk = s.chunk; a.mask = s.mask; a.order = s.order;
+  a.c01 = s.c01; a.ptr = s.ptr; a.chunk = s.chunk; a.mask = s.mask; a.sub = s.sub; a.order = s.order;
+  a.fine = tv.fine;
 }
 
 }  // namespace

@@ -427,7 +427,7 @@ int bsp_meta_build(const int64_t* layout, int H, int Mb, int Nb,
 namespace {
 
 struct TileLists {
-  std::vector<int32_t> c01, ptr{0}, chunk, mask;   // c01: two outer chunk ids per tile (-1: none)
+  std::vector<int32_t> c01, ptr{0}, chunk, mask, sub;   // c01: two outer chunk ids per tile (-1: none)
 };
 
 // rows[i] = sorted nonzero positions of block-row (or block-column) i of one head
@@ -463,16 +463,19 @@ void pair_blocks(const std::vector<std::vector<int>>& sets, int nb, std::vector<
   }
 }
 
-// `fine(outer, inner)`: for block 32, the 2 x 2 presence bits of the 32-blocks inside the coarse
-// 64 x 64 position (outer block of this side, inner block of the other side), bit a * 2 + b for
-// outer sub-block a and inner sub-block b; NULL: every sub-block present.  The bits of the two
-// halves of a tile go to bits 8-11 and 12-15 of the entry's mask word.
+// `fine(outer, inner)`: for blocks 16 and 32, which 16 x 16 pieces of the coarse 64 x 64 position
+// (outer block of this side, inner block of the other side) lie in a nonzero block of the
+// layout: bit 4 a + b for outer group a and inner group b of 16; NULL: all of them.  `sub`
+// holds these 16 bits for the first half of the tile in its low half-word and for the second
+// half in its high half-word.
 void build_lists(const std::vector<std::vector<int>>& sets, int nb, int block, TileLists& out,
                  const std::function<int(int, int)>* fine = nullptr) {
   if (block == 128) {
     for (size_t i = 0; i < sets.size(); ++i) {
       out.c01.push_back(int32_t(2 * i)); out.c01.push_back(int32_t(2 * i + 1));
-      for (int j : sets[i]) { out.chunk.push_back(2 * j); out.mask.push_back(3 | 0xFF00); out.chunk.push_back(2 * j + 1); out.mask.push_back(3 | 0xFF00); }
+      for (int j : sets[i]) {
+        for (int c = 0; c < 2; ++c) { out.chunk.push_back(2 * j + c); out.mask.push_back(3); out.sub.push_back(-1); }
+      }
       out.ptr.push_back(int32_t(out.chunk.size()));
     }
     return;
@@ -491,9 +494,9 @@ void build_lists(const std::vector<std::vector<int>>& sets, int nb, int block, T
       int m = 0;
       if (ja == j) { m |= 1; ++ia; }
       if (jb == j) { m |= 2; ++ib; }
-      int sub = 0xFF;
-      if (fine) sub = ((m & 1) ? (*fine)(pr.first, j) : 0) | (((m & 2) ? (*fine)(pr.second, j) : 0) << 4);
-      out.chunk.push_back(j); out.mask.push_back(m | (sub << 8));
+      uint32_t sub = ((m & 1) ? 0xFFFFu : 0u) | ((m & 2) ? 0xFFFF0000u : 0u);
+      if (fine) sub = uint32_t((m & 1) ? (*fine)(pr.first, j) : 0) | (uint32_t((m & 2) ? (*fine)(pr.second, j) : 0) << 16);
+      out.chunk.push_back(j); out.mask.push_back(m); out.sub.push_back(int32_t(sub));
     }
     out.ptr.push_back(int32_t(out.chunk.size()));
   }
@@ -505,35 +508,43 @@ int bsp_attn_tiles_build(const int64_t* layout, int H, int nb, int block,
                          int32_t* out, int64_t out_cap, int64_t* total) {
   if (int rc = check_layout_args(layout, H, nb, nb)) return rc;
   if (!total) return fail(BSP_ERR_INVALID, "NULL result pointer");
-  if (block != 32 && block != 64 && block != 128) return fail(BSP_ERR_UNSUPPORTED, "attention tiles exist for block 32, 64 and 128 (got %d)", block);
-  if (block == 32 && (nb & 1)) return fail(BSP_ERR_UNSUPPORTED, "attention tiles for block 32 need an even number of blocks per side (got %d)", nb);
-  // block 32 is handled as block 64 on the coarsened layout, with the presence of the four
-  // 32-blocks of every position in the mask words
-  const int fine_nb = nb, fine_block = block;
-  if (block == 32) { nb /= 2; block = 64; }
+  if (block != 16 && block != 32 && block != 64 && block != 128)
+    return fail(BSP_ERR_UNSUPPORTED, "attention tiles exist for block 16, 32, 64 and 128 (got %d)", block);
+  // blocks 16 and 32 are handled as block 64 on the coarsened layout, with the presence of the
+  // 16 x 16 pieces of every position in `sub`
+  const int fine_nb = nb, fine_block = block, f = block < 64 ? 64 / block : 1;
+  if (nb % f) return fail(BSP_ERR_UNSUPPORTED, "attention tiles for block %d need a number of blocks per side that is a multiple of %d (got %d)", block, f, nb);
+  if (f > 1) { nb /= f; block = 64; }
   const int nt = block == 128 ? nb : (nb + 1) / 2;   // tiles per head
   std::vector<TileLists> rt(H), ct(H);
   parallel_heads(H, [&](int h) {
     std::vector<std::vector<int>> rows(nb), cols(nb);
     const int64_t* lay = layout + size_t(h) * fine_nb * fine_nb;
-    if (fine_block != 32) {
+    if (f == 1) {
       for (int i = 0; i < nb; ++i)
         for (int j = 0; j < nb; ++j)
           if (lay[size_t(i) * nb + j] != 0) { rows[i].push_back(j); cols[j].push_back(i); }
       build_lists(rows, nb, block, rt[h]);
       build_lists(cols, nb, block, ct[h]);
     } else {
-      auto at = [&](int i, int j) { return lay[size_t(i) * fine_nb + j] != 0 ? 1 : 0; };
+      // 16 bits of a coarse position: piece (a, b) of 16 rows x 16 columns lies in fine block (a * block16, ...)
+      auto piece = [&](int i, int j, int a, int b) {   // a, b: groups of 16 inside coarse position (i, j)
+        const int fi = (i * 64 + a * 16) / fine_block, fj = (j * 64 + b * 16) / fine_block;
+        return lay[size_t(fi) * fine_nb + fj] != 0 ? 1 : 0;
+      };
+      const std::function<int(int, int)> by_row = [&](int i, int j) {   // outer = query block, inner = key block
+        int v = 0;
+        for (int a = 0; a < 4; ++a) for (int b = 0; b < 4; ++b) v |= piece(i, j, a, b) << (4 * a + b);
+        return v;
+      };
+      const std::function<int(int, int)> by_col = [&](int j, int i) {   // outer = key block, inner = query block
+        int v = 0;
+        for (int a = 0; a < 4; ++a) for (int b = 0; b < 4; ++b) v |= piece(i, j, b, a) << (4 * a + b);
+        return v;
+      };
       for (int i = 0; i < nb; ++i)
         for (int j = 0; j < nb; ++j)
-          if (at(2 * i, 2 * j) | at(2 * i, 2 * j + 1) | at(2 * i + 1, 2 * j) | at(2 * i + 1, 2 * j + 1)) { rows[i].push_back(j); cols[j].push_back(i); }
-      // row tiles: outer = query block, inner = key block; column tiles: outer = key block, inner = query block
-      const std::function<int(int, int)> by_row = [&](int i, int j) {
-        return at(2 * i, 2 * j) | (at(2 * i, 2 * j + 1) << 1) | (at(2 * i + 1, 2 * j) << 2) | (at(2 * i + 1, 2 * j + 1) << 3);
-      };
-      const std::function<int(int, int)> by_col = [&](int j, int i) {
-        return at(2 * i, 2 * j) | (at(2 * i + 1, 2 * j) << 1) | (at(2 * i, 2 * j + 1) << 2) | (at(2 * i + 1, 2 * j + 1) << 3);
-      };
+          if (by_row(i, j)) { rows[i].push_back(j); cols[j].push_back(i); }
       build_lists(rows, nb, block, rt[h], &by_row);
       build_lists(cols, nb, block, ct[h], &by_col);
     }
@@ -541,7 +552,7 @@ int bsp_attn_tiles_build(const int64_t* layout, int H, int nb, int block,
   int64_t er = 0, ec = 0;
   for (int h = 0; h < H; ++h) { er += int64_t(rt[h].chunk.size()); ec += int64_t(ct[h].chunk.size()); }
   const int64_t n = int64_t(H) * nt;
-  const int64_t need = BSP_TILES_HEADER + 2 * (2 * n + (n + 1) + n) + 2 * er + 2 * ec;
+  const int64_t need = BSP_TILES_HEADER + 2 * (2 * n + (n + 1) + n) + 3 * er + 3 * ec;
   *total = need;
   if (!out) return BSP_OK;
   if (out_cap < need) return fail(BSP_ERR_CAPACITY, "attention tile lists need %lld ints, buffer holds %lld", (long long)need, (long long)out_cap);
@@ -553,6 +564,7 @@ int bsp_attn_tiles_build(const int64_t* layout, int H, int nb, int block,
     int32_t* ptr = p; p += n + 1;
     int32_t* chunk = p; p += entries;
     int32_t* mask = p; p += entries;
+    int32_t* sub = p; p += entries;
     int32_t* order = p; p += n;
     int32_t base = 0;
     ptr[0] = 0;
@@ -561,6 +573,7 @@ int bsp_attn_tiles_build(const int64_t* layout, int H, int nb, int block,
       for (int t = 0; t < nt; ++t) ptr[size_t(h) * nt + t + 1] = base + v[h].ptr[t + 1];
       std::copy(v[h].chunk.begin(), v[h].chunk.end(), chunk + base);
       std::copy(v[h].mask.begin(), v[h].mask.end(), mask + base);
+      std::copy(v[h].sub.begin(), v[h].sub.end(), sub + base);
       base += int32_t(v[h].chunk.size());
     }
     std::iota(order, order + n, 0);

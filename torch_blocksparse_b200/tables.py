@@ -143,9 +143,9 @@ class AttnTiles:
 
 def build_attn_tiles(layout, block):
     """Returns the AttnTiles of a square [H, nb, nb] layout, or None when the
-    tcgen05 kernels do not cover it (blocks 32 with an even block count, 64, 128 are covered)."""
+    tcgen05 kernels do not cover it (blocks 64 and 128, and blocks 16 / 32 whose count per side is a multiple of 4 / 2, are covered)."""
     lay, H, Mb, Nb = _layout_i64(layout)
-    if Mb != Nb or block not in (32, 64, 128) or (block == 32 and Mb % 2):
+    if Mb != Nb or block not in (16, 32, 64, 128) or (block < 64 and Mb % (64 // block)):
         return None
     L = _lib.lib()
 
