@@ -249,12 +249,16 @@ int bsp_dds(const void* a, const void* s, void* c, int dtype, int block,
  * log2(sum_j exp(f_j)) of the pre-softmax values f, consumed by the backward.  D is 64 or 128; dtype F16 or BF16.
  * tiles / tiles_hdr: optional device copy of the buffer written by
  * bsp_attn_tiles_build and a HOST pointer to its first BSP_TILES_HEADER ints.
- * When given (and block is 64 or 128, no rpe, no attention mask; a key-padding
- * mask is accepted when kpm and kpm_sz * element size are 16-byte aligned) the
- * tcgen05 + tensor-memory + TMA kernels run; otherwise, or with NULL, the
- * mma.sync kernels do.  Both give the same result within rounding.  A query
- * row whose keys are all masked out gets zeros (the reference's softmax gives
- * NaN there).
+ * When given (lists built for this block size, no rpe; a key-padding mask is
+ * accepted when kpm and kpm_sz * element size are 16-byte aligned; an
+ * attention mask only with am_mul = 2) the tcgen05 + tensor-memory + TMA
+ * kernels run; otherwise, or with NULL, the mma.sync kernels do.  Both give the
+ * same result within rounding.  A query row whose keys are all masked out gets
+ * zeros (the reference's softmax gives NaN there).
+ * am_mul = 2: the caller vouches that `am` is the lower-triangular causal mask
+ * in 'mul' form (am[i][j] != 0 exactly for j <= i); kernels that can do so
+ * derive it from the indices instead of reading it, the others read it as with
+ * am_mul = 1.
  */
 int bsp_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse,
                  int dtype, int block, int Z, int H, int L, int D,

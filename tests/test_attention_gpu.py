@@ -170,6 +170,45 @@ def test_small_blocks_on_tcgen05_path(block, D, dtype):
         assert_close(a.cpu(), b.cpu(), name + ' tcgen05 vs mma.sync')
 
 
+@pytest.mark.parametrize('block,D', [(16, 64), (32, 64), (64, 64), (128, 64), (64, 128), (128, 128)])
+@pytest.mark.parametrize('with_kpm', [False, True])
+def test_causal_mask_on_tcgen05_path(block, D, with_kpm):
+    """A 'mul' attention mask that is exactly lower triangular (the usual causal mask given
+    with a unidirectional layout) is recognised and derived from the indices on the tcgen05
+    kernels; any other mask is read as given.  Against the oracle and the mma.sync kernels."""
+    from torch_blocksparse_b200 import fused as F
+    Z, H, nbc = 2, 2, 4
+    L = nbc * 128
+    nb = L // block
+    dtype = torch.float16
+    g = torch.Generator().manual_seed(block + D + 5)
+    layout = torch.tril((torch.rand((H, nb, nb), generator=g) > 0.3).long())
+    layout[:, torch.arange(nb), torch.arange(nb)] = 1          # every row sees itself
+    layout[:, :, 0] = 1
+    q, k, v, do = rand_qkv(Z, H, L, D, dtype, seed=block + 2)
+    am = torch.tril(torch.ones((L, L))).to(dtype)
+    kw = dict(attn_mask=am)
+    if with_kpm:
+        keep = torch.rand((Z, L), generator=g) > 0.2
+        keep[:, 0] = True
+        kw['key_padding_mask'] = torch.where(keep, 0.0, float('-inf')).to(dtype)
+    check(layout, block, q, k, v, do, True, 'add', 'mul', **kw)
+    mod = SparseSelfAttention(layout=layout, block=block, fused=True)
+    assert mod._is_causal(am.to(DEV))
+    try:
+        tc = run_module(mod, q, k, v, do, **kw)
+        F.PATH = 'mma'
+        mma = run_module(mod, q, k, v, do, **kw)
+    finally:
+        F.PATH = 'tc'
+    for name, a, b in zip(('o', 'dq', 'dk', 'dv'), tc, mma):
+        assert_close(a.cpu(), b.cpu(), name + ' tcgen05 vs mma.sync')
+    am2 = am.clone()
+    am2[5, 3] = 0                                              # not causal any more: read as given
+    assert not mod._is_causal(am2.to(DEV))
+    check(layout, block, q, k, v, do, True, 'add', 'mul', attn_mask=am2)
+
+
 def test_sparsity_config_path_and_key_transposed():
     """The reference's constructor path: SparsityConfig 'fixed', key handed over
     pre-transposed as [.., head_dim, L] (deepspeedsparseselfattention.py:119-123)."""

@@ -17,6 +17,8 @@ Differences, all additive:
     one kernel without storing the score tensor; `fused=False` runs the
     reference's three-op chain sdd -> softmax -> dsd.
 """
+import weakref
+
 import torch
 import torch.nn as nn
 
@@ -64,6 +66,7 @@ class DeepSpeedSparseSelfAttention(nn.Module):
         self.fused = fused
         self.ops = dict()
         self.tiles = dict()
+        self._causal_cache = dict()
 
     def get_layout(self, H, L):
         """The [H, L/block, L/block] layout used for H heads and sequence length L."""
@@ -92,6 +95,22 @@ class DeepSpeedSparseSelfAttention(nn.Module):
             self.ops[key] = (sdd_nt, dsd_nn, Softmax(layout, self.block))
             self.tiles[key] = tables.build_attn_tiles(layout, self.block) if self.fused else None
         return self.ops[key]
+
+    def _is_causal(self, attn_mask):
+        """True when a 'mul' attention mask is exactly the lower-triangular (causal) mask: the
+        fused kernels then derive it from the indices.  The answer is remembered per tensor
+        object and version (not per address: a freed tensor's address is reused); a caller
+        that builds a new mask tensor for every call pays the comparison every time."""
+        entry = self._causal_cache.get(id(attn_mask))
+        if entry is not None and entry[0]() is attn_mask and entry[1] == attn_mask._version:
+            return entry[2]
+        L = attn_mask.size(-1)
+        hit = (attn_mask.dim() == 2 and attn_mask.size(0) == L and
+               bool(torch.equal(attn_mask != 0, torch.ones((L, L), dtype=torch.bool, device=attn_mask.device).tril())))
+        if len(self._causal_cache) > 16:
+            self._causal_cache.clear()
+        self._causal_cache[id(attn_mask)] = (weakref.ref(attn_mask), attn_mask._version, hit)
+        return hit
 
     def transpose_key_for_scores(self, x, L):
         """deepspeedsparseselfattention.py:119-123: a key given as [.., hd, L] is
@@ -136,9 +155,12 @@ class DeepSpeedSparseSelfAttention(nn.Module):
         if self.fused:
             from .fused import fused_attention, fused_supported
             if fused_supported(query, self.block):
+                am_mode = self.attn_mask_mode
+                if attn_mask is not None and am_mode == 'mul' and self._is_causal(attn_mask):
+                    am_mode = 'causal'
                 return fused_attention(query, key, value, sdd_nt.meta, self.block, scaling, rpe,
                                        key_padding_mask, attn_mask,
-                                       self.key_padding_mask_mode, self.attn_mask_mode,
+                                       self.key_padding_mask_mode, am_mode,
                                        tiles=self.tiles[(num_heads, tgt_len)])
         w = sdd_nt(query, key)
         w = softmax(w, scale=scaling, rpe=rpe, key_padding_mask=key_padding_mask, attn_mask=attn_mask,

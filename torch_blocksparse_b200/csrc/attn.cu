@@ -17,24 +17,25 @@ int attn_fwd_tc(const void* q, const void* k, const void* v, void* o, float* lse
                 int64_t q_sz, int64_t q_sh, int64_t q_sr, int64_t k_sz, int64_t k_sh, int64_t k_sr,
                 int64_t v_sz, int64_t v_sh, int64_t v_sr, int64_t o_sz, int64_t o_sh, int64_t o_sr,
                 const int32_t* tiles_hdr, const int32_t* tiles, float scale,
-                const void* kpm, int64_t kpm_sz, int kpm_mul, cudaStream_t st);
+                const void* kpm, int64_t kpm_sz, int kpm_mul, int causal, cudaStream_t st);
 int attn_bwd_tc(const void* q, const void* k, const void* v, const void* dout, const float* lse, const float* delta,
                 void* dq, void* dk, void* dv, int dtype, int Z, int H, int L, int D,
                 int64_t q_sz, int64_t q_sh, int64_t q_sr, int64_t k_sz, int64_t k_sh, int64_t k_sr,
                 int64_t v_sz, int64_t v_sh, int64_t v_sr, int64_t do_sz, int64_t do_sh, int64_t do_sr,
                 const int32_t* tiles_hdr, const int32_t* tiles, float scale,
-                const void* kpm, int64_t kpm_sz, int kpm_mul, int parts, cudaStream_t st);
+                const void* kpm, int64_t kpm_sz, int kpm_mul, int causal, int parts, cudaStream_t st);
 int tc_device_status(int* out);
 int dsd_tc_device_status(int* out);
 int sdd_tc_device_status(int* out);
 
 namespace {
 
-// The tcgen05 kernels cover FP16 / BF16 on 128-row tiles, without rpe and attention mask; a
-// key-padding mask is taken when its rows can be fetched in 16-byte pieces.
+// The tcgen05 kernels cover FP16 / BF16 on 128-row tiles, without rpe; a key-padding mask is
+// taken when its rows can be fetched in 16-byte pieces, an attention mask when it is the causal one.
 bool tc_eligible(const int32_t* tiles_hdr, const int32_t* tiles, int block, int L, int D,
-                 const void* rpe, const void* kpm, int64_t kpm_sz, const void* am) {
-  if (!(tiles_hdr && tiles && (D == 64 || D == 128)) || rpe || am) return false;
+                 const void* rpe, const void* kpm, int64_t kpm_sz, const void* am, int am_mul) {
+  // an attention mask is only taken when the caller vouches that it is the causal one (flag 2)
+  if (!(tiles_hdr && tiles && (D == 64 || D == 128)) || rpe || (am && am_mul != 2)) return false;
   // the lists were built for this block size (blocks 16 and 32 run on 64-wide lists with masks of 16 x 16 pieces)
   if (!((block == 16 || block == 32 || block == 64 || block == 128) && tiles_hdr[7] == block)) return false;
   if (kpm && ((reinterpret_cast<uintptr_t>(kpm) & 15) || (kpm_sz & 7))) return false;
@@ -127,9 +128,9 @@ extern "C" int bsp_attn_fwd(const void* q, const void* k, const void* v, void* o
   p.q_sz = q_sz; p.q_sh = q_sh; p.q_sr = q_sr; p.k_sz = k_sz; p.k_sh = k_sh; p.k_sr = k_sr;
   p.v_sz = v_sz; p.v_sh = v_sh; p.v_sr = v_sr; p.o_sz = o_sz; p.o_sh = o_sh; p.o_sr = o_sr;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  if (tc_eligible(tiles_hdr, tiles, block, L, D, rpe, kpm, kpm_sz, am))
+  if (tc_eligible(tiles_hdr, tiles, block, L, D, rpe, kpm, kpm_sz, am, am_mul))
     return attn_fwd_tc(q, k, v, o, lse, dtype, Z, H, L, D, q_sz, q_sh, q_sr, k_sz, k_sh, k_sr, v_sz, v_sh, v_sr,
-                       o_sz, o_sh, o_sr, tiles_hdr, tiles, scale, kpm, kpm_sz, kpm_mul, st);
+                       o_sz, o_sh, o_sr, tiles_hdr, tiles, scale, kpm, kpm_sz, kpm_mul, am != nullptr, st);
   if (dtype == BSP_F16) return attn_fwd_t<__half>(p, block, D, Z, st);
   return attn_fwd_t<__nv_bfloat16>(p, block, D, Z, st);
 }
@@ -167,7 +168,7 @@ extern "C" int bsp_attn_bwd_parts(const void* q, const void* k, const void* v, c
   p.v_sz = v_sz; p.v_sh = v_sh; p.v_sr = v_sr; p.o_sz = o_sz; p.o_sh = o_sh; p.o_sr = o_sr;
   p.do_sz = do_sz; p.do_sh = do_sh; p.do_sr = do_sr;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  if (tc_eligible(tiles_hdr, tiles, block, L, D, rpe, kpm, kpm_sz, am)) {
+  if (tc_eligible(tiles_hdr, tiles, block, L, D, rpe, kpm, kpm_sz, am, am_mul)) {
     // delta = rowsum(o * do) by the streaming kernel, the two matrix kernels on tcgen05
     if (parts & 1) {
       const int rc = dtype == BSP_F16 ? attn_bwd_t<__half>(p, block, D, Z, 1, st) : attn_bwd_t<__nv_bfloat16>(p, block, D, Z, 1, st);
@@ -175,7 +176,7 @@ extern "C" int bsp_attn_bwd_parts(const void* q, const void* k, const void* v, c
     }
     if (!(parts & 6)) return BSP_OK;
     return attn_bwd_tc(q, k, v, dout, lse, delta, dq, dk, dv, dtype, Z, H, L, D, q_sz, q_sh, q_sr, k_sz, k_sh, k_sr,
-                       v_sz, v_sh, v_sr, do_sz, do_sh, do_sr, tiles_hdr, tiles, scale, kpm, kpm_sz, kpm_mul, parts & 6, st);
+                       v_sz, v_sh, v_sr, do_sz, do_sh, do_sr, tiles_hdr, tiles, scale, kpm, kpm_sz, kpm_mul, am != nullptr, parts & 6, st);
   }
   if (dtype == BSP_F16) return attn_bwd_t<__half>(p, block, D, Z, parts, st);
   return attn_bwd_t<__nv_bfloat16>(p, block, D, Z, parts, st);

@@ -73,6 +73,7 @@ struct TcArgs {
   float scale, scale_log2;
   const int32_t *c01, *ptr, *chunk, *mask, *sub, *order;
   int fine;                            // the layout's blocks are smaller than 64: pieces of a position may be absent
+  int causal;                          // key j is visible to query i only for j <= i (handled by the FINE instantiation)
   const void* kpm; int64_t kpm_sz; int kpm_mul;   // key-padding mask [Z, L] (KPM variants), 'mul' mode flag
 };
 
@@ -123,6 +124,16 @@ BSP_DEVI void mask_pieces(uint32_t (&s)[32], int pieces) {
 #pragma unroll
     for (int i = 16; i < 32; ++i) s[i] = kNegInfBits;
   }
+}
+// Causal mask on N score registers: column col0 + i against this thread's row.  Forward and dQ
+// (rows are queries, columns keys): a key after the query is hidden; dK / dV (rows are keys,
+// columns queries): a query before the key does not see it.
+template <int N, bool ROWS_ARE_KEYS>
+BSP_DEVI void mask_causal(uint32_t (&s)[N], int col0, int row) {
+  if (ROWS_ARE_KEYS ? (col0 >= row) : (col0 + N - 1 <= row)) return;   // nothing hidden in this stretch
+#pragma unroll
+  for (int i = 0; i < N; ++i)
+    if (ROWS_ARE_KEYS ? (col0 + i < row) : (col0 + i > row)) s[i] = kNegInfBits;
 }
 template <typename T> struct IsBf16 { static constexpr int v = 0; };
 template <> struct IsBf16<__nv_bfloat16> { static constexpr int v = 1; };
@@ -512,6 +523,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
         tmem_ld_wait();
         TC_TRACE(2, t, 2);
         if (partial) mask_pieces(sr, pieces);
+        if (FINE && a.causal) mask_causal<32, false>(sr, a.chunk[first + t] * 64 + chalf * 32, (int)grow);
         float mt = kNegInfT;
         if (valid) {
           if constexpr (KPM) {                               // scores become s * scale + bias (base 2) in place
@@ -653,6 +665,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
           fence_before();
           warp_arrive(&bar_rd, lane);
           if (partial) mask_pieces(sr, pieces);
+          if (FINE && a.causal) mask_causal<32, false>(sr, a.chunk[first + t] * 64 + chalf * 32, (int)grow);
           if (valid) {
             const unsigned char* bp = stg + (t % ST) * C::STAGE + 2 * C::CH_BYTES + chalf * 64;
 #pragma unroll
@@ -706,6 +719,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
             fence_before();
             warp_arrive(&bar_rd, lane);
             if (partial) mask_pieces(sr, pieces);
+            if (FINE && a.causal) mask_causal<32, true>(sr, a.chunk[first + t] * 64 + chalf * 32, (int)grow);
 #pragma unroll
             for (int i = 0; i < 32; i += 4) {
               float4 lv = vec[i / 4];                           // per-query lse of this chunk
@@ -776,6 +790,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
 #pragma unroll
               for (int i = 0; i < 16; ++i) sr[i] = kNegInfBits;
             }
+            if (FINE && a.causal) mask_causal<16, MODE == DKV>(sr, a.chunk[first + t] * 64 + chalf * 32 + hv * 16, (int)grow);
 #pragma unroll
             for (int i = 0; i < 16; i += 4) {
               float ls[4], es[4];
@@ -928,10 +943,10 @@ template <int MODE>
 int launch_any(int dtype, int D, const CUtensorMap& r0, const CUtensorMap& r1, const CUtensorMap& c0,
                const CUtensorMap& c1, const TcArgs& a, int n_tiles, int Z, cudaStream_t st, const char* what) {
   if (a.kpm) {
-    if (a.fine) return launch_dt<MODE, true, true>(dtype, D, r0, r1, c0, c1, a, n_tiles, Z, st, what);
+    if (a.fine || a.causal) return launch_dt<MODE, true, true>(dtype, D, r0, r1, c0, c1, a, n_tiles, Z, st, what);
     return launch_dt<MODE, true, false>(dtype, D, r0, r1, c0, c1, a, n_tiles, Z, st, what);
   }
-  if (a.fine) return launch_dt<MODE, false, true>(dtype, D, r0, r1, c0, c1, a, n_tiles, Z, st, what);
+  if (a.fine || a.causal) return launch_dt<MODE, false, true>(dtype, D, r0, r1, c0, c1, a, n_tiles, Z, st, what);
   return launch_dt<MODE, false, false>(dtype, D, r0, r1, c0, c1, a, n_tiles, Z, st, what);
 }
 
@@ -951,7 +966,7 @@ int attn_fwd_tc(const void* q, const void* k, const void* v, void* o, float* lse
                 int64_t q_sz, int64_t q_sh, int64_t q_sr, int64_t k_sz, int64_t k_sh, int64_t k_sr,
                 int64_t v_sz, int64_t v_sh, int64_t v_sr, int64_t o_sz, int64_t o_sh, int64_t o_sr,
                 const int32_t* tiles_hdr, const int32_t* tiles, float scale,
-                const void* kpm, int64_t kpm_sz, int kpm_mul, cudaStream_t st) {
+                const void* kpm, int64_t kpm_sz, int kpm_mul, int causal, cudaStream_t st) {
   TilesView tv;
   if (int rc = decode_tiles(tiles_hdr, tiles, tv)) return rc;
   if (tv.H != H || tv.nb * tv.block != L) return fail(BSP_ERR_INVALID, "attention tile lists do not fit %d heads of length %d", H, L);
@@ -962,7 +977,7 @@ int attn_fwd_tc(const void* q, const void* k, const void* v, void* o, float* lse
   TcArgs a = {};
   a.out0 = o; a.lse_out = lse; a.o_sz = o_sz; a.o_sh = o_sh; a.o_sr = o_sr;
   a.H = H; a.L = L; a.scale = scale; a.scale_log2 = scale * kLog2eT;
-  a.kpm = kpm; a.kpm_sz = kpm_sz; a.kpm_mul = kpm_mul;
+  a.kpm = kpm; a.kpm_sz = kpm_sz; a.kpm_mul = kpm_mul; a.causal = causal;
   fill_tiles(a, tv, tv.rt);
   return launch_any<FWD>(dtype, D, mq, mq, mk, mv, a, H * tv.tiles_per_head, Z, st, "forward");
 }
@@ -973,7 +988,7 @@ int attn_bwd_tc(const void* q, const void* k, const void* v, const void* dout, c
                 int64_t q_sz, int64_t q_sh, int64_t q_sr, int64_t k_sz, int64_t k_sh, int64_t k_sr,
                 int64_t v_sz, int64_t v_sh, int64_t v_sr, int64_t do_sz, int64_t do_sh, int64_t do_sr,
                 const int32_t* tiles_hdr, const int32_t* tiles, float scale,
-                const void* kpm, int64_t kpm_sz, int kpm_mul, int parts, cudaStream_t st) {
+                const void* kpm, int64_t kpm_sz, int kpm_mul, int causal, int parts, cudaStream_t st) {
   TilesView tv;
   if (int rc = decode_tiles(tiles_hdr, tiles, tv)) return rc;
   if (tv.H != H || tv.nb * tv.block != L) return fail(BSP_ERR_INVALID, "attention tile lists do not fit %d heads of length %d", H, L);
@@ -984,7 +999,7 @@ int attn_bwd_tc(const void* q, const void* k, const void* v, const void* dout, c
   if (int rc = make_map(&md, dout, dtype, Z, H, L, D, do_sz, do_sh, do_sr)) return rc;
   TcArgs a = {};
   a.lse = lse; a.delta = delta; a.H = H; a.L = L; a.scale = scale; a.scale_log2 = scale * kLog2eT;
-  a.kpm = kpm; a.kpm_sz = kpm_sz; a.kpm_mul = kpm_mul;
+  a.kpm = kpm; a.kpm_sz = kpm_sz; a.kpm_mul = kpm_mul; a.causal = causal;
   const int n_tiles = H * tv.tiles_per_head;
   if (parts & 2) {
     a.out0 = dk; a.out1 = dv;

@@ -86,10 +86,14 @@ def _mask_args(Z, H, L, dtype, rpe, kpm, am, kp_mode, am_mode):
             am = am.contiguous()
         keep.append(am)
         a_ptr, ar = am.data_ptr(), am.stride(0)
-    for name, mode in (('key_padding_mask_mode', kp_mode), ('attn_mask_mode', am_mode)):
-        if mode not in ('add', 'mul'):
-            raise ValueError("%s must be 'add' or 'mul'" % name)
-    return (r_ptr, rz, rh, rr, k_ptr, kz, 1 if kp_mode == 'mul' else 0, a_ptr, ar, 1 if am_mode == 'mul' else 0), keep
+    # 'causal' (internal): a 'mul' mask known to be lower triangular; the kernels that can do so
+    # derive it from the indices instead of reading it (flag 2), the others read it as 'mul'
+    if kp_mode not in ('add', 'mul'):
+        raise ValueError("key_padding_mask_mode must be 'add' or 'mul'")
+    if am_mode not in ('add', 'mul', 'causal'):
+        raise ValueError("attn_mask_mode must be 'add' or 'mul'")
+    am_flag = {'add': 0, 'mul': 1, 'causal': 2}[am_mode]
+    return (r_ptr, rz, rh, rr, k_ptr, kz, 1 if kp_mode == 'mul' else 0, a_ptr, ar, am_flag), keep
 
 
 class _fused_attention(torch.autograd.Function):
