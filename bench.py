@@ -44,10 +44,10 @@ UNIT = 'TFLOP/s'
 FALLBACK_PEAKS = {'hbm_gbs': 6650.0, 'bf16_tflops': 1590.0, 'bf16_tflops_sustained': 1400.0}
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures
-# summarised under profiles/.  The attention figure was captured at Z=2 (184.5 MB)
+# summarised under profiles/.  The attention figure was captured at Z=2 (225.8 MB)
 # and scaled by 4 to the Z=8 launch: every (batch, head) pair is independent, so
 # traffic grows in proportion.
-NCU_TRAFFIC_BYTES = {'attn_bwd_dkdv': 4 * 184.5e6, 'softmax_fwd': 638.5e6, 'softmax_bwd': 924.3e6}
+NCU_TRAFFIC_BYTES = {'attn_bwd_dkdv': 4 * 225.8e6, 'softmax_fwd': 638.5e6, 'softmax_bwd': 924.3e6}
 
 
 def peaks():
