@@ -108,6 +108,20 @@ int bsp_fixed_layout_build(int num_heads, int num_blocks, int mode, int block_st
                            int unidirectional, int numverts, int vertsize, int64_t* out);
 
 /*
+ * Sliding-window layouts: block-row i sees block-columns [i - below, i + above],
+ * the first `global_cols` block-columns and, per head, the `num_random`
+ * block-columns listed for it in random_cols [num_heads, num_blocks, num_random]
+ * (the caller draws them, so that any seeded generator can be used); the first
+ * `global_rows` block-rows see everything.  below = band - 1, above = 0 gives a
+ * causal band; below = above = window / 2 with random and global blocks a
+ * BigBird-style layout.  Writes int64 [num_heads, num_blocks, num_blocks].
+ * No counterpart in the reference (its SparsityConfig only knows "dense" and
+ * "fixed", deepspeedsparseselfattention.py:16-17).
+ */
+int bsp_window_layout_build(int num_heads, int num_blocks, int below, int above, int global_rows, int global_cols,
+                            const int32_t* random_cols, int num_random, int64_t* out);
+
+/*
  * Execution metadata consumed by the compute kernels (no counterpart in the
  * reference, whose kernels read the tables above; those tables can contain
  * duplicate / out-of-layout entries and are therefore never executed from).
@@ -332,7 +346,13 @@ int bsp_attn_bwd_parts(const void* q, const void* k, const void* v, const void* 
  *   limit     Z*H*L <= BSP_ATTN_STATIC_ROWS, else BSP_ERR_UNSUPPORTED.
  *   set-up    the first call on each device looks up the device address of the
  *             array (cudaGetSymbolAddress, with that device current) and caches
- *             it; make that first call outside any stream capture.
+ *             it; make that first call outside any stream capture.  The device
+ *             that `stream` belongs to must be the current device of the calling
+ *             thread.  That first call may also be the moment the driver loads
+ *             the library's device code and reserves the 4 MiB, so a caller that
+ *             forbids allocation after start-up should make one warm-up call
+ *             during start-up.  The cached address does not survive
+ *             cudaDeviceReset.
  *   sharing   every call on a device uses the same array, which keeps whatever
  *             the previous call left in it.  Nothing in it has to start at
  *             zero: the first kernel of the call overwrites the Z*H*L entries

@@ -12,9 +12,9 @@ table builders (MatMul.make_lut, _sparse_matmul.make_sdd_lut / make_dxx_lut /
 load_balance, _sparse_softmax.make_lut, _make_layout) run without a GPU.
 
 The reference checkout is located through the environment variable
-BSP_REFERENCE_ROOT (default: REFERENCE_ROOT below).  When it is absent every entry
-point here returns None / False; callers then fall back to the committed
-fixtures.
+BSP_REFERENCE_ROOT; without it a directory named `reference` beside this
+repository is tried.  When neither exists every entry point here returns
+None / False; callers then fall back to the committed fixtures.
 """
 import importlib
 import importlib.util
@@ -23,7 +23,7 @@ import sys
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
 REF_DIR = os.path.join(_HERE, '_ref')
-REFERENCE_ROOT = os.environ.get('BSP_REFERENCE_ROOT', '/root/reference')
+REFERENCE_ROOT = os.environ.get('BSP_REFERENCE_ROOT') or os.path.join(os.path.dirname(os.path.dirname(_HERE)), 'reference')
 _MOD = 'torch_blocksparse_cpp_utils'
 
 

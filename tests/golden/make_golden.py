@@ -11,6 +11,9 @@ fixtures it writes are committed so that the tests run without it.
                       stored in full
   lut_configs.json    SHA-256 + sizes of the same tables for the layouts of the
                       five benchmark configurations (too large to store)
+  fixed_layouts.npz   layouts returned by the reference's
+                      DeepSpeedSparseSelfAttention._make_layout
+                      (deepspeedsparseselfattention.py:51-65) for six argument sets
   dense_masked.npz    inputs and outputs of the reference's dense-masked test
                       oracles (tests/test_matmul.py:run_mm_reference,
                       tests/test_softmax.py:run_softmax_reference, with the
@@ -101,6 +104,20 @@ def config_layouts():
     return out
 
 
+FIXED_LAYOUT_ARGS = [(4, 16, 'fixed', 4, 'unidirectional', 1, 1), (4, 16, 'fixed', 4, 'bidirectional', 2, 2),
+                     (3, 32, 'fixed', 8, 'unidirectional', 4, 2), (2, 8, 'dense', 4, 'unidirectional', 1, 1),
+                     (16, 128, 'fixed', 4, 'bidirectional', 1, 1), (16, 128, 'fixed', 4, 'unidirectional', 1, 1)]
+
+
+def fixed_layout_cases(ref):
+    """The reference's own _make_layout on each argument set; keys are the arguments joined by '_'."""
+    make = ref.deepspeedsparseselfattention.DeepSpeedSparseSelfAttention._make_layout
+    out = {}
+    for args in FIXED_LAYOUT_ARGS:
+        out['_'.join(str(a) for a in args)] = make(*args).numpy().astype(np.int8)
+    return out
+
+
 def sha(a):
     return hashlib.sha256(np.ascontiguousarray(a).tobytes()).hexdigest()
 
@@ -188,7 +205,8 @@ def main():
         cfg[name] = entry
     json.dump(cfg, open(os.path.join(HERE, 'lut_configs.json'), 'w'), indent=1, sort_keys=True)
     np.savez_compressed(os.path.join(HERE, 'dense_masked.npz'), **dense_masked_cases())
-    for f in ('lut_small.npz', 'lut_configs.json', 'dense_masked.npz'):
+    np.savez_compressed(os.path.join(HERE, 'fixed_layouts.npz'), **fixed_layout_cases(ref))
+    for f in ('lut_small.npz', 'lut_configs.json', 'dense_masked.npz', 'fixed_layouts.npz'):
         print(f, os.path.getsize(os.path.join(HERE, f)))
 
 

@@ -209,6 +209,38 @@ def test_causal_mask_on_tcgen05_path(block, D, with_kpm):
     check(layout, block, q, k, v, do, True, 'add', 'mul', attn_mask=am2)
 
 
+def test_causal_check_runs_once_per_mask_tensor():
+    """forward() squeezes and casts the caller's mask into a new tensor object on every call; the
+    comparison against the causal mask is still made once per tensor the caller holds, and again
+    after the caller modifies it in place."""
+    Z, H, L, D, block = 1, 2, 256, 64, 64
+    layout = torch.tril(torch.ones((H, L // block, L // block), dtype=torch.long))
+    mod = SparseSelfAttention(layout=layout, block=block, fused=True)
+    q, k, v, _ = (t.to(DEV) for t in rand_qkv(Z, H, L, D, torch.float16))
+    am = torch.tril(torch.ones((1, 1, L, L))).to(DEV)          # 4-D and FP32, as a model would hold it
+    for _ in range(3):
+        mod(q, k, v, attn_mask=am)
+    assert mod.causal_checks == 1
+    am[0, 0, 0, 5] = 1                                          # in-place change: checked again, no longer causal
+    mod(q, k, v, attn_mask=am)
+    assert mod.causal_checks == 2 and not mod._is_causal(am.squeeze(), am)
+
+
+def test_operands_expanded_over_the_batch_fall_back_to_mma_sync():
+    """q, k, v expanded over the batch (stride 0) cannot be described to the tensor-map encoder:
+    the call still succeeds (on the mma.sync kernels) and matches the oracle."""
+    Z, H, L, D, block = 3, 2, 256, 64, 64
+    g = torch.Generator().manual_seed(4)
+    layout = (torch.rand((H, L // block, L // block), generator=g) > 0.4).long()
+    layout[:, :, 0] = 1
+    q, k, v, do = rand_qkv(1, H, L, D, torch.float16, seed=9)
+    mod = SparseSelfAttention(layout=layout, block=block, fused=True)
+    o = mod(*(t.to(DEV).expand(Z, -1, -1, -1) for t in (q, k, v)))
+    want = dm.attention_reference(q, k, v, layout, block, D ** -0.5)[0]
+    for z in range(Z):
+        assert_close(o[z:z + 1], want, 'expanded batch entry %d' % z)
+
+
 def test_sparsity_config_path_and_key_transposed():
     """The reference's constructor path: SparsityConfig 'fixed', key handed over
     pre-transposed as [.., head_dim, L] (deepspeedsparseselfattention.py:119-123)."""
@@ -294,20 +326,21 @@ def test_tcgen05_and_mma_sync_paths_agree(block, nb, dtype, D):
 
 def test_config5_full_layout_slice():
     """Benchmark configuration 5 at its full layout and length (L = 16384, block 128,
-    head_dim 128, BF16), batch reduced to 1: oracle on one head, both kernel families."""
+    head_dim 128, BF16), batch reduced to 1: oracle on three heads, both kernel families."""
     from torch_blocksparse_b200 import fused
     c = workloads.config5(small=False, Z=1)
     layout, block = c['layout'], c['block']
-    h = 7
-    want = dm.attention_reference(c['q'][:, h:h + 1], c['k'][:, h:h + 1], c['v'][:, h:h + 1], layout[h:h + 1], block,
-                                  c['scale'], do=c['do'][:, h:h + 1])
+    heads = (0, 7, 15)
+    want = {h: dm.attention_reference(c['q'][:, h:h + 1], c['k'][:, h:h + 1], c['v'][:, h:h + 1], layout[h:h + 1], block,
+                                      c['scale'], do=c['do'][:, h:h + 1]) for h in heads}
     try:
         for path in ('tc', 'mma'):
             fused.PATH = path
             mod = SparseSelfAttention(layout=layout, block=block, fused=True)
             got = run_module(mod, c['q'], c['k'], c['v'], c['do'])
-            for name, g_, w in zip(('o', 'dq', 'dk', 'dv'), got, want):
-                assert_close(g_[:, h:h + 1], w, 'config 5 %s on path %s' % (name, path))
+            for h in heads:
+                for name, g_, w in zip(('o', 'dq', 'dk', 'dv'), got, want[h]):
+                    assert_close(g_[:, h:h + 1], w, 'config 5 head %d %s on path %s' % (h, name, path))
     finally:
         fused.PATH = 'tc'
 
@@ -338,6 +371,81 @@ def test_multihead_attention_matches_torch_dense():
     ref_w = model[0].in_proj_weight.detach().clone()
     replace_mha(model, (layout, block))
     assert isinstance(model[0], MultiheadAttention) and torch.equal(model[0].in_proj_weight, ref_w)
+
+
+@pytest.mark.parametrize('kp_mode', ['add', 'mul'])
+@pytest.mark.parametrize('block,D', [(64, 64), (128, 128), (32, 64)])
+def test_fully_padded_window_gives_zeros_on_both_paths(block, D, kp_mode):
+    """Query rows whose every visible key is padded out (a padded tail inside a local window):
+    both kernel families return zeros for them, a log-sum-exp of -inf and finite gradients
+    everywhere (the reference's softmax would give NaN for such rows); the unpadded batch
+    entry still matches the oracle."""
+    from torch_blocksparse_b200 import fused as F
+    Z, H, nb = 2, 2, 6
+    L = nb * block
+    dtype = torch.float16
+    layout = torch.zeros((H, nb, nb), dtype=torch.long)
+    for i in range(nb):
+        layout[:, i, max(0, i - 1):i + 1] = 1                 # a band of two blocks, no global column
+    q, k, v, do = rand_qkv(Z, H, L, D, dtype, seed=block + D)
+    keep = torch.ones((Z, L), dtype=torch.bool)
+    keep[1, 3 * block:] = False                               # rows from block 4 on see padded keys only
+    kp = keep.to(dtype) if kp_mode == 'mul' else torch.where(keep, 0.0, float('-inf')).to(dtype)
+    mod = SparseSelfAttention(layout=layout, block=block, fused=True, key_padding_mask_mode=kp_mode)
+    try:
+        tc = run_module(mod, q, k, v, do, key_padding_mask=kp)
+        F.PATH = 'mma'
+        mma = run_module(mod, q, k, v, do, key_padding_mask=kp)
+    finally:
+        F.PATH = 'tc'
+    for name, a, b in zip(('o', 'dq', 'dk', 'dv'), tc, mma):
+        assert bool(torch.isfinite(a).all()) and bool(torch.isfinite(b).all()), name + ' has non-finite values'
+        assert_close(a.cpu(), b.cpu(), name + ' tcgen05 vs mma.sync')
+    assert float(tc[0].detach()[1, :, 4 * block:].abs().max()) == 0.0
+    assert float(mma[0].detach()[1, :, 4 * block:].abs().max()) == 0.0
+    want = dm.attention_reference(q[:1], k[:1], v[:1], layout, block, D ** -0.5, do=do[:1], key_padding_mask=kp[:1],
+                                  key_padding_mask_mode=kp_mode)
+    for name, g_, w in zip(('o', 'dq', 'dk', 'dv'), tc, want):
+        assert_close(g_[:1], w, 'unpadded batch entry ' + name)
+
+
+def test_config4_bidirectional_full_slices():
+    """Configuration 4 with the bidirectional layout at full length (L = 8192, 71 680 blocks),
+    batch reduced to 1: the oracle on two (batch, head) slices."""
+    c = workloads.config4('bidirectional', small=False, Z=1)
+    layout, block = c['layout'], c['block']
+    assert int(layout.sum()) == 71680
+    mod = SparseSelfAttention(layout=layout, block=block, fused=True)
+    got = run_module(mod, c['q'], c['k'], c['v'], c['do'])
+    for h in (0, 11):
+        want = dm.attention_reference(c['q'][:, h:h + 1], c['k'][:, h:h + 1], c['v'][:, h:h + 1], layout[h:h + 1], block,
+                                      c['scale'], do=c['do'][:, h:h + 1])
+        for name, g_, w in zip(('o', 'dq', 'dk', 'dv'), got, want):
+            assert_close(g_[:, h:h + 1], w, 'bidirectional head %d %s' % (h, name))
+
+
+def test_multihead_attention_backward_matches_torch_dense():
+    """Gradients of the seq-first drop-in (input and every parameter) against
+    torch.nn.MultiheadAttention on an all-ones layout."""
+    from torch_blocksparse_b200 import MultiheadAttention
+    torch.manual_seed(1)
+    block, B, H, L, E = 16, 2, 2, 128, 128
+    layout = torch.ones(H, L // block, L // block).long()
+    sparse = MultiheadAttention(E, H, layout, block).to(DEV).half()
+    dense = torch.nn.MultiheadAttention(E, H).to(DEV).half()
+    for ps, pd in zip(sparse.parameters(), dense.parameters()):
+        ps.data.copy_(pd.data)
+    x0 = torch.rand(L, B, E, device=DEV).half()
+    dy = (torch.rand(L, B, E, device=DEV) - 0.5).half()
+    grads = []
+    for mod in (sparse, dense):
+        x = x0.clone().requires_grad_()
+        y, _ = mod(x, x, x, need_weights=False)
+        y.backward(dy)
+        grads.append([x.grad] + [p.grad for p in mod.parameters()])
+    names = ['x'] + [n for n, _ in sparse.named_parameters()]
+    for name, a, b in zip(names, *grads):
+        assert_close(a, b, 'MultiheadAttention backward: ' + name)
 
 
 def test_host_pipeline_matches_device_path():

@@ -145,6 +145,20 @@ def test_non_contiguous_and_odd_inputs():
         MatMul(layout, block, 'sdd')(torch.zeros((1, 2, 128, 40), device=DEV), torch.zeros((1, 2, 40, 96), device=DEV))
 
 
+@pytest.mark.parametrize('block', [32, 64, 128])
+def test_layout_without_blocks_gives_zeros(block):
+    """dsd / dds with an all-zero layout: the sparse operand has no block and the dense result
+    is all zeros (the reference zero-fills through zero-length segments, matmul.py:246-264)."""
+    H, nb, Z, N = 2, 2, 2, 128
+    layout = torch.zeros((H, nb, nb), dtype=torch.long)
+    s = torch.zeros((Z, 0, block, block), dtype=torch.float16, device=DEV)
+    d = torch.randn((Z, H, nb * block, N), dtype=torch.float16, device=DEV)
+    out = MatMul(layout, block, 'dsd')(s, d)
+    assert out.shape == (Z, H, nb * block, N) and float(out.abs().max()) == 0.0
+    out = MatMul(layout, block, 'dds')(d.transpose(2, 3).contiguous(), s)
+    assert out.shape == (Z, H, N, nb * block) and float(out.abs().max()) == 0.0
+
+
 def test_config1():
     c = workloads.config1()
     want, _, _ = dm.matmul_reference(c['a'], c['b'], 'sdd', True, False, c['layout'], 16)
@@ -161,7 +175,9 @@ def test_config2_small(mode, ta, tb):
     run_both(c['layout'], 32, mode, ta, tb, c['a'], c['b'], c['dc'], 'config 2 small')
 
 
-@pytest.mark.parametrize('mode,ta,tb', [('dsd', False, False), ('dds', True, True)])
+@pytest.mark.parametrize('mode', ['dsd', 'dds'])
+@pytest.mark.parametrize('ta', [False, True])
+@pytest.mark.parametrize('tb', [False, True])
 def test_config2_full_slice(mode, ta, tb):
     """Full-size configuration 2 on the GPU; the oracle checks one (batch, head)
     slice of the result and of both gradients."""

@@ -180,3 +180,20 @@ def test_config3_small_and_full():
                                    rpe=c['rpe'][h:h + 1], key_padding_mask=c['key_padding_mask'][z:z + 1],
                                    attn_mask=c['attn_mask'], key_padding_mask_mode='add', attn_mask_mode='mul')
     assert_close(y[z:z + 1, b0:b1], want, 'config3 slice')
+    # backward at full size: dx = y (dy - sum_row y dy) scale, written over dy; rows of dx sum to
+    # zero, and the same slice against the oracle
+    dy = c['dy'].to(DEV)
+    _, want_dx = dm.softmax_reference(c['x'][z:z + 1, b0:b1], layout[h:h + 1], block, scale=c['scale'],
+                                      rpe=c['rpe'][h:h + 1], key_padding_mask=c['key_padding_mask'][z:z + 1],
+                                      attn_mask=c['attn_mask'], key_padding_mask_mode='add', attn_mask_mode='mul',
+                                      dy=c['dy'][z:z + 1, b0:b1])
+    xg = c['x'].to(DEV).requires_grad_()
+    y2 = op(xg * 1, scale=c['scale'], rpe=rpe[None].expand(x.size(0), -1, -1, -1),
+            key_padding_mask=c['key_padding_mask'].to(DEV), attn_mask=c['attn_mask'].to(DEV),
+            key_padding_mask_mode='add', attn_mask_mode='mul')
+    y2.backward(dy)
+    dx = xg.grad
+    rowsum.zero_()
+    rowsum.index_add_(1, owner, dx.float().sum(-1))
+    assert float(rowsum.abs().max()) < 2e-2
+    assert_close(dx[z:z + 1, b0:b1], want_dx, 'config3 backward slice')

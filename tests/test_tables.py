@@ -1,13 +1,18 @@
 """The native table builders (through the C ABI) against the reference's tables
 (fixtures), the CPU restatement (random layouts) and the live reference when mounted."""
 import ctypes
+import hashlib
+import json
+import os
 
 import numpy as np
 import pytest
 import torch
 
 from oracle import lut as olut
-from tests.util import load_npz
+import workloads
+from tests.util import GOLDEN, load_npz
+from torch_blocksparse_b200 import layouts
 from torch_blocksparse_b200 import _lib, tables
 
 
@@ -94,6 +99,48 @@ def test_fixed_layout_matches_restatement():
         tables.make_fixed_layout(2, 8, 'fixed', 4, 'unidirectional', 5, 1)
     with pytest.raises(NotImplementedError):
         tables.make_fixed_layout(2, 8, 'variable', 4, 'unidirectional', 1, 1)
+
+
+def test_fixed_layout_matches_reference_fixture():
+    """Native generator and CPU restatement against layouts the reference's own
+    _make_layout (deepspeedsparseselfattention.py:51-65) returned."""
+    z = load_npz('fixed_layouts.npz')
+    assert len(z.files) == 6
+    for key in z.files:
+        f = key.split('_')
+        args = (int(f[0]), int(f[1]), f[2], int(f[3]), f[4], int(f[5]), int(f[6]))
+        want = z[key].astype(np.int64)
+        assert np.array_equal(tables.make_fixed_layout(*args).numpy(), want), key
+        assert np.array_equal(olut.make_fixed_layout(*args), want), key
+
+
+def test_native_builders_hash_to_reference_on_config_layouts():
+    """The native builders on the full-size layouts of the benchmark configurations against
+    SHA-256 digests of the reference's own tables (matmul.py:281-297, 372-458; softmax.py:201-221)."""
+    cfg = json.load(open(os.path.join(GOLDEN, 'lut_configs.json')))
+    sha = lambda a: hashlib.sha256(np.ascontiguousarray(a).tobytes()).hexdigest()
+    cases = {
+        'c1': workloads.config1()['layout'],
+        'c2': torch.bernoulli(torch.full((8, 64, 64), 0.25), generator=torch.Generator().manual_seed(0)).long(),
+        'c3_full': layouts.causal_band(16, 64, 4, 1),
+        'c4_uni_full': layouts.fixed(16, 128, 4, 'unidirectional'),
+        'c4_bi_full': layouts.fixed(16, 128, 4, 'bidirectional'),
+        'c5_full': layouts.bigbird(16, 128, 3, 3, 2, seed=0),
+    }
+    for name, layout in cases.items():
+        e = cfg[name]
+        assert sha(layout.numpy()) == e['layout_sha'], name + ': generator drifted from the fixture'
+        assert int(layout.sum()) == e['nnz']
+        block = e['block']
+        luts, _, widths, packs = tables.make_sdd_lut(layout, block)
+        assert sha(_flat(luts)) == e['sdd_b%d_lut' % block]['sha'], name
+        assert _flat(luts).size == e['sdd_b%d_lut' % block]['size'], name
+        for step in (8, 16):
+            for trans in (0, 1):
+                lut, _, _, _ = tables.make_dxx_lut(layout, block, step, bool(trans))
+                assert sha(lut.numpy()) == e['dxx_b%d_s%d_t%d_lut' % (block, step, trans)]['sha'], (name, step, trans)
+        lut, _ = tables.make_softmax_lut(layout)
+        assert sha(lut.numpy()) == e['softmax_lut']['sha'], name
 
 
 def test_meta_is_consistent_csr_and_csc():

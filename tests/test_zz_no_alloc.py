@@ -19,7 +19,18 @@ pytestmark = pytest.mark.gpu
 DEV = 'cuda'
 
 
-def _backward(entry, t, meta, block, scale, delta=None):
+def _tile_args(tiles, device):
+    """(header, device buffer) of the tcgen05 tile lists, or two NULLs for the mma.sync kernels."""
+    if tiles is None:
+        return [None, None]
+    return [tiles.hdr.data_ptr(), tiles.on(device).data_ptr()]
+
+
+def _code(x):
+    return _lib.F16 if x.dtype == torch.float16 else _lib.BF16
+
+
+def _backward(entry, t, meta, block, scale, delta=None, tiles=None):
     q, k, v, o, do, lse = t
     Z, H, L, D = q.shape
     grads = [torch.empty_like(q) for _ in range(3)]
@@ -27,9 +38,9 @@ def _backward(entry, t, meta, block, scale, delta=None):
     head = [q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), do.data_ptr(), lse.data_ptr()]
     if delta is not None:
         head.append(delta.data_ptr())
-    args = head + [g.data_ptr() for g in grads] + [_lib.F16, block, Z, H, L, D] \
+    args = head + [g.data_ptr() for g in grads] + [_code(q), block, Z, H, L, D] \
         + [*st(q), *st(k), *st(v), *st(o), *st(do)] \
-        + [meta.hdr.data_ptr(), meta.on(q.device).data_ptr(), None, None, scale] \
+        + [meta.hdr.data_ptr(), meta.on(q.device).data_ptr()] + _tile_args(tiles, q.device) + [scale] \
         + [None, 0, 0, 0, None, 0, 0, None, 0, 0] \
         + [torch.cuda.current_stream().cuda_stream]
     _lib.check(entry(*args))
@@ -37,33 +48,41 @@ def _backward(entry, t, meta, block, scale, delta=None):
     return grads
 
 
-def _forward(c, meta):
+def _forward(c, meta, tiles=None):
     q, k, v, do = (c[n].to(DEV) for n in ('q', 'k', 'v', 'do'))
     Z, H, L, D = q.shape
     o = torch.empty_like(q)
     lse = torch.empty((Z, H, L), dtype=torch.float32, device=DEV)
     st = lambda x: (x.stride(0), x.stride(1), x.stride(2))
     _lib.check(_lib.lib().bsp_attn_fwd(
-        q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(), _lib.F16, c['block'], Z, H, L, D,
-        *st(q), *st(k), *st(v), *st(o), meta.hdr.data_ptr(), meta.on(q.device).data_ptr(), None, None, c['scale'],
+        q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(), _code(q), c['block'], Z, H, L, D,
+        *st(q), *st(k), *st(v), *st(o), meta.hdr.data_ptr(), meta.on(q.device).data_ptr(), *_tile_args(tiles, q.device), c['scale'],
         None, 0, 0, 0, None, 0, 0, None, 0, 0, torch.cuda.current_stream().cuda_stream))
     return q, k, v, o, do, lse
 
 
-def test_static_scratch_backward_matches_caller_scratch_backward_twice():
+@pytest.mark.parametrize('with_tiles', [False, True])
+def test_static_scratch_backward_matches_caller_scratch_backward_twice(with_tiles):
+    """Without tile lists the mma.sync kernels read the built-in scratch; with them the tcgen05
+    dK/dV kernel fetches it by bulk copies and the dQ kernel by plain loads."""
+    from torch_blocksparse_b200 import fused
     L = _lib.lib()
-    for attention in ('unidirectional', 'bidirectional'):       # two different problems back to back
-        c = workloads.config4(attention, small=True)
+    cases = [workloads.config4('unidirectional', small=True), workloads.config4('bidirectional', small=True),
+             workloads.config5(small=True)]                      # FP16 head_dim 64 twice, then BF16 head_dim 128
+    for c in cases:                                              # different problems back to back
         meta = tables.build_meta(c['layout'])
-        t = _forward(c, meta)
+        tiles = tables.build_attn_tiles(c['layout'], c['block']) if with_tiles else None
+        assert (tiles is not None) == with_tiles
+        t = _forward(c, meta, tiles)
         Z, H, Ln, _ = t[0].shape
         delta = torch.empty((Z, H, Ln), dtype=torch.float32, device=DEV)
-        want = _backward(L.bsp_attn_bwd, t, meta, c['block'], c['scale'], delta)
+        want = _backward(L.bsp_attn_bwd, t, meta, c['block'], c['scale'], delta, tiles)
         for call in range(2):
-            got = _backward(L.bsp_attn_bwd_static, t, meta, c['block'], c['scale'])
+            got = _backward(L.bsp_attn_bwd_static, t, meta, c['block'], c['scale'], None, tiles)
             for name, g, w in zip(('dq', 'dk', 'dv'), got, want):
-                assert torch.equal(g, w), '%s differs on call %d (%s)' % (name, call, attention)
+                assert torch.equal(g, w), '%s differs on call %d' % (name, call)
                 assert_close(g, w, name)
+    assert fused.device_status() == 0, 'a bounded device-side wait expired'
 
 
 def test_static_scratch_size_limit_is_reported():

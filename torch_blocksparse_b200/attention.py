@@ -67,6 +67,7 @@ class DeepSpeedSparseSelfAttention(nn.Module):
         self.ops = dict()
         self.tiles = dict()
         self._causal_cache = dict()
+        self.causal_checks = 0            # comparisons of a mask against the causal one made so far
 
     def get_layout(self, H, L):
         """The [H, L/block, L/block] layout used for H heads and sequence length L."""
@@ -96,20 +97,25 @@ class DeepSpeedSparseSelfAttention(nn.Module):
             self.tiles[key] = tables.build_attn_tiles(layout, self.block) if self.fused else None
         return self.ops[key]
 
-    def _is_causal(self, attn_mask):
+    def _is_causal(self, attn_mask, owner=None):
         """True when a 'mul' attention mask is exactly the lower-triangular (causal) mask: the
         fused kernels then derive it from the indices.  The answer is remembered per tensor
-        object and version (not per address: a freed tensor's address is reused); a caller
+        object and version (not per address: a freed tensor's address is reused).  `owner` is
+        the tensor the caller handed in when `attn_mask` is a view or a converted copy made from
+        it on the way here (forward() squeezes and casts the mask, which creates a new tensor
+        object on every call): the answer is then remembered for the caller's tensor.  A caller
         that builds a new mask tensor for every call pays the comparison every time."""
-        entry = self._causal_cache.get(id(attn_mask))
-        if entry is not None and entry[0]() is attn_mask and entry[1] == attn_mask._version:
+        key = attn_mask if owner is None else owner
+        entry = self._causal_cache.get(id(key))
+        if entry is not None and entry[0]() is key and entry[1] == key._version:
             return entry[2]
+        self.causal_checks += 1
         L = attn_mask.size(-1)
         hit = (attn_mask.dim() == 2 and attn_mask.size(0) == L and
                bool(torch.equal(attn_mask != 0, torch.ones((L, L), dtype=torch.bool, device=attn_mask.device).tril())))
         if len(self._causal_cache) > 16:
             self._causal_cache.clear()
-        self._causal_cache[id(attn_mask)] = (weakref.ref(attn_mask), attn_mask._version, hit)
+        self._causal_cache[id(key)] = (weakref.ref(key), key._version, hit)
         return hit
 
     def transpose_key_for_scores(self, x, L):
@@ -139,24 +145,29 @@ class DeepSpeedSparseSelfAttention(nn.Module):
             key_padding_mask = self.transpose_mask_for_sparse(query.dtype, key_padding_mask, is_key_padding_mask=True)
             if key_padding_mask.dim() == 1:
                 key_padding_mask = key_padding_mask.unsqueeze(0)
+        mask_owner = attn_mask
         if attn_mask is not None:
             attn_mask = self.transpose_mask_for_sparse(query.dtype, attn_mask)
-        return self.attend(query, key, value, float(head_dim) ** -0.5, rpe, key_padding_mask, attn_mask)
+        return self.attend(query, key, value, float(head_dim) ** -0.5, rpe, key_padding_mask, attn_mask,
+                           mask_owner=mask_owner)
 
-    def attend(self, query, key, value, scaling, rpe=None, key_padding_mask=None, attn_mask=None):
+    def attend(self, query, key, value, scaling, rpe=None, key_padding_mask=None, attn_mask=None, mask_owner=None):
         """The attention core on [bsz, heads, L, head_dim] operands with an explicit score scale
-        (masks already in the dtype of the operands)."""
+        (masks already in the dtype of the operands).  `mask_owner`: the caller's own attention
+        mask tensor when `attn_mask` was derived from it (see _is_causal)."""
         bsz, num_heads, tgt_len, head_dim = query.size()
         if key_padding_mask is not None and key_padding_mask.dtype != query.dtype:
             key_padding_mask = key_padding_mask.to(query.dtype)
         if attn_mask is not None and attn_mask.dtype != query.dtype:
+            if mask_owner is None:
+                mask_owner = attn_mask
             attn_mask = attn_mask.to(query.dtype)
         sdd_nt, dsd_nn, softmax = self.get_ops(num_heads, tgt_len)
         if self.fused:
             from .fused import fused_attention, fused_supported
             if fused_supported(query, self.block):
                 am_mode = self.attn_mask_mode
-                if attn_mask is not None and am_mode == 'mul' and self._is_causal(attn_mask):
+                if attn_mask is not None and am_mode == 'mul' and self._is_causal(attn_mask, mask_owner):
                     am_mode = 'causal'
                 return fused_attention(query, key, value, sdd_nt.meta, self.block, scaling, rpe,
                                        key_padding_mask, attn_mask,

@@ -32,6 +32,12 @@ namespace {
 
 // The tcgen05 kernels cover FP16 / BF16 on 128-row tiles, without rpe; a key-padding mask is
 // taken when its rows can be fetched in 16-byte pieces, an attention mask when it is the causal one.
+// Strides the tensor-map encoder takes: positive (an operand expanded over the batch or the heads
+// has stride 0 and stays on the mma.sync kernels).
+bool tma_strides(int Z, int H, int64_t sz, int64_t sh, int64_t sr) {
+  return sr > 0 && (H == 1 || sh > 0) && (Z == 1 || sz > 0);
+}
+
 bool tc_eligible(const int32_t* tiles_hdr, const int32_t* tiles, int block, int L, int D,
                  const void* rpe, const void* kpm, int64_t kpm_sz, const void* am, int am_mul) {
   // an attention mask is only taken when the caller vouches that it is the causal one (flag 2)
@@ -128,7 +134,8 @@ extern "C" int bsp_attn_fwd(const void* q, const void* k, const void* v, void* o
   p.q_sz = q_sz; p.q_sh = q_sh; p.q_sr = q_sr; p.k_sz = k_sz; p.k_sh = k_sh; p.k_sr = k_sr;
   p.v_sz = v_sz; p.v_sh = v_sh; p.v_sr = v_sr; p.o_sz = o_sz; p.o_sh = o_sh; p.o_sr = o_sr;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  if (tc_eligible(tiles_hdr, tiles, block, L, D, rpe, kpm, kpm_sz, am, am_mul))
+  if (tc_eligible(tiles_hdr, tiles, block, L, D, rpe, kpm, kpm_sz, am, am_mul) &&
+      tma_strides(Z, H, q_sz, q_sh, q_sr) && tma_strides(Z, H, k_sz, k_sh, k_sr) && tma_strides(Z, H, v_sz, v_sh, v_sr))
     return attn_fwd_tc(q, k, v, o, lse, dtype, Z, H, L, D, q_sz, q_sh, q_sr, k_sz, k_sh, k_sr, v_sz, v_sh, v_sr,
                        o_sz, o_sh, o_sr, tiles_hdr, tiles, scale, kpm, kpm_sz, kpm_mul, am != nullptr, st);
   if (dtype == BSP_F16) return attn_fwd_t<__half>(p, block, D, Z, st);
@@ -168,7 +175,9 @@ extern "C" int bsp_attn_bwd_parts(const void* q, const void* k, const void* v, c
   p.v_sz = v_sz; p.v_sh = v_sh; p.v_sr = v_sr; p.o_sz = o_sz; p.o_sh = o_sh; p.o_sr = o_sr;
   p.do_sz = do_sz; p.do_sh = do_sh; p.do_sr = do_sr;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  if (tc_eligible(tiles_hdr, tiles, block, L, D, rpe, kpm, kpm_sz, am, am_mul)) {
+  if (tc_eligible(tiles_hdr, tiles, block, L, D, rpe, kpm, kpm_sz, am, am_mul) &&
+      tma_strides(Z, H, q_sz, q_sh, q_sr) && tma_strides(Z, H, k_sz, k_sh, k_sr) && tma_strides(Z, H, v_sz, v_sh, v_sr) &&
+      tma_strides(Z, H, do_sz, do_sh, do_sr)) {
     // delta = rowsum(o * do) by the streaming kernel, the two matrix kernels on tcgen05
     if (parts & 1) {
       const int rc = dtype == BSP_F16 ? attn_bwd_t<__half>(p, block, D, Z, 1, st) : attn_bwd_t<__nv_bfloat16>(p, block, D, Z, 1, st);

@@ -247,8 +247,9 @@ __global__ void __launch_bounds__(AttnCfg<B, D>::NT) attn_fwd_kernel(AttnArgs p)
     lsum[hr] += __shfl_xor_sync(0xffffffffu, lsum[hr], 1);
     lsum[hr] += __shfl_xor_sync(0xffffffffu, lsum[hr], 2);
   }
-  // a row whose every entry is masked has l == 0: 0 * inf = NaN, as the reference's softmax gives
-  const float inv[2] = {1.f / lsum[0], 1.f / lsum[1]};
+  // a row whose every entry is masked has l == 0: its output is zero and its log-sum-exp -inf
+  // (the reference's softmax gives NaN there; the tcgen05 kernels agree with this choice)
+  const float inv[2] = {lsum[0] > 0.f ? 1.f / lsum[0] : 0.f, lsum[1] > 0.f ? 1.f / lsum[1] : 0.f};
 #pragma unroll
   for (int j = 0; j < DI; ++j) {
     *reinterpret_cast<uint32_t*>(orow + (int64_t)g * p.o_sr + j * 8 + 2 * t4) = pack2<T>(oacc[j][0] * inv[0], oacc[j][1] * inv[0]);
@@ -256,8 +257,8 @@ __global__ void __launch_bounds__(AttnCfg<B, D>::NT) attn_fwd_kernel(AttnArgs p)
   }
   if (t4 == 0) {
     // base-2 units, the domain the row maximum is tracked in: log2(sum_j 2^(f_j * log2 e))
-    lrow[g] = mrow[0] + log2f(lsum[0]);
-    lrow[g + 8] = mrow[1] + log2f(lsum[1]);
+    lrow[g] = lsum[0] > 0.f ? mrow[0] + log2f(lsum[0]) : kNegInfA;
+    lrow[g + 8] = lsum[1] > 0.f ? mrow[1] + log2f(lsum[1]) : kNegInfA;
   }
 }
 
@@ -391,7 +392,9 @@ __global__ void __launch_bounds__(AttnCfg<B, D>::NT) attn_bwd_kv_kernel(AttnArgs
       for (int r = 0; r < 4; ++r) {
         const int m = c * 8 + 2 * t4 + (r & 1);            // query row inside the tile
         float pr;                                          // P = 2^(f * log2 e - lse)
-        if (has_mask) pr = fast_exp2(fmaf(apply_masks<T>(st[c][r], p, z, h, grow0 + c * 8 + (r & 1), gcol0 + 8 * (r >> 1)), kLog2e, -ls[m]));
+        // (a query row without any visible key has lse = -inf: +inf makes its probabilities 0, not NaN)
+        if (has_mask) pr = fast_exp2(fmaf(apply_masks<T>(st[c][r], p, z, h, grow0 + c * 8 + (r & 1), gcol0 + 8 * (r >> 1)), kLog2e,
+                                          ls[m] == kNegInfA ? kNegInfA : -ls[m]));
         else pr = fast_exp2(fmaf(st[c][r], sl2, -ls[m]));
         st[c][r] = pr;
         dp[c][r] = pr * (dp[c][r] - es[m]) * p.scale;
@@ -471,7 +474,10 @@ __global__ void __launch_bounds__(AttnCfg<B, D>::NT) attn_bwd_q_kernel(AttnArgs 
   load_a_frags<T, D, PD>(df, Ds, warp * 16, lane);
   const int grow0 = i * B + warp * 16 + g;
   const int64_t zhl = (int64_t)(z * p.H + h) * p.L;
-  const float lse[2] = {p.lse[zhl + grow0], p.lse[zhl + grow0 + 8]};
+  float lse[2] = {p.lse[zhl + grow0], p.lse[zhl + grow0 + 8]};
+  // (a query row without any visible key has lse = -inf: +inf makes its probabilities 0, not NaN)
+  if (lse[0] == kNegInfA) lse[0] = -kNegInfA;
+  if (lse[1] == kNegInfA) lse[1] = -kNegInfA;
   const float dlt[2] = {p.delta[zhl + grow0], p.delta[zhl + grow0 + 8]};
 
   float dq[DI][4];

@@ -48,13 +48,6 @@ namespace bsp {
 // Set by a kernel whose bounded wait expired; read by bsp_device_status().
 static __device__ int g_tc_status;
 
-#ifdef BSP_TC_TRACE
-// Development aid, compiled out of the library: timestamps of the first CTA's pipeline events.
-__device__ long long g_tc_trace[3][64][6];
-#define TC_TRACE(role, t, k) do { if (blockIdx.x == 0 && blockIdx.y == 0 && (t) < 64) g_tc_trace[role][t][k] = clock64(); } while (0)
-#else
-#define TC_TRACE(role, t, k) do { } while (0)
-#endif
 
 namespace {
 
@@ -135,6 +128,40 @@ BSP_DEVI void mask_causal(uint32_t (&s)[N], int col0, int row) {
   for (int i = 0; i < N; ++i)
     if (ROWS_ARE_KEYS ? (col0 + i < row) : (col0 + i > row)) s[i] = kNegInfBits;
 }
+// ---- packed FP32 arithmetic (two values per instruction on sm_100)
+BSP_DEVI float2 f2(float a, float b) { return make_float2(a, b); }
+BSP_DEVI float2 u2f(uint32_t a, uint32_t b) { return make_float2(__uint_as_float(a), __uint_as_float(b)); }
+BSP_DEVI float max3(float a, float b, float c) {
+  float r;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+  return r;
+}
+// Maximum of 32 score registers with three-input maxima.
+BSP_DEVI float max32(const uint32_t (&s)[32]) {
+  float m0 = max3(__uint_as_float(s[0]), __uint_as_float(s[1]), __uint_as_float(s[2]));
+  float m1 = max3(__uint_as_float(s[3]), __uint_as_float(s[4]), __uint_as_float(s[5]));
+  float m2 = max3(__uint_as_float(s[6]), __uint_as_float(s[7]), __uint_as_float(s[8]));
+  float m3 = max3(__uint_as_float(s[9]), __uint_as_float(s[10]), __uint_as_float(s[11]));
+#pragma unroll
+  for (int i = 12; i < 28; i += 8) {
+    m0 = max3(m0, __uint_as_float(s[i]), __uint_as_float(s[i + 1]));
+    m1 = max3(m1, __uint_as_float(s[i + 2]), __uint_as_float(s[i + 3]));
+    m2 = max3(m2, __uint_as_float(s[i + 4]), __uint_as_float(s[i + 5]));
+    m3 = max3(m3, __uint_as_float(s[i + 6]), __uint_as_float(s[i + 7]));
+  }
+  m0 = max3(m0, __uint_as_float(s[28]), __uint_as_float(s[29]));
+  m1 = max3(m1, __uint_as_float(s[30]), __uint_as_float(s[31]));
+  return fmaxf(max3(m0, m1, m2), m3);
+}
+// The exponentials of a pair on the special-function unit; y is the exponent (SIGN = 1) or its
+// negative (SIGN = -1: the negation folds into the instruction's operand).  A cubic on the FMA
+// pipe for a share of the pairs was measured and lost: in an isolated loop the best mix gave
+// 17.0 instead of 13.9 exponentials per clock and SM, inside these kernels every share was slower.
+template <int SIGN>
+BSP_DEVI float2 exp2_pair(float2 y) {
+  return f2(fast_exp2(SIGN > 0 ? y.x : -y.x), fast_exp2(SIGN > 0 ? y.y : -y.y));
+}
+
 template <typename T> struct IsBf16 { static constexpr int v = 0; };
 template <> struct IsBf16<__nv_bfloat16> { static constexpr int v = 1; };
 
@@ -218,7 +245,6 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
   __shared__ int failed;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  if (tid == 0) TC_TRACE(0, 60, 0);
   // One-dimensional grid, batch entries of a tile adjacent: CTAs start in the order of the
   // tiles' lengths (longest first) over the whole launch, not per batch entry.
   const int z = blockIdx.x % a.Z;
@@ -251,7 +277,6 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
   auto load_chunk = [&](int t, int crow) {
     const int stage = t % ST;
     unsigned char* sp = stg + stage * C::STAGE;
-    TC_TRACE(0, t, 0);
     mbar_expect_tx(&bar_full[stage], 2 * C::CH_BYTES + C::TAIL_BYTES);
     for (int at = 0; at < ATOMS; ++at) {
       tma_load_4d(sp + at * 8192, &m_ch0, &bar_full[stage], at * 64, crow, h, z);
@@ -298,7 +323,6 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
   fence_after();
   const uint32_t tmem = tmem_slot;
   volatile int* fl = &failed;
-  if (tid == 0) TC_TRACE(0, 60, 1);
 
   if (warp >= NC) {
     // ------------------------------------------------------------------ loader and MMA issuers
@@ -359,7 +383,6 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
             for (int ks = 1; ks < KS; ++ks) mma_ss_acc(ts + 64, a1[ks], sb1[ks], idesc_kk);
           }
         }
-        TC_TRACE(1, t, 5);
         commit(bar);
       };
       uint64_t vb0[ATOMS * 4], vb1[ATOMS * 4];              // chunk operands of the accumulation being prepared
@@ -417,18 +440,14 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
       // issuer, which has less to issue, also refills the ring of chunk operands.
       if (warp == NC) {
         bool ok = mbar_wait(C::RES_T ? &bar_rt : &bar_res, 0, fl);
-        TC_TRACE(0, 60, 2);
         for (int t = 0; ok && t < ntiles; ++t) {
           prep_scores(t);
-          TC_TRACE(0, t, 5);
           ok = mbar_wait(&bar_full[t % ST], (t / ST) & 1, fl);
-          TC_TRACE(1, t, 0);
           if (C::ER || C::ER2) {
             if (ok && t >= 1) ok = mbar_wait(&bar_rd, (t - 1) & 1, fl);     // scores of chunk t - 1 are in registers
           } else {
             if (ok && t >= NBUF) ok = mbar_wait(&bar_acc[(t - NBUF) & 3], ((t - NBUF) >> 2) & 1, fl);
           }
-          TC_TRACE(1, t, 1);
           if (!ok) break;
           fence_after();
           if (C::ER2) {
@@ -442,7 +461,6 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
           } else {
             scores(t, 3, &bar_s[t % NBUF]);
           }
-          TC_TRACE(1, t, 2);
         }
       } else {
         bool ok = true;
@@ -459,11 +477,9 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
           prep_acc(t);
           ok = mbar_wait(&bar_full[t % ST], (t / ST) & 1, fl) &&
                (C::ER ? mbar_wait(&bar_p[t & 1], (t >> 1) & 1, fl) : mbar_wait(&bar_p[t % NBUF], (t / NBUF) & 1, fl));
-          TC_TRACE(1, t, 3);
           if (!ok) break;
           fence_after();
           accumulate(t);
-          TC_TRACE(1, t, 4);
         }
         if (ok) commit(&bar_done);
       }
@@ -513,15 +529,12 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
         } else {
           valid = (a.mask[first + t] >> half) & 1;                    // uniform per warp
         }
-        TC_TRACE(2, t, 0);
         ok = mbar_wait_warp(&bar_s[t % NBUF], (t / NBUF) & 1, fl);
-        TC_TRACE(2, t, 1);
         if (!ok) break;
         fence_after();
         uint32_t sr[32];
         tmem_ld32(ts, sr);
         tmem_ld_wait();
-        TC_TRACE(2, t, 2);
         if (partial) mask_pieces(sr, pieces);
         if (FINE && a.causal) mask_causal<32, false>(sr, a.chunk[first + t] * 64 + chalf * 32, (int)grow);
         float mt = kNegInfT;
@@ -533,13 +546,13 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
               float b[8];
               kpm_terms8<T>(bp + g * 16, a.kpm_mul, b);
 #pragma unroll
-              for (int i = 0; i < 8; ++i) sr[8 * g + i] = __float_as_uint(fmaf(__uint_as_float(sr[8 * g + i]), a.scale_log2, b[i]));
+              for (int i = 0; i < 8; i += 2) {
+                const float2 y = __ffma2_rn(u2f(sr[8 * g + i], sr[8 * g + i + 1]), f2(a.scale_log2, a.scale_log2), f2(b[i], b[i + 1]));
+                sr[8 * g + i] = __float_as_uint(y.x); sr[8 * g + i + 1] = __float_as_uint(y.y);
+              }
             }
           }
-          float m4[4] = {kNegInfT, kNegInfT, kNegInfT, kNegInfT};
-#pragma unroll
-          for (int i = 0; i < 32; ++i) m4[i & 3] = fmaxf(m4[i & 3], __uint_as_float(sr[i]));
-          mt = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])) * (KPM ? 1.f : a.scale_log2);
+          mt = max32(sr) * (KPM ? 1.f : a.scale_log2);
         }
         // the reference maximum is only raised when the row maximum outgrows it by 2^8
         const bool grow_m = mt > m_ref + 8.f;
@@ -565,41 +578,39 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
         }
         // exponentials in two halves of 16 columns: eight packed registers live at a time
         if (valid) {
-          float s4[4] = {0.f, 0.f, 0.f, 0.f};
+          float2 s2[2] = {f2(0.f, 0.f), f2(0.f, 0.f)};
           // (with a mask or absent pieces a row may still have seen -inf only: its reference stays 0 then)
           const float m_use = ((KPM || FINE) && m_ref == kNegInfT) ? 0.f : m_ref;
+          const float2 nm2 = f2(-m_use, -m_use), sl2 = f2(a.scale_log2, a.scale_log2);
 #pragma unroll
           for (int hp = 0; hp < 2; ++hp) {
             uint32_t ph[8];
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
-              const float s0 = __uint_as_float(sr[16 * hp + 2 * i]), s1 = __uint_as_float(sr[16 * hp + 2 * i + 1]);
-              const float p0 = KPM ? fast_exp2(s0 - m_use) : fast_exp2(fmaf(s0, a.scale_log2, -m_use));
-              const float p1 = KPM ? fast_exp2(s1 - m_use) : fast_exp2(fmaf(s1, a.scale_log2, -m_use));
-              s4[i & 3] += p0 + p1;
-              ph[i] = pack16<T>(p0, p1);
+              const float2 s01 = u2f(sr[16 * hp + 2 * i], sr[16 * hp + 2 * i + 1]);
+              const float2 y = KPM ? __fadd2_rn(s01, nm2) : __ffma2_rn(s01, sl2, nm2);
+              const float2 p = exp2_pair<1>(y);
+              s2[i & 1] = __fadd2_rn(s2[i & 1], p);
+              ph[i] = pack16<T>(p.x, p.y);
             }
             tmem_st8(ts + hp * 8, ph);
           }
-          l += (s4[0] + s4[1]) + (s4[2] + s4[3]);
+          l += (s2[0].x + s2[0].y) + (s2[1].x + s2[1].y);
         } else {
           uint32_t pz[16];
 #pragma unroll
           for (int i = 0; i < 16; ++i) pz[i] = 0u;
           tmem_st16(ts, pz);
         }
-        TC_TRACE(2, t, 3);
         tmem_st_wait();
         fence_before();
         warp_arrive(&bar_p[t % NBUF], lane);
-        TC_TRACE(2, t, 4);
       }
       // merge the two halves of every row: O = (O_a 2^(m_a - m) + O_b 2^(m_b - m)) / l
       xch[chalf][0][trow] = m_ref;
       xch[chalf][1][trow] = l;
       asm volatile("bar.sync 1, 256;" ::: "memory");          // the eight compute warps, always executed
       if (ok && mbar_wait_warp(&bar_done, 0, fl)) {
-        if (tid == 0) TC_TRACE(0, 60, 3);
         fence_after();
         if (mychunk >= 0) {                                   // uniform per warp: a warp lies inside one chunk
           const float ma = xch[0][0][trow], mb = xch[1][0][trow], la = xch[0][1][trow], lb = xch[1][1][trow];
@@ -636,7 +647,9 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
       // dK/dV: the bias of this thread's key row
       const float my_b = (KPM && MODE == DKV && row_ok)
           ? kpm_term(static_cast<float>(reinterpret_cast<const T*>(a.kpm)[z * a.kpm_sz + grow]), a.kpm_mul) : 0.f;
-      const float my_ds = (MODE == DQ && row_ok) ? a.delta[zh + grow] * a.scale : 0.f;
+      const float my_d = (MODE == DQ && row_ok) ? a.delta[zh + grow] : 0.f;
+      const float my_ds = my_d * a.scale;
+      const float2 nd2 = f2(-my_d, -my_d), sl2 = f2(a.scale_log2, a.scale_log2);
       for (int t = 0; ok && t < ntiles; ++t) {
         const uint32_t ts = tmem + (t % NBUF) * C::SCORE_COLS + lane_base + chalf * 32;
         int pieces = 3;
@@ -649,9 +662,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
           valid = (a.mask[first + t] >> half) & 1;                    // uniform per warp
         }
         const float4* vec = reinterpret_cast<const float4*>(stg + (t % ST) * C::STAGE + 2 * C::CH_BYTES) + chalf * 8;
-        TC_TRACE(2, t, 0);
         ok = mbar_wait_warp(&bar_s[t % NBUF], (t / NBUF) & 1, fl);
-        TC_TRACE(2, t, 1);
         if (!ok) break;
         fence_after();
         if constexpr (C::ER) {
@@ -661,7 +672,6 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
           tmem_ld32(ts, sr);
           tmem_ld32(ts + 64, qr);
           tmem_ld_wait();
-          TC_TRACE(2, t, 2);
           fence_before();
           warp_arrive(&bar_rd, lane);
           if (partial) mask_pieces(sr, pieces);
@@ -681,17 +691,16 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
               }
 #pragma unroll
               for (int i = 8 * g; i < 8 * g + 8; i += 2) {
-                const float p0 = fast_exp2(fmaf(__uint_as_float(sr[i]), a.scale_log2, b[i - 8 * g]));
-                const float p1 = fast_exp2(fmaf(__uint_as_float(sr[i + 1]), a.scale_log2, b[i + 1 - 8 * g]));
-                dr[i / 2] = pack16<T>(p0 * fmaf(__uint_as_float(qr[i]), a.scale, -my_ds),
-                                      p1 * fmaf(__uint_as_float(qr[i + 1]), a.scale, -my_ds));   // P (dP - delta) scale
+                const float2 y = __ffma2_rn(u2f(sr[i], sr[i + 1]), sl2, f2(b[i - 8 * g], b[i + 1 - 8 * g]));
+                const float2 p = exp2_pair<1>(y);
+                const float2 d = __fmul2_rn(p, __fadd2_rn(u2f(qr[i], qr[i + 1]), nd2));   // P (dP - delta); the scale is applied to dQ
+                dr[i / 2] = pack16<T>(d.x, d.y);
               }
             }
           } else {
 #pragma unroll
             for (int i = 0; i < 16; ++i) dr[i] = 0u;
           }
-          TC_TRACE(2, t, 3);
           if (t >= 2) {                                     // the accumulation of chunk t - 2 has read its operand
             ok = mbar_wait_warp(&bar_acc[(t - 2) & 3], ((t - 2) >> 2) & 1, fl);
             if (!ok) break;
@@ -701,7 +710,6 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
           tmem_st_wait();
           fence_before();
           warp_arrive(&bar_p[t & 1], lane);
-          TC_TRACE(2, t, 4);
           continue;
         }
         if constexpr (C::ER2) {
@@ -711,7 +719,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
           // dS^T in the next 8 columns of this thread's 32 columns of dP^T, all read before.
           // dS is formed with P as the accumulating product sees it (rounded to 16 bits),
           // which is also how a stored softmax output would enter the product.
-          uint32_t pr[16];
+          float pf[32];                                        // P^T of this thread's 32 columns
           if (valid) {
             uint32_t sr[32];
             tmem_ld32(ts, sr);
@@ -720,6 +728,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
             warp_arrive(&bar_rd, lane);
             if (partial) mask_pieces(sr, pieces);
             if (FINE && a.causal) mask_causal<32, true>(sr, a.chunk[first + t] * 64 + chalf * 32, (int)grow);
+            const float2 nsl2 = f2(-a.scale_log2, -a.scale_log2);
 #pragma unroll
             for (int i = 0; i < 32; i += 4) {
               float4 lv = vec[i / 4];                           // per-query lse of this chunk
@@ -727,52 +736,48 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
                 lv.x = lv.x == kNegInfT ? -kNegInfT : lv.x - my_b; lv.y = lv.y == kNegInfT ? -kNegInfT : lv.y - my_b;
                 lv.z = lv.z == kNegInfT ? -kNegInfT : lv.z - my_b; lv.w = lv.w == kNegInfT ? -kNegInfT : lv.w - my_b;
               }
-              pr[i / 2] = pack16<T>(fast_exp2(fmaf(__uint_as_float(sr[i]), a.scale_log2, -lv.x)),
-                                    fast_exp2(fmaf(__uint_as_float(sr[i + 1]), a.scale_log2, -lv.y)));
-              pr[i / 2 + 1] = pack16<T>(fast_exp2(fmaf(__uint_as_float(sr[i + 2]), a.scale_log2, -lv.z)),
-                                        fast_exp2(fmaf(__uint_as_float(sr[i + 3]), a.scale_log2, -lv.w)));
+              // the negated exponent lse - s c: the lse comes from shared memory as it is
+              const float2 z0 = __ffma2_rn(u2f(sr[i], sr[i + 1]), nsl2, f2(lv.x, lv.y));
+              const float2 z1 = __ffma2_rn(u2f(sr[i + 2], sr[i + 3]), nsl2, f2(lv.z, lv.w));
+              const float2 p0 = exp2_pair<-1>(z0);
+              const float2 p1 = exp2_pair<-1>(z1);
+              pf[i] = p0.x; pf[i + 1] = p0.y; pf[i + 2] = p1.x; pf[i + 3] = p1.y;
             }
           } else {
             fence_before();
             warp_arrive(&bar_rd, lane);
 #pragma unroll
-            for (int i = 0; i < 16; ++i) pr[i] = 0u;
+            for (int i = 0; i < 32; ++i) pf[i] = 0.f;
           }
           ok = mbar_wait_warp(&bar_s[2], t & 1, fl);
           if (!ok) break;
           fence_after();
-          TC_TRACE(2, t, 2);
 #pragma unroll
           for (int hv = 0; hv < 2; ++hv) {
-            uint32_t qr[16], dr[8];
+            uint32_t qr[16], dr[8], ph[8];
             if (valid) {
               tmem_ld16(ts + 64 + hv * 16, qr);
               tmem_ld_wait();
 #pragma unroll
               for (int i = 0; i < 16; i += 4) {
                 const float4 ev = vec[16 + hv * 4 + i / 4];     // per-query delta of this chunk
-                const float2 p01 = unpack16<T>(pr[hv * 8 + i / 2]), p23 = unpack16<T>(pr[hv * 8 + i / 2 + 1]);
-                const float d0 = p01.x * fmaf(__uint_as_float(qr[i]), a.scale, -ev.x * a.scale);
-                const float d1 = p01.y * fmaf(__uint_as_float(qr[i + 1]), a.scale, -ev.y * a.scale);
-                const float d2 = p23.x * fmaf(__uint_as_float(qr[i + 2]), a.scale, -ev.z * a.scale);
-                const float d3 = p23.y * fmaf(__uint_as_float(qr[i + 3]), a.scale, -ev.w * a.scale);
-                dr[i / 2] = pack16<T>(d0, d1); dr[i / 2 + 1] = pack16<T>(d2, d3);
+                const float2 pa = f2(pf[hv * 16 + i], pf[hv * 16 + i + 1]), pb = f2(pf[hv * 16 + i + 2], pf[hv * 16 + i + 3]);
+                // P (dP - delta); the score scale is applied to dK when it is stored
+                const float2 d0 = __fmul2_rn(pa, __ffma2_rn(f2(ev.x, ev.y), f2(-1.f, -1.f), u2f(qr[i], qr[i + 1])));
+                const float2 d1 = __fmul2_rn(pb, __ffma2_rn(f2(ev.z, ev.w), f2(-1.f, -1.f), u2f(qr[i + 2], qr[i + 3])));
+                dr[i / 2] = pack16<T>(d0.x, d0.y); dr[i / 2 + 1] = pack16<T>(d1.x, d1.y);
+                ph[i / 2] = pack16<T>(pa.x, pa.y); ph[i / 2 + 1] = pack16<T>(pb.x, pb.y);
               }
             } else {
 #pragma unroll
-              for (int i = 0; i < 8; ++i) dr[i] = 0u;
+              for (int i = 0; i < 8; ++i) { dr[i] = 0u; ph[i] = 0u; }
             }
-            uint32_t ph[8];
-#pragma unroll
-            for (int i = 0; i < 8; ++i) ph[i] = pr[hv * 8 + i];
             tmem_st8(ts + 64 + hv * 16, ph);
             tmem_st8(ts + 64 + hv * 16 + 8, dr);
-            if (hv == 0) TC_TRACE(2, t, 3);
           }
           tmem_st_wait();
           fence_before();
           warp_arrive(&bar_p[0], lane);
-          TC_TRACE(2, t, 4);
           continue;
         }
         // Two passes of 16 columns keep the live registers of a pass at 48.  The packed
@@ -785,7 +790,6 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
             tmem_ld16(ts + hv * 16, sr);
             tmem_ld16(ts + 64 + hv * 16, qr);
             tmem_ld_wait();
-            if (hv == 0) TC_TRACE(2, t, 2);
             if (partial && !((pieces >> hv) & 1)) {             // this pass is one group of 16 columns
 #pragma unroll
               for (int i = 0; i < 16; ++i) sr[i] = kNegInfBits;
@@ -828,34 +832,31 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
           if (MODE == DKV) tmem_st8(ts + hv * 8, pr);
           tmem_st8(ts + 64 + hv * 8, dr);
         }
-        TC_TRACE(2, t, 3);
         tmem_st_wait();
         fence_before();
         warp_arrive(&bar_p[t % NBUF], lane);
-        TC_TRACE(2, t, 4);
       }
       if (ok && mbar_wait_warp(&bar_done, 0, fl)) {
-        if (tid == 0) TC_TRACE(0, 60, 3);
         fence_after();
         if (mychunk >= 0) {                                   // uniform per warp
           // the two threads of a row split the D output columns
           const uint32_t ta = tmem + C::ACC_BASE + lane_base;
           T* o0 = reinterpret_cast<T*>(a.out0) + (zh + grow) * D;
+          // (the variants that form dS without the score scale apply it here)
+          const float ds_scale = (C::ER || C::ER2) ? a.scale : 1.f;
           if (MODE == DQ) {
-            store_acc<T>(o0, ta, chalf * (D / 2), D / 2, 1.f);
+            store_acc<T>(o0, ta, chalf * (D / 2), D / 2, ds_scale);
           } else {
             T* o1 = reinterpret_cast<T*>(a.out1) + (zh + grow) * D;
             store_acc<T>(o1, ta, chalf * (D / 2), D / 2, 1.f);            // dV: accumulator columns [0, D)
-            store_acc<T>(o0 - D, ta, D + chalf * (D / 2), D / 2, 1.f);    // dK: accumulator columns [D, 2D)
+            store_acc<T>(o0 - D, ta, D + chalf * (D / 2), D / 2, ds_scale);    // dK: accumulator columns [D, 2D)
           }
         }
       }
     }
   }
-  if (tid == 0) TC_TRACE(0, 60, 4);
   fence_before();
   __syncthreads();
-  if (tid == 0) TC_TRACE(0, 60, 5);
   if (warp == 1) tmem_dealloc(tmem, C::TMEM);
   if (tid == 0 && failed) atomicExch(&g_tc_status, 1 + MODE);
 }
@@ -1014,11 +1015,6 @@ int attn_bwd_tc(const void* q, const void* k, const void* v, const void* dout, c
   return BSP_OK;
 }
 
-#ifdef BSP_TC_TRACE
-extern "C" int bsp_tc_trace_read(long long* out) {
-  return (int)cudaMemcpyFromSymbol(out, g_tc_trace, sizeof(long long) * 3 * 64 * 6);
-}
-#endif
 
 int tc_device_status(int* out) {
   int v = 0;

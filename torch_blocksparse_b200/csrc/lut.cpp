@@ -352,6 +352,33 @@ int bsp_fixed_layout_build(int num_heads, int num_blocks, int mode, int block_st
   return BSP_OK;
 }
 
+int bsp_window_layout_build(int num_heads, int num_blocks, int below, int above, int global_rows, int global_cols,
+                            const int32_t* random_cols, int num_random, int64_t* out) {
+  if (!out) return fail(BSP_ERR_INVALID, "out is NULL");
+  if (num_heads <= 0 || num_blocks <= 0) return fail(BSP_ERR_INVALID, "num_heads and num_blocks must be positive");
+  if (below < 0 || above < 0 || global_rows < 0 || global_cols < 0 || num_random < 0)
+    return fail(BSP_ERR_INVALID, "window, global and random counts must not be negative");
+  if (num_random > 0 && !random_cols) return fail(BSP_ERR_INVALID, "random_cols is NULL");
+  const size_t nb = size_t(num_blocks);
+  for (size_t k = 0; k < size_t(num_heads) * nb * size_t(num_random); ++k)
+    if (random_cols[k] < 0 || random_cols[k] >= num_blocks)
+      return fail(BSP_ERR_INVALID, "random column %d is outside [0, %d)", int(random_cols[k]), num_blocks);
+  parallel_heads(num_heads, [&](int h) {
+    int64_t* L = out + size_t(h) * nb * nb;
+    for (int i = 0; i < num_blocks; ++i) {
+      int64_t* row = L + size_t(i) * nb;
+      if (i < global_rows) { std::fill(row, row + nb, int64_t(1)); continue; }
+      std::fill(row, row + nb, int64_t(0));
+      const int j0 = std::max(0, i - below), j1 = std::min(num_blocks - 1, i + above);
+      for (int j = j0; j <= j1; ++j) row[j] = 1;
+      for (int j = 0; j < std::min(global_cols, num_blocks); ++j) row[j] = 1;
+      const int32_t* rc = random_cols + (size_t(h) * nb + i) * size_t(num_random);
+      for (int r = 0; r < num_random; ++r) row[rc[r]] = 1;
+    }
+  });
+  return BSP_OK;
+}
+
 int bsp_meta_build(const int64_t* layout, int H, int Mb, int Nb,
                    int32_t* out, int64_t out_cap, int64_t* total) {
   if (int rc = check_layout_args(layout, H, Mb, Nb)) return rc;

@@ -84,7 +84,9 @@ int run_dsd(const void* s, const void* b, void* c, int dtype, int block, int Z, 
             int64_t b_sz, int64_t b_sh, int64_t b_sk, int64_t b_sn,
             int64_t c_sz, int64_t c_sh, int64_t c_sm, int64_t c_sn,
             const Meta& m, cudaStream_t st) {
-  if (g_matmul_tc.load() && Z <= 65535 &&
+  // (a layout without any block has no sparse tensor to describe to the tensor-map encoder: the
+  // mma.sync kernel writes the zeros)
+  if (g_matmul_tc.load() && Z <= 65535 && m.nnz > 0 &&
       dsd_tc_eligible(s, b, c, dtype, block, N, trans_s, s_sz, b_sz, b_sh, b_sk, b_sn, c_sz, c_sh, c_sm, c_sn))
     return dsd_tc(s, b, c, dtype, block, Z, N, s_sz, trans_s, b_sz, b_sh, b_sk, b_sn, c_sz, c_sh, c_sm, c_sn, m, st);
   if (dtype == BSP_F32)
@@ -133,7 +135,8 @@ extern "C" int bsp_dsd(const void* s, const void* b, void* c, int dtype, int blo
   if (int rc = check_basic("dsd", dtype, block, Z, H, m)) return rc;
   const int vec = dtype == BSP_F32 ? 4 : 8;
   if (N <= 0 || N % vec) return fail(BSP_ERR_INVALID, "dsd: dense width %d must be a positive multiple of %d", N, vec);
-  if (int rc = check_sparse("dsd", "a", s, dtype, s_sz)) return rc;
+  if (m.nnz > 0)                 // (a layout without blocks has an empty sparse operand, never dereferenced)
+    if (int rc = check_sparse("dsd", "a", s, dtype, s_sz)) return rc;
   if (int rc = check_dense("dsd", "b", b, dtype, b_sz, b_sh, b_sk, b_sn)) return rc;
   if (!c) return fail(BSP_ERR_INVALID, "dsd: c is NULL");
   return run_dsd(s, b, c, dtype, block, Z, N, s_sz, trans_s, b_sz, b_sh, b_sk, b_sn, c_sz, c_sh, c_sm, c_sn, m,
@@ -155,7 +158,8 @@ extern "C" int bsp_dds(const void* a, const void* s, void* c, int dtype, int blo
   const int vec = dtype == BSP_F32 ? 4 : 8;
   if (M <= 0 || M % vec) return fail(BSP_ERR_INVALID, "dds: dense height %d must be a positive multiple of %d", M, vec);
   if (int rc = check_dense("dds", "a", a, dtype, a_sz, a_sh, a_sm, a_sk)) return rc;
-  if (int rc = check_sparse("dds", "b", s, dtype, s_sz)) return rc;
+  if (m.nnz > 0)
+    if (int rc = check_sparse("dds", "b", s, dtype, s_sz)) return rc;
   if (!c) return fail(BSP_ERR_INVALID, "dds: c is NULL");
   return run_dsd(s, a, c, dtype, block, Z, M, s_sz, !trans_s, a_sz, a_sh, a_sk, a_sm, c_sz, c_sh, c_sn, c_sm, m,
                  reinterpret_cast<cudaStream_t>(stream));

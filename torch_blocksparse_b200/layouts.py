@@ -7,7 +7,7 @@ ops through their explicit `layout` argument.
 """
 import torch
 
-from . import tables
+from . import _lib, tables
 
 
 def fixed(num_heads, num_blocks, block_stride, attention='unidirectional', numverts=1, vertsize=1):
@@ -20,28 +20,37 @@ def dense(num_heads, num_blocks):
     return torch.ones((num_heads, num_blocks, num_blocks), dtype=torch.int64)
 
 
+def window(num_heads, num_blocks, below, above, global_rows=0, global_cols=0, random_cols=None):
+    """Sliding-window layout built natively: block-row i sees block-columns
+    [i - below, i + above], the first `global_cols` block-columns and the columns
+    `random_cols[h, i, :]` (int tensor [H, nb, r], optional); the first
+    `global_rows` block-rows see everything."""
+    out = torch.empty((num_heads, num_blocks, num_blocks), dtype=torch.int64)
+    if random_cols is not None:
+        random_cols = random_cols.to(torch.int32).contiguous()
+        if random_cols.dim() != 3 or tuple(random_cols.shape[:2]) != (num_heads, num_blocks):
+            raise ValueError('random_cols must be [num_heads, num_blocks, r]')
+    _lib.check(_lib.lib().bsp_window_layout_build(
+        num_heads, num_blocks, below, above, global_rows, global_cols,
+        random_cols.data_ptr() if random_cols is not None else None,
+        random_cols.size(2) if random_cols is not None else 0, out.data_ptr()))
+    return out
+
+
 def causal_band(num_heads, num_blocks, band, global_cols=1):
     """Block-row i sees block-columns max(0, i-band+1) .. i and the first
     `global_cols` block-columns."""
-    i = torch.arange(num_blocks)[:, None]
-    j = torch.arange(num_blocks)[None, :]
-    lay = ((j <= i) & (j > i - band)) | (j < global_cols)
-    return lay.to(torch.int64)[None].repeat(num_heads, 1, 1)
+    return window(num_heads, num_blocks, band - 1, 0, 0, global_cols)
 
 
-def bigbird(num_heads, num_blocks, num_random=3, window=3, num_global=2, seed=0):
-    """BigBird-style layout: a sliding window of `window` blocks, `num_random`
-    random block-columns per block-row (head h drawn from seed + h) and
-    `num_global` global block-rows and block-columns."""
-    half = window // 2
-    i = torch.arange(num_blocks)[:, None]
-    j = torch.arange(num_blocks)[None, :]
-    base = ((j - i).abs() <= half) | (i < num_global) | (j < num_global)
-    out = torch.zeros((num_heads, num_blocks, num_blocks), dtype=torch.int64)
+def bigbird(num_heads, num_blocks, num_random=3, window_blocks=3, num_global=2, seed=0):
+    """BigBird-style layout: a sliding window of `window_blocks` blocks, `num_random`
+    random block-columns per block-row (head h drawn from torch.Generator(seed + h),
+    one randperm per block-row) and `num_global` global block-rows and block-columns."""
+    cols = torch.empty((num_heads, num_blocks, num_random), dtype=torch.int32)
     for h in range(num_heads):
         g = torch.Generator().manual_seed(seed + h)
-        lay = base.clone()
         for r in range(num_blocks):
-            lay[r, torch.randperm(num_blocks, generator=g)[:num_random]] = True
-        out[h] = lay.to(torch.int64)
-    return out
+            cols[h, r] = torch.randperm(num_blocks, generator=g)[:num_random]
+    half = window_blocks // 2
+    return window(num_heads, num_blocks, half, half, num_global, num_global, cols)
