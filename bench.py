@@ -3,10 +3,11 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 
 Workload (config.workload): sparse self-attention forward + backward, FP16,
-Z=8 per GPU, H=16, L=8192, head_dim 64, block 64, "fixed" layout (local windows
-of 4 blocks, last block of every window global, unidirectional) -- the
-configuration the headline metric is quoted on.  Inputs are seeded synthetic
-N(0,1) tensors of that shape (the reference measures on no dataset).
+Z=8, H=16, L=8192, head_dim 64, block 64, "fixed" layout (local windows of 4
+blocks, last block of every window global, unidirectional) -- the configuration
+the headline metric is quoted on.  Inputs are seeded synthetic N(0,1) tensors of
+that shape (the reference measures on no dataset): batch entry z is drawn from
+torch.Generator(seed = z), so every rank count sees the same problem.
 
 One "step" is one forward + backward through the public wrapper
 (SparseSelfAttention).  `value` counts only the FLOPs of nonzero blocks
@@ -15,16 +16,26 @@ with inputs resident in HBM; `e2e` is the same step on operands in pinned host
 memory through the library's host entry (HostAttention): every step copies its
 inputs in and its four results out inside the timed region, streamed by batch
 slices so that transfers and kernels overlap.
-With N > 1 every rank runs the same-size shard of a Z = 8N batch (independent
-(batch, head) units, no collective on the timed path: weak scaling); NCCL is
-only used to reduce the timings and to all-gather outputs for verification.
+
+With N > 1 the ONE problem above is split over the ranks by (batch, head)
+shards (torch_blocksparse_b200.shard.plan: Z first, then H), no collective on
+the timed path: strong scaling, `value` = FLOPs of the whole problem / the
+slowest rank's time.  Off the clock the outputs and gradients of all ranks are
+all-gathered over NCCL into full tensors and sampled (batch, head) slices are
+compared with the CPU oracle.  Two secondary measurements at N > 1: `head_split`
+(a problem of N/2 batch entries, so that every batch entry is split over the
+heads of two ranks: layout slices, re-based tables) and `weak` (every rank runs
+a full Z=8 problem of its own).  At N = 1 the line also carries the other
+configurations: C4 bidirectional, C5 (BigBird, BF16, Z=32), C3 softmax, C1 / C2
+and the large-block MatMul cases.
 
 `--impl reference` times the reference's dense-masked definition of the same
-op on the host cores (the CPU restatement under oracle/), on a bounded sample
-of (batch, head) slices.
+op on the host cores (the CPU restatement under oracle/; nothing of the
+product is imported), on a bounded sample of (batch, head) slices.
 """
 import argparse
 import json
+import math
 import os
 import statistics
 import subprocess
@@ -42,12 +53,13 @@ import workloads  # noqa: E402
 METRIC = 'sparse_attn_fwd_bwd_tflops_nnz_blocks_L8192'
 UNIT = 'TFLOP/s'
 FALLBACK_PEAKS = {'hbm_gbs': 6650.0, 'bf16_tflops': 1590.0, 'bf16_tflops_sustained': 1400.0}
+Z_TOTAL, HEADS, SEQ, HEAD_DIM, BLOCK = 8, 16, 8192, 64, 64
 
-# dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures
-# summarised under profiles/.  The attention figure was captured at Z=2 (225.8 MB)
-# and scaled by 4 to the Z=8 launch: every (batch, head) pair is independent, so
-# traffic grows in proportion.
-NCU_TRAFFIC_BYTES = {'attn_bwd_dkdv': 4 * 225.8e6, 'softmax_fwd': 638.5e6, 'softmax_bwd': 924.3e6}
+# dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures summarised
+# under profiles/.  The attention figures were captured at Z=2 and are scaled to the launch's
+# batch: every (batch, head) pair is independent, so traffic grows in proportion.
+NCU_TRAFFIC_BYTES_PER_Z = {'attn_bwd_dkdv': 225.8e6 / 2, 'attn_fwd': 115.7e6 / 2, 'attn_bwd_dq': 154.3e6 / 2}
+NCU_TRAFFIC_BYTES = {'softmax_fwd': 638.5e6, 'softmax_bwd': 924.3e6}
 
 
 def peaks():
@@ -123,49 +135,66 @@ def dist_env():
     return rank, world, local
 
 
-def cpu_attention_sample(c, n_slices, repeats=1):
-    """Times the dense-masked CPU definition on `n_slices` (batch, head) slices of
-    the workload.  Returns (seconds per pass over the sample, counted FLOPs of the sample)."""
+def problem_entries(attention, zs, h0=0, h1=HEADS):
+    """Batch entries `zs` of the benchmark problem (entry z is drawn from seed z), heads [h0, h1):
+    dict with q, k, v, do [len(zs), h1-h0, L, D] and the layout slice."""
+    parts = [workloads.config4(attention, Z=1, seed=z) for z in zs]
+    c = {n: torch.cat([p[n][:, h0:h1] for p in parts]).contiguous() for n in ('q', 'k', 'v', 'do')}
+    c.update(layout=parts[0]['layout'][h0:h1].contiguous(), full_layout=parts[0]['layout'], block=parts[0]['block'],
+             scale=parts[0]['scale'])
+    return c
+
+
+def cpu_attention_sample(attention, n_slices, Z=Z_TOTAL):
+    """Times the dense-masked CPU definition on `n_slices` (batch, head) slices of the
+    workload.  Returns (seconds for the sample, counted FLOPs of the sample)."""
     from oracle import dense_masked as dm
-    layout, block = c['layout'], c['block']
-    Z, H = c['q'].shape[:2]
-    slices = [(i % Z, (i * 7) % H) for i in range(n_slices)]
+    slices = [(i % Z, (i * 7) % HEADS) for i in range(n_slices)]
+    data = {}
+    for z in sorted({z for z, _ in slices}):
+        data[z] = workloads.config4(attention, Z=1, seed=z)
     flops = 0
+    t0 = time.perf_counter()
     for z, h in slices:
-        flops += workloads.attention_flops(layout[h:h + 1], block, 1, c['q'].size(-1))
-    best = None
-    for _ in range(repeats):
-        t0 = time.perf_counter()
-        for z, h in slices:
-            dm.attention_reference(c['q'][z:z + 1, h:h + 1], c['k'][z:z + 1, h:h + 1], c['v'][z:z + 1, h:h + 1],
-                                   layout[h:h + 1], block, c['scale'], do=c['do'][z:z + 1, h:h + 1])
-        dt = time.perf_counter() - t0
-        best = dt if best is None else min(best, dt)
-    return best, flops
+        c = data[z]
+        flops += workloads.attention_flops(c['layout'][h:h + 1], c['block'], 1, c['q'].size(-1))
+        dm.attention_reference(c['q'][:, h:h + 1], c['k'][:, h:h + 1], c['v'][:, h:h + 1],
+                               c['layout'][h:h + 1], c['block'], c['scale'], do=c['do'][:, h:h + 1])
+    return time.perf_counter() - t0, flops
+
+
+def config_dict(args, world, n_sets=1):
+    return {'workload': 'config4: sparse self-attention fwd+bwd FP16, Z=%d, H=16, L=8192, head_dim=64, block=64, '
+                        'fixed layout (windows of 4 blocks, last block global), %s' % (Z_TOTAL, args.attention),
+            'global_batch': Z_TOTAL, 'seq_len': SEQ, 'heads': HEADS, 'head_dim': HEAD_DIM, 'block': BLOCK,
+            'parallelism': 'one problem split into (batch, head) shards over %d GPU(s), no collective on the timed path'
+                           % world,
+            'l2': ('inputs (4 x 134 MB) exceed the 126 MB L2; no explicit flush' if n_sets == 1 else
+                   'the shard is smaller than L2: steps rotate over %d copies of the inputs (> 400 MB in all), '
+                   'no explicit flush' % n_sets)}
 
 
 def run_reference(args):
     rank, world, _ = dist_env()
     if rank != 0:
         return
+    workloads.LAYOUT_SOURCE = 'oracle'          # nothing of the product is imported on this arm
     torch.set_num_threads(os.cpu_count() or 1)
-    c = workloads.config4(args.attention, Z=1)
     n_slices = args.ref_slices
-    for _ in range(args.warmup):
-        cpu_attention_sample(c, n_slices)
-    t0 = time.perf_counter()
-    flops = 0
-    for _ in range(args.steps):
-        _, f = cpu_attention_sample(c, n_slices)
+    for _ in range(min(args.warmup, 1)):
+        cpu_attention_sample(args.attention, n_slices)
+    flops, dt = 0, 0.0
+    for _ in range(args.steps):                 # (drawing the inputs is not part of a step's time)
+        t, f = cpu_attention_sample(args.attention, n_slices)
         flops += f
-    dt = time.perf_counter() - t0
+        dt += t
     value = flops / dt / 1e12
     sample = ('%d of the %d (batch, head) slices per step, dense-masked FP32 torch on FP16-rounded inputs'
-              % (n_slices, 8 * 16 * max(1, args.gpus)))
+              % (n_slices, Z_TOTAL * HEADS))
     line = {
         'impl': 'reference', 'metric': METRIC, 'value': value, 'unit': UNIT, 'n_gpus': args.gpus,
         'steps': args.steps, 'warmup': args.warmup, 'ms_per_step': dt / args.steps * 1e3,
-        'higher_is_better': True, 'scaling': 'weak', 'vs_baseline': None, 'dtype': 'f32', 'data': 'synthetic',
+        'higher_is_better': True, 'scaling': 'strong', 'vs_baseline': None, 'dtype': 'f32', 'data': 'synthetic',
         'config': config_dict(args, world),
         'cpu_baseline': {'value': value, 'unit': UNIT, 'cores': torch.get_num_threads(), 'kind': 'port', 'sample': sample},
         'e2e': {'value': value, 'unit': UNIT, 'h2d_bytes_per_step': 0, 'd2h_bytes_per_step': 0},
@@ -174,20 +203,106 @@ def run_reference(args):
     print(json.dumps(line))
 
 
-def config_dict(args, world):
-    return {'workload': 'config4: sparse self-attention fwd+bwd FP16, Z=8 per GPU, H=16, L=8192, head_dim=64, '
-                        'block=64, fixed layout (windows of 4 blocks, last block global), %s' % args.attention,
-            'global_batch': 8 * world, 'seq_len': 8192, 'heads': 16, 'head_dim': 64, 'block': 64,
-            'parallelism': '(batch, head) shards, one per GPU, no collective',
-            'l2': 'inputs (4 x 134 MB per GPU) exceed the 126 MB L2; no explicit flush'}
+# ---------------------------------------------------------------------------------------------
+# our arm
+# ---------------------------------------------------------------------------------------------
+class Timing:
+    """Shared timing helpers of one rank: barrier + synchronize on both sides, CUDA events on the
+    current stream, max over ranks."""
+
+    def __init__(self, dev, world):
+        self.dev, self.world = dev, world
+
+    def barrier(self):
+        if self.world > 1:
+            import torch.distributed as dist
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(self, seconds):
+        el = torch.tensor([seconds], device=self.dev, dtype=torch.float64)
+        if self.world > 1:
+            import torch.distributed as dist
+            dist.all_reduce(el, op=dist.ReduceOp.MAX)
+        return float(el)
+
+    def run(self, step, steps, warmup=3, profile=False):
+        """`steps` calls of step(i) between two events.  Returns (seconds as the max over ranks,
+        per-kernel event triples when profile)."""
+        from torch_blocksparse_b200 import fused
+        fused.PROFILE = [] if profile else None
+        for i in range(warmup):
+            step(i)
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        fused.PROFILE = [] if profile else None
+        self.barrier()
+        t0.record()
+        for i in range(steps):
+            step(i)
+        t1.record()
+        self.barrier()
+        prof, fused.PROFILE = fused.PROFILE, None
+        return self.max_over_ranks(t0.elapsed_time(t1) * 1e-3), prof
+
+
+def make_steps(mod, c, dev, n_sets):
+    """Device copies of the shard's inputs (n_sets of them, rotated step by step so that a small
+    shard does not live in L2) and the step function: forward + backward through the module."""
+    sets = []
+    for _ in range(n_sets):
+        q, k, v = (c[n].to(dev).requires_grad_() for n in ('q', 'k', 'v'))
+        sets.append((q, k, v, c['do'].to(dev)))
+    state = {}
+
+    def step(i):
+        q, k, v, do = sets[i % n_sets]
+        q.grad = k.grad = v.grad = None
+        o = mod(q, k, v)
+        o.backward(do)
+        state['last'] = (o, q, k, v)
+        return o
+
+    return step, state
+
+
+def attention_section(name, c, dev, steps, pk, T, dtype_name):
+    """One-GPU timing of a whole configuration (extra keys of the N = 1 line)."""
+    from torch_blocksparse_b200 import SparseSelfAttention
+    layout, block = c['layout'], c['block']
+    Z, _, L, D = c['q'].shape
+    mod = SparseSelfAttention(layout=layout, block=block, fused=True)
+    q, k, v = (c[n].to(dev).requires_grad_() for n in ('q', 'k', 'v'))
+    do = c['do'].to(dev)
+
+    def step(i):
+        q.grad = k.grad = v.grad = None
+        mod(q, k, v).backward(do)
+
+    t, prof = T.run(step, steps, warmup=3, profile=True)
+    flops = workloads.attention_flops(layout, block, Z, D)
+    kern = {}
+    for n, a, b in prof:
+        kern.setdefault(n, []).append(a.elapsed_time(b))
+    kern_ms = {n: sum(x) / len(x) for n, x in kern.items()}
+    top = max(kern_ms, key=kern_ms.get)
+    per_product = 2 * Z * int(layout.sum()) * block * block * D
+    counted = {'attn_fwd': 2, 'attn_bwd_dkdv': 2, 'attn_bwd_dq': 1, 'attn_bwd_delta': 0, 'attn_bwd_fused': 3}
+    ach = counted.get(top, 0) * per_product / (kern_ms[top] * 1e-3) / 1e12
+    return {'workload': name, 'tflops': flops / t * steps / 1e12, 'ms_per_step': t / steps * 1e3, 'dtype': dtype_name,
+            'kernel_ms': kern_ms, 'frac_of_nominal_peak': flops / t * steps / 1e12 / 2250.0,
+            'roofline': {'bound': 'tensor', 'kernel': top, 'achieved': ach, 'peak': pk['bf16_tflops'], 'unit': UNIT,
+                         'frac': ach / pk['bf16_tflops'], 'traffic': None,
+                         'peak_source': pk['source'] + ' (bf16 dense, burst)'},
+            'gpu_launches': steps * 4}
 
 
 def matmul_bench(dev, pk, iters=10, z=8):
-    """Block-sparse MatMul (configuration 2: dsd / dds, FP16, block 32, Z=8, H=8, 2048^3, layout
-    Bernoulli(0.25)), forward and forward + backward, TFLOP/s on nonzero-block FLOPs."""
+    """Block-sparse MatMul: configuration 1 (sdd FP32 block 16), configuration 2 (dsd / dds, FP16,
+    block 32, Z=8, H=8, 2048^3, layout Bernoulli(0.25)) forward and forward + backward, and blocks
+    64 / 128 on a compute-bound shape; TFLOP/s on nonzero-block FLOPs."""
     from torch_blocksparse_b200 import MatMul
     out = {'workload': 'config2: dsd / dds FP16, block 32, Z=%d, H=8, M=N=K=2048, Bernoulli(0.25) layout' % z, 'cases': []}
-    peak_tf = pk.get('bf16_tflops_sustained', pk['bf16_tflops'])
+    peak_tf = pk['bf16_tflops']
 
     def timed(fn):
         for _ in range(3):
@@ -200,6 +315,17 @@ def matmul_bench(dev, pk, iters=10, z=8):
         e1.record()
         torch.cuda.synchronize()
         return e0.elapsed_time(e1) / iters * 1e-3
+
+    c1 = workloads.config1()
+    op = MatMul(c1['layout'], 16, 'sdd', trans_a=True, trans_b=False)
+    a, b = c1['a'].to(dev), c1['b'].to(dev)
+    t = timed(lambda: op(a, b))
+    nnz = int(c1['layout'].sum())
+    fl = 2 * 4 * nnz * 16 * 16 * 384
+    by = 4 * (a.numel() + b.numel() + 4 * nnz * 256)
+    out['config1'] = {'workload': 'config1: sdd FP32 block 16, trans_a, A [4,2,384,256], B [4,2,384,512], Bernoulli(0.5) layout',
+                      'fwd_ms': t * 1e3, 'fwd_tflops': fl / t / 1e12, 'fwd_gbs': by / t / 1e9,
+                      'note': '0.40 GFLOP and 5.3 MB: one launch of a few microseconds, bound by launch latency'}
 
     for mode in ('dsd', 'dds'):
         for ta in (False, True):
@@ -222,6 +348,12 @@ def matmul_bench(dev, pk, iters=10, z=8):
                                      'fwd_frac_of_measured_peak': flops / tf / 1e12 / peak_tf})
                 del a, b, dc, c
                 torch.cuda.empty_cache()
+    best = max(out['cases'], key=lambda e: e['fwd_tflops'])
+    worst = min(out['cases'], key=lambda e: e['fwd_tflops'])
+    out['roofline'] = {'bound': 'tensor', 'kernel': 'dsd_kernel (block 32)', 'achieved': worst['fwd_tflops'],
+                       'achieved_best': best['fwd_tflops'], 'peak': peak_tf, 'unit': UNIT,
+                       'frac': worst['fwd_tflops'] / peak_tf, 'traffic': None,
+                       'peak_source': pk['source'] + ' (bf16 dense, burst)'}
 
     # blocks 64 and 128 (the tcgen05 kernels) on a compute-bound shape: Z=2, H=8, M=N=K=4096,
     # layout Bernoulli(0.25), forward only, every mode, plain and one transposed variant
@@ -250,7 +382,8 @@ def matmul_bench(dev, pk, iters=10, z=8):
 
 
 def softmax_bench(dev, pk, iters=20):
-    """Sparse softmax (configuration 3) forward / backward bandwidth."""
+    """Sparse softmax (configuration 3) forward / backward bandwidth: through the raw C ABI and
+    through the public op (Softmax.__call__ and its autograd backward)."""
     from torch_blocksparse_b200 import Softmax
     c = workloads.config3()
     layout, block = c['layout'], c['block']
@@ -274,6 +407,11 @@ def softmax_bench(dev, pk, iters=20):
         _lib.check(L.bsp_softmax_bwd(x.data_ptr(), dy.data_ptr(), _dtype_code(x), x.size(0), x.stride(0), dy.stride(0),
                                      block, H, Mb, lut.data_ptr(), maxlut, c['scale'], _stream(x)))
 
+    def op_fwd():
+        with torch.no_grad():
+            op(x, scale=c['scale'], rpe=rpe, key_padding_mask=kpm, attn_mask=am,
+               key_padding_mask_mode='add', attn_mask_mode='mul')
+
     def timeit(fn):
         for _ in range(3):
             fn()
@@ -292,25 +430,87 @@ def softmax_bench(dev, pk, iters=20):
     xb = x.numel() * e
     fwd_bytes = 2 * xb + nnz * block * block * e + nnz_head * block * block * e + kpm.numel() * e
     bwd_bytes = 3 * xb
-    tf, tb = timeit(fwd), timeit(bwd)
+    tf, tb, tof = timeit(fwd), timeit(bwd), timeit(op_fwd)
     return {
         'workload': 'config3: FP16, block 64, Z=8, H=16, 4096x4096, causal band of 4 + first column, scale, rpe, '
                     'key-padding mask (add), causal mask (mul)',
         'fwd_gbs': fwd_bytes / tf / 1e9, 'bwd_gbs': bwd_bytes / tb / 1e9,
         'fwd_ms': tf * 1e3, 'bwd_ms': tb * 1e3, 'fwd_bytes': fwd_bytes, 'bwd_bytes': bwd_bytes,
+        'op_call_fwd_gbs': fwd_bytes / tof / 1e9, 'op_call_fwd_ms': tof * 1e3,
+        'frac_of_8tbs': fwd_bytes / tf / 1e9 / 8000.0,
         'roofline': {'bound': 'hbm', 'achieved': fwd_bytes / tf / 1e9, 'peak': pk['hbm_gbs'], 'unit': 'GB/s',
                      'frac': fwd_bytes / tf / 1e9 / pk['hbm_gbs'], 'traffic': NCU_TRAFFIC_BYTES['softmax_fwd'],
-                     'kernel': 'softmax_fwd_zloop', 'peak_source': pk['source']},
+                     'kernel': 'softmax_fwd', 'peak_source': pk['source']},
         'roofline_bwd': {'bound': 'hbm', 'achieved': bwd_bytes / tb / 1e9, 'peak': pk['hbm_gbs'], 'unit': 'GB/s',
                          'frac': bwd_bytes / tb / 1e9 / pk['hbm_gbs'], 'traffic': NCU_TRAFFIC_BYTES['softmax_bwd'],
                          'kernel': 'softmax_bwd_group', 'peak_source': pk['source']},
-        'gpu_launches': 2 * (iters + 3),
+        'gpu_launches': 3 * (iters + 3),
     }
+
+
+def oracle_check(gathered, entries, slices):
+    """Compares (batch, head) slices of the gathered o, dq, dk, dv with the CPU oracle on the
+    problem's own inputs.  `entries`: {z: config dict of batch entry z}.  Returns the largest
+    error in units of the tolerance (<= 1 passes) and the slices."""
+    from oracle import dense_masked as dm
+    worst = 0.0
+    for z, h in slices:
+        c = entries[z]
+        want = dm.attention_reference(c['q'][:, h:h + 1], c['k'][:, h:h + 1], c['v'][:, h:h + 1], c['layout'][h:h + 1],
+                                      c['block'], c['scale'], do=c['do'][:, h:h + 1])
+        for g, w in zip(gathered, want):
+            got = g[z:z + 1, h:h + 1].float().cpu()
+            w = w.float()
+            worst = max(worst, float(((got - w).abs() / (1e-2 + 1e-2 * w.abs())).max()))
+    return worst
+
+
+def run_sharded(args, T, dev, rank, world, Z, pk, profile, n_slices_checked=2, sampler=None):
+    """Splits the problem of batch entries 0..Z-1 over the ranks, times `steps` steps of every
+    rank's shard and (world > 1) gathers the results and checks them.  Returns a dict."""
+    import torch.distributed as dist
+    from torch_blocksparse_b200 import SparseSelfAttention, shard
+    shards = shard.plan(Z, HEADS, world)
+    s = shards[rank]
+    c = problem_entries(args.attention, list(range(s.z0, s.z1)), s.h0, s.h1)
+    in_bytes = 4 * c['q'].numel() * 2
+    n_sets = max(1, min(8, math.ceil(400e6 / in_bytes)))
+    mod = SparseSelfAttention(layout=c['layout'], block=c['block'], fused=True)
+    step, state = make_steps(mod, c, dev, n_sets)
+    attempts = 0
+    if sampler is not None:
+        sampler.start()
+    while True:                     # a run in which the kernels account for < 90 % of the elapsed time of a
+        attempts += 1               # large shard was disturbed from outside (shared box): at most twice more
+        elapsed, prof = T.run(step, args.steps, warmup=max(args.warmup, 3), profile=profile)
+        busy = sum(a.elapsed_time(b) for _, a, b in prof) * 1e-3 if profile else elapsed
+        again = 1 if (profile and world == 1 and busy < 0.9 * elapsed and attempts < 3) else 0
+        if not again:
+            break
+    clocks = sampler.stop() if sampler is not None else None
+    flops_total = workloads.attention_flops(c['full_layout'], c['block'], Z, HEAD_DIM)
+    out = {'elapsed': elapsed, 'flops_total': flops_total, 'prof': prof, 'attempts': attempts, 'n_sets': n_sets,
+           'shard': c, 'mod': mod, 'shards': shards, 'state': state, 'busy': busy,
+           'local_shape': [s.z1 - s.z0, s.h1 - s.h0], 'clocks': clocks}
+    if world > 1:
+        o, q, k, v = state['last']
+        full = [shard.gather_dense(t.detach(), shards, Z, HEADS) for t in (o, q.grad, k.grad, v.grad)]
+        digest = [float(t.double().sum()) for t in full]
+        if rank == 0:
+            # the sets rotate, but every set holds the same values: the last step's results are the problem's
+            picks = [(Z - 1, HEADS - 1), (0, 5)][:n_slices_checked]
+            entries = {z: workloads.config4(args.attention, Z=1, seed=z) for z in {z for z, _ in picks}}
+            err = oracle_check(full, entries, picks)
+            out['verify'] = {'gathered': 'o, dq, dk, dv all-gathered over NCCL into [%d, %d, %d, %d] tensors' % (Z, HEADS, SEQ, HEAD_DIM),
+                             'oracle_slices': picks, 'max_err_over_tolerance': err, 'ok': bool(err <= 1.0),
+                             'digest': digest}
+        del full
+    return out
 
 
 def run_ours(args):
     import torch.distributed as dist
-    from torch_blocksparse_b200 import SparseSelfAttention, fused
+    from torch_blocksparse_b200 import SparseSelfAttention, fused, shard
     rank, world, local = dist_env()
     if not torch.cuda.is_available():
         raise SystemExit('bench.py needs a CUDA device (there is no CPU code path)')
@@ -320,6 +520,7 @@ def run_ours(args):
         os.environ.setdefault('MASTER_ADDR', '127.0.0.1')
         dist.init_process_group('nccl', device_id=dev)
     pk = peaks()
+    T = Timing(dev, world)
     if args.only_matmul:
         if rank == 0:
             print(json.dumps({'matmul': matmul_bench(dev, pk, iters=max(1, args.steps), z=args.z)}))
@@ -331,151 +532,131 @@ def run_ours(args):
 
     from torch_blocksparse_b200.host import bind_near_gpu
     numa_node = bind_near_gpu(dev)          # before any pinned allocation: host buffers local to the GPU
-    c = workloads.config4(args.attention, Z=args.z, seed=rank)
-    layout, block, D = c['layout'], c['block'], c['q'].size(-1)
-    Z = c['q'].size(0)
-    flops_step = workloads.attention_flops(layout, block, Z, D)       # this rank's shard
-    mod = SparseSelfAttention(layout=layout, block=block, fused=True)
-    host = {n: c[n].pin_memory() for n in ('q', 'k', 'v', 'do')}
-    q, k, v = (host[n].to(dev).requires_grad_() for n in ('q', 'k', 'v'))
-    do = host['do'].to(dev)
+    Z = args.z
+    main = run_sharded(args, T, dev, rank, world, Z, pk, profile=True, sampler=ClockSampler(local) if rank == 0 else None)
+    clocks = main['clocks']
+    elapsed, prof, c = main['elapsed'], main['prof'], main['shard']
+    value = main['flops_total'] * args.steps / elapsed / 1e12
+    Zl, Hl = main['local_shape']
+    layout_l, block = c['layout'], c['block']
 
-    def step():
-        q.grad = k.grad = v.grad = None
-        o = mod(q, k, v)
-        o.backward(do)
-        return o
-
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    def timed_steps():
-        """K steps between two events on the current stream, barrier + synchronize on both
-        sides, max over ranks.  Returns (seconds, per-kernel event triples)."""
-        fused.PROFILE = []
-        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        barrier()
-        t0.record()
-        for _ in range(args.steps):
-            step()
-        t1.record()
-        barrier()
-        prof, fused.PROFILE = fused.PROFILE, None
-        el = torch.tensor([t0.elapsed_time(t1) * 1e-3], device=dev, dtype=torch.float64)
-        if world > 1:
-            dist.all_reduce(el, op=dist.ReduceOp.MAX)
-        return float(el), prof
-
-    fused.PROFILE = []                      # warm up on the code path that is timed
-    for _ in range(max(args.warmup, 3)):
-        step()
-    fused.PROFILE = None
-    barrier()
-    sampler = ClockSampler(local)
-    if rank == 0:
-        sampler.start()
-    # A measurement in which the kernels account for less than 90 % of the elapsed time was
-    # disturbed from outside the kernels (the box is shared); it is taken again, at most twice.
-    attempts = 0
-    while True:
-        attempts += 1
-        elapsed, prof = timed_steps()
-        busy = sum(a.elapsed_time(b) for _, a, b in prof) * 1e-3
-        retry = torch.tensor([1 if (busy < 0.9 * elapsed and attempts < 3) else 0], device=dev)
-        if world > 1:
-            dist.all_reduce(retry, op=dist.ReduceOp.MAX)
-        if not int(retry):
-            break
-    clocks = sampler.stop() if rank == 0 else None
-    value = flops_step * world * args.steps / elapsed / 1e12
-
-    # per-kernel durations inside the timed region
+    # per-kernel durations inside the timed region (this rank's shard)
     kern = {}
     for name, a, b in prof:
         kern.setdefault(name, []).append(a.elapsed_time(b))
     kern_ms = {n: sum(t) / len(t) for n, t in kern.items()}
     top = max(kern_ms, key=kern_ms.get)
-    per_product = 2 * Z * int(layout.sum()) * block * block * D
-    counted = {'attn_fwd': 2, 'attn_bwd_dkdv': 2, 'attn_bwd_dq': 1, 'attn_bwd_delta': 0}
-    executed = {'attn_fwd': 2, 'attn_bwd_dkdv': 4, 'attn_bwd_dq': 3, 'attn_bwd_delta': 0}
-    peak_tf = pk.get('bf16_tflops_sustained', pk['bf16_tflops'])
+    per_product = 2 * Zl * int(layout_l.sum()) * block * block * HEAD_DIM
+    counted = {'attn_fwd': 2, 'attn_bwd_dkdv': 2, 'attn_bwd_dq': 1, 'attn_bwd_delta': 0, 'attn_bwd_fused': 3}
+    executed = {'attn_fwd': 2, 'attn_bwd_dkdv': 4, 'attn_bwd_dq': 3, 'attn_bwd_delta': 0, 'attn_bwd_fused': 5}
     achieved = counted[top] * per_product / (kern_ms[top] * 1e-3) / 1e12
-    roofline = {'bound': 'tensor', 'achieved': achieved, 'peak': peak_tf, 'unit': 'TFLOP/s', 'frac': achieved / peak_tf,
-                'traffic': NCU_TRAFFIC_BYTES.get(top), 'kernel': top,
+    traffic = NCU_TRAFFIC_BYTES_PER_Z.get(top)
+    roofline = {'bound': 'tensor', 'achieved': achieved, 'peak': pk['bf16_tflops'], 'unit': UNIT,
+                'frac': achieved / pk['bf16_tflops'],
+                'traffic': traffic * Zl * Hl / HEADS if traffic else None, 'kernel': top,
                 'flops_counted_per_launch': counted[top] * per_product,
                 'executed_tflops': executed[top] * per_product / (kern_ms[top] * 1e-3) / 1e12,
-                'peak_source': pk['source'] + ' (bf16 dense, sustained)'}
+                'frac_of_sustained_peak': achieved / pk.get('bf16_tflops_sustained', pk['bf16_tflops']),
+                'peak_source': pk['source'] + ' (bf16 dense, burst: the timed region lasts tens of milliseconds)'}
 
     # end to end: host -> device inputs and device -> host results inside the timed region,
     # through the library's host-operand entry (batch slices streamed over three CUDA streams)
     from torch_blocksparse_b200 import HostAttention
+    mod = main['mod']
+    host = {n: c[n].pin_memory() for n in ('q', 'k', 'v', 'do')}
     outs = [torch.empty_like(host['q']).pin_memory() for _ in range(4)]
-    pipe = HostAttention(mod, c['q'].size(1), c['q'].size(2), D, c['q'].dtype, dev, slice_batch=1, depth=3)
+    pipe = HostAttention(mod, Hl, SEQ, HEAD_DIM, c['q'].dtype, dev, slice_batch=1, depth=3)
     ins = [host[n] for n in ('q', 'k', 'v', 'do')]
-
-    def e2e_step():
-        return pipe.run(*ins, *outs)
-
     e2e_steps = max(3, min(args.steps, 10))
-    e2e_step().synchronize()
-    barrier()
+    pipe.run(*ins, *outs).synchronize()
+    T.barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(e2e_steps):
-        done = e2e_step()
+        done = pipe.run(*ins, *outs)
     torch.cuda.current_stream().wait_event(done)     # the last results are in host memory
     e1.record()
-    barrier()
-    e2e_t = torch.tensor([e0.elapsed_time(e1) * 1e-3], device=dev, dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(e2e_t, op=dist.ReduceOp.MAX)
+    T.barrier()
+    e2e_t = T.max_over_ranks(e0.elapsed_time(e1) * 1e-3)
     tensor_bytes = host['q'].numel() * host['q'].element_size()
-    e2e = {'value': flops_step * world * e2e_steps / float(e2e_t) / 1e12, 'unit': UNIT,
-           'h2d_bytes_per_step': 4 * tensor_bytes, 'd2h_bytes_per_step': 4 * tensor_bytes,
-           'ms_per_step': float(e2e_t) / e2e_steps * 1e3, 'steps': e2e_steps, 'numa_node': numa_node}
+    e2e = {'value': main['flops_total'] * e2e_steps / e2e_t / 1e12, 'unit': UNIT,
+           'h2d_bytes_per_step': 4 * tensor_bytes * world, 'd2h_bytes_per_step': 4 * tensor_bytes * world,
+           'ms_per_step': e2e_t / e2e_steps * 1e3, 'steps': e2e_steps, 'numa_node': numa_node,
+           'host_copy_gbs_per_gpu_per_direction': 4 * tensor_bytes * e2e_steps / e2e_t / 1e9}
+    del pipe, outs, host, ins
 
-    # verification off the clock: all-gather a digest of every rank's outputs, and
-    # have rank 0 recompute the last rank's shard and compare bit for bit
-    verify = None
-    if world > 1:
-        o = step()
-        digest = torch.stack([t.double().sum() for t in (o.detach(), q.grad, k.grad, v.grad)])
-        parts = [torch.empty_like(digest) for _ in range(world)]
-        dist.all_gather(parts, digest)
-        if rank == 0:
-            other = workloads.config4(args.attention, Z=args.z, seed=world - 1)
-            q2, k2, v2 = (other[n].to(dev).requires_grad_() for n in ('q', 'k', 'v'))
-            o2 = mod(q2, k2, v2)
-            o2.backward(other['do'].to(dev))
-            mine = torch.stack([t.double().sum() for t in (o2.detach(), q2.grad, k2.grad, v2.grad)])
-            verify = {'gathered_ranks': world, 'recomputed_rank': world - 1,
-                      'digest_equal': bool(torch.equal(mine, parts[world - 1]))}
+    extra = {}
+    if world > 1 and not args.no_secondary:
+        # every batch entry split over the heads of two ranks: layout slices and re-based tables on GPUs
+        zs = max(1, world // 2)
+        hs = run_sharded(args, T, dev, rank, world, zs, pk, profile=False, n_slices_checked=1)
+        extra['head_split'] = {'workload': 'the same layout with Z=%d: every batch entry split over the heads of %d ranks'
+                                           % (zs, world // zs),
+                               'local_shape_z_h': hs['local_shape'], 'ms_per_step': hs['elapsed'] / args.steps * 1e3,
+                               'tflops': hs['flops_total'] * args.steps / hs['elapsed'] / 1e12,
+                               'verify': hs.get('verify')}
+        del hs
+        torch.cuda.empty_cache()
+        # weak scaling: every rank a whole Z = Z_TOTAL problem of its own (entries rank*Z .. rank*Z + Z - 1)
+        cw = problem_entries(args.attention, list(range(rank * Z, rank * Z + Z)))
+        modw = SparseSelfAttention(layout=cw['layout'], block=cw['block'], fused=True)
+        stepw, _ = make_steps(modw, cw, dev, 1)
+        tw, _ = T.run(stepw, args.steps, warmup=3)
+        extra['weak'] = {'workload': 'one full Z=%d problem per rank' % Z, 'ms_per_step': tw / args.steps * 1e3,
+                         'tflops': workloads.attention_flops(cw['layout'], cw['block'], Z, HEAD_DIM) * world * args.steps / tw / 1e12}
+        del cw, modw, stepw
 
     if rank == 0:
         line = {
             'metric': METRIC, 'value': value, 'unit': UNIT, 'n_gpus': world, 'steps': args.steps,
             'warmup': max(args.warmup, 3), 'ms_per_step': elapsed / args.steps * 1e3, 'higher_is_better': True,
-            'scaling': 'weak', 'vs_baseline': None, 'dtype': 'f16', 'data': 'synthetic',
-            'config': config_dict(args, world), 'clocks': clocks, 'e2e': e2e,
+            'scaling': 'strong', 'vs_baseline': None, 'dtype': 'f16', 'data': 'synthetic',
+            'config': config_dict(args, world, main['n_sets']), 'clocks': clocks, 'e2e': e2e,
             'gpu_launches': args.steps * (fused.KERNELS_PER_FWD + fused.KERNELS_PER_BWD),
-            'roofline': roofline, 'kernel_ms': kern_ms, 'attempts': attempts,
+            'roofline': roofline, 'kernel_ms': kern_ms, 'attempts': main['attempts'],
+            'shard_z_h': main['local_shape'],
+            'host_overhead': {'kernel_busy_ms_per_step': main['busy'] / args.steps * 1e3,
+                              'elapsed_ms_per_step': elapsed / args.steps * 1e3},
             'frac_of_nominal_fp16_peak': value / world / 2250.0,
-            'frac_of_measured_peak': value / world / peak_tf,
+            'frac_of_measured_peak': value / world / pk['bf16_tflops'],
         }
-        if args.z != 8:
-            line['reduced_workload'] = 'Z=%d per GPU instead of 8: not the headline configuration' % args.z
+        if Z != Z_TOTAL:
+            line['reduced_workload'] = 'Z=%d instead of %d: not the headline configuration' % (Z, Z_TOTAL)
+        if 'verify' in main:
+            line['verify'] = main['verify']
+        line.update(extra)
+    del main
+    torch.cuda.empty_cache()
+    if rank == 0:
         if not args.no_cpu_baseline and world == 1:          # the host cores are timed on one rank at N = 1 only
             torch.set_num_threads(os.cpu_count() or 1)
-            dt, fl = cpu_attention_sample(c, args.cpu_slices)
+            dt, fl = cpu_attention_sample(args.attention, args.cpu_slices)
             line['cpu_baseline'] = {'value': fl / dt / 1e12, 'unit': UNIT, 'cores': torch.get_num_threads(), 'kind': 'port',
                                     'sample': '%d of the %d (batch, head) slices, dense-masked FP32 torch on FP16-rounded '
-                                              'inputs, %.1f s' % (args.cpu_slices, Z * 16 * world, dt)}
-        if not args.no_softmax:
+                                              'inputs, %.1f s' % (args.cpu_slices, Z_TOTAL * HEADS, dt)}
+        if world == 1 and not args.no_extras:
+            T1 = Timing(dev, 1)
+            other = 'bidirectional' if args.attention == 'unidirectional' else 'unidirectional'
+            cb = problem_entries(other, list(range(Z)))
+            line['config4_' + other] = attention_section('config4 %s, FP16, Z=%d' % (other, Z), cb, dev,
+                                                         max(3, args.steps // 2), pk, T1, 'f16')
+            del cb
+            torch.cuda.empty_cache()
+            # configuration 5 at its full size on one GPU (17 GB of operands and results); the inputs
+            # are drawn on the device (the CPU generator needs a minute for 4 x 1 G values)
+            c5 = workloads.config5(small=False, Z=1)
+            g = torch.Generator(device=dev).manual_seed(0)
+            shape = (32,) + tuple(c5['q'].shape[1:])
+            for n in ('q', 'k', 'v', 'do'):
+                c5[n] = torch.randn(shape, generator=g, device=dev, dtype=torch.bfloat16)
+            line['config5'] = attention_section('config5: BigBird-style BF16, Z=32, H=16, L=16384, head_dim 128, block 128 '
+                                                '(all of it on one GPU)', c5, dev, 3, pk, T1, 'bf16')
+            del c5
+            torch.cuda.empty_cache()
+        if world == 1 and not args.no_softmax:
             line['softmax'] = softmax_bench(dev, pk)
-        if verify is not None:
-            line['verify'] = verify
+        if world == 1 and not args.no_extras:
+            line['matmul'] = matmul_bench(dev, pk, iters=5)
         print(json.dumps(line))
     if world > 1:
         dist.barrier()
@@ -490,11 +671,13 @@ def main():
     ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
     ap.add_argument('--attention', default='unidirectional', choices=['unidirectional', 'bidirectional'])
     ap.add_argument('--cpu-slices', type=int, default=16, help='(batch, head) slices timed for cpu_baseline')
-    ap.add_argument('--ref-slices', type=int, default=2, help='(batch, head) slices per step of --impl reference')
+    ap.add_argument('--ref-slices', type=int, default=16, help='(batch, head) slices per step of --impl reference')
     ap.add_argument('--no-softmax', action='store_true')
+    ap.add_argument('--no-extras', action='store_true', help='skip the other configurations (C4 bidirectional, C5, MatMul)')
+    ap.add_argument('--no-secondary', action='store_true', help='N > 1: skip the head-split and weak-scaling runs')
     ap.add_argument('--only-softmax', action='store_true', help='run only the softmax section (profiling aid)')
-    ap.add_argument('--only-matmul', action='store_true', help='run only the MatMul section (configuration 2)')
-    ap.add_argument('--z', type=int, default=8, help='batch entries per GPU; anything but 8 is a reduced, '
+    ap.add_argument('--only-matmul', action='store_true', help='run only the MatMul section')
+    ap.add_argument('--z', type=int, default=Z_TOTAL, help='batch entries of the problem; anything but 8 is a reduced, '
                     'non-headline workload (profiling aid) and is flagged in the output')
     ap.add_argument('--no-cpu-baseline', action='store_true')
     args = ap.parse_args()

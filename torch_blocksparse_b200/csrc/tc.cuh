@@ -69,6 +69,14 @@ BSP_DEVI void bulk_load(void* dst, const void* src, uint32_t bytes, uint64_t* ba
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                ::"r"(saddr(dst)), "l"(reinterpret_cast<uint64_t>(src)), "r"(bytes), "r"(saddr(bar)) : "memory");
 }
+// Makes this thread's earlier writes to shared memory visible to the asynchronous proxy (the
+// tensor core reads MMA operands through it).
+BSP_DEVI void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+// Four consecutive FP32 values added to global memory in one reduction (16-byte aligned).
+BSP_DEVI void red_add4(float* p, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};"
+               ::"l"(p), "f"(__uint_as_float(a)), "f"(__uint_as_float(b)), "f"(__uint_as_float(c)), "f"(__uint_as_float(d)) : "memory");
+}
 BSP_DEVI void prefetch_map(const CUtensorMap* map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
 }

@@ -9,7 +9,17 @@ finishes in seconds (same layout family, same distributions).
 """
 import torch
 
-from torch_blocksparse_b200 import layouts
+# Layout generators: the package's native ones, or (LAYOUT_SOURCE = 'oracle') the CPU restatement
+# under oracle/, so that the CPU reference arm of the benchmark needs nothing of the product.
+LAYOUT_SOURCE = 'package'
+
+
+def _fixed_layout(H, nb, stride, attention):
+    if LAYOUT_SOURCE == 'oracle':
+        from oracle import lut
+        return torch.from_numpy(lut.make_fixed_layout(H, nb, 'fixed', stride, attention, 1, 1)).long()
+    from torch_blocksparse_b200 import layouts
+    return layouts.fixed(H, nb, stride, attention, 1, 1)
 
 
 def _gen(seed):
@@ -60,6 +70,7 @@ def config3(small=False):
     else:
         Z, H, L = 8, 16, 4096
     nb = L // 64
+    from torch_blocksparse_b200 import layouts
     layout = layouts.causal_band(H, nb, 4, 1)
     nnz = int(layout.sum())
     x = torch.randn((Z, nnz, 64, 64), generator=g).half()
@@ -84,7 +95,7 @@ def config4(attention='unidirectional', small=False, Z=None, seed=0):
         z, H, L = 8, 16, 8192
     if Z is not None:
         z = Z
-    layout = layouts.fixed(H, L // 64, 4, attention, 1, 1)
+    layout = _fixed_layout(H, L // 64, 4, attention)
     q, k, v, do = (torch.randn((z, H, L, 64), generator=g).half() for _ in range(4))
     return dict(layout=layout, block=64, q=q, k=k, v=v, do=do, scale=64 ** -0.5, dtype=torch.float16,
                 attention=attention)
@@ -100,6 +111,7 @@ def config5(small=False, Z=None):
         z, H, L = 32, 16, 16384
     if Z is not None:
         z = Z
+    from torch_blocksparse_b200 import layouts
     layout = layouts.bigbird(H, L // 128, 3, 3, 2, seed=0)
     q, k, v, do = (torch.randn((z, H, L, 128), generator=g).bfloat16() for _ in range(4))
     return dict(layout=layout, block=128, q=q, k=k, v=v, do=do, scale=128 ** -0.5, dtype=torch.bfloat16)
