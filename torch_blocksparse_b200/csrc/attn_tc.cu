@@ -55,14 +55,10 @@ using namespace tc;
 
 constexpr float kLog2eT = 1.4426950408889634f;
 constexpr float kNegInfT = -__builtin_huge_valf();
-constexpr int FWD = 0, DQ = 1, DKV = 2, BWD = 3;
-// BWD is dK / dV with dQ on top: the same tiles, lists and arithmetic, plus one more product per
-// chunk (dQ_chunk += dS K) whose result is added to an FP32 dQ in global memory.
-constexpr bool kv(int mode) { return mode == DKV || mode == BWD; }
+constexpr int FWD = 0, DQ = 1, DKV = 2;
 
 struct TcArgs {
-  void* out0; void* out1;             // FWD: O | DQ: dQ | DKV, BWD: dK, dV
-  float* dq_acc;                      // BWD: FP32 dQ [Z, H, L, D], accumulated with atomic adds
+  void* out0; void* out1;             // FWD: O | DQ: dQ | DKV: dK, dV
   float* lse_out;                     // FWD
   const float* lse; const float* delta;   // backward
   int64_t o_sz, o_sh, o_sr;           // strides of O (FWD); gradients are contiguous [Z, H, L, D]
@@ -178,19 +174,14 @@ template <int D, int MODE, bool KPM = false> struct Cfg {
   static constexpr int CH_BYTES = ATOMS * 64 * 128;
   // A key-padding mask is a bias per key: per column of the scores in the forward and in dQ
   // (64 values travel with every chunk), per row in dK/dV (read once per tile).
-  static constexpr bool BIAS = KPM && !kv(MODE);
-  static constexpr int STAGE = 2 * CH_BYTES + ((kv(MODE) || BIAS) ? 1024 : 0);   // + lse / delta, or the bias, of the chunk
-  static constexpr int TAIL_BYTES = kv(MODE) ? 512 : (BIAS ? 128 : 0);
+  static constexpr bool BIAS = KPM && MODE != DKV;
+  static constexpr int STAGE = 2 * CH_BYTES + ((MODE == DKV || BIAS) ? 1024 : 0);   // + lse / delta, or the bias, of the chunk
+  static constexpr int TAIL_BYTES = MODE == DKV ? 512 : (BIAS ? 128 : 0);
   // score buffers in tensor memory: two (scores of the next chunk are computed while this
   // one is consumed) where the columns allow it with two CTAs per SM, else one
   static constexpr int NBUF = MODE == FWD ? 2 : (D == 64 ? 1 : 2);
-  // BWD: the dS^T of a chunk is also written to shared memory (128 key rows x 64 queries, the
-  // layout of an MN-major operand), from where it is the A side of the dQ product.
-  static constexpr bool QP = MODE == BWD;
-  static constexpr int QP_BYTES = QP ? 128 * 128 : 0;
-  static constexpr int NSTAGE = ((MODE != FWD && D == 128) || QP) ? 3 : 4;
-  static constexpr int SMEM = QP_BYTES + NRES * RES_BYTES + NSTAGE * STAGE + 1024;
-  static_assert(!QP || D == 64, "the fused backward exists for head dimension 64");
+  static constexpr int NSTAGE = (MODE != FWD && D == 128) ? 3 : 4;
+  static constexpr int SMEM = NRES * RES_BYTES + NSTAGE * STAGE + 1024;
   static constexpr int SCORE_COLS = MODE == FWD ? 64 : 128;    // per buffer: S (and dP)
   // Early release (dQ at head_dim 64): the packed dS operand of the accumulating product gets
   // its own double-buffered columns instead of overwriting the scores, so the score buffer is
@@ -200,7 +191,7 @@ template <int D, int MODE, bool KPM = false> struct Cfg {
   // dK/dV at head_dim 64 has no spare columns.  There the packed P^T and dS^T both go over
   // dP^T's columns (a thread's 32 columns of dP^T hold its 16 + 16 packed columns), so S^T's
   // columns are released after the read and only dP^T waits for the accumulation.
-  static constexpr bool ER2 = kv(MODE) && D == 64;
+  static constexpr bool ER2 = MODE == DKV && D == 64;
   static constexpr int PK_BASE = NBUF * SCORE_COLS;
   static constexpr int ACC_BASE = PK_BASE + (ER ? 64 : 0);
   // forward: one O accumulator per half of the key chunk (the two threads of a row keep
@@ -246,10 +237,9 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
   constexpr int ATOMS = C::ATOMS, ST = C::NSTAGE, NC = C::NC, NBUF = C::NBUF;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = smem_raw + ((1024 - (saddr(smem_raw) & 1023)) & 1023);
-  unsigned char* stq = smem;                                   // BWD: dS^T of the chunk, [128 key rows][128 B], swizzled
-  unsigned char* res = smem + C::QP_BYTES;                     // [NRES][ATOMS][128 rows][128 B]
+  unsigned char* res = smem;                                   // [NRES][ATOMS][128 rows][128 B]
   unsigned char* stg = res + C::NRES * C::RES_BYTES;           // [ST][ch0 | ch1 | lse, delta]
-  __shared__ uint64_t bar_res, bar_rt, bar_rd, bar_qr, bar_full[ST], bar_s[4], bar_p[4], bar_acc[4], bar_done;
+  __shared__ uint64_t bar_res, bar_rt, bar_rd, bar_full[ST], bar_s[4], bar_p[4], bar_acc[4], bar_done;
   __shared__ float xch[2][2][128];                           // forward: (max, sum) of the two halves of every row
   __shared__ uint32_t tmem_slot;
   __shared__ int failed;
@@ -277,7 +267,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
                           : reinterpret_cast<T*>(a.out0) + (zh + grow) * D;
       for (int c = 0; c < D; c += 8) {
         *reinterpret_cast<uint4*>(o0 + c) = make_uint4(0, 0, 0, 0);
-        if (kv(MODE)) *reinterpret_cast<uint4*>(reinterpret_cast<T*>(a.out1) + (zh + grow) * D + c) = make_uint4(0, 0, 0, 0);
+        if (MODE == DKV) *reinterpret_cast<uint4*>(reinterpret_cast<T*>(a.out1) + (zh + grow) * D + c) = make_uint4(0, 0, 0, 0);
       }
       if (MODE == FWD) a.lse_out[zh + grow] = kNegInfT;
     }
@@ -292,7 +282,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
       tma_load_4d(sp + at * 8192, &m_ch0, &bar_full[stage], at * 64, crow, h, z);
       tma_load_4d(sp + C::CH_BYTES + at * 8192, &m_ch1, &bar_full[stage], at * 64, crow, h, z);
     }
-    if (kv(MODE)) {
+    if (MODE == DKV) {
       bulk_load(sp + 2 * C::CH_BYTES, a.lse + zh + crow, 256, &bar_full[stage]);
       bulk_load(sp + 2 * C::CH_BYTES + 256, a.delta + zh + crow, 256, &bar_full[stage]);
     }
@@ -320,7 +310,6 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
     failed = 0;
     mbar_init(&bar_rt, NC);
     mbar_init(&bar_rd, NC);
-    mbar_init(&bar_qr, NC);
     if (C::ER) mbar_init(&bar_p[1], NC);
     if (C::ER2) mbar_init(&bar_s[2], 1);
     for (int b = 0; b < 4; ++b) mbar_init(&bar_acc[b], 1);
@@ -412,7 +401,6 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
       // (64 cycles instead of 2 x 48)
       constexpr bool WIDE = ATOMS == 2;
       const uint32_t idesc_acc = WIDE ? instr_desc(128, 128, 1, IsBf16<T>::v) : idesc_mn;
-      const uint32_t idesc_qp = idesc_mn | (1u << 15);      // A MN-major as well
       auto wide = [](uint64_t d) { return WIDE ? ((d & ~0x3FFF0000ull) | (512ull << 16)) : d; };
       auto accumulate = [&](int t) {
         const uint32_t ts = tmem + (t % NBUF) * C::SCORE_COLS;
@@ -444,19 +432,6 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
               }
             }
           }
-        if constexpr (C::QP) {
-          // dQ_chunk (64 queries x D) = dS (64 x 128 keys) . K (128 x D), as an M = 128 product whose
-          // upper 64 rows are never read: the A operand is dS^T in shared memory, MN-major, its
-          // second group of 64 rows taken from the resident V tile (any finite data would do);
-          // the B operand is the resident K tile, MN-major.  Eight K-steps of 16 keys.  The
-          // result goes over S^T's columns, which the compute warps have read.
-          const uint32_t a_lo = ((saddr(stq) & 0x3FFFF) >> 4) | ((uint32_t)((C::QP_BYTES + C::RES_BYTES) >> 4) << 16);
-#pragma unroll
-          for (int ks = 0; ks < 8; ++ks) {
-            if (ks > 0) mma_ss_acc(ts, desc_from_lo(a_lo + ks * 128), desc_from_lo(res_lo + ks * 128), idesc_qp);
-            else mma_ss(ts, desc_from_lo(a_lo), desc_from_lo(res_lo), idesc_qp, 0u);
-          }
-        }
         commit(&bar_acc[t & 3]);      // chunk t fully consumed: its score buffer and its stage are free
       };
       // Two issuing threads, one per kind of product, each in its own warp: the scores of chunk
@@ -469,8 +444,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
           prep_scores(t);
           ok = mbar_wait(&bar_full[t % ST], (t / ST) & 1, fl);
           if (C::ER || C::ER2) {
-            // scores of chunk t - 1 are in registers (BWD: its dQ product, which took their columns, has been read)
-            if (ok && t >= 1) ok = mbar_wait(C::QP ? &bar_qr : &bar_rd, (t - 1) & 1, fl);
+            if (ok && t >= 1) ok = mbar_wait(&bar_rd, (t - 1) & 1, fl);     // scores of chunk t - 1 are in registers
           } else {
             if (ok && t >= NBUF) ok = mbar_wait(&bar_acc[(t - NBUF) & 3], ((t - NBUF) >> 2) & 1, fl);
           }
@@ -671,7 +645,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
       float my_lse = (MODE == DQ && row_ok) ? a.lse[zh + grow] : 0.f;
       if ((KPM || FINE) && my_lse == kNegInfT) my_lse = -kNegInfT;
       // dK/dV: the bias of this thread's key row
-      const float my_b = (KPM && kv(MODE) && row_ok)
+      const float my_b = (KPM && MODE == DKV && row_ok)
           ? kpm_term(static_cast<float>(reinterpret_cast<const T*>(a.kpm)[z * a.kpm_sz + grow]), a.kpm_mul) : 0.f;
       const float my_d = (MODE == DQ && row_ok) ? a.delta[zh + grow] : 0.f;
       const float my_ds = my_d * a.scale;
@@ -800,36 +774,10 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
             }
             tmem_st8(ts + 64 + hv * 16, ph);
             tmem_st8(ts + 64 + hv * 16 + 8, dr);
-            if constexpr (C::QP) {
-              // the same 16 values of dS^T to this key row of the shared-memory copy: 16-byte units
-              // 4 chalf + 2 hv and the next, swizzled by the row as the MMA expects
-              unsigned char* row = stq + trow * 128;
-              const int u = 4 * chalf + 2 * hv;
-              *reinterpret_cast<uint4*>(row + ((u ^ (trow & 7)) << 4)) = make_uint4(dr[0], dr[1], dr[2], dr[3]);
-              *reinterpret_cast<uint4*>(row + (((u + 1) ^ (trow & 7)) << 4)) = make_uint4(dr[4], dr[5], dr[6], dr[7]);
-            }
           }
-          if constexpr (C::QP) fence_async_smem();
           tmem_st_wait();
           fence_before();
           warp_arrive(&bar_p[0], lane);
-          if constexpr (C::QP) {
-            // the dQ product of this chunk: rows 0 .. 63 of the accumulator (the warps of the tile's
-            // first half hold them), 32 columns per thread, added to the FP32 dQ of the chunk's rows
-            ok = mbar_wait_warp(&bar_acc[t & 3], (t >> 2) & 1, fl);
-            if (!ok) break;
-            fence_after();
-            if (quarter < 2) {
-              uint32_t qa[32];
-              tmem_ld32(tmem + lane_base + chalf * 32, qa);
-              tmem_ld_wait();
-              float* dst = a.dq_acc + (zh + (int64_t)a.chunk[first + t] * 64 + trow) * D + chalf * 32;
-#pragma unroll
-              for (int i = 0; i < 32; i += 4) red_add4(dst + i, qa[i], qa[i + 1], qa[i + 2], qa[i + 3]);
-            }
-            fence_before();
-            warp_arrive(&bar_qr, lane);
-          }
           continue;
         }
         // Two passes of 16 columns keep the live registers of a pass at 48.  The packed
@@ -846,11 +794,11 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
 #pragma unroll
               for (int i = 0; i < 16; ++i) sr[i] = kNegInfBits;
             }
-            if (FINE && a.causal) mask_causal<16, kv(MODE)>(sr, a.chunk[first + t] * 64 + chalf * 32 + hv * 16, (int)grow);
+            if (FINE && a.causal) mask_causal<16, MODE == DKV>(sr, a.chunk[first + t] * 64 + chalf * 32 + hv * 16, (int)grow);
 #pragma unroll
             for (int i = 0; i < 16; i += 4) {
               float ls[4], es[4];
-              if (kv(MODE)) {                            // per-query lse and delta * scale of this chunk
+              if (MODE == DKV) {                            // per-query lse and delta * scale of this chunk
                 const float4 lv = vec[hv * 4 + i / 4], ev = vec[16 + hv * 4 + i / 4];
                 ls[0] = lv.x; ls[1] = lv.y; ls[2] = lv.z; ls[3] = lv.w;
                 es[0] = ev.x * a.scale; es[1] = ev.y * a.scale; es[2] = ev.z * a.scale; es[3] = ev.w * a.scale;
@@ -881,7 +829,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
 #pragma unroll
             for (int i = 0; i < 8; ++i) { pr[i] = 0u; dr[i] = 0u; }
           }
-          if (kv(MODE)) tmem_st8(ts + hv * 8, pr);
+          if (MODE == DKV) tmem_st8(ts + hv * 8, pr);
           tmem_st8(ts + 64 + hv * 8, dr);
         }
         tmem_st_wait();
@@ -932,7 +880,7 @@ EncodeTiledFn encode_fn() {
 
 // [Z, H, L, D] operand with unit stride on D: boxes of 64 columns x 64 rows, 128-byte swizzle.
 int encode_map(CUtensorMap* m, const void* ptr, int dtype, int Z, int H, int L, int D,
-               int64_t sz, int64_t sh, int64_t sr) {
+             int64_t sz, int64_t sh, int64_t sr) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return fail(BSP_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
   // The encoder is a driver call and needs the primary context bound to this thread; a thread
