@@ -448,6 +448,41 @@ def softmax_bench(dev, pk, iters=20):
     }
 
 
+def table_build_times(dev):
+    """One-off costs of the layout-derived data for the configuration-4 layout (milliseconds):
+    the three reference-format tables and the kernels' metadata on the host, the metadata on the
+    device, the attention tile lists.  The reference spends 0.2 - 0.35 s in its Python builders
+    for this layout (measured on its own code, CPU only)."""
+    from torch_blocksparse_b200 import layouts, tables
+    layout = layouts.fixed(HEADS, SEQ // BLOCK, 4, 'unidirectional')
+
+    def ms(fn, n=3):
+        best = None
+        for _ in range(n):
+            tables.clear_cache()
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            fn()
+            torch.cuda.synchronize()
+            dt = (time.perf_counter() - t0) * 1e3
+            best = dt if best is None else min(best, dt)
+        return best
+
+    lay_dev = layout.to(dev)
+    out = {'layout': 'config4 unidirectional [16,128,128], 36 864 blocks',
+           'reference_tables_host_ms': ms(lambda: (tables.make_sdd_lut(layout, BLOCK), tables.make_dxx_lut(layout, BLOCK, 16, False),
+                                                   tables.make_dxx_lut(layout, BLOCK, 16, True), tables.make_softmax_lut(layout))),
+           'metadata_host_build_and_upload_ms': ms(lambda: tables.build_meta(layout).on(dev)),
+           'metadata_device_build_ms': ms(lambda: tables.build_meta_device(lay_dev)),
+           'attention_tiles_host_build_and_upload_ms': ms(lambda: tables.build_attn_tiles(layout, BLOCK).on(dev)),
+           'cached_lookup_ms': None}
+    tables.build_meta(layout)
+    t0 = time.perf_counter()
+    tables.build_meta(layout)
+    out['cached_lookup_ms'] = (time.perf_counter() - t0) * 1e3
+    return out
+
+
 def oracle_check(gathered, entries, slices):
     """Compares (batch, head) slices of the gathered o, dq, dk, dv with the CPU oracle on the
     problem's own inputs.  `entries`: {z: config dict of batch entry z}.  Returns the largest
@@ -657,6 +692,7 @@ def run_ours(args):
             line['softmax'] = softmax_bench(dev, pk)
         if world == 1 and not args.no_extras:
             line['matmul'] = matmul_bench(dev, pk, iters=5)
+            line['table_build'] = table_build_times(dev)
         print(json.dumps(line))
     if world > 1:
         dist.barrier()

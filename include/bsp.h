@@ -144,6 +144,23 @@ int bsp_meta_build(const int64_t* layout, int H, int Mb, int Nb,
                    int32_t* out, int64_t out_cap, int64_t* total);
 
 /*
+ * bsp_meta_build on the device: `layout` is a DEVICE pointer to [H, Mb, Nb]
+ * elements of elem_bytes (1, 4 or 8) bytes, nonzero = present; `out` a DEVICE
+ * buffer of at least bsp_meta_device_capacity(H, Mb, Nb) ints (the worst case:
+ * the number of nonzero blocks is only known once the kernels have counted
+ * them).  The buffer's leading ints are bit-identical to what bsp_meta_build
+ * writes for the same layout.  Runs on `stream`; when hdr_host is not NULL the
+ * BSP_META_HEADER header ints are copied to it and the stream is synchronised
+ * (the launch code and the caller need the block count): those 32 bytes are the
+ * only host traffic.  Replaces, for the execution metadata, the reference's
+ * host-side table rebuild and upload per (dtype, device)
+ * (torch_blocksparse/matmul.py:611-641, 293, 455; softmax.py:220).
+ */
+int64_t bsp_meta_device_capacity(int H, int Mb, int Nb);
+int bsp_meta_build_device(const void* layout, int elem_bytes, int H, int Mb, int Nb,
+                          int32_t* out, int64_t out_cap, int32_t* hdr_host, void* stream);
+
+/*
  * Tile lists of the tcgen05 attention kernels (no counterpart in the
  * reference).  Those kernels work on tiles of 128 query rows (forward, dQ) or
  * 128 key rows (dK, dV), made of two 64-row chunks, and walk 64-row chunks of

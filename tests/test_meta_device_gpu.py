@@ -1,0 +1,85 @@
+"""Execution metadata built on the device against the host builder (bit-exact), and the
+process-wide cache keyed by the layout's content."""
+import numpy as np
+import pytest
+import torch
+
+from tests.util import assert_close, load_npz
+from torch_blocksparse_b200 import MatMul, Softmax, SparseSelfAttention, layouts, tables
+
+pytestmark = pytest.mark.gpu
+DEV = 'cuda'
+
+
+def _host_meta(lay):
+    tables.clear_cache()
+    return tables.build_meta(lay)
+
+
+def _check_equal(lay_cpu, dtype=torch.int64):
+    want = _host_meta(lay_cpu)
+    dev_layout = lay_cpu.to(DEV).to(dtype) if dtype != torch.bool else (lay_cpu != 0).to(DEV)
+    got = tables.build_meta_device(dev_layout)
+    assert torch.equal(got.hdr, want.hdr), 'header differs'
+    assert torch.equal(got.on(DEV).cpu(), want.host), 'metadata buffer differs'
+    assert (got.H, got.Mb, got.Nb, got.nnz, got.max_row, got.max_col) == \
+           (want.H, want.Mb, want.Nb, want.nnz, want.max_row, want.max_col)
+
+
+def test_device_build_equals_host_build_on_fixture_layouts():
+    z = load_npz('lut_small.npz')
+    for name in sorted({k.split('/')[0] for k in z.files}):
+        _check_equal(torch.from_numpy(z[name + '/layout']))
+    for lay in (layouts.fixed(16, 128, 4, 'unidirectional'), layouts.fixed(16, 128, 4, 'bidirectional'),
+                layouts.bigbird(16, 128, 3, 3, 2, seed=0), layouts.causal_band(16, 64, 4, 1),
+                torch.zeros((2, 3, 5), dtype=torch.long), torch.ones((1, 1, 1), dtype=torch.long)):
+        _check_equal(lay)
+
+
+def test_device_build_equals_host_build_on_1000_random_layouts():
+    rng = np.random.default_rng(2024)
+    dtypes = [torch.int64, torch.int32, torch.uint8, torch.bool]
+    for i in range(1000):
+        H, Mb, Nb = int(rng.integers(1, 6)), int(rng.integers(1, 40)), int(rng.integers(1, 40))
+        if i % 50 == 0:
+            H, Mb, Nb = 3, int(rng.integers(300, 500)), int(rng.integers(300, 500))     # more than one scan chunk
+        p = rng.choice([0.0, 0.05, 0.3, 0.6, 0.95, 1.0])
+        lay = torch.from_numpy((rng.random((H, Mb, Nb)) < p).astype(np.int64))
+        _check_equal(lay, dtypes[i % 4])
+
+
+def test_ops_on_one_layout_share_one_buffer_and_a_changed_layout_is_rebuilt():
+    tables.clear_cache()
+    g = torch.Generator().manual_seed(1)
+    layout = (torch.rand((2, 4, 4), generator=g) > 0.4).long()
+    layout[:, :, 0] = 1
+    a = MatMul(layout, 64, 'sdd', trans_b=True)
+    b = MatMul(layout.clone(), 64, 'dsd')                      # another tensor object, same content
+    assert a.meta is b.meta and a.meta.on(DEV).data_ptr() == b.meta.on(DEV).data_ptr()
+    m1 = SparseSelfAttention(layout=layout, block=64)
+    m2 = SparseSelfAttention(layout=layout.clone(), block=64)
+    m1.get_ops(2, 256), m2.get_ops(2, 256)
+    assert m1.tiles[(2, 256)] is m2.tiles[(2, 256)] and m1.ops[(2, 256)][0].meta is a.meta
+    s1, s2 = Softmax(layout, 64), Softmax(layout.clone(), 64)
+    assert s1.make_lut(torch.device(DEV))[0].data_ptr() == s2.make_lut(torch.device(DEV))[0].data_ptr()
+    changed = layout.clone()
+    changed[0, 3, 3] = 1 - changed[0, 3, 3]
+    c = MatMul(changed, 64, 'sdd', trans_b=True)
+    assert c.meta is not a.meta and c.meta.nnz != a.meta.nnz
+
+
+def test_matmul_with_a_device_layout_matches_the_host_layout_path():
+    tables.clear_cache()
+    g = torch.Generator().manual_seed(5)
+    layout = (torch.rand((2, 4, 6), generator=g) > 0.5).long()
+    layout[:, 0, 0] = 1
+    before = dict(tables.CACHE_STATS)
+    x = torch.randn((2, 2, 256, 128), generator=g).half().to(DEV)
+    y = torch.randn((2, 2, 128, 384), generator=g).half().to(DEV)
+    on_host = MatMul(layout, 64, 'sdd')(x, y)
+    on_dev = MatMul(layout.to(DEV), 64, 'sdd')(x, y)
+    assert tables.CACHE_STATS['device_builds'] == before['device_builds'] + 1
+    assert torch.equal(on_host, on_dev)
+    s = torch.randn((2, int(layout.sum()), 64, 64), generator=g).half().to(DEV)
+    w = torch.randn((2, 2, 384, 128), generator=g).half().to(DEV)
+    assert_close(MatMul(layout.to(DEV), 64, 'dsd')(s, w), MatMul(layout, 64, 'dsd')(s, w), 'dsd')

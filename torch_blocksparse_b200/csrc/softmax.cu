@@ -75,6 +75,29 @@ __device__ __forceinline__ void store_vec(T* p, const float (&f)[Vec<T>::N]) {
   __stcs(reinterpret_cast<uint4*>(p), raw);
 }
 
+// Two 16-bit values of one 32-bit word <-> a pair of floats.
+template <typename T> __device__ __forceinline__ float2 word_to_f2(uint32_t w);
+template <> __device__ __forceinline__ float2 word_to_f2<__half>(uint32_t w) { return __half22float2(*reinterpret_cast<__half2*>(&w)); }
+template <> __device__ __forceinline__ float2 word_to_f2<__nv_bfloat16>(uint32_t w) {
+  return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
+}
+template <> __device__ __forceinline__ float2 word_to_f2<float>(uint32_t w) { return make_float2(__uint_as_float(w), 0.f); }
+template <typename T> __device__ __forceinline__ uint32_t f2_to_word(float2 v);
+template <> __device__ __forceinline__ uint32_t f2_to_word<__half>(float2 v) {
+  __half2 h = __floats2half2_rn(v.x, v.y);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+template <> __device__ __forceinline__ uint32_t f2_to_word<__nv_bfloat16>(float2 v) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(v.x, v.y);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+template <> __device__ __forceinline__ uint32_t f2_to_word<float>(float2 v) { return __float_as_uint(v.x); }
+__device__ __forceinline__ float max3f(float a, float b, float c) {
+  float r;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+  return r;
+}
+
 // 2^x on the special-function unit (ex2.approx: about 2 ulp, denormals flushed).
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
@@ -475,7 +498,13 @@ softmax_fwd_group(FwdArgs a, int Z, int lpr_log2, int header_ints) {
 // kept in registers as one term per element, and the x vectors of the next two
 // batch entries are in flight while the current one is reduced.
 template <typename T, int NV, typename S>
-__global__ void __launch_bounds__(kGroupWarps * 32, 3)
+#ifndef BSP_SM_CTAS
+#define BSP_SM_CTAS 3
+#endif
+#ifndef BSP_SM_DEPTH
+#define BSP_SM_DEPTH 2
+#endif
+__global__ void __launch_bounds__(kGroupWarps * 32, BSP_SM_CTAS)
 softmax_fwd_zloop(FwdArgs a, int Z, int lpr_log2, int header_ints) {
   constexpr int N = Vec<T>::N;
   constexpr float kLog2e = 1.4426950408889634f;
@@ -506,7 +535,7 @@ softmax_fwd_zloop(FwdArgs a, int Z, int lpr_log2, int header_ints) {
 #pragma unroll
   for (int k = 0; k < NV; ++k)
     if (k < size) cur[k] = __ldcs(reinterpret_cast<const uint4*>(xp + ((int64_t)k << (2 * bl))));
-  if (Z > 1) {
+  if (BSP_SM_DEPTH == 2 && Z > 1) {
 #pragma unroll
     for (int k = 0; k < NV; ++k)
       if (k < size) nxt[k] = __ldcs(reinterpret_cast<const uint4*>(xp + a.x_sz + ((int64_t)k << (2 * bl))));
@@ -576,72 +605,139 @@ softmax_fwd_zloop(FwdArgs a, int Z, int lpr_log2, int header_ints) {
   // x of the next two batch entries is in flight while this one is reduced
   for (int z = 0; z < Z; ++z) {
     uint4 nx2[NV];
-    if (z + 2 < Z) {
+    if (z + BSP_SM_DEPTH < Z) {
 #pragma unroll
       for (int k = 0; k < NV; ++k)
-        if (k < size) nx2[k] = __ldcs(reinterpret_cast<const uint4*>(xp + 2 * a.x_sz + ((int64_t)k << (2 * bl))));
+        if (k < size) nx2[k] = __ldcs(reinterpret_cast<const uint4*>(xp + BSP_SM_DEPTH * a.x_sz + ((int64_t)k << (2 * bl))));
     }
-    float f[NV][N];
-    float m = kNegInf;
+    if constexpr (N == 8) {
+      // 16-bit storage: two elements per instruction through the packed FP32 operations of
+      // sm_100 (multiply-add, add, multiply) and three-input maxima; per pair of elements
+      // about fifteen instructions, most of them the conversions from and to 16 bits.
+      float2 f[NV][4];
+      float m0 = kNegInf, m1 = kNegInf;
+      const float2 sc2 = make_float2(a.scale, a.scale);
 #pragma unroll
-    for (int k = 0; k < NV; ++k) {
-      if (k < size) {
-        expand<T>(cur[k], f[k]);
-        if constexpr (PACKED) {
-          float r[N];
-          expand<T>(pterm[k], r);
+      for (int k = 0; k < NV; ++k) {
+        if (k < size) {
+          const uint32_t* xw = reinterpret_cast<const uint32_t*>(&cur[k]);
 #pragma unroll
-          for (int i = 0; i < N; ++i) f[k][i] = fmaf(f[k][i], a.scale, r[i]);
-        } else if constexpr (TERM) {
-#pragma unroll
-          for (int i = 0; i < N; ++i) f[k][i] = fmaf(f[k][i], a.scale, term[k][i]);
-        } else {
-#pragma unroll
-          for (int i = 0; i < N; ++i) f[k][i] *= a.scale;
+          for (int i = 0; i < 4; ++i) {
+            float2 v = word_to_f2<T>(xw[i]);
+            if constexpr (PACKED) v = __ffma2_rn(v, sc2, word_to_f2<T>(reinterpret_cast<const uint32_t*>(&pterm[k])[i]));
+            else if constexpr (TERM) v = __ffma2_rn(v, sc2, make_float2(term[k][2 * i], term[k][2 * i + 1]));
+            else v = __fmul2_rn(v, sc2);
+            if constexpr (S::KPM != 0) {
+              const float2 r = word_to_f2<T>(reinterpret_cast<const uint32_t*>(&kcur[k])[i]);
+              if constexpr (S::KPM == 2) { v.x = r.x == 0.f ? kNegInf : v.x; v.y = r.y == 0.f ? kNegInf : v.y; }
+              else v = __fadd2_rn(v, r);
+            }
+            f[k][i] = v;
+            if (i & 1) m1 = max3f(m1, v.x, v.y); else m0 = max3f(m0, v.x, v.y);
+          }
         }
-        if constexpr (S::KPM != 0) {
-          float r[N];
-          expand<T>(kcur[k], r);
+      }
+      float m = fmaxf(m0, m1);
+      kpm += a.kpm_sz;
+      if constexpr (S::KPM != 0) {
+        if (z + 1 < Z) {
 #pragma unroll
-          for (int i = 0; i < N; ++i) f[k][i] = S::KPM == 2 ? (r[i] == 0.f ? kNegInf : f[k][i]) : f[k][i] + r[i];
+          for (int k = 0; k < NV; ++k)
+            if (k < size) kcur[k] = load_raw(kpm + col[k], true);
         }
-#pragma unroll
-        for (int i = 0; i < N; ++i) m = fmaxf(m, f[k][i]);
       }
-    }
-    // the key-padding vectors of the next batch entry take over the registers of
-    // the current ones as soon as those are consumed
-    kpm += a.kpm_sz;
-    if constexpr (S::KPM != 0) {
-      if (z + 1 < Z) {
+      for (int o = (1 << lpr_log2) >> 1; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+      const float ml2 = m * kLog2e;
+      const float2 l2 = make_float2(kLog2e, kLog2e), nm2 = make_float2(-ml2, -ml2);
+      float2 s2 = make_float2(0.f, 0.f);
 #pragma unroll
-        for (int k = 0; k < NV; ++k)
-          if (k < size) kcur[k] = load_raw(kpm + col[k], true);
+      for (int k = 0; k < NV; ++k) {
+        if (k < size) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float2 y = __ffma2_rn(f[k][i], l2, nm2);
+            f[k][i] = make_float2(fast_exp2(y.x), fast_exp2(y.y));
+            s2 = __fadd2_rn(s2, f[k][i]);
+          }
+        }
       }
-    }
-    for (int o = (1 << lpr_log2) >> 1; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-    const float ml2 = m * kLog2e;
-    float sum = 0.f;
+      float sum = s2.x + s2.y;
+      for (int o = (1 << lpr_log2) >> 1; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+      const float inv = 1.f / sum;
+      const float2 inv2 = make_float2(inv, inv);
 #pragma unroll
-    for (int k = 0; k < NV; ++k) {
-      if (k < size) {
+      for (int k = 0; k < NV; ++k) {
+        if (k < size) {
+          uint4 o;
+          uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
 #pragma unroll
-        for (int i = 0; i < N; ++i) { f[k][i] = fast_exp2(fmaf(f[k][i], kLog2e, -ml2)); sum += f[k][i]; }
+          for (int i = 0; i < 4; ++i) ow[i] = f2_to_word<T>(__fmul2_rn(f[k][i], inv2));
+          __stcs(reinterpret_cast<uint4*>(xp + ((int64_t)k << (2 * bl))), o);
+        }
       }
-    }
-    for (int o = (1 << lpr_log2) >> 1; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-    const float inv = 1.f / sum;
-#pragma unroll
-    for (int k = 0; k < NV; ++k) {
-      if (k < size) {
-#pragma unroll
-        for (int i = 0; i < N; ++i) f[k][i] *= inv;
-        store_vec(xp + ((int64_t)k << (2 * bl)), f[k]);
+    } else {
+      float f[NV][N];
+      float m = kNegInf;
+  #pragma unroll
+      for (int k = 0; k < NV; ++k) {
+        if (k < size) {
+          expand<T>(cur[k], f[k]);
+          if constexpr (PACKED) {
+            float r[N];
+            expand<T>(pterm[k], r);
+  #pragma unroll
+            for (int i = 0; i < N; ++i) f[k][i] = fmaf(f[k][i], a.scale, r[i]);
+          } else if constexpr (TERM) {
+  #pragma unroll
+            for (int i = 0; i < N; ++i) f[k][i] = fmaf(f[k][i], a.scale, term[k][i]);
+          } else {
+  #pragma unroll
+            for (int i = 0; i < N; ++i) f[k][i] *= a.scale;
+          }
+          if constexpr (S::KPM != 0) {
+            float r[N];
+            expand<T>(kcur[k], r);
+  #pragma unroll
+            for (int i = 0; i < N; ++i) f[k][i] = S::KPM == 2 ? (r[i] == 0.f ? kNegInf : f[k][i]) : f[k][i] + r[i];
+          }
+  #pragma unroll
+          for (int i = 0; i < N; ++i) m = fmaxf(m, f[k][i]);
+        }
+      }
+      // the key-padding vectors of the next batch entry take over the registers of
+      // the current ones as soon as those are consumed
+      kpm += a.kpm_sz;
+      if constexpr (S::KPM != 0) {
+        if (z + 1 < Z) {
+  #pragma unroll
+          for (int k = 0; k < NV; ++k)
+            if (k < size) kcur[k] = load_raw(kpm + col[k], true);
+        }
+      }
+      for (int o = (1 << lpr_log2) >> 1; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+      const float ml2 = m * kLog2e;
+      float sum = 0.f;
+  #pragma unroll
+      for (int k = 0; k < NV; ++k) {
+        if (k < size) {
+  #pragma unroll
+          for (int i = 0; i < N; ++i) { f[k][i] = fast_exp2(fmaf(f[k][i], kLog2e, -ml2)); sum += f[k][i]; }
+        }
+      }
+      for (int o = (1 << lpr_log2) >> 1; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+      const float inv = 1.f / sum;
+  #pragma unroll
+      for (int k = 0; k < NV; ++k) {
+        if (k < size) {
+  #pragma unroll
+          for (int i = 0; i < N; ++i) f[k][i] *= inv;
+          store_vec(xp + ((int64_t)k << (2 * bl)), f[k]);
+        }
       }
     }
     xp += a.x_sz;
 #pragma unroll
-    for (int k = 0; k < NV; ++k) { cur[k] = nxt[k]; nxt[k] = nx2[k]; }
+    for (int k = 0; k < NV; ++k) { cur[k] = BSP_SM_DEPTH == 2 ? nxt[k] : nx2[k]; nxt[k] = nx2[k]; }
   }
 }
 

@@ -108,7 +108,9 @@ class Softmax:
         """Table cache per device (softmax.py:332-336)."""
         key = (device, )
         if key not in self.lut_cache:
-            self.lut_cache[key] = _sparse_softmax.make_lut(self.layout, self.block, device)
+            # (one table per layout content and device for the whole process: ops on the same layout share it)
+            self.lut_cache[key] = tables._cached('softmax_lut', self.layout, (str(device),),
+                                                 lambda: _sparse_softmax.make_lut(self.layout, self.block, device))
         return self.lut_cache[key]
 
     def __init__(self, layout, block, bench=False):

@@ -9,7 +9,9 @@ the reference's builders return:
   make_fixed_layout torch_blocksparse/deepspeedsparseselfattention.py:33-65
 `build_meta` produces the CSR/CSC execution metadata the kernels read.
 """
+import collections
 import ctypes
+import hashlib
 
 import torch
 
@@ -99,31 +101,122 @@ def make_fixed_layout(num_heads, num_blocks, mode, block_stride, attention, numv
     return out
 
 
-class Meta:
-    """Execution metadata of one layout: host header + device buffer."""
+# ---------------------------------------------------------------------------------------------
+# Process-wide cache of the execution metadata and the attention tile lists, keyed by the
+# layout's content: ops built on one layout share one buffer, a changed layout is rebuilt.
+# ---------------------------------------------------------------------------------------------
+_CACHE = collections.OrderedDict()
+_CACHE_ENTRIES = 64
+CACHE_STATS = {'hits': 0, 'misses': 0, 'device_builds': 0, 'host_builds': 0}
 
-    def __init__(self, host):
-        self.host = host                      # int32 CPU tensor (whole buffer)
-        self.hdr = host[:_lib.META_HEADER].clone()
-        self.H, self.Mb, self.Nb, self.nnz = (int(v) for v in host[1:5])
-        self.max_row, self.max_col = int(host[5]), int(host[6])
+
+def layout_key(layout):
+    """Content key of a layout: for a host tensor the SHA-1 of its nonzero pattern, for a device
+    tensor two 64-bit checksums computed on the device (16 bytes come back to the host)."""
+    if layout.dim() != 3:
+        raise ValueError('layout must be a [H, Mb, Nb] tensor')
+    present = layout != 0
+    if layout.is_cuda:
+        flat = present.reshape(-1).to(torch.int64)
+        idx = torch.arange(flat.numel(), device=layout.device, dtype=torch.int64)
+        c1 = (flat * (idx * -7046029254386353131 + 1442695040888963407)).sum()
+        c2 = (flat * ((idx ^ (idx >> 7)) * 6364136223846793005 + 1)).sum()
+        sums = torch.stack((c1, c2, flat.sum())).tolist()
+        return ('cuda', layout.device.index, tuple(layout.shape)) + tuple(sums)
+    return ('cpu', tuple(layout.shape), hashlib.sha1(present.contiguous().numpy().tobytes()).hexdigest())
+
+
+def _cached(kind, layout, extra, build):
+    key = (kind,) + layout_key(layout) + tuple(extra)
+    hit = _CACHE.get(key)
+    if hit is not None:
+        _CACHE.move_to_end(key)
+        CACHE_STATS['hits'] += 1
+        return hit
+    CACHE_STATS['misses'] += 1
+    obj = build()
+    _CACHE[key] = obj
+    while len(_CACHE) > _CACHE_ENTRIES:
+        _CACHE.popitem(last=False)
+    return obj
+
+
+def clear_cache():
+    _CACHE.clear()
+
+
+class Meta:
+    """Execution metadata of one layout: host header + device buffer(s).  Built on the host
+    (host layout) and uploaded once per device, or built on the device the layout lives on."""
+
+    def __init__(self, host=None, hdr=None, dev=None):
+        self._host = host                     # int32 CPU tensor (whole buffer), or None when built on a device
+        self.hdr = host[:_lib.META_HEADER].clone() if hdr is None else hdr
+        self.H, self.Mb, self.Nb, self.nnz = (int(v) for v in self.hdr[1:5])
+        self.max_row, self.max_col = int(self.hdr[5]), int(self.hdr[6])
         self._dev = {}
+        if dev is not None:
+            self._dev[str(dev.device)] = dev
+
+    @property
+    def host(self):
+        if self._host is None:
+            self._host = next(iter(self._dev.values())).cpu()
+        return self._host
 
     def on(self, device):
-        key = str(device)
+        key = str(torch.device(device)) if not isinstance(device, str) else device
         if key not in self._dev:
-            self._dev[key] = self.host.to(device)
+            if self._host is not None:
+                self._dev[key] = self._host.to(device)
+            else:
+                self._dev[key] = next(iter(self._dev.values())).to(device)
         return self._dev[key]
 
 
-def build_meta(layout):
-    lay, H, Mb, Nb = _layout_i64(layout)
+def _meta_total(H, Mb, Nb, nnz):
+    return _lib.META_HEADER + (H * Mb + 1) + 3 * nnz + (H * Nb + 1) + 2 * nnz + H * Mb + H * Nb
+
+
+def build_meta_device(layout):
+    """Builds the metadata on the device `layout` lives on (any integer / bool dtype of 1, 4 or 8
+    bytes): the layout never travels to the host, only the 8-int header comes back."""
+    if not layout.is_cuda or layout.dim() != 3:
+        raise ValueError('build_meta_device: a [H, Mb, Nb] CUDA tensor is required')
+    lay = layout
+    if lay.dtype == torch.bool:
+        lay = lay.view(torch.uint8)
+    if lay.element_size() not in (1, 4, 8) or lay.is_floating_point():
+        lay = (layout != 0).view(torch.uint8)
+    lay = lay.contiguous()
+    H, Mb, Nb = lay.shape
     L = _lib.lib()
+    cap = L.bsp_meta_device_capacity(H, Mb, Nb)
+    hdr = torch.zeros(_lib.META_HEADER, dtype=torch.int32)
+    with torch.cuda.device(lay.device):
+        out = torch.empty(cap, dtype=torch.int32, device=lay.device)
+        _lib.check(L.bsp_meta_build_device(lay.data_ptr(), lay.element_size(), H, Mb, Nb, out.data_ptr(), cap,
+                                           hdr.data_ptr(), torch.cuda.current_stream(lay.device).cuda_stream))
+    total = _meta_total(H, Mb, Nb, int(hdr[4]))
+    CACHE_STATS['device_builds'] += 1
+    return Meta(hdr=hdr, dev=out[:total])
 
-    def call(ptr, cap, total):
-        return L.bsp_meta_build(lay.data_ptr(), H, Mb, Nb, ptr, cap, total)
 
-    return Meta(_two_pass(call).clone())
+def build_meta(layout):
+    """Execution metadata of `layout`, from the process-wide cache when a layout with the same
+    content has been seen.  A layout in device memory is processed there."""
+    def build():
+        if layout.is_cuda:
+            return build_meta_device(layout)
+        lay, H, Mb, Nb = _layout_i64(layout)
+        L = _lib.lib()
+
+        def call(ptr, cap, total):
+            return L.bsp_meta_build(lay.data_ptr(), H, Mb, Nb, ptr, cap, total)
+
+        CACHE_STATS['host_builds'] += 1
+        return Meta(_two_pass(call).clone())
+    return _cached('meta', layout, (), build)
 
 
 class AttnTiles:
@@ -142,14 +235,21 @@ class AttnTiles:
 
 
 def build_attn_tiles(layout, block):
-    """Returns the AttnTiles of a square [H, nb, nb] layout, or None when the
-    tcgen05 kernels do not cover it (blocks 64 and 128, and blocks 16 / 32 whose count per side is a multiple of 4 / 2, are covered)."""
-    lay, H, Mb, Nb = _layout_i64(layout)
+    """Returns the AttnTiles of a square [H, nb, nb] layout (from the process-wide cache when the
+    same content has been seen), or None when the tcgen05 kernels do not cover it (blocks 64 and
+    128, and blocks 16 / 32 whose count per side is a multiple of 4 / 2, are covered)."""
+    if layout.dim() != 3:
+        raise ValueError('layout must be a [H, Mb, Nb] tensor')
+    H, Mb, Nb = layout.shape
     if Mb != Nb or block not in (16, 32, 64, 128) or (block < 64 and Mb % (64 // block)):
         return None
-    L = _lib.lib()
 
-    def call(ptr, cap, total):
-        return L.bsp_attn_tiles_build(lay.data_ptr(), H, Mb, block, ptr, cap, total)
+    def build():
+        lay, H, Mb, Nb = _layout_i64(layout)
+        L = _lib.lib()
 
-    return AttnTiles(_two_pass(call).clone())
+        def call(ptr, cap, total):
+            return L.bsp_attn_tiles_build(lay.data_ptr(), H, Mb, block, ptr, cap, total)
+
+        return AttnTiles(_two_pass(call).clone())
+    return _cached('tiles', layout, (block,), build)
