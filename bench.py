@@ -613,6 +613,7 @@ def run_ours(args):
     e1.record()
     T.barrier()
     e2e_t = T.max_over_ranks(e0.elapsed_time(e1) * 1e-3)
+    pipe.check()                                     # (off the clock) no bounded device-side wait expired
     tensor_bytes = host['q'].numel() * host['q'].element_size()
     e2e = {'value': main['flops_total'] * e2e_steps / e2e_t / 1e12, 'unit': UNIT,
            'h2d_bytes_per_step': 4 * tensor_bytes * world, 'd2h_bytes_per_step': 4 * tensor_bytes * world,

@@ -395,11 +395,25 @@ int bsp_attn_bwd_static(const void* q, const void* k, const void* v, const void*
                         void* stream);
 
 /*
- * Reads the device-side status word (synchronises the device): 0, or non-zero
- * when a bounded wait inside a tcgen05 kernel expired, in which case that
- * launch's outputs are not valid.  No counterpart in the reference.
+ * Reads and clears the device-side status words (synchronises the device).
+ * *status = 0 and BSP_OK when no bounded wait inside a tcgen05 kernel has expired
+ * since the last read; otherwise *status = 1 (attention forward), 2 (attention
+ * dQ), 3 (attention dK/dV), 4 (dsd / dds) or 5 (sdd), the return value is
+ * BSP_ERR_TIMEOUT and the outputs of the launch that set it are not valid.  A
+ * caller checks it where it synchronises anyway.  No counterpart in the
+ * reference.
  */
 int bsp_device_status(int* status);
+
+/*
+ * Test hook of the bounded waits (no counterpart in the reference): the number
+ * of attempts a wait inside the tcgen05 attention kernels may make
+ * (wait_budget <= 0: the default, 2^21) and, with skip_chunk >= 0, the loads of
+ * that chunk of every tile are withheld, so that the waits for it run out and
+ * the kernels return with the status word set instead of waiting for ever.
+ * Process-wide; applies to launches made afterwards.
+ */
+int bsp_debug_attn_wait(int wait_budget, int skip_chunk);
 
 /*
  * Kernel family of bsp_sdd / bsp_dsd / bsp_dds for block 64 / 128 with FP16 /

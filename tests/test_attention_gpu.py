@@ -241,6 +241,38 @@ def test_operands_expanded_over_the_batch_fall_back_to_mma_sync():
         assert_close(o[z:z + 1], want, 'expanded batch entry %d' % z)
 
 
+def test_bounded_wait_expires_into_a_status_code_and_the_context_stays_usable():
+    """A wait inside a tcgen05 kernel that can never complete (the loads of one chunk of every
+    tile are withheld through the test hook, and the waits get a short limit) ends the kernel
+    with the status word set: no hang, no trap.  Reading the status reports BSP_ERR_TIMEOUT once
+    and clears it; the next launch on the same context is correct."""
+    from torch_blocksparse_b200 import _lib
+    c = workloads.config4('unidirectional', small=True)
+    mod = SparseSelfAttention(layout=c['layout'], block=c['block'], fused=True)
+    q, k, v = (c[n].to(DEV) for n in ('q', 'k', 'v'))
+    L = _lib.lib()
+    try:
+        _lib.check(L.bsp_debug_attn_wait(4000, 1))
+        with torch.no_grad():
+            mod(q, k, v)
+        torch.cuda.synchronize()                       # the launch returns by itself
+        import ctypes
+        st = ctypes.c_int(0)
+        assert L.bsp_device_status(ctypes.byref(st)) == _lib.ERR_TIMEOUT and st.value == 1
+        assert b'bounded wait expired' in L.bsp_last_error()
+        with pytest.raises(RuntimeError):              # what the Python layer raises where it synchronises
+            with torch.no_grad():
+                mod(q, k, v)
+            _lib.check_device()
+    finally:
+        _lib.check(L.bsp_debug_attn_wait(0, -1))
+    assert _lib.device_status() == 0                   # reading cleared it
+    with torch.no_grad():
+        o = mod(q, k, v)
+    want = dm.attention_reference(c['q'], c['k'], c['v'], c['layout'], c['block'], c['scale'])[0]
+    assert_close(o, want, 'forward after a timed-out launch')
+
+
 def test_sparsity_config_path_and_key_transposed():
     """The reference's constructor path: SparsityConfig 'fixed', key handed over
     pre-transposed as [.., head_dim, L] (deepspeedsparseselfattention.py:119-123)."""

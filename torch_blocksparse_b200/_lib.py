@@ -35,6 +35,7 @@ _SIGNATURES = {
     'bsp_fixed_layout_build': (c_int, [c_int] * 7 + [c_void_p]),
     'bsp_window_layout_build': (c_int, [c_int] * 6 + [c_void_p, c_int, c_void_p]),
     'bsp_device_status': (c_int, [_IP]),
+    'bsp_debug_attn_wait': (c_int, [c_int, c_int]),
     'bsp_matmul_use_tcgen05': (c_int, [c_int]),
     'bsp_attn_tiles_build': (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, c_int64, _I64P]),
     'bsp_meta_build': (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, c_int64, _I64P]),
@@ -86,6 +87,22 @@ def lib():
 
 _EXC = {ERR_INVALID: ValueError, ERR_UNSUPPORTED: NotImplementedError, ERR_CAPACITY: RuntimeError,
         ERR_CUDA: RuntimeError, ERR_EMPTY_HEAD: RuntimeError, ERR_TIMEOUT: RuntimeError}
+
+
+def device_status():
+    """Reads and clears the device status words (synchronises): 0, or the code of the tcgen05
+    kernel family in which a bounded wait expired."""
+    out = c_int(0)
+    rc = lib().bsp_device_status(ctypes.byref(out))
+    if rc not in (OK, ERR_TIMEOUT):
+        check(rc)
+    return out.value
+
+
+def check_device():
+    """Raises RuntimeError when a bounded device-side wait has expired since the last check."""
+    out = c_int(0)
+    check(lib().bsp_device_status(ctypes.byref(out)))
 
 
 def check(status):

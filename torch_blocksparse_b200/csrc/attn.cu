@@ -25,6 +25,7 @@ int attn_bwd_tc(const void* q, const void* k, const void* v, const void* dout, c
                 const int32_t* tiles_hdr, const int32_t* tiles, float scale,
                 const void* kpm, int64_t kpm_sz, int kpm_mul, int causal, int parts, cudaStream_t st);
 int tc_device_status(int* out);
+int tc_debug_wait(int wait_budget, int skip_chunk);
 int dsd_tc_device_status(int* out);
 int sdd_tc_device_status(int* out);
 
@@ -246,5 +247,10 @@ extern "C" int bsp_device_status(int* status) {
   if (int rc = dsd_tc_device_status(&dsd)) return rc;
   if (int rc = sdd_tc_device_status(&sdd)) return rc;
   *status = attn ? attn : (dsd ? dsd : sdd);
+  if (*status)
+    return fail(BSP_ERR_TIMEOUT, "a bounded wait expired inside a tcgen05 kernel (%s): the outputs of that launch are not valid",
+                attn == 1 ? "attention forward" : attn == 2 ? "attention dQ" : attn == 3 ? "attention dK/dV" : dsd ? "dsd / dds" : "sdd");
   return BSP_OK;
 }
+
+extern "C" int bsp_debug_attn_wait(int wait_budget, int skip_chunk) { return tc_debug_wait(wait_budget, skip_chunk); }

@@ -37,6 +37,7 @@
 // loads of the ring of inner chunks.  They talk through mbarriers only (one
 // arrival per warp); every wait is bounded (tc.cuh) and a wait that expires
 // sets the device status word.
+#include <atomic>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include "common.h"
@@ -68,6 +69,8 @@ struct TcArgs {
   int fine;                            // the layout's blocks are smaller than 64: pieces of a position may be absent
   int causal;                          // key j is visible to query i only for j <= i (handled by the FINE instantiation)
   const void* kpm; int64_t kpm_sz; int kpm_mul;   // key-padding mask [Z, L] (KPM variants), 'mul' mode flag
+  int wait_budget;                     // attempts a bounded wait may make
+  int skip_chunk;                      // test hook: the loads of this chunk of every tile are not issued (-1: none)
 };
 
 template <typename T> BSP_DEVI uint32_t pack16(float a, float b);
@@ -242,7 +245,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
   __shared__ uint64_t bar_res, bar_rt, bar_rd, bar_full[ST], bar_s[4], bar_p[4], bar_acc[4], bar_done;
   __shared__ float xch[2][2][128];                           // forward: (max, sum) of the two halves of every row
   __shared__ uint32_t tmem_slot;
-  __shared__ int failed;
+  __shared__ int failed[2];
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   // One-dimensional grid, batch entries of a tile adjacent: CTAs start in the order of the
@@ -278,6 +281,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
     const int stage = t % ST;
     unsigned char* sp = stg + stage * C::STAGE;
     mbar_expect_tx(&bar_full[stage], 2 * C::CH_BYTES + C::TAIL_BYTES);
+    if (t == a.skip_chunk) return;                             // (test hook: this stage never fills, its consumers' waits run out)
     for (int at = 0; at < ATOMS; ++at) {
       tma_load_4d(sp + at * 8192, &m_ch0, &bar_full[stage], at * 64, crow, h, z);
       tma_load_4d(sp + C::CH_BYTES + at * 8192, &m_ch1, &bar_full[stage], at * 64, crow, h, z);
@@ -307,7 +311,8 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
     for (int t = 0; t < ST && t < ntiles; ++t) load_chunk(t, a.chunk[first + t] * 64);
   }
   if (tid == 0) {
-    failed = 0;
+    failed[0] = 0;
+    failed[1] = a.wait_budget;
     mbar_init(&bar_rt, NC);
     mbar_init(&bar_rd, NC);
     if (C::ER) mbar_init(&bar_p[1], NC);
@@ -322,7 +327,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
   __syncthreads();
   fence_after();
   const uint32_t tmem = tmem_slot;
-  volatile int* fl = &failed;
+  volatile int* fl = failed;
 
   if (warp >= NC) {
     // ------------------------------------------------------------------ loader and MMA issuers
@@ -858,7 +863,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
   fence_before();
   __syncthreads();
   if (warp == 1) tmem_dealloc(tmem, C::TMEM);
-  if (tid == 0 && failed) atomicExch(&g_tc_status, 1 + MODE);
+  if (tid == 0 && failed[0]) atomicExch(&g_tc_status, 1 + MODE);
 }
 
 // ---------------------------------------------------------------------------
@@ -924,6 +929,9 @@ int make_map(CUtensorMap* m, const void* ptr, int dtype, int Z, int H, int L, in
   return BSP_OK;
 }
 
+// Test hooks (bsp_debug_attn_wait): the budget of the bounded waits and a chunk whose loads are withheld.
+std::atomic<int> g_wait_budget{kWaitBudget}, g_skip_chunk{-1};
+
 struct TileSet { const int32_t *c01, *ptr, *chunk, *mask, *sub, *order; };
 struct TilesView { int H, nb, block, tiles_per_head, fine; TileSet rt, ct; };
 
@@ -949,6 +957,8 @@ int launch(const CUtensorMap& r0, const CUtensorMap& r1, const CUtensorMap& c0, 
   if (e != cudaSuccess) return fail(BSP_ERR_CUDA, "attention (tcgen05 %s): cannot reserve shared memory: %s", what, cudaGetErrorString(e));
   TcArgs b = a;
   b.Z = Z;
+  b.wait_budget = g_wait_budget.load();
+  b.skip_chunk = g_skip_chunk.load();
   kern<<<(unsigned)((int64_t)n_tiles * Z), C::NT, C::SMEM, st>>>(r0, r1, c0, c1, b);
   e = cudaGetLastError();
   if (e != cudaSuccess) return fail(BSP_ERR_CUDA, "attention (tcgen05 %s) launch failed: %s", what, cudaGetErrorString(e));
@@ -1041,9 +1051,17 @@ int attn_bwd_tc(const void* q, const void* k, const void* v, const void* dout, c
 }
 
 
+// Test hook: wait_budget <= 0 restores the default; skip_chunk < 0 withholds nothing.
+int tc_debug_wait(int wait_budget, int skip_chunk) {
+  g_wait_budget.store(wait_budget > 0 ? wait_budget : kWaitBudget);
+  g_skip_chunk.store(skip_chunk < 0 ? -1 : skip_chunk);
+  return BSP_OK;
+}
+
 int tc_device_status(int* out) {
   int v = 0;
   cudaError_t e = cudaMemcpyFromSymbol(&v, g_tc_status, sizeof(int));
+  if (e == cudaSuccess && v != 0) { const int zero = 0; e = cudaMemcpyToSymbol(g_tc_status, &zero, sizeof(int)); }   // reading clears
   if (e != cudaSuccess) return fail(BSP_ERR_CUDA, "reading the device status failed: %s", cudaGetErrorString(e));
   *out = v;
   return BSP_OK;

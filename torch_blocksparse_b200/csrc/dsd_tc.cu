@@ -64,7 +64,7 @@ dsd_tc_kernel(const __grid_constant__ CUtensorMap m_s, const __grid_constant__ C
   unsigned char* smem = smem_raw + ((1024 - (saddr(smem_raw) & 1023)) & 1023);
   __shared__ uint64_t bar_full[kStages], bar_empty[kStages], bar_done;
   __shared__ uint32_t tmem_slot;
-  __shared__ int n_stages, failed;
+  __shared__ int n_stages, failed[2];
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int tile = blockIdx.x, n0 = blockIdx.y * kTN, z = blockIdx.z;
@@ -77,7 +77,8 @@ dsd_tc_kernel(const __grid_constant__ CUtensorMap m_s, const __grid_constant__ C
   const int p1 = r1 >= 0 ? a.row_ptr[h * a.Mb + r1] : 0, e1 = r1 >= 0 ? a.row_ptr[h * a.Mb + r1 + 1] : 0;
 
   if (tid == 0) {
-    failed = 0;
+    failed[0] = 0;
+    failed[1] = kWaitBudget;
     for (int s = 0; s < kStages; ++s) { mbar_init(&bar_full[s], 1); mbar_init(&bar_empty[s], 1); }
     mbar_init(&bar_done, 1);
     mbar_init_fence();
@@ -101,7 +102,7 @@ dsd_tc_kernel(const __grid_constant__ CUtensorMap m_s, const __grid_constant__ C
   fence_after();
   const uint32_t tmem = tmem_slot;
   const int ns = n_stages;
-  volatile int* fl = &failed;
+  volatile int* fl = failed;
 
   if (warp == 4) {
     // ------------------------------------------------------------------ TMA producer
@@ -212,7 +213,7 @@ dsd_tc_kernel(const __grid_constant__ CUtensorMap m_s, const __grid_constant__ C
   fence_before();
   __syncthreads();
   if (warp == 1) tmem_dealloc(tmem, kTN);
-  if (tid == 0 && failed) atomicExch(&g_dsd_status, 4);
+  if (tid == 0 && failed[0]) atomicExch(&g_dsd_status, 4);
 }
 
 template <typename T, bool AM, bool BK, bool CR>
@@ -292,6 +293,7 @@ int dsd_tc(const void* s, const void* b, void* c, int dtype, int block, int Z, i
 int dsd_tc_device_status(int* out) {
   int v = 0;
   cudaError_t e = cudaMemcpyFromSymbol(&v, g_dsd_status, sizeof(int));
+  if (e == cudaSuccess && v != 0) { const int zero = 0; e = cudaMemcpyToSymbol(g_dsd_status, &zero, sizeof(int)); }   // reading clears
   if (e != cudaSuccess) return fail(BSP_ERR_CUDA, "device status: %s", cudaGetErrorString(e));
   *out = v;
   return BSP_OK;

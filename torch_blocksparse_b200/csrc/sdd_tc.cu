@@ -50,7 +50,7 @@ sdd_tc_kernel(const __grid_constant__ CUtensorMap m_a, const __grid_constant__ C
   unsigned char* smem = smem_raw + ((1024 - (saddr(smem_raw) & 1023)) & 1023);
   __shared__ uint64_t bar_full[kStages], bar_empty[kStages], bar_done;
   __shared__ uint32_t tmem_slot;
-  __shared__ int failed;
+  __shared__ int failed[2];
   // work of this CTA: head, first row of A, the two 64-wide column blocks (first column of B,
   // or -1) and the ids of the up to four blocks to store ([row half][column half], -1: none)
   __shared__ int w_h, w_m0, w_n[2], w_id[2][2];
@@ -59,7 +59,8 @@ sdd_tc_kernel(const __grid_constant__ CUtensorMap m_a, const __grid_constant__ C
   const int z = blockIdx.z, block = a.block;
 
   if (tid == 0) {
-    failed = 0;
+    failed[0] = 0;
+    failed[1] = kWaitBudget;
     w_n[0] = w_n[1] = -1;
     w_id[0][0] = w_id[0][1] = w_id[1][0] = w_id[1][1] = -1;
     if (block == 128) {
@@ -104,7 +105,7 @@ sdd_tc_kernel(const __grid_constant__ CUtensorMap m_a, const __grid_constant__ C
   const uint32_t tmem = tmem_slot;
   const int ns = a.K / 64;
   const int h = w_h, m0 = w_m0;
-  volatile int* fl = &failed;
+  volatile int* fl = failed;
 
   if (warp == 4) {
     // ------------------------------------------------------------------ TMA producer
@@ -190,7 +191,7 @@ sdd_tc_kernel(const __grid_constant__ CUtensorMap m_a, const __grid_constant__ C
   fence_before();
   __syncthreads();
   if (warp == 1) tmem_dealloc(tmem, 128);
-  if (tid == 0 && failed) atomicExch(&g_sdd_status, 5);
+  if (tid == 0 && failed[0]) atomicExch(&g_sdd_status, 5);
 }
 
 template <typename T, bool AM, bool BM>
@@ -265,6 +266,7 @@ int sdd_tc(const void* a, const void* b, void* c, int dtype, int block, int Z, i
 int sdd_tc_device_status(int* out) {
   int v = 0;
   cudaError_t e = cudaMemcpyFromSymbol(&v, g_sdd_status, sizeof(int));
+  if (e == cudaSuccess && v != 0) { const int zero = 0; e = cudaMemcpyToSymbol(g_sdd_status, &zero, sizeof(int)); }   // reading clears
   if (e != cudaSuccess) return fail(BSP_ERR_CUDA, "device status: %s", cudaGetErrorString(e));
   *out = v;
   return BSP_OK;

@@ -41,15 +41,18 @@ BSP_DEVI void warp_arrive(uint64_t* bar, int lane) {
   __syncwarp();
   if (lane == 0) mbar_arrive(bar);
 }
-constexpr int kWaitBudget = 1 << 21;   // try_wait attempts before a wait is declared failed
-// Returns false when the phase did not complete in time, or at once when the
-// CTA has already failed (*failed != 0), so that a failed CTA drains quickly.
+constexpr int kWaitBudget = 1 << 21;   // default number of try_wait attempts before a wait is declared failed
+// `failed` points at two ints of the CTA's shared memory: [0] is set once a wait of the CTA has
+// expired, [1] holds the number of attempts a wait may make (kWaitBudget unless the launch says
+// otherwise).  Returns false when the phase did not complete in time, or soon after the CTA
+// has failed (failed[0] != 0), so that a failed CTA drains quickly.
 BSP_DEVI bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* failed) {
-  for (int i = 0; i < kWaitBudget; ++i) {
+  const int budget = failed[1];
+  for (int i = 0; i < budget; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
-    if ((i & 1023) == 1023 && *failed) return false;
+    if ((i & 255) == 255 && failed[0]) return false;
   }
-  *failed = 1;
+  failed[0] = 1;
   return false;
 }
 

@@ -153,11 +153,9 @@ def _tile_args(tiles, device):
 
 
 def device_status():
-    """0, or non-zero when a bounded wait inside a tcgen05 kernel expired (synchronises)."""
-    import ctypes
-    out = ctypes.c_int(0)
-    _lib.check(_lib.lib().bsp_device_status(ctypes.byref(out)))
-    return out.value
+    """0, or non-zero when a bounded wait inside a tcgen05 kernel expired since the last read
+    (synchronises; reading clears the status)."""
+    return _lib.device_status()
 
 
 def fused_attention(q, k, v, meta, block, scale, rpe=None, key_padding_mask=None, attn_mask=None,

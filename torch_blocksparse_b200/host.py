@@ -108,6 +108,13 @@ class HostAttention:
             code, self.block, z, self.H, self.L, self.D, *strides, *strides, *strides, *strides, *strides,
             *meta, *tiles, scale, *none_masks, stream))
 
+    def check(self):
+        """Waits for everything queued so far and raises RuntimeError if a bounded wait inside one of
+        the kernels expired (the results of that run are then not valid)."""
+        for s in self.streams:
+            s.synchronize()
+        _lib.check_device()
+
     def run(self, q, k, v, do, o, dq, dk, dv, scale=None):
         """Queues forward + backward for host operands q, k, v, do and host results o, dq, dk,
         dv.  Returns a CUDA event that completes when every result is in host memory."""

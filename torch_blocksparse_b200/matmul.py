@@ -80,6 +80,7 @@ class _Timer:
             self.t1.record()
             self.t1.synchronize()
             self.slot[0] = self.t0.elapsed_time(self.t1) * 1e-3
+            _lib.check_device()              # this path synchronises anyway: a bounded wait that expired raises here
         return False
 
 
