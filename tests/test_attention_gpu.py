@@ -77,6 +77,58 @@ def test_masks_and_rpe(kp_mode, am_mode, fused):
     check(layout, block, q, k, v, do, fused, kp_mode, am_mode, rpe=rpe, key_padding_mask=kp, attn_mask=am)
 
 
+@pytest.mark.parametrize('what', ['rpe', 'rpe3d+am_mul', 'am_add', 'rpe+am_add+kpm', 'am_mul+kpm_mul'])
+@pytest.mark.parametrize('block,D,dtype', [(64, 64, torch.float16), (128, 128, torch.bfloat16), (32, 64, torch.float16),
+                                            (64, 128, torch.float16), (16, 64, torch.bfloat16)])
+def test_rpe_and_attention_masks_on_tcgen05_path(block, D, dtype, what):
+    """A relative position bias and an arbitrary attention mask (added or 'mul') travel with
+    the chunks of the tcgen05 kernels (softmax.py:48-56, 63-70, 114-128 of the reference fuse them
+    into its softmax).  Against the dense-masked definition and against the mma.sync kernels; an
+    odd number of block-rows leaves a tile with a single half."""
+    from torch_blocksparse_b200 import fused as F
+    Z, H = 2, 2
+    nb = {16: 12, 32: 6, 64: 5, 128: 3}[block]
+    L = nb * block
+    g = torch.Generator().manual_seed(block + D + len(what))
+    layout = (torch.rand((H, nb, nb), generator=g) > 0.45).long()
+    layout[:, :, 0] = 1
+    layout[1, nb - 1, 1:] = 0
+    q, k, v, do = rand_qkv(Z, H, L, D, dtype, seed=block + 11)
+    kw, kp_mode, am_mode = {}, 'add', 'mul'
+    if 'rpe3d' in what:
+        kw['rpe'] = (0.5 * torch.randn((H, L, L), generator=g)).to(dtype)          # broadcast over the batch
+    elif 'rpe' in what:
+        kw['rpe'] = (0.5 * torch.randn((Z, H, L, L), generator=g)).to(dtype)
+    if 'am_mul' in what:
+        keep = torch.rand((L, L), generator=g) > 0.3
+        keep[:, 0] = True
+        kw['attn_mask'] = keep.to(dtype)
+    if 'am_add' in what:
+        am_mode = 'add'
+        keep = torch.rand((L, L), generator=g) > 0.2
+        keep[:, 0] = True
+        kw['attn_mask'] = torch.where(keep, 0.3 * torch.randn((L, L), generator=g), torch.tensor(float('-inf'))).to(dtype)
+    if 'kpm_mul' in what:
+        kp_mode = 'mul'
+        keepk = torch.rand((Z, L), generator=g) > 0.3
+        keepk[:, 0] = True
+        kw['key_padding_mask'] = keepk.to(dtype)
+    elif 'kpm' in what:
+        keepk = torch.rand((Z, L), generator=g) > 0.3
+        keepk[:, 0] = True
+        kw['key_padding_mask'] = torch.where(keepk, 0.0, float('-inf')).to(dtype)
+    check(layout, block, q, k, v, do, True, kp_mode, am_mode, **kw)
+    mod = SparseSelfAttention(layout=layout, block=block, fused=True, key_padding_mask_mode=kp_mode, attn_mask_mode=am_mode)
+    try:
+        tc = run_module(mod, q, k, v, do, **kw)
+        F.PATH = 'mma'
+        mma = run_module(mod, q, k, v, do, **kw)
+    finally:
+        F.PATH = 'tc'
+    for name, a, b in zip(('o', 'dq', 'dk', 'dv'), tc, mma):
+        assert_close(a.cpu(), b.cpu(), name + ' tcgen05 vs mma.sync')
+
+
 @pytest.mark.parametrize('kp_mode', ['add', 'mul'])
 @pytest.mark.parametrize('block,D', [(16, 64), (32, 64), (64, 64), (128, 64), (16, 128), (32, 128), (64, 128), (128, 128)])
 @pytest.mark.parametrize('dtype', [torch.float16, torch.bfloat16])

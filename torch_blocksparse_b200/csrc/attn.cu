@@ -12,18 +12,19 @@ static __device__ __align__(256) float g_static_delta[BSP_ATTN_STATIC_ROWS];
 
 namespace bsp {
 
+struct XtHost { const void* rpe; int64_t rpe_sz, rpe_sh, rpe_sr; const void* am; int64_t am_sr; int am_mode; };
 int attn_fwd_tc(const void* q, const void* k, const void* v, void* o, float* lse,
                 int dtype, int Z, int H, int L, int D,
                 int64_t q_sz, int64_t q_sh, int64_t q_sr, int64_t k_sz, int64_t k_sh, int64_t k_sr,
                 int64_t v_sz, int64_t v_sh, int64_t v_sr, int64_t o_sz, int64_t o_sh, int64_t o_sr,
                 const int32_t* tiles_hdr, const int32_t* tiles, float scale,
-                const void* kpm, int64_t kpm_sz, int kpm_mul, int causal, cudaStream_t st);
+                const void* kpm, int64_t kpm_sz, int kpm_mul, int causal, const XtHost* xt, cudaStream_t st);
 int attn_bwd_tc(const void* q, const void* k, const void* v, const void* dout, const float* lse, const float* delta,
                 void* dq, void* dk, void* dv, int dtype, int Z, int H, int L, int D,
                 int64_t q_sz, int64_t q_sh, int64_t q_sr, int64_t k_sz, int64_t k_sh, int64_t k_sr,
                 int64_t v_sz, int64_t v_sh, int64_t v_sr, int64_t do_sz, int64_t do_sh, int64_t do_sr,
                 const int32_t* tiles_hdr, const int32_t* tiles, float scale,
-                const void* kpm, int64_t kpm_sz, int kpm_mul, int causal, int parts, cudaStream_t st);
+                const void* kpm, int64_t kpm_sz, int kpm_mul, int causal, int parts, const XtHost* xt, cudaStream_t st);
 int tc_device_status(int* out);
 int tc_debug_wait(int wait_budget, int skip_chunk);
 int dsd_tc_device_status(int* out);
@@ -31,22 +32,34 @@ int sdd_tc_device_status(int* out);
 
 namespace {
 
-// The tcgen05 kernels cover FP16 / BF16 on 128-row tiles, without rpe; a key-padding mask is
-// taken when its rows can be fetched in 16-byte pieces, an attention mask when it is the causal one.
+// The tcgen05 kernels cover FP16 / BF16 on 128-row tiles.  A key-padding mask, a relative
+// position bias and an attention mask are taken when they can be fetched in 16-byte pieces
+// (aligned base, strides that are multiples of 8 elements); an attention mask the caller vouches
+// to be the causal one (flag 2) is derived from the indices instead of being read.
+bool tc_eligible(const int32_t* tiles_hdr, const int32_t* tiles, int block, int L, int D,
+                 const void* rpe, int64_t rpe_sz, int64_t rpe_sh, int64_t rpe_sr,
+                 const void* kpm, int64_t kpm_sz, const void* am, int64_t am_sr) {
+  if (!(tiles_hdr && tiles && (D == 64 || D == 128))) return false;
+  // the lists were built for this block size (blocks 16 and 32 run on 64-wide lists with masks of 16 x 16 pieces)
+  if (!((block == 16 || block == 32 || block == 64 || block == 128) && tiles_hdr[7] == block)) return false;
+  if (kpm && ((reinterpret_cast<uintptr_t>(kpm) & 15) || (kpm_sz & 7))) return false;
+  if (rpe && ((reinterpret_cast<uintptr_t>(rpe) & 15) || (rpe_sz & 7) || (rpe_sh & 7) || (rpe_sr & 7) ||
+              rpe_sz < 0 || rpe_sh <= 0 || rpe_sr <= 0)) return false;
+  if (am && ((reinterpret_cast<uintptr_t>(am) & 15) || (am_sr & 7) || am_sr <= 0)) return false;
+  return true;
+}
+
+// rpe / attention mask of a call in the form the tcgen05 launchers take (a causal-flagged mask is not read).
+XtHost xt_of(const void* rpe, int64_t rpe_sz, int64_t rpe_sh, int64_t rpe_sr, const void* am, int64_t am_sr, int am_mul) {
+  XtHost x = {rpe, rpe_sz, rpe_sh, rpe_sr, nullptr, 0, 0};
+  if (am && am_mul != 2) { x.am = am; x.am_sr = am_sr; x.am_mode = am_mul ? 2 : 1; }
+  return x;
+}
+
 // Strides the tensor-map encoder takes: positive (an operand expanded over the batch or the heads
 // has stride 0 and stays on the mma.sync kernels).
 bool tma_strides(int Z, int H, int64_t sz, int64_t sh, int64_t sr) {
   return sr > 0 && (H == 1 || sh > 0) && (Z == 1 || sz > 0);
-}
-
-bool tc_eligible(const int32_t* tiles_hdr, const int32_t* tiles, int block, int L, int D,
-                 const void* rpe, const void* kpm, int64_t kpm_sz, const void* am, int am_mul) {
-  // an attention mask is only taken when the caller vouches that it is the causal one (flag 2)
-  if (!(tiles_hdr && tiles && (D == 64 || D == 128)) || rpe || (am && am_mul != 2)) return false;
-  // the lists were built for this block size (blocks 16 and 32 run on 64-wide lists with masks of 16 x 16 pieces)
-  if (!((block == 16 || block == 32 || block == 64 || block == 128) && tiles_hdr[7] == block)) return false;
-  if (kpm && ((reinterpret_cast<uintptr_t>(kpm) & 15) || (kpm_sz & 7))) return false;
-  return true;
 }
 
 constexpr int kMaxDevices = 64;
@@ -135,10 +148,12 @@ extern "C" int bsp_attn_fwd(const void* q, const void* k, const void* v, void* o
   p.q_sz = q_sz; p.q_sh = q_sh; p.q_sr = q_sr; p.k_sz = k_sz; p.k_sh = k_sh; p.k_sr = k_sr;
   p.v_sz = v_sz; p.v_sh = v_sh; p.v_sr = v_sr; p.o_sz = o_sz; p.o_sh = o_sh; p.o_sr = o_sr;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  if (tc_eligible(tiles_hdr, tiles, block, L, D, rpe, kpm, kpm_sz, am, am_mul) &&
-      tma_strides(Z, H, q_sz, q_sh, q_sr) && tma_strides(Z, H, k_sz, k_sh, k_sr) && tma_strides(Z, H, v_sz, v_sh, v_sr))
+  if (tc_eligible(tiles_hdr, tiles, block, L, D, rpe, rpe_sz, rpe_sh, rpe_sr, kpm, kpm_sz, am, am_sr) &&
+      tma_strides(Z, H, q_sz, q_sh, q_sr) && tma_strides(Z, H, k_sz, k_sh, k_sr) && tma_strides(Z, H, v_sz, v_sh, v_sr)) {
+    const XtHost xt = xt_of(rpe, rpe_sz, rpe_sh, rpe_sr, am, am_sr, am_mul);
     return attn_fwd_tc(q, k, v, o, lse, dtype, Z, H, L, D, q_sz, q_sh, q_sr, k_sz, k_sh, k_sr, v_sz, v_sh, v_sr,
-                       o_sz, o_sh, o_sr, tiles_hdr, tiles, scale, kpm, kpm_sz, kpm_mul, am != nullptr, st);
+                       o_sz, o_sh, o_sr, tiles_hdr, tiles, scale, kpm, kpm_sz, kpm_mul, am != nullptr && am_mul == 2, &xt, st);
+  }
   if (dtype == BSP_F16) return attn_fwd_t<__half>(p, block, D, Z, st);
   return attn_fwd_t<__nv_bfloat16>(p, block, D, Z, st);
 }
@@ -176,7 +191,7 @@ extern "C" int bsp_attn_bwd_parts(const void* q, const void* k, const void* v, c
   p.v_sz = v_sz; p.v_sh = v_sh; p.v_sr = v_sr; p.o_sz = o_sz; p.o_sh = o_sh; p.o_sr = o_sr;
   p.do_sz = do_sz; p.do_sh = do_sh; p.do_sr = do_sr;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  if (tc_eligible(tiles_hdr, tiles, block, L, D, rpe, kpm, kpm_sz, am, am_mul) &&
+  if (tc_eligible(tiles_hdr, tiles, block, L, D, rpe, rpe_sz, rpe_sh, rpe_sr, kpm, kpm_sz, am, am_sr) &&
       tma_strides(Z, H, q_sz, q_sh, q_sr) && tma_strides(Z, H, k_sz, k_sh, k_sr) && tma_strides(Z, H, v_sz, v_sh, v_sr) &&
       tma_strides(Z, H, do_sz, do_sh, do_sr)) {
     // delta = rowsum(o * do) by the streaming kernel, the two matrix kernels on tcgen05
@@ -185,8 +200,10 @@ extern "C" int bsp_attn_bwd_parts(const void* q, const void* k, const void* v, c
       if (rc) return rc;
     }
     if (!(parts & 6)) return BSP_OK;
+    const XtHost xt = xt_of(rpe, rpe_sz, rpe_sh, rpe_sr, am, am_sr, am_mul);
     return attn_bwd_tc(q, k, v, dout, lse, delta, dq, dk, dv, dtype, Z, H, L, D, q_sz, q_sh, q_sr, k_sz, k_sh, k_sr,
-                       v_sz, v_sh, v_sr, do_sz, do_sh, do_sr, tiles_hdr, tiles, scale, kpm, kpm_sz, kpm_mul, am != nullptr, parts & 6, st);
+                       v_sz, v_sh, v_sr, do_sz, do_sh, do_sr, tiles_hdr, tiles, scale, kpm, kpm_sz, kpm_mul,
+                       am != nullptr && am_mul == 2, parts & 6, &xt, st);
   }
   if (dtype == BSP_F16) return attn_bwd_t<__half>(p, block, D, Z, parts, st);
   return attn_bwd_t<__nv_bfloat16>(p, block, D, Z, parts, st);

@@ -46,6 +46,10 @@
 
 namespace bsp {
 
+// Relative position bias [Z or 1, H, L, L] (rpe_sz == 0: no batch dimension) and attention mask
+// [L, L] of a call, as the tcgen05 kernels take them: am_mode 1 = added, 2 = 'mul'.
+struct XtHost { const void* rpe; int64_t rpe_sz, rpe_sh, rpe_sr; const void* am; int64_t am_sr; int am_mode; };
+
 // Set by a kernel whose bounded wait expired; read by bsp_device_status().
 static __device__ int g_tc_status;
 
@@ -69,6 +73,7 @@ struct TcArgs {
   int fine;                            // the layout's blocks are smaller than 64: pieces of a position may be absent
   int causal;                          // key j is visible to query i only for j <= i (handled by the FINE instantiation)
   const void* kpm; int64_t kpm_sz; int kpm_mul;   // key-padding mask [Z, L] (KPM variants), 'mul' mode flag
+  int has_rpe, rpe_z, am_mode;         // XT variants: rpe present, rpe has a batch dimension, attention mask absent (0) / added (1) / 'mul' (2)
   int wait_budget;                     // attempts a bounded wait may make
   int skip_chunk;                      // test hook: the loads of this chunk of every tile are not issued (-1: none)
 };
@@ -100,6 +105,56 @@ BSP_DEVI void kpm_terms8(const unsigned char* p, int mul, float (&b)[8]) {
     b[2 * i] = kpm_term(f.x, mul);
     b[2 * i + 1] = kpm_term(f.y, mul);
   }
+}
+// Relative position bias and attention mask (XT variants).  Their 64 x 64 pieces for a chunk
+// travel with it: per half of the tile one box of rpe at `xt` and one of the mask 16 KB further,
+// rows of 128 bytes, 16-byte units swizzled by the row as TMA writes them.  Rows of a box are
+// query rows, columns key columns.  The terms are added in the base-2 domain; a 'mul' mask
+// turns a zero into -inf and anything else into 0 (softmax.py:104-110 of the reference).
+BSP_DEVI uint32_t xt_off(int half, int row, int col) {
+  return (uint32_t)(half * 8192 + row * 128 + ((((col >> 3) ^ (row & 7)) << 4) | ((col & 7) << 1)));
+}
+// Eight consecutive columns (one 16-byte unit `unit`) of query row `row`: b[i] += terms.
+template <typename T>
+BSP_DEVI void xt_add8(const unsigned char* xt, const int has_rpe, const int am_mode, int half, int row, int unit, float (&b)[8]) {
+  const uint32_t off = (uint32_t)(half * 8192 + row * 128 + ((unit ^ (row & 7)) << 4));
+  if (has_rpe) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(xt + off);
+    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 f = unpack16<T>(w[i]);
+      b[2 * i] = fmaf(f.x, kLog2eT, b[2 * i]);
+      b[2 * i + 1] = fmaf(f.y, kLog2eT, b[2 * i + 1]);
+    }
+  }
+  if (am_mode) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(xt + 16384 + off);
+    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 f = unpack16<T>(w[i]);
+      if (am_mode == 2) {
+        if (f.x == 0.f) b[2 * i] = kNegInfT;
+        if (f.y == 0.f) b[2 * i + 1] = kNegInfT;
+      } else {
+        b[2 * i] = fmaf(f.x, kLog2eT, b[2 * i]);
+        b[2 * i + 1] = fmaf(f.y, kLog2eT, b[2 * i + 1]);
+      }
+    }
+  }
+}
+// The term of one element (query row `row`, key column `col` of the box of `half`).
+template <typename T>
+BSP_DEVI float xt_term(const unsigned char* xt, const int has_rpe, const int am_mode, int half, int row, int col) {
+  const uint32_t off = xt_off(half, row, col);
+  float t = 0.f;
+  if (has_rpe) t = static_cast<float>(*reinterpret_cast<const T*>(xt + off)) * kLog2eT;
+  if (am_mode) {
+    const float m = static_cast<float>(*reinterpret_cast<const T*>(xt + 16384 + off));
+    t = am_mode == 2 ? (m == 0.f ? kNegInfT : t) : fmaf(m, kLog2eT, t);
+  }
+  return t;
 }
 // Which of this thread's two groups of 16 columns of a chunk exist (bit 0, bit 1)?  `sub` holds,
 // per half of the tile, 16 bits: bit 4 a + b for the piece of row group a and column group b (of
@@ -168,7 +223,7 @@ BSP_DEVI float2 exp2_pair(float2 y) {
 template <typename T> struct IsBf16 { static constexpr int v = 0; };
 template <> struct IsBf16<__nv_bfloat16> { static constexpr int v = 1; };
 
-template <int D, int MODE, bool KPM = false> struct Cfg {
+template <int D, int MODE, bool KPM = false, bool XT = false> struct Cfg {
   static constexpr int ATOMS = D / 64;                         // 64-element (128-byte) column groups
   static constexpr int NRES = MODE == FWD ? 1 : 2;             // resident 128-row operands
   static constexpr int NC = 8;                                 // compute warps: two threads per tile row
@@ -178,12 +233,16 @@ template <int D, int MODE, bool KPM = false> struct Cfg {
   // A key-padding mask is a bias per key: per column of the scores in the forward and in dQ
   // (64 values travel with every chunk), per row in dK/dV (read once per tile).
   static constexpr bool BIAS = KPM && MODE != DKV;
-  static constexpr int STAGE = 2 * CH_BYTES + ((MODE == DKV || BIAS) ? 1024 : 0);   // + lse / delta, or the bias, of the chunk
+  // XT: a relative position bias and / or an attention mask; their 64 x 64 pieces for the chunk
+  // (one box per half of the tile and tensor) travel with it, 32 KB per stage, and the kernel
+  // runs with one CTA per SM.
+  static constexpr int XT_OFF = 2 * CH_BYTES + 1024;
+  static constexpr int STAGE = 2 * CH_BYTES + ((MODE == DKV || BIAS || XT) ? 1024 : 0) + (XT ? 4 * 8192 : 0);   // + lse / delta, or the bias, of the chunk
   static constexpr int TAIL_BYTES = MODE == DKV ? 512 : (BIAS ? 128 : 0);
   // score buffers in tensor memory: two (scores of the next chunk are computed while this
   // one is consumed) where the columns allow it with two CTAs per SM, else one
   static constexpr int NBUF = MODE == FWD ? 2 : (D == 64 ? 1 : 2);
-  static constexpr int NSTAGE = (MODE != FWD && D == 128) ? 3 : 4;
+  static constexpr int NSTAGE = XT ? (D == 64 ? (MODE == FWD ? 4 : 3) : 2) : ((MODE != FWD && D == 128) ? 3 : 4);
   static constexpr int SMEM = NRES * RES_BYTES + NSTAGE * STAGE + 1024;
   static constexpr int SCORE_COLS = MODE == FWD ? 64 : 128;    // per buffer: S (and dP)
   // Early release (dQ at head_dim 64): the packed dS operand of the accumulating product gets
@@ -208,7 +267,7 @@ template <int D, int MODE, bool KPM = false> struct Cfg {
   static constexpr int RES_BASE = ACC_BASE + ACC_COLS;
   static constexpr int RES_COLS = RES_T ? NRES * (D / 2) : 0;
   static constexpr int TMEM = RES_BASE + RES_COLS <= 256 ? 256 : 512;
-  static constexpr int CTAS = D == 64 ? 2 : 1;
+  static constexpr int CTAS = (D == 64 && !XT) ? 2 : 1;
 };
 
 // Writes accumulator columns [c0, c0 + n) of this thread's tensor-memory lane to dst[c0 .. c0 + n) as 16-bit values.
@@ -232,11 +291,13 @@ BSP_DEVI void store_acc(T* dst, uint32_t taddr, int c0, int n, float mul) {
 
 // FINE: the lists come from a layout with blocks smaller than 64 (pieces of a position may be
 // absent); a separate instantiation keeps the other case free of that bookkeeping.
-template <typename T, int D, int MODE, bool KPM, bool FINE>
-__global__ void __launch_bounds__(Cfg<D, MODE, KPM>::NT, Cfg<D, MODE, KPM>::CTAS)
+template <typename T, int D, int MODE, bool KPM, bool FINE, bool XT>
+__global__ void __launch_bounds__(Cfg<D, MODE, KPM, XT>::NT, Cfg<D, MODE, KPM, XT>::CTAS)
 attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant__ CUtensorMap m_res1,
-               const __grid_constant__ CUtensorMap m_ch0, const __grid_constant__ CUtensorMap m_ch1, TcArgs a) {
-  using C = Cfg<D, MODE, KPM>;
+               const __grid_constant__ CUtensorMap m_ch0, const __grid_constant__ CUtensorMap m_ch1,
+               const __grid_constant__ CUtensorMap m_rpe, const __grid_constant__ CUtensorMap m_am, TcArgs a) {
+  using C = Cfg<D, MODE, KPM, XT>;
+  static_assert(!XT || FINE, "the variants with rpe / attention mask use the masked code path");
   constexpr int ATOMS = C::ATOMS, ST = C::NSTAGE, NC = C::NC, NBUF = C::NBUF;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = smem_raw + ((1024 - (saddr(smem_raw) & 1023)) & 1023);
@@ -280,7 +341,9 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
   auto load_chunk = [&](int t, int crow) {
     const int stage = t % ST;
     unsigned char* sp = stg + stage * C::STAGE;
-    mbar_expect_tx(&bar_full[stage], 2 * C::CH_BYTES + C::TAIL_BYTES);
+    uint32_t bytes = 2 * C::CH_BYTES + C::TAIL_BYTES;
+    if constexpr (XT) bytes += (uint32_t)((c1 < 0 ? 1 : 2) * 8192 * ((a.has_rpe ? 1 : 0) + (a.am_mode ? 1 : 0)));
+    mbar_expect_tx(&bar_full[stage], bytes);
     if (t == a.skip_chunk) return;                             // (test hook: this stage never fills, its consumers' waits run out)
     for (int at = 0; at < ATOMS; ++at) {
       tma_load_4d(sp + at * 8192, &m_ch0, &bar_full[stage], at * 64, crow, h, z);
@@ -291,6 +354,16 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
       bulk_load(sp + 2 * C::CH_BYTES + 256, a.delta + zh + crow, 256, &bar_full[stage]);
     }
     if (C::BIAS) bulk_load(sp + 2 * C::CH_BYTES, reinterpret_cast<const T*>(a.kpm) + z * a.kpm_sz + crow, 128, &bar_full[stage]);
+    if constexpr (XT) {
+      // rows of rpe / the mask are queries, columns keys: the tile's rows are queries in the
+      // forward and in dQ (the chunk brings keys), keys in dK / dV (the chunk brings queries)
+      for (int hf = 0; hf < (c1 < 0 ? 1 : 2); ++hf) {
+        const int outer = (hf == 0 ? c0 : c1) * 64;
+        const int col = MODE == DKV ? outer : crow, row = MODE == DKV ? crow : outer;
+        if (a.has_rpe) tma_load_4d(sp + C::XT_OFF + hf * 8192, &m_rpe, &bar_full[stage], col, row, h, a.rpe_z ? z : 0);
+        if (a.am_mode) tma_load_4d(sp + C::XT_OFF + 16384 + hf * 8192, &m_am, &bar_full[stage], col, row, 0, 0);
+      }
+    }
   };
   // The thread that issues the loads sets up their barriers itself and starts the resident
   // operands and the first chunks at once: their latency overlaps the rest of the set-up
@@ -300,6 +373,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
     for (int s = 0; s < ST; ++s) mbar_init(&bar_full[s], 1);
     mbar_init_fence();
     prefetch_map(&m_res0); prefetch_map(&m_ch0); prefetch_map(&m_ch1);
+    if constexpr (XT) { if (a.has_rpe) prefetch_map(&m_rpe); if (a.am_mode) prefetch_map(&m_am); }
     mbar_expect_tx(&bar_res, C::NRES * C::RES_BYTES);
     for (int hf = 0; hf < 2; ++hf) {
       const int crow = (hf == 0 || c1 < 0 ? c0 : c1) * 64;
@@ -544,12 +618,17 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
         if (FINE && a.causal) mask_causal<32, false>(sr, a.chunk[first + t] * 64 + chalf * 32, (int)grow);
         float mt = kNegInfT;
         if (valid) {
-          if constexpr (KPM) {                               // scores become s * scale + bias (base 2) in place
+          if constexpr (KPM || XT) {                         // scores become s * scale + bias (base 2) in place
             const unsigned char* bp = stg + (t % ST) * C::STAGE + 2 * C::CH_BYTES + chalf * 64;
 #pragma unroll
             for (int g = 0; g < 4; ++g) {
               float b[8];
-              kpm_terms8<T>(bp + g * 16, a.kpm_mul, b);
+              if constexpr (KPM) kpm_terms8<T>(bp + g * 16, a.kpm_mul, b);
+              else {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) b[i] = 0.f;
+              }
+              if constexpr (XT) xt_add8<T>(stg + (t % ST) * C::STAGE + C::XT_OFF, a.has_rpe, a.am_mode, half, trow & 63, chalf * 4 + g, b);
 #pragma unroll
               for (int i = 0; i < 8; i += 2) {
                 const float2 y = __ffma2_rn(u2f(sr[8 * g + i], sr[8 * g + i + 1]), f2(a.scale_log2, a.scale_log2), f2(b[i], b[i + 1]));
@@ -557,7 +636,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
               }
             }
           }
-          mt = max32(sr) * (KPM ? 1.f : a.scale_log2);
+          mt = max32(sr) * ((KPM || XT) ? 1.f : a.scale_log2);
         }
         // the reference maximum is only raised when the row maximum outgrows it by 2^8
         const bool grow_m = mt > m_ref + 8.f;
@@ -593,7 +672,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
               const float2 s01 = u2f(sr[16 * hp + 2 * i], sr[16 * hp + 2 * i + 1]);
-              const float2 y = KPM ? __fadd2_rn(s01, nm2) : __ffma2_rn(s01, sl2, nm2);
+              const float2 y = (KPM || XT) ? __fadd2_rn(s01, nm2) : __ffma2_rn(s01, sl2, nm2);
               const float2 p = exp2_pair<1>(y);
               s2[i & 1] = __fadd2_rn(s2[i & 1], p);
               ph[i] = pack16<T>(p.x, p.y);
@@ -686,8 +765,13 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
 #pragma unroll
             for (int g = 0; g < 4; ++g) {
               float b[8];
-              if constexpr (KPM) {
-                kpm_terms8<T>(bp + g * 16, a.kpm_mul, b);
+              if constexpr (KPM || XT) {
+                if constexpr (KPM) kpm_terms8<T>(bp + g * 16, a.kpm_mul, b);
+                else {
+#pragma unroll
+                  for (int i = 0; i < 8; ++i) b[i] = 0.f;
+                }
+                if constexpr (XT) xt_add8<T>(stg + (t % ST) * C::STAGE + C::XT_OFF, a.has_rpe, a.am_mode, half, trow & 63, chalf * 4 + g, b);
 #pragma unroll
                 for (int i = 0; i < 8; ++i) b[i] -= my_lse;
               } else {
@@ -740,6 +824,13 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
               if (KPM || FINE) {                              // own bias; a query row without any key counts as +inf
                 lv.x = lv.x == kNegInfT ? -kNegInfT : lv.x - my_b; lv.y = lv.y == kNegInfT ? -kNegInfT : lv.y - my_b;
                 lv.z = lv.z == kNegInfT ? -kNegInfT : lv.z - my_b; lv.w = lv.w == kNegInfT ? -kNegInfT : lv.w - my_b;
+              }
+              if constexpr (XT) {                             // rpe / mask of (query chalf * 32 + i .. + 3, this key)
+                const unsigned char* xt = stg + (t % ST) * C::STAGE + C::XT_OFF;
+                lv.x -= xt_term<T>(xt, a.has_rpe, a.am_mode, half, chalf * 32 + i, trow & 63);
+                lv.y -= xt_term<T>(xt, a.has_rpe, a.am_mode, half, chalf * 32 + i + 1, trow & 63);
+                lv.z -= xt_term<T>(xt, a.has_rpe, a.am_mode, half, chalf * 32 + i + 2, trow & 63);
+                lv.w -= xt_term<T>(xt, a.has_rpe, a.am_mode, half, chalf * 32 + i + 3, trow & 63);
               }
               // the negated exponent lse - s c: the lse comes from shared memory as it is
               const float2 z0 = __ffma2_rn(u2f(sr[i], sr[i + 1]), nsl2, f2(lv.x, lv.y));
@@ -820,6 +911,14 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
                   ls[0] -= kpm_term(b01.x, a.kpm_mul); ls[1] -= kpm_term(b01.y, a.kpm_mul);
                   ls[2] -= kpm_term(b23.x, a.kpm_mul); ls[3] -= kpm_term(b23.y, a.kpm_mul);
                 }
+              }
+              if constexpr (XT) {                             // rpe / mask of the four (query, key) pairs
+                const unsigned char* xt = stg + (t % ST) * C::STAGE + C::XT_OFF;
+                const int cc = chalf * 32 + hv * 16 + i;        // column of the chunk: a key (dQ) or a query (dK / dV)
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                  ls[j] -= MODE == DKV ? xt_term<T>(xt, a.has_rpe, a.am_mode, half, cc + j, trow & 63)
+                                       : xt_term<T>(xt, a.has_rpe, a.am_mode, half, trow & 63, cc + j);
               }
               float pv[4], dv[4];
 #pragma unroll
@@ -948,42 +1047,63 @@ int decode_tiles(const int32_t* hdr, const int32_t* dev, TilesView& v) {
   return BSP_OK;
 }
 
-template <typename T, int D, int MODE, bool KPM, bool FINE>
-int launch(const CUtensorMap& r0, const CUtensorMap& r1, const CUtensorMap& c0, const CUtensorMap& c1,
-           const TcArgs& a, int n_tiles, int Z, cudaStream_t st, const char* what) {
-  using C = Cfg<D, MODE, KPM>;
-  auto kern = attn_tc_kernel<T, D, MODE, KPM, FINE>;
+// The maps a launch needs: resident operands, chunk operands and (XT variants) rpe / attention mask.
+struct Maps { CUtensorMap r0, r1, c0, c1, rpe, am; };
+
+template <typename T, int D, int MODE, bool KPM, bool FINE, bool XT>
+int launch(const Maps& m, const TcArgs& a, int n_tiles, int Z, cudaStream_t st, const char* what) {
+  using C = Cfg<D, MODE, KPM, XT>;
+  auto kern = attn_tc_kernel<T, D, MODE, KPM, FINE, XT>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM);
   if (e != cudaSuccess) return fail(BSP_ERR_CUDA, "attention (tcgen05 %s): cannot reserve shared memory: %s", what, cudaGetErrorString(e));
   TcArgs b = a;
   b.Z = Z;
   b.wait_budget = g_wait_budget.load();
   b.skip_chunk = g_skip_chunk.load();
-  kern<<<(unsigned)((int64_t)n_tiles * Z), C::NT, C::SMEM, st>>>(r0, r1, c0, c1, b);
+  kern<<<(unsigned)((int64_t)n_tiles * Z), C::NT, C::SMEM, st>>>(m.r0, m.r1, m.c0, m.c1, m.rpe, m.am, b);
   e = cudaGetLastError();
   if (e != cudaSuccess) return fail(BSP_ERR_CUDA, "attention (tcgen05 %s) launch failed: %s", what, cudaGetErrorString(e));
   return BSP_OK;
 }
 
-template <int MODE, bool KPM, bool FINE>
-int launch_dt(int dtype, int D, const CUtensorMap& r0, const CUtensorMap& r1, const CUtensorMap& c0,
-              const CUtensorMap& c1, const TcArgs& a, int n_tiles, int Z, cudaStream_t st, const char* what) {
+template <int MODE, bool KPM, bool FINE, bool XT>
+int launch_dt(int dtype, int D, const Maps& m, const TcArgs& a, int n_tiles, int Z, cudaStream_t st, const char* what) {
   if (dtype == BSP_F16) {
-    if (D == 64) return launch<__half, 64, MODE, KPM, FINE>(r0, r1, c0, c1, a, n_tiles, Z, st, what);
-    return launch<__half, 128, MODE, KPM, FINE>(r0, r1, c0, c1, a, n_tiles, Z, st, what);
+    if (D == 64) return launch<__half, 64, MODE, KPM, FINE, XT>(m, a, n_tiles, Z, st, what);
+    return launch<__half, 128, MODE, KPM, FINE, XT>(m, a, n_tiles, Z, st, what);
   }
-  if (D == 64) return launch<__nv_bfloat16, 64, MODE, KPM, FINE>(r0, r1, c0, c1, a, n_tiles, Z, st, what);
-  return launch<__nv_bfloat16, 128, MODE, KPM, FINE>(r0, r1, c0, c1, a, n_tiles, Z, st, what);
+  if (D == 64) return launch<__nv_bfloat16, 64, MODE, KPM, FINE, XT>(m, a, n_tiles, Z, st, what);
+  return launch<__nv_bfloat16, 128, MODE, KPM, FINE, XT>(m, a, n_tiles, Z, st, what);
 }
 template <int MODE>
-int launch_any(int dtype, int D, const CUtensorMap& r0, const CUtensorMap& r1, const CUtensorMap& c0,
-               const CUtensorMap& c1, const TcArgs& a, int n_tiles, int Z, cudaStream_t st, const char* what) {
-  if (a.kpm) {
-    if (a.fine || a.causal) return launch_dt<MODE, true, true>(dtype, D, r0, r1, c0, c1, a, n_tiles, Z, st, what);
-    return launch_dt<MODE, true, false>(dtype, D, r0, r1, c0, c1, a, n_tiles, Z, st, what);
+int launch_any(int dtype, int D, const Maps& m, const TcArgs& a, int n_tiles, int Z, cudaStream_t st, const char* what) {
+  if (a.has_rpe || a.am_mode) {           // rpe / an attention mask that is read: the masked code path
+    if (a.kpm) return launch_dt<MODE, true, true, true>(dtype, D, m, a, n_tiles, Z, st, what);
+    return launch_dt<MODE, false, true, true>(dtype, D, m, a, n_tiles, Z, st, what);
   }
-  if (a.fine || a.causal) return launch_dt<MODE, false, true>(dtype, D, r0, r1, c0, c1, a, n_tiles, Z, st, what);
-  return launch_dt<MODE, false, false>(dtype, D, r0, r1, c0, c1, a, n_tiles, Z, st, what);
+  if (a.kpm) {
+    if (a.fine || a.causal) return launch_dt<MODE, true, true, false>(dtype, D, m, a, n_tiles, Z, st, what);
+    return launch_dt<MODE, true, false, false>(dtype, D, m, a, n_tiles, Z, st, what);
+  }
+  if (a.fine || a.causal) return launch_dt<MODE, false, true, false>(dtype, D, m, a, n_tiles, Z, st, what);
+  return launch_dt<MODE, false, false, false>(dtype, D, m, a, n_tiles, Z, st, what);
+}
+
+// rpe [Z or 1, H, L, L] and the attention mask [L, L] as maps of 64 x 64 boxes; an absent one gets
+// a copy of `any` (never dereferenced).
+int xt_maps(Maps& m, TcArgs& a, const XtHost* xt, const CUtensorMap& any, int dtype, int Z, int H, int L) {
+  m.rpe = any; m.am = any;
+  a.has_rpe = 0; a.rpe_z = 0; a.am_mode = 0;
+  if (!xt) return BSP_OK;
+  if (xt->rpe) {
+    a.has_rpe = 1; a.rpe_z = xt->rpe_sz != 0 ? 1 : 0;
+    if (int rc = make_map(&m.rpe, xt->rpe, dtype, a.rpe_z ? Z : 1, H, L, L, xt->rpe_sz, xt->rpe_sh, xt->rpe_sr)) return rc;
+  }
+  if (xt->am) {
+    a.am_mode = xt->am_mode;
+    if (int rc = make_map(&m.am, xt->am, dtype, 1, 1, L, L, 0, 0, xt->am_sr)) return rc;
+  }
+  return BSP_OK;
 }
 
 void fill_tiles(TcArgs& a, const TilesView& tv, const TileSet& s) {
@@ -1002,7 +1122,7 @@ int attn_fwd_tc(const void* q, const void* k, const void* v, void* o, float* lse
                 int64_t q_sz, int64_t q_sh, int64_t q_sr, int64_t k_sz, int64_t k_sh, int64_t k_sr,
                 int64_t v_sz, int64_t v_sh, int64_t v_sr, int64_t o_sz, int64_t o_sh, int64_t o_sr,
                 const int32_t* tiles_hdr, const int32_t* tiles, float scale,
-                const void* kpm, int64_t kpm_sz, int kpm_mul, int causal, cudaStream_t st) {
+                const void* kpm, int64_t kpm_sz, int kpm_mul, int causal, const XtHost* xt, cudaStream_t st) {
   TilesView tv;
   if (int rc = decode_tiles(tiles_hdr, tiles, tv)) return rc;
   if (tv.H != H || tv.nb * tv.block != L) return fail(BSP_ERR_INVALID, "attention tile lists do not fit %d heads of length %d", H, L);
@@ -1010,12 +1130,15 @@ int attn_fwd_tc(const void* q, const void* k, const void* v, void* o, float* lse
   if (int rc = make_map(&mq, q, dtype, Z, H, L, D, q_sz, q_sh, q_sr)) return rc;
   if (int rc = make_map(&mk, k, dtype, Z, H, L, D, k_sz, k_sh, k_sr)) return rc;
   if (int rc = make_map(&mv, v, dtype, Z, H, L, D, v_sz, v_sh, v_sr)) return rc;
+  Maps m;
+  m.r0 = mq; m.r1 = mq; m.c0 = mk; m.c1 = mv;
   TcArgs a = {};
+  if (int rc = xt_maps(m, a, xt, mq, dtype, Z, H, L)) return rc;
   a.out0 = o; a.lse_out = lse; a.o_sz = o_sz; a.o_sh = o_sh; a.o_sr = o_sr;
   a.H = H; a.L = L; a.scale = scale; a.scale_log2 = scale * kLog2eT;
   a.kpm = kpm; a.kpm_sz = kpm_sz; a.kpm_mul = kpm_mul; a.causal = causal;
   fill_tiles(a, tv, tv.rt);
-  return launch_any<FWD>(dtype, D, mq, mq, mk, mv, a, H * tv.tiles_per_head, Z, st, "forward");
+  return launch_any<FWD>(dtype, D, m, a, H * tv.tiles_per_head, Z, st, "forward");
 }
 
 // dK/dV (parts & 2) and dQ (parts & 4) on the tcgen05 path; `delta` must already hold rowsum(o * do).
@@ -1024,7 +1147,7 @@ int attn_bwd_tc(const void* q, const void* k, const void* v, const void* dout, c
                 int64_t q_sz, int64_t q_sh, int64_t q_sr, int64_t k_sz, int64_t k_sh, int64_t k_sr,
                 int64_t v_sz, int64_t v_sh, int64_t v_sr, int64_t do_sz, int64_t do_sh, int64_t do_sr,
                 const int32_t* tiles_hdr, const int32_t* tiles, float scale,
-                const void* kpm, int64_t kpm_sz, int kpm_mul, int causal, int parts, cudaStream_t st) {
+                const void* kpm, int64_t kpm_sz, int kpm_mul, int causal, int parts, const XtHost* xt, cudaStream_t st) {
   TilesView tv;
   if (int rc = decode_tiles(tiles_hdr, tiles, tv)) return rc;
   if (tv.H != H || tv.nb * tv.block != L) return fail(BSP_ERR_INVALID, "attention tile lists do not fit %d heads of length %d", H, L);
@@ -1033,19 +1156,23 @@ int attn_bwd_tc(const void* q, const void* k, const void* v, const void* dout, c
   if (int rc = make_map(&mk, k, dtype, Z, H, L, D, k_sz, k_sh, k_sr)) return rc;
   if (int rc = make_map(&mv, v, dtype, Z, H, L, D, v_sz, v_sh, v_sr)) return rc;
   if (int rc = make_map(&md, dout, dtype, Z, H, L, D, do_sz, do_sh, do_sr)) return rc;
+  Maps m;
   TcArgs a = {};
+  if (int rc = xt_maps(m, a, xt, mq, dtype, Z, H, L)) return rc;
   a.lse = lse; a.delta = delta; a.H = H; a.L = L; a.scale = scale; a.scale_log2 = scale * kLog2eT;
   a.kpm = kpm; a.kpm_sz = kpm_sz; a.kpm_mul = kpm_mul; a.causal = causal;
   const int n_tiles = H * tv.tiles_per_head;
   if (parts & 2) {
     a.out0 = dk; a.out1 = dv;
     fill_tiles(a, tv, tv.ct);
-    if (int rc = launch_any<DKV>(dtype, D, mk, mv, mq, md, a, n_tiles, Z, st, "dK/dV")) return rc;
+    m.r0 = mk; m.r1 = mv; m.c0 = mq; m.c1 = md;
+    if (int rc = launch_any<DKV>(dtype, D, m, a, n_tiles, Z, st, "dK/dV")) return rc;
   }
   if (parts & 4) {
     a.out0 = dq; a.out1 = nullptr;
     fill_tiles(a, tv, tv.rt);
-    if (int rc = launch_any<DQ>(dtype, D, mq, md, mk, mv, a, n_tiles, Z, st, "dQ")) return rc;
+    m.r0 = mq; m.r1 = md; m.c0 = mk; m.c1 = mv;
+    if (int rc = launch_any<DQ>(dtype, D, m, a, n_tiles, Z, st, "dQ")) return rc;
   }
   return BSP_OK;
 }
