@@ -266,6 +266,22 @@ int bsp_dds(const void* a, const void* s, void* c, int dtype, int block,
             int64_t c_sz, int64_t c_sh, int64_t c_sm, int64_t c_sn,
             const int32_t* meta_hdr, const int32_t* meta, void* stream);
 
+/*
+ * Debug aids (no counterpart in the reference): check every index the compute
+ * kernels will derive from a DEVICE metadata buffer (bsp_meta_build /
+ * bsp_meta_build_device) or from DEVICE attention tile lists
+ * (bsp_attn_tiles_build) of `len` ints against the sizes in the buffer's own
+ * header - pointers monotone and in range, block ids below the block count,
+ * rows / columns / heads / chunk ids inside the layout, orders inside their
+ * range.  Returns BSP_OK, or BSP_ERR_INVALID with the number of the failed check
+ * in *code and the offending entry in *pos.  Synchronises `stream`.  The Python
+ * layer runs them on every buffer it uploads when BSP_DEBUG=1 is set in the
+ * environment; they stand in for a device memory checker on systems where none
+ * can be run.
+ */
+int bsp_meta_validate(const int32_t* meta, int64_t len, int* code, int* pos, void* stream);
+int bsp_attn_tiles_validate(const int32_t* tiles, int64_t len, int* code, int* pos, void* stream);
+
 /* ------------------------------------------------------------------------ */
 /* Fused sparse self-attention (device)                                     */
 /* ------------------------------------------------------------------------ */

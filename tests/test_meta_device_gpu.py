@@ -83,3 +83,34 @@ def test_matmul_with_a_device_layout_matches_the_host_layout_path():
     s = torch.randn((2, int(layout.sum()), 64, 64), generator=g).half().to(DEV)
     w = torch.randn((2, 2, 384, 128), generator=g).half().to(DEV)
     assert_close(MatMul(layout.to(DEV), 64, 'dsd')(s, w), MatMul(layout, 64, 'dsd')(s, w), 'dsd')
+
+
+def test_validation_accepts_built_buffers_and_names_the_corrupt_entry():
+    """The debug-time validation kernels: buffers from the builders pass; a block column, a block
+    id, a row pointer, a chunk id or a tile order out of range is reported with its check
+    number and position."""
+    tables.clear_cache()
+    for lay, block in ((layouts.fixed(4, 16, 4, 'unidirectional'), 64), (layouts.bigbird(3, 12, 2, 3, 1, seed=1), 128),
+                       (layouts.fixed(2, 16, 4, 'bidirectional'), 16)):
+        m = tables.build_meta(lay)
+        tables.validate_device_buffer(m.on(DEV))
+        tables.validate_device_buffer(tables.build_meta_device(lay.to(DEV)).on(DEV))
+        t = tables.build_attn_tiles(lay, block)
+        tables.validate_device_buffer(t.on(DEV), tiles=True)
+    lay = layouts.fixed(2, 8, 4, 'unidirectional')
+    m = tables.build_meta(lay)
+    H, Mb, Nb, nnz = m.H, m.Mb, m.Nb, m.nnz
+    base = 8 + (H * Mb + 1)
+    for offset, value, code in ((base + nnz + 3, Nb, 6),               # blk_col out of range
+                                (base + 3 * nnz + (H * Nb + 1) + nnz + 1, nnz, 7),   # col_bid out of range
+                                (8 + 2, 10 ** 6, 3)):                  # row_ptr jumps
+        bad = m.on(DEV).clone()
+        bad[offset] = value
+        with pytest.raises(ValueError, match='check %d failed' % code):
+            tables.validate_device_buffer(bad)
+    t = tables.build_attn_tiles(lay, 64)
+    n = int(t.hdr[1]) * int(t.hdr[4])
+    bad = t.on(DEV).clone()
+    bad[8 + 2 * n + (n + 1) + 1] = 10 ** 4                            # a chunk id of the row tiles
+    with pytest.raises(ValueError, match='check 16 failed'):
+        tables.validate_device_buffer(bad, tiles=True)

@@ -4,7 +4,7 @@ import torch
 
 import workloads
 from oracle import dense_masked as dm
-from tests.util import assert_close, load_npz
+from tests.util import Guarded, assert_close, load_npz
 from torch_blocksparse_b200 import Softmax
 
 pytestmark = pytest.mark.gpu
@@ -15,13 +15,23 @@ def run_both(layout, block, x, dy, dtype, **kw):
     """Runs the CUDA op (forward + backward through autograd) and the oracle."""
     want_y, want_dx = dm.softmax_reference(x, layout, block, dy=dy, **kw)
     op = Softmax(layout, block)
+    gkw = {k: (v.to(DEV) if torch.is_tensor(v) else v) for k, v in kw.items()}
+    # forward alone on an input inside a NaN-margined allocation: nothing is written outside it
+    gx = Guarded(x.shape, x.dtype, DEV, fill=x.to(DEV))
+    with torch.no_grad():
+        y0 = op(gx.t, **gkw)
+    torch.cuda.synchronize()
+    gx.check('x')
+    assert_close(y0, want_y, 'y (guarded input)')
     xg = x.to(DEV).requires_grad_()
     xin = xg * 1                      # non-leaf: the op works in place
-    gkw = {k: (v.to(DEV) if torch.is_tensor(v) else v) for k, v in kw.items()}
     y = op(xin, **gkw)
     assert y.data_ptr() == xin.data_ptr(), 'softmax must overwrite its input'
     y_copy = y.detach().clone()
-    y.backward(dy.to(DEV))
+    gdy = Guarded(dy.shape, dy.dtype, DEV, fill=dy.to(DEV))
+    y.backward(gdy.t)                 # the backward overwrites the incoming gradient
+    torch.cuda.synchronize()
+    gdy.check('dy')
     assert_close(y_copy, want_y, 'y')
     assert_close(xg.grad, want_dx, 'dx')
 

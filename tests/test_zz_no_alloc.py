@@ -12,7 +12,7 @@ import pytest
 import torch
 
 import workloads
-from tests.util import assert_close
+from tests.util import Guarded, assert_close
 from torch_blocksparse_b200 import _lib, tables
 
 pytestmark = pytest.mark.gpu
@@ -33,7 +33,8 @@ def _code(x):
 def _backward(entry, t, meta, block, scale, delta=None, tiles=None):
     q, k, v, o, do, lse = t
     Z, H, L, D = q.shape
-    grads = [torch.empty_like(q) for _ in range(3)]
+    guards = [Guarded(q.shape, q.dtype, q.device) for _ in range(3)]       # NaN margins around dq, dk, dv
+    grads = [g.t for g in guards]
     st = lambda x: (x.stride(0), x.stride(1), x.stride(2))
     head = [q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), do.data_ptr(), lse.data_ptr()]
     if delta is not None:
@@ -45,6 +46,8 @@ def _backward(entry, t, meta, block, scale, delta=None, tiles=None):
         + [torch.cuda.current_stream().cuda_stream]
     _lib.check(entry(*args))
     torch.cuda.synchronize()
+    for g, name in zip(guards, ('dq', 'dk', 'dv')):
+        g.check(name)
     return grads
 
 

@@ -34,3 +34,24 @@ def head_blocks(layout, h):
 
 def load_npz(name):
     return np.load(os.path.join(GOLDEN, name))
+
+
+class Guarded:
+    """A tensor in the middle of a larger allocation whose margins are filled with NaN (the idea
+    of the reference's unused `mempad`, tests/utils.py:36-40): a kernel that writes outside the
+    tensor it was given destroys a NaN, and check() sees it.  Stands in for a device memory
+    checker in the small GPU tests."""
+
+    def __init__(self, shape, dtype, device, pad_elems=8192, fill=None):
+        n = 1
+        for d in shape:
+            n *= d
+        self.pad = pad_elems
+        self.buf = torch.full((n + 2 * pad_elems,), float('nan'), dtype=dtype, device=device)
+        self.t = self.buf[pad_elems:pad_elems + n].view(*shape)
+        if fill is not None:
+            self.t.copy_(fill)
+
+    def check(self, what=''):
+        lo, hi = self.buf[:self.pad], self.buf[-self.pad:]
+        assert bool(torch.isnan(lo).all()) and bool(torch.isnan(hi).all()), 'write outside %s' % (what or 'the tensor')

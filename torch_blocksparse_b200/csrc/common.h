@@ -6,6 +6,12 @@
 #include <cstdio>
 #include "../../include/bsp.h"
 
+#ifdef __CUDACC__
+#define BSP_HD __host__ __device__
+#else
+#define BSP_HD
+#endif
+
 namespace bsp {
 
 // Stores a printf-style message in the calling thread's error slot and
@@ -32,13 +38,13 @@ struct Meta {
   const int32_t* col_order;
 };
 
-inline int64_t meta_total(int H, int Mb, int Nb, int64_t nnz) {
+BSP_HD inline int64_t meta_total(int H, int Mb, int Nb, int64_t nnz) {
   return BSP_META_HEADER + (int64_t)(H * Mb + 1) + 3 * nnz + (int64_t)(H * Nb + 1) + 2 * nnz +
          (int64_t)H * Mb + (int64_t)H * Nb;
 }
 
 // Lays the section pointers of a metadata buffer out from its base address.
-inline Meta meta_view(const int32_t* base, int H, int Mb, int Nb, int nnz, int max_row, int max_col) {
+BSP_HD inline Meta meta_view(const int32_t* base, int H, int Mb, int Nb, int nnz, int max_row, int max_col) {
   Meta m;
   m.H = H; m.Mb = Mb; m.Nb = Nb; m.nnz = nnz; m.max_row = max_row; m.max_col = max_col;
   const int32_t* p = base + BSP_META_HEADER;

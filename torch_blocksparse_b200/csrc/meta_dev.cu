@@ -159,10 +159,100 @@ int build(const L* lay, int H, int Mb, int Nb, int32_t* out, int32_t* scratch, c
   return BSP_OK;
 }
 
+// ---- validation -----------------------------------------------------------------------------
+// Every index a compute kernel will derive from a metadata buffer or from attention tile
+// lists, checked against the sizes in the buffer's header: the first violation found is
+// recorded as (code, position) in `err` (two ints, zero on entry).  Used instead of a memory
+// checker: a corrupt table shows up as an error code before any kernel dereferences it.
+__device__ void report(int* err, int code, int pos) {
+  if (atomicCAS(&err[0], 0, code) == 0) err[1] = pos;
+}
+
+__global__ void meta_validate_kernel(const int32_t* __restrict__ m, int64_t len, int* err) {
+  const int H = m[1], Mb = m[2], Nb = m[3], nnz = m[4];
+  if (m[0] != BSP_META_MAGIC || H <= 0 || Mb <= 0 || Nb <= 0 || nnz < 0 || meta_total(H, Mb, Nb, nnz) > len) {
+    if (blockIdx.x == 0 && threadIdx.x == 0) report(err, 1, 0);
+    return;
+  }
+  const Meta v = meta_view(m, H, Mb, Nb, nnz, m[5], m[6]);
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i <= H * Mb) {
+    if (i == 0 && v.row_ptr[0] != 0) report(err, 2, 0);
+    if (i == H * Mb && v.row_ptr[i] != nnz) report(err, 2, (int)i);
+    if (i < H * Mb && (v.row_ptr[i + 1] < v.row_ptr[i] || v.row_ptr[i + 1] - v.row_ptr[i] > m[5])) report(err, 3, (int)i);
+    if (i < H * Mb && (v.row_order[i] < 0 || v.row_order[i] >= H * Mb)) report(err, 8, (int)i);
+  }
+  if (i <= H * Nb) {
+    if (i == 0 && v.col_ptr[0] != 0) report(err, 4, 0);
+    if (i == H * Nb && v.col_ptr[i] != nnz) report(err, 4, (int)i);
+    if (i < H * Nb && (v.col_ptr[i + 1] < v.col_ptr[i] || v.col_ptr[i + 1] - v.col_ptr[i] > m[6])) report(err, 5, (int)i);
+    if (i < H * Nb && (v.col_order[i] < 0 || v.col_order[i] >= H * Nb)) report(err, 9, (int)i);
+  }
+  if (i < nnz) {
+    if (v.blk_row[i] < 0 || v.blk_row[i] >= Mb || v.blk_col[i] < 0 || v.blk_col[i] >= Nb || v.blk_head[i] < 0 || v.blk_head[i] >= H)
+      report(err, 6, (int)i);
+    if (v.col_row[i] < 0 || v.col_row[i] >= Mb || v.col_bid[i] < 0 || v.col_bid[i] >= nnz) report(err, 7, (int)i);
+  }
+}
+
+__global__ void tiles_validate_kernel(const int32_t* __restrict__ t, int64_t len, int* err) {
+  const int H = t[1], nb = t[2], block = t[3], nt = t[4], er = t[5], ec = t[6];
+  const int64_t n = (int64_t)H * nt;
+  if (t[0] != BSP_TILES_MAGIC || H <= 0 || nb <= 0 || nt <= 0 || er < 0 || ec < 0 || (block != 64 && block != 128) ||
+      BSP_TILES_HEADER + 2 * (4 * n + 1) + 3 * (int64_t)er + 3 * (int64_t)ec > len) {
+    if (blockIdx.x == 0 && threadIdx.x == 0) report(err, 11, 0);
+    return;
+  }
+  const int chunks = nb * (block / 64);                   // 64-row chunks per side
+  const int32_t* p = t + BSP_TILES_HEADER;
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  for (int set = 0; set < 2; ++set) {
+    const int e = set == 0 ? er : ec;
+    const int32_t *c01 = p, *ptr = c01 + 2 * n, *chunk = ptr + n + 1, *mask = chunk + e, *order = mask + 2 * (int64_t)e;
+    if (i < 2 * n && (c01[i] < -1 || c01[i] >= chunks)) report(err, 12 + 10 * set, (int)i);
+    if (i <= n) {
+      if (i == 0 && ptr[0] != 0) report(err, 13 + 10 * set, 0);
+      if (i == n && ptr[i] != e) report(err, 13 + 10 * set, (int)i);
+      if (i < n && ptr[i + 1] < ptr[i]) report(err, 14 + 10 * set, (int)i);
+      if (i < n && (order[i] < 0 || order[i] >= n)) report(err, 15 + 10 * set, (int)i);
+    }
+    if (i < e && (chunk[i] < 0 || chunk[i] >= chunks || mask[i] < 0 || mask[i] > 3)) report(err, 16 + 10 * set, (int)i);
+    p = order + n;
+  }
+}
+
+int validate(bool tiles, const int32_t* buf, int64_t len, int* code, int* pos, cudaStream_t st) {
+  if (!buf || len < 8 || !code || !pos) return fail(BSP_ERR_INVALID, "validation: NULL buffer or result pointer");
+  int* err = nullptr;
+  cudaError_t e = cudaMallocAsync(reinterpret_cast<void**>(&err), 2 * sizeof(int), st);
+  if (e == cudaSuccess) e = cudaMemsetAsync(err, 0, 2 * sizeof(int), st);
+  if (e != cudaSuccess) return fail(BSP_ERR_CUDA, "validation: scratch allocation failed: %s", cudaGetErrorString(e));
+  const int grid = (int)((len + 255) / 256);
+  if (tiles) tiles_validate_kernel<<<grid, 256, 0, st>>>(buf, len, err);
+  else meta_validate_kernel<<<grid, 256, 0, st>>>(buf, len, err);
+  int host[2] = {0, 0};
+  e = cudaMemcpyAsync(host, err, sizeof(host), cudaMemcpyDeviceToHost, st);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+  cudaFreeAsync(err, st);
+  if (e != cudaSuccess) return fail(BSP_ERR_CUDA, "validation failed to run: %s", cudaGetErrorString(e));
+  *code = host[0]; *pos = host[1];
+  if (host[0]) return fail(BSP_ERR_INVALID, "%s buffer is corrupt: check %d failed at entry %d",
+                           tiles ? "attention tile-list" : "metadata", host[0], host[1]);
+  return BSP_OK;
+}
+
 }  // namespace
 }  // namespace bsp
 
 using namespace bsp;
+
+extern "C" int bsp_meta_validate(const int32_t* meta, int64_t len, int* code, int* pos, void* stream) {
+  return validate(false, meta, len, code, pos, reinterpret_cast<cudaStream_t>(stream));
+}
+
+extern "C" int bsp_attn_tiles_validate(const int32_t* tiles, int64_t len, int* code, int* pos, void* stream) {
+  return validate(true, tiles, len, code, pos, reinterpret_cast<cudaStream_t>(stream));
+}
 
 extern "C" int64_t bsp_meta_device_capacity(int H, int Mb, int Nb) {
   if (H <= 0 || Mb <= 0 || Nb <= 0) return 0;

@@ -12,6 +12,7 @@ the reference's builders return:
 import collections
 import ctypes
 import hashlib
+import os
 
 import torch
 
@@ -145,6 +146,20 @@ def clear_cache():
     _CACHE.clear()
 
 
+DEBUG = os.environ.get('BSP_DEBUG', '') not in ('', '0')
+
+
+def validate_device_buffer(buf, tiles=False):
+    """Checks every table-derived index of a device metadata buffer (or attention tile lists)
+    against the buffer's header; raises ValueError naming the failed check.  Run on every
+    upload when BSP_DEBUG=1 is set."""
+    code, pos = ctypes.c_int(0), ctypes.c_int(0)
+    fn = _lib.lib().bsp_attn_tiles_validate if tiles else _lib.lib().bsp_meta_validate
+    with torch.cuda.device(buf.device):
+        _lib.check(fn(buf.data_ptr(), buf.numel(), ctypes.byref(code), ctypes.byref(pos),
+                      torch.cuda.current_stream(buf.device).cuda_stream))
+
+
 class Meta:
     """Execution metadata of one layout: host header + device buffer(s).  Built on the host
     (host layout) and uploaded once per device, or built on the device the layout lives on."""
@@ -171,6 +186,8 @@ class Meta:
                 self._dev[key] = self._host.to(device)
             else:
                 self._dev[key] = next(iter(self._dev.values())).to(device)
+            if DEBUG:
+                validate_device_buffer(self._dev[key])
         return self._dev[key]
 
 
@@ -231,6 +248,8 @@ class AttnTiles:
         key = str(device)
         if key not in self._dev:
             self._dev[key] = self.host.to(device)
+            if DEBUG:
+                validate_device_buffer(self._dev[key], tiles=True)
         return self._dev[key]
 
 
