@@ -159,6 +159,38 @@ def test_layout_without_blocks_gives_zeros(block):
     assert out.shape == (Z, H, N, nb * block) and float(out.abs().max()) == 0.0
 
 
+@pytest.mark.parametrize('mode', ['dsd', 'dds'])
+@pytest.mark.parametrize('ta', [False, True])
+@pytest.mark.parametrize('tb', [False, True])
+@pytest.mark.parametrize('dtype', [torch.float16, torch.float32])
+def test_free_dimension_that_is_not_a_multiple_of_the_vector_width(mode, ta, tb, dtype):
+    """The reference's kernels bounds-check the dense operand's free dimension and accept any
+    size; here an odd width / height (77 = 72 + 5) is padded and cut off again."""
+    g = torch.Generator().manual_seed(3)
+    block, H, Z, F = 16, 2, 2, 77
+    layout = (torch.rand((H, 4, 6), generator=g) > 0.4).long()
+    layout[:, 0, 0] = 1
+    sp_rows, sp_cols = 4 * block, 6 * block
+    s_ = torch.randn((Z, int(layout.sum()), block, block), generator=g).to(dtype)
+    if mode == 'dsd':                                    # C = op(S) . op(B): the free dimension is N
+        K = sp_rows if ta else sp_cols
+        d_ = torch.randn((Z, H, F, K) if tb else (Z, H, K, F), generator=g).to(dtype)
+        a, b = s_, d_
+        M = sp_cols if ta else sp_rows
+        dc = torch.randn((Z, H, M, F), generator=g).to(dtype)
+    else:                                                # C = op(A) . op(S): the free dimension is M
+        K = sp_cols if tb else sp_rows
+        d_ = torch.randn((Z, H, K, F) if ta else (Z, H, F, K), generator=g).to(dtype)
+        a, b = d_, s_
+        N = sp_rows if tb else sp_cols
+        dc = torch.randn((Z, H, F, N), generator=g).to(dtype)
+    # forward only: the gradient of the sparse operand is an sdd product whose reduction runs over
+    # this dimension and must be a multiple of 16, in the reference as here (matmul.py:318-319)
+    want_c, _, _ = dm.matmul_reference(a, b, mode, ta, tb, layout, block)
+    got = MatMul(layout, block, mode, trans_a=ta, trans_b=tb)(a.to(DEV), b.to(DEV))
+    assert_close(got, want_c, 'odd free dimension')
+
+
 def test_config1():
     c = workloads.config1()
     want, _, _ = dm.matmul_reference(c['a'], c['b'], 'sdd', True, False, c['layout'], 16)

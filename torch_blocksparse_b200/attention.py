@@ -151,10 +151,13 @@ class DeepSpeedSparseSelfAttention(nn.Module):
         return self.attend(query, key, value, float(head_dim) ** -0.5, rpe, key_padding_mask, attn_mask,
                            mask_owner=mask_owner)
 
-    def attend(self, query, key, value, scaling, rpe=None, key_padding_mask=None, attn_mask=None, mask_owner=None):
+    def attend(self, query, key, value, scaling, rpe=None, key_padding_mask=None, attn_mask=None, mask_owner=None,
+               seq_first_out=False):
         """The attention core on [bsz, heads, L, head_dim] operands with an explicit score scale
         (masks already in the dtype of the operands).  `mask_owner`: the caller's own attention
-        mask tensor when `attn_mask` was derived from it (see _is_causal)."""
+        mask tensor when `attn_mask` was derived from it (see _is_causal).  `seq_first_out`: the
+        fused kernel writes its result in [L, bsz, heads * head_dim] memory order (returned as the
+        [bsz, heads, L, head_dim] view of it)."""
         bsz, num_heads, tgt_len, head_dim = query.size()
         if key_padding_mask is not None and key_padding_mask.dtype != query.dtype:
             key_padding_mask = key_padding_mask.to(query.dtype)
@@ -172,7 +175,7 @@ class DeepSpeedSparseSelfAttention(nn.Module):
                 return fused_attention(query, key, value, sdd_nt.meta, self.block, scaling, rpe,
                                        key_padding_mask, attn_mask,
                                        self.key_padding_mask_mode, am_mode,
-                                       tiles=self.tiles[(num_heads, tgt_len)])
+                                       tiles=self.tiles[(num_heads, tgt_len)], seq_first_out=seq_first_out)
         w = sdd_nt(query, key)
         w = softmax(w, scale=scaling, rpe=rpe, key_padding_mask=key_padding_mask, attn_mask=attn_mask,
                     key_padding_mask_mode=self.key_padding_mask_mode, attn_mask_mode=self.attn_mask_mode)

@@ -99,12 +99,17 @@ def _mask_args(Z, H, L, dtype, rpe, kpm, am, kp_mode, am_mode):
 class _fused_attention(torch.autograd.Function):
 
     @staticmethod
-    def forward(ctx, q, k, v, meta, tiles, block, scale, rpe, kpm, am, kp_mode, am_mode):
+    def forward(ctx, q, k, v, meta, tiles, block, scale, rpe, kpm, am, kp_mode, am_mode, seq_first_out=False):
         _require_cuda(q, k, v)
         Z, H, L, D = q.shape
         q, k, v = _rows(q), _rows(k), _rows(v)
         margs, keep = _mask_args(Z, H, L, q.dtype, rpe, kpm, am, kp_mode, am_mode)
-        o = torch.empty((Z, H, L, D), dtype=q.dtype, device=q.device)
+        if seq_first_out:
+            # the result in [L, Z, H * D] memory order (what a sequence-first caller reshapes it to
+            # anyway), handed to the kernel through its batch / head / row strides: no copy later
+            o = torch.empty((L, Z, H, D), dtype=q.dtype, device=q.device).permute(1, 2, 0, 3)
+        else:
+            o = torch.empty((Z, H, L, D), dtype=q.dtype, device=q.device)
         lse = torch.empty((Z, H, L), dtype=torch.float32, device=q.device)
         _timed('attn_fwd', lambda: _lib.check(_lib.lib().bsp_attn_fwd(
             q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(),
@@ -128,7 +133,7 @@ class _fused_attention(torch.autograd.Function):
         Z, H, L, D = q.shape
         do = _rows(do)
         margs, _ = _mask_args(Z, H, L, q.dtype, rpe, kpm, am, kp_mode, am_mode)
-        dq, dk, dv = torch.empty_like(o), torch.empty_like(o), torch.empty_like(o)
+        dq, dk, dv = (torch.empty((Z, H, L, D), dtype=q.dtype, device=q.device) for _ in range(3))   # the kernels write these densely
         delta = torch.empty((Z, H, L), dtype=torch.float32, device=q.device)
         args = (q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), do.data_ptr(), lse.data_ptr(), delta.data_ptr(),
                 dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), _dtype_code(q), ctx.block, Z, H, L, D,
@@ -143,7 +148,7 @@ class _fused_attention(torch.autograd.Function):
         else:
             for name, part in (('attn_bwd_delta', 1), ('attn_bwd_dkdv', 2), ('attn_bwd_dq', 4)):
                 _timed(name, lambda part=part: _lib.check(L_.bsp_attn_bwd_parts(*args, part, _stream(q))))
-        return (dq, dk, dv) + (None,) * 9
+        return (dq, dk, dv) + (None,) * 10
 
 
 def _tile_args(tiles, device):
@@ -159,10 +164,10 @@ def device_status():
 
 
 def fused_attention(q, k, v, meta, block, scale, rpe=None, key_padding_mask=None, attn_mask=None,
-                    key_padding_mask_mode='add', attn_mask_mode='mul', tiles=None):
+                    key_padding_mask_mode='add', attn_mask_mode='mul', tiles=None, seq_first_out=False):
     """O = softmax(scale * Q K^T + rpe + masks, on the layout) V for [Z, H, L, D] operands."""
     if meta.H != q.size(1) or meta.Mb != meta.Nb or meta.Mb * block != q.size(2):
         raise ValueError('layout [%d,%d,%d] with block %d does not fit operands of shape %s'
                          % (meta.H, meta.Mb, meta.Nb, block, tuple(q.shape)))
     return _fused_attention.apply(q, k, v, meta, tiles, block, float(scale), rpe, key_padding_mask, attn_mask,
-                                  key_padding_mask_mode, attn_mask_mode)
+                                  key_padding_mask_mode, attn_mask_mode, seq_first_out)

@@ -131,6 +131,12 @@ class _sparse_matmul(torch.autograd.Function):
     def _dsd_matmul(a, b, trans_a, trans_b, trans_c, spdims, block, meta, bench, time):
         """matmul.py:507-552."""
         a = _prep_sparse(a, block)
+        # the kernels read the dense operand in 16-byte pieces along its free dimension: a width that
+        # is not a multiple of 8 (4 for FP32) is padded with zero columns, which are cut off again
+        n_dim = 2 if trans_b else 3
+        pad = (-b.size(n_dim)) % (4 if b.dtype == torch.float32 else 8)
+        if pad:
+            b = torch.nn.functional.pad(b, (0, pad) if n_dim == 3 else (0, 0, 0, pad))
         b, sb = _prep_dense(b)
         Z, H = b.size(0), b.size(1)
         M = block * spdims[2 if trans_a else 1]
@@ -148,11 +154,17 @@ class _sparse_matmul(torch.autograd.Function):
                 a.stride(0), 1 if trans_a else 0, sb[0], sb[1], b_sk, b_sn,
                 c.stride(0), c.stride(1), c_sm, c_sn,
                 meta.hdr.data_ptr(), meta.on(b.device).data_ptr(), _stream(b)))
+        if pad:
+            c = c[:, :, :N - pad] if trans_c else c[:, :, :, :N - pad]
         return c
 
     @staticmethod
     def _dds_matmul(a, b, trans_a, trans_b, trans_c, spdims, block, meta, bench, time):
         """matmul.py:460-505."""
+        m_dim = 3 if trans_a else 2                      # (see _dsd_matmul: zero rows up to a multiple of 8 / 4)
+        pad = (-a.size(m_dim)) % (4 if a.dtype == torch.float32 else 8)
+        if pad:
+            a = torch.nn.functional.pad(a, (0, pad) if m_dim == 3 else (0, 0, 0, pad))
         a, sa = _prep_dense(a)
         b = _prep_sparse(b, block)
         Z, H = a.size(0), a.size(1)
@@ -171,6 +183,8 @@ class _sparse_matmul(torch.autograd.Function):
                 sa[0], sa[1], a_sm, a_sk, b.stride(0), 1 if trans_b else 0,
                 c.stride(0), c.stride(1), c_sm, c_sn,
                 meta.hdr.data_ptr(), meta.on(a.device).data_ptr(), _stream(a)))
+        if pad:
+            c = c[:, :, :, :M - pad] if trans_c else c[:, :, :M - pad]
         return c
 
     fn = {'sdd': _sdd_matmul.__get__(object),

@@ -72,10 +72,13 @@ class MultiheadAttention(nn.modules.activation.MultiheadAttention):
             k = F.linear(key, self.k_proj_weight, bk)
             v = F.linear(value, self.v_proj_weight, bv)
         q = q * (float(head_dim) ** -0.5)
-        # [L, B, E] -> [B, H, L, head_dim]
-        to_heads = lambda t: t.contiguous().view(tgt_len, bsz * H, head_dim).transpose(0, 1).reshape(bsz, H, tgt_len, head_dim)
-        out = self.core.attend(to_heads(q), to_heads(k), to_heads(v), 1.0, None, key_padding_mask, attn_mask)
-        out = out.reshape(bsz * H, tgt_len, head_dim).transpose(0, 1).contiguous().view(tgt_len, bsz, embed_dim)
+        # [L, B, E] -> [B, H, L, head_dim] as views: the kernels address their operands through
+        # batch / head / row strides, so the projections are used where they lie, and the result
+        # is written in [L, B, E] order by the kernel (no transposed copies on the way in or out)
+        to_heads = lambda t: t.view(tgt_len, bsz, H, head_dim).permute(1, 2, 0, 3)
+        out = self.core.attend(to_heads(q), to_heads(k), to_heads(v), 1.0, None, key_padding_mask, attn_mask,
+                               seq_first_out=True)
+        out = out.permute(2, 0, 1, 3).reshape(tgt_len, bsz, embed_dim)
         return F.linear(out, self.out_proj.weight, self.out_proj.bias), None
 
 
