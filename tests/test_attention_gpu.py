@@ -325,6 +325,26 @@ def test_bounded_wait_expires_into_a_status_code_and_the_context_stays_usable():
     assert_close(o, want, 'forward after a timed-out launch')
 
 
+@pytest.mark.parametrize('attention', ['unidirectional', 'bidirectional'])
+def test_graphed_step_equals_the_eager_step_bit_for_bit(attention):
+    """module.graphed(): forward + backward captured in a CUDA graph (the dQ kernel on its second
+    stream included) and replayed on changed inputs gives what module(q, k, v).backward(do) gives."""
+    c = workloads.config4(attention, small=True, Z=2)
+    mod = SparseSelfAttention(layout=c['layout'], block=c['block'], fused=True)
+    q, k, v, do = (c[n].to(DEV) for n in ('q', 'k', 'v', 'do'))
+    step = mod.graphed(q, k, v, do)
+    for trial in range(2):
+        if trial == 1:                                   # new values in the same buffers
+            for t in (q, k, v, do):
+                t.copy_(torch.randn_like(t))
+        step.replay()
+        qg, kg, vg = (t.clone().requires_grad_() for t in (q, k, v))
+        o = mod(qg, kg, vg)
+        o.backward(do)
+        for name, a, b in zip(('o', 'dq', 'dk', 'dv'), (step.o, step.dq, step.dk, step.dv), (o, qg.grad, kg.grad, vg.grad)):
+            assert torch.equal(a, b), '%s differs on trial %d' % (name, trial)
+
+
 def test_sparsity_config_path_and_key_transposed():
     """The reference's constructor path: SparsityConfig 'fixed', key handed over
     pre-transposed as [.., head_dim, L] (deepspeedsparseselfattention.py:119-123)."""

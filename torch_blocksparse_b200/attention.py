@@ -118,6 +118,17 @@ class DeepSpeedSparseSelfAttention(nn.Module):
         self._causal_cache[id(key)] = (weakref.ref(key), key._version, hit)
         return hit
 
+    def graphed(self, query, key, value, dout, scale=None):
+        """Forward + backward on the given [bsz, heads, L, head_dim] buffers as one CUDA graph (see
+        fused.GraphedStep): `step = module.graphed(q, k, v, do)`, then `step.replay()` per step;
+        results in step.o, step.dq, step.dk, step.dv.  No rpe / masks."""
+        from .fused import GraphedStep
+        bsz, num_heads, tgt_len, head_dim = query.size()
+        sdd_nt, _, _ = self.get_ops(num_heads, tgt_len)
+        tiles = self.tiles.get((num_heads, tgt_len))
+        return GraphedStep(sdd_nt.meta, tiles, self.block, float(head_dim) ** -0.5 if scale is None else float(scale),
+                           query, key, value, dout)
+
     def transpose_key_for_scores(self, x, L):
         """deepspeedsparseselfattention.py:119-123: a key given as [.., hd, L] is
         viewed back as [.., L, hd]."""

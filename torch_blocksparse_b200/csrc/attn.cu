@@ -24,7 +24,8 @@ int attn_bwd_tc(const void* q, const void* k, const void* v, const void* dout, c
                 int64_t q_sz, int64_t q_sh, int64_t q_sr, int64_t k_sz, int64_t k_sh, int64_t k_sr,
                 int64_t v_sz, int64_t v_sh, int64_t v_sr, int64_t do_sz, int64_t do_sh, int64_t do_sr,
                 const int32_t* tiles_hdr, const int32_t* tiles, float scale,
-                const void* kpm, int64_t kpm_sz, int kpm_mul, int causal, int parts, const XtHost* xt, cudaStream_t st);
+                const void* kpm, int64_t kpm_sz, int kpm_mul, int causal, int parts, const XtHost* xt, int overlap,
+                cudaStream_t st);
 int tc_device_status(int* out);
 int tc_debug_wait(int wait_budget, int skip_chunk);
 int dsd_tc_device_status(int* out);
@@ -61,6 +62,14 @@ XtHost xt_of(const void* rpe, int64_t rpe_sz, int64_t rpe_sh, int64_t rpe_sr, co
 bool tma_strides(int Z, int H, int64_t sz, int64_t sh, int64_t sr) {
   return sr > 0 && (H == 1 || sh > 0) && (Z == 1 || sz > 0);
 }
+
+// Whether a backward may put its dQ kernel on a second stream (off inside bsp_attn_bwd_static).
+thread_local int g_allow_overlap = 1;
+struct NoOverlap {
+  int saved;
+  NoOverlap() : saved(g_allow_overlap) { g_allow_overlap = 0; }
+  ~NoOverlap() { g_allow_overlap = saved; }
+};
 
 constexpr int kMaxDevices = 64;
 std::mutex g_static_mutex;
@@ -203,7 +212,7 @@ extern "C" int bsp_attn_bwd_parts(const void* q, const void* k, const void* v, c
     const XtHost xt = xt_of(rpe, rpe_sz, rpe_sh, rpe_sr, am, am_sr, am_mul);
     return attn_bwd_tc(q, k, v, dout, lse, delta, dq, dk, dv, dtype, Z, H, L, D, q_sz, q_sh, q_sr, k_sz, k_sh, k_sr,
                        v_sz, v_sh, v_sr, do_sz, do_sh, do_sr, tiles_hdr, tiles, scale, kpm, kpm_sz, kpm_mul,
-                       am != nullptr && am_mul == 2, parts & 6, &xt, st);
+                       am != nullptr && am_mul == 2, parts & 6, &xt, g_allow_overlap, st);
   }
   if (dtype == BSP_F16) return attn_bwd_t<__half>(p, block, D, Z, parts, st);
   return attn_bwd_t<__nv_bfloat16>(p, block, D, Z, parts, st);
@@ -251,6 +260,8 @@ extern "C" int bsp_attn_bwd_static(const void* q, const void* k, const void* v, 
                 "use bsp_attn_bwd with caller-provided scratch", (long long)rows, BSP_ATTN_STATIC_ROWS);
   float* delta = nullptr;
   if (int rc = static_delta_address(&delta)) return rc;
+  // (one stream only: creating the second stream of bsp_attn_bwd would allocate)
+  NoOverlap guard;
   return bsp_attn_bwd_parts(q, k, v, o, dout, lse, delta, dq, dk, dv, dtype, block, Z, H, L, D,
                             q_sz, q_sh, q_sr, k_sz, k_sh, k_sr, v_sz, v_sh, v_sr, o_sz, o_sh, o_sr,
                             do_sz, do_sh, do_sr, meta_hdr, meta, tiles_hdr, tiles, scale, rpe, rpe_sz, rpe_sh, rpe_sr,

@@ -1106,6 +1106,27 @@ int xt_maps(Maps& m, TcArgs& a, const XtHost* xt, const CUtensorMap& any, int dt
   return BSP_OK;
 }
 
+// A second stream per calling thread and device, on which the dQ kernel of a backward runs
+// beside the dK / dV kernel (they are independent): the CTAs of the one fill the SMs the other
+// leaves idle in its last wave, which is most of the time when a shard is small.
+struct SideStream { cudaStream_t stream = nullptr; cudaEvent_t fork = nullptr, join = nullptr; };
+
+int side_stream(SideStream** out) {
+  constexpr int kMaxDev = 64;
+  static thread_local SideStream table[kMaxDev];
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDev) return fail(BSP_ERR_CUDA, "attention: cannot tell the current device");
+  SideStream& s = table[dev];
+  if (!s.stream) {
+    cudaError_t e = cudaStreamCreateWithFlags(&s.stream, cudaStreamNonBlocking);
+    if (e == cudaSuccess) e = cudaEventCreateWithFlags(&s.fork, cudaEventDisableTiming);
+    if (e == cudaSuccess) e = cudaEventCreateWithFlags(&s.join, cudaEventDisableTiming);
+    if (e != cudaSuccess) { s = SideStream(); return fail(BSP_ERR_CUDA, "attention: cannot create the second stream: %s", cudaGetErrorString(e)); }
+  }
+  *out = &s;
+  return BSP_OK;
+}
+
 void fill_tiles(TcArgs& a, const TilesView& tv, const TileSet& s) {
   a.tiles_per_head = tv.tiles_per_head;
   a.c01 = s.c01; a.ptr = s.ptr; a.chunk = s.chunk; a.mask = s.mask; a.sub = s.sub; a.order = s.order;
@@ -1147,7 +1168,8 @@ int attn_bwd_tc(const void* q, const void* k, const void* v, const void* dout, c
                 int64_t q_sz, int64_t q_sh, int64_t q_sr, int64_t k_sz, int64_t k_sh, int64_t k_sr,
                 int64_t v_sz, int64_t v_sh, int64_t v_sr, int64_t do_sz, int64_t do_sh, int64_t do_sr,
                 const int32_t* tiles_hdr, const int32_t* tiles, float scale,
-                const void* kpm, int64_t kpm_sz, int kpm_mul, int causal, int parts, const XtHost* xt, cudaStream_t st) {
+                const void* kpm, int64_t kpm_sz, int kpm_mul, int causal, int parts, const XtHost* xt, int overlap,
+                cudaStream_t st) {
   TilesView tv;
   if (int rc = decode_tiles(tiles_hdr, tiles, tv)) return rc;
   if (tv.H != H || tv.nb * tv.block != L) return fail(BSP_ERR_INVALID, "attention tile lists do not fit %d heads of length %d", H, L);
@@ -1162,6 +1184,16 @@ int attn_bwd_tc(const void* q, const void* k, const void* v, const void* dout, c
   a.lse = lse; a.delta = delta; a.H = H; a.L = L; a.scale = scale; a.scale_log2 = scale * kLog2eT;
   a.kpm = kpm; a.kpm_sz = kpm_sz; a.kpm_mul = kpm_mul; a.causal = causal;
   const int n_tiles = H * tv.tiles_per_head;
+  // dK / dV on the caller's stream; dQ beside it on the thread's second stream when both are
+  // asked for and the caller allows it (fork and join by events, so the caller's stream order,
+  // and a stream capture, see one backward)
+  SideStream* side = nullptr;
+  if (overlap && (parts & 6) == 6) {
+    if (int rc = side_stream(&side)) return rc;
+    cudaError_t e = cudaEventRecord(side->fork, st);
+    if (e == cudaSuccess) e = cudaStreamWaitEvent(side->stream, side->fork, 0);
+    if (e != cudaSuccess) return fail(BSP_ERR_CUDA, "attention: forking to the second stream failed: %s", cudaGetErrorString(e));
+  }
   if (parts & 2) {
     a.out0 = dk; a.out1 = dv;
     fill_tiles(a, tv, tv.ct);
@@ -1172,7 +1204,12 @@ int attn_bwd_tc(const void* q, const void* k, const void* v, const void* dout, c
     a.out0 = dq; a.out1 = nullptr;
     fill_tiles(a, tv, tv.rt);
     m.r0 = mq; m.r1 = md; m.c0 = mk; m.c1 = mv;
-    if (int rc = launch_any<DQ>(dtype, D, m, a, n_tiles, Z, st, "dQ")) return rc;
+    if (int rc = launch_any<DQ>(dtype, D, m, a, n_tiles, Z, side ? side->stream : st, "dQ")) return rc;
+  }
+  if (side) {
+    cudaError_t e = cudaEventRecord(side->join, side->stream);
+    if (e == cudaSuccess) e = cudaStreamWaitEvent(st, side->join, 0);
+    if (e != cudaSuccess) return fail(BSP_ERR_CUDA, "attention: joining the second stream failed: %s", cudaGetErrorString(e));
   }
   return BSP_OK;
 }

@@ -47,10 +47,11 @@ constexpr int kWaitBudget = 1 << 21;   // default number of try_wait attempts be
 // otherwise).  Returns false when the phase did not complete in time, or soon after the CTA
 // has failed (failed[0] != 0), so that a failed CTA drains quickly.
 BSP_DEVI bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* failed) {
+  if (mbar_try_wait(bar, parity)) return true;          // (the common case pays for nothing else)
   const int budget = failed[1];
-  for (int i = 0; i < budget; ++i) {
+  for (int i = 1; i < budget; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
-    if ((i & 255) == 255 && failed[0]) return false;
+    if ((i & 1023) == 1023 && failed[0]) return false;
   }
   failed[0] = 1;
   return false;

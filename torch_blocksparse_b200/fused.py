@@ -171,3 +171,65 @@ def fused_attention(q, k, v, meta, block, scale, rpe=None, key_padding_mask=None
                          % (meta.H, meta.Mb, meta.Nb, block, tuple(q.shape)))
     return _fused_attention.apply(q, k, v, meta, tiles, block, float(scale), rpe, key_padding_mask, attn_mask,
                                   key_padding_mask_mode, attn_mask_mode, seq_first_out)
+
+
+class GraphedStep:
+    """Forward + backward of the fused attention on fixed buffers, captured once in a CUDA graph
+    and replayed with one launch: for steady-state loops whose steps are short enough for the
+    launches themselves to matter (a small shard of a problem split over several GPUs).
+
+        step = module.graphed(q, k, v, do)      # q, k, v, do: [Z, H, L, D] device tensors, kept by the caller
+        step.replay()                            # reads q, k, v, do as they are now; fills step.o, .dq, .dk, .dv
+
+    No rpe / masks (use the module's forward for those).  The captured work is exactly what
+    module(q, k, v) followed by backward(do) launches, the dQ kernel beside the dK / dV kernel
+    included; results are bit-identical to that path."""
+
+    def __init__(self, meta, tiles, block, scale, q, k, v, do):
+        _require_cuda(q, k, v, do)
+        if not fused_supported(q, block):
+            raise NotImplementedError('graphed step: FP16 / BF16 operands with head dimension 64 or 128')
+        self.q, self.k, self.v, self.do = (_rows(t) for t in (q, k, v, do))
+        for a, b in zip((self.q, self.k, self.v, self.do), (q, k, v, do)):
+            if a is not b:
+                raise ValueError('graphed step: operands need unit stride on the last dimension, 16-byte alignment and '
+                                 'strides that are multiples of 8 elements')
+        Z, H, L, D = q.shape
+        dev = q.device
+        self.o, self.dq, self.dk, self.dv = (torch.empty((Z, H, L, D), dtype=q.dtype, device=dev) for _ in range(4))
+        self.lse = torch.empty((Z, H, L), dtype=torch.float32, device=dev)
+        self.delta = torch.empty((Z, H, L), dtype=torch.float32, device=dev)
+        self._keep = (meta, tiles)
+        L_ = _lib.lib()
+        code = _dtype_code(q)
+        st3 = lambda t: (t.stride(0), t.stride(1), t.stride(2))
+        none_masks = (None, 0, 0, 0, None, 0, 0, None, 0, 0)
+        tile_args = _tile_args(tiles, dev)
+        meta_args = (meta.hdr.data_ptr(), meta.on(dev).data_ptr())
+
+        def launch():
+            stream = torch.cuda.current_stream(dev).cuda_stream
+            _lib.check(L_.bsp_attn_fwd(
+                self.q.data_ptr(), self.k.data_ptr(), self.v.data_ptr(), self.o.data_ptr(), self.lse.data_ptr(),
+                code, block, Z, H, L, D, *st3(self.q), *st3(self.k), *st3(self.v), *st3(self.o),
+                *meta_args, *tile_args, scale, *none_masks, stream))
+            _lib.check(L_.bsp_attn_bwd(
+                self.q.data_ptr(), self.k.data_ptr(), self.v.data_ptr(), self.o.data_ptr(), self.do.data_ptr(),
+                self.lse.data_ptr(), self.delta.data_ptr(), self.dq.data_ptr(), self.dk.data_ptr(), self.dv.data_ptr(),
+                code, block, Z, H, L, D, *st3(self.q), *st3(self.k), *st3(self.v), *st3(self.o), *st3(self.do),
+                *meta_args, *tile_args, scale, *none_masks, stream))
+
+        with torch.cuda.device(dev):
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):          # once eagerly: tensor maps, second stream and kernel attributes exist
+                launch()
+            torch.cuda.current_stream().wait_stream(side)
+            torch.cuda.synchronize()
+            self.graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(self.graph):
+                launch()
+
+    def replay(self):
+        self.graph.replay()
+        return self.o
