@@ -296,10 +296,11 @@ int bsp_attn_tiles_validate(const int32_t* tiles, int64_t len, int* code, int* p
  * log2(sum_j exp(f_j)) of the pre-softmax values f, consumed by the backward.  D is 64 or 128; dtype F16 or BF16.
  * tiles / tiles_hdr: optional device copy of the buffer written by
  * bsp_attn_tiles_build and a HOST pointer to its first BSP_TILES_HEADER ints.
- * When given (lists built for this block size, no rpe; a key-padding mask is
- * accepted when kpm and kpm_sz * element size are 16-byte aligned; an
- * attention mask only with am_mul = 2) the tcgen05 + tensor-memory + TMA
- * kernels run; otherwise, or with NULL, the mma.sync kernels do.  Both give the
+ * When given (lists built for this block size; q, k, v with positive strides;
+ * rpe, key-padding mask and attention mask, where present, with 16-byte
+ * aligned bases and strides that are multiples of 8 elements) the tcgen05 +
+ * tensor-memory + TMA kernels run; otherwise, or with NULL, the mma.sync
+ * kernels do.  Both give the
  * same result within rounding.  A query row whose keys are all masked out gets
  * zeros (the reference's softmax gives NaN there).
  * am_mul = 2: the caller vouches that `am` is the lower-triangular causal mask
@@ -324,6 +325,10 @@ int bsp_attn_fwd(const void* q, const void* k, const void* v, void* o, float* ls
  * Backward of bsp_attn_fwd: dq, dk, dv from q, k, v, o, do and lse, recomputing
  * the probabilities block by block.  `delta` is caller-provided FP32 scratch of
  * Z*H*L elements (row sums of o*do).  dq/dk/dv are contiguous [Z, H, L, D].
+ * On the tcgen05 kernels the dQ kernel is launched on a second stream that the
+ * library keeps per calling thread and device (created on first use), forked
+ * from and joined to `stream` by events: work queued on `stream` after the call
+ * sees all three gradients.
  */
 int bsp_attn_bwd(const void* q, const void* k, const void* v, const void* o,
                  const void* dout, const float* lse, float* delta,
