@@ -185,6 +185,19 @@ int bsp_meta_build_device(const void* layout, int elem_bytes, int H, int Mb, int
 int bsp_attn_tiles_build(const int64_t* layout, int H, int nb, int block,
                          int32_t* out, int64_t out_cap, int64_t* total);
 
+/*
+ * bsp_attn_tiles_build on the device, for blocks 64 and 128 and at most 512
+ * blocks per side (BSP_ERR_UNSUPPORTED otherwise: build on the host): `layout`
+ * is a DEVICE pointer to [H, nb, nb] elements of elem_bytes (1, 4 or 8) bytes,
+ * `out` a DEVICE buffer of at least bsp_attn_tiles_device_capacity(H, nb, block)
+ * ints.  Its leading ints are bit-identical to the host builder's output; the
+ * BSP_TILES_HEADER header ints are copied to hdr_host when it is not NULL (the
+ * stream is then synchronised).  No counterpart in the reference.
+ */
+int64_t bsp_attn_tiles_device_capacity(int H, int nb, int block);
+int bsp_attn_tiles_build_device(const void* layout, int elem_bytes, int H, int nb, int block,
+                                int32_t* out, int64_t out_cap, int32_t* hdr_host, void* stream);
+
 /* ------------------------------------------------------------------------ */
 /* Softmax (device)                                                         */
 /* ------------------------------------------------------------------------ */

@@ -4,6 +4,7 @@ import numpy as np
 import pytest
 import torch
 
+import workloads
 from tests.util import assert_close, load_npz
 from torch_blocksparse_b200 import MatMul, Softmax, SparseSelfAttention, layouts, tables
 
@@ -114,3 +115,44 @@ def test_validation_accepts_built_buffers_and_names_the_corrupt_entry():
     bad[8 + 2 * n + (n + 1) + 1] = 10 ** 4                            # a chunk id of the row tiles
     with pytest.raises(ValueError, match='check 16 failed'):
         tables.validate_device_buffer(bad, tiles=True)
+
+
+def test_device_tile_lists_equal_host_tile_lists():
+    """Attention tile lists built on the device (greedy pairing of block-rows by similarity, one CTA
+    per head and side) against the host builder: fixtures, the benchmark layouts, random layouts
+    with odd counts, empty and identical rows, blocks 64 and 128."""
+    rng = np.random.default_rng(77)
+    cases = [(layouts.fixed(16, 128, 4, 'unidirectional'), 64), (layouts.fixed(16, 128, 4, 'bidirectional'), 64),
+             (layouts.bigbird(16, 128, 3, 3, 2, seed=0), 128), (layouts.causal_band(4, 64, 4, 1), 64),
+             (torch.zeros((2, 5, 5), dtype=torch.long), 64), (torch.ones((1, 1, 1), dtype=torch.long), 128),
+             (torch.ones((3, 7, 7), dtype=torch.long), 64)]
+    for i in range(300):
+        H, nb = int(rng.integers(1, 5)), int(rng.integers(1, 40))
+        if i % 60 == 0:
+            nb = int(rng.integers(200, 300))
+        p = rng.choice([0.0, 0.05, 0.3, 0.6, 0.95, 1.0])
+        lay = torch.from_numpy((rng.random((H, nb, nb)) < p).astype(np.int64))
+        if i % 7 == 0 and nb > 3:
+            lay[:, 2] = lay[:, 1]                                # identical rows
+        cases.append((lay, 64 if i % 3 else 128))
+    for lay, block in cases:
+        tables.clear_cache()
+        want = tables.build_attn_tiles(lay, block)
+        got = tables.build_attn_tiles_device(lay.to(DEV), block)
+        assert torch.equal(got.hdr, want.hdr), (tuple(lay.shape), block, got.hdr.tolist(), want.hdr.tolist())
+        assert torch.equal(got.on(DEV).cpu(), want.host), (tuple(lay.shape), block)
+
+
+def test_attention_with_a_device_layout_builds_everything_on_the_device():
+    tables.clear_cache()
+    c = workloads.config4('unidirectional', small=True)
+    before = dict(tables.CACHE_STATS)
+    mod = SparseSelfAttention(layout=c['layout'].to(DEV), block=c['block'], fused=True)
+    q, k, v = (c[n].to(DEV) for n in ('q', 'k', 'v'))
+    with torch.no_grad():
+        o = mod(q, k, v)
+    assert tables.CACHE_STATS['device_builds'] == before['device_builds'] + 2        # metadata and tile lists
+    assert tables.CACHE_STATS['host_builds'] == before['host_builds']
+    from oracle import dense_masked as dm
+    want = dm.attention_reference(c['q'], c['k'], c['v'], c['layout'], c['block'], c['scale'])[0]
+    assert_close(o, want, 'attention on a device layout')

@@ -39,6 +39,8 @@ _SIGNATURES = {
     'bsp_matmul_use_tcgen05': (c_int, [c_int]),
     'bsp_attn_tiles_build': (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, c_int64, _I64P]),
     'bsp_meta_build': (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, c_int64, _I64P]),
+    'bsp_attn_tiles_device_capacity': (c_int64, [c_int, c_int, c_int]),
+    'bsp_attn_tiles_build_device': (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int64, c_void_p, c_void_p]),
     'bsp_meta_validate': (c_int, [c_void_p, c_int64, _IP, _IP, c_void_p]),
     'bsp_attn_tiles_validate': (c_int, [c_void_p, c_int64, _IP, _IP, c_void_p]),
     'bsp_meta_device_capacity': (c_int64, [c_int, c_int, c_int]),

@@ -285,3 +285,236 @@ extern "C" int bsp_meta_build_device(const void* layout, int elem_bytes, int H, 
   }
   return BSP_OK;
 }
+
+// ---------------------------------------------------------------------------------------------
+// Attention tile lists (the buffer bsp_attn_tiles_build writes on the host) built on the device,
+// for blocks 64 and 128 and at most kTilesMaxNb blocks per side.  Bit-identical to the host
+// builder: per head and side (rows, columns) the block-rows are sorted by size (stable,
+// descending) and paired greedily, each with the unused later one whose nonzero set is most
+// similar (|A and B| / |A or B|, first best wins); a tile's list is the union of its two sets in
+// ascending order with a 2-bit mask per entry.  One CTA per (head, side) does the pairing; the
+// candidates of a row are scored in parallel, the rows are taken one after the other as the
+// greedy rule demands.
+// ---------------------------------------------------------------------------------------------
+namespace bsp {
+namespace {
+
+constexpr int kTilesMaxNb = 512;
+constexpr int kTilesWords = kTilesMaxNb / 64;
+
+template <typename L>
+__device__ __forceinline__ bool present(const L* lay, int nb, int side, int h, int outer, int inner) {
+  // side 0: outer = row, inner = column; side 1: outer = column, inner = row
+  const size_t r = side == 0 ? outer : inner, c = side == 0 ? inner : outer;
+  return lay[((size_t)h * nb + r) * nb + c] != 0;
+}
+
+// c01s: [2][H * nt][2] pairs; lens: [2][H * nt] list lengths
+template <typename L>
+__global__ void __launch_bounds__(256) tiles_pair_kernel(const L* __restrict__ lay, int H, int nb, int block, int nt,
+                                                         int32_t* __restrict__ c01s, int32_t* __restrict__ lens) {
+  const int h = blockIdx.x, side = blockIdx.y, tid = threadIdx.x;
+  const int words = (nb + 63) / 64;
+  __shared__ unsigned long long bits[kTilesMaxNb][kTilesWords];
+  __shared__ short size[kTilesMaxNb], order[kTilesMaxNb];
+  __shared__ unsigned char used[kTilesMaxNb];
+  __shared__ int red_inter[256], red_uni[256], red_oj[256];
+  int32_t* c01 = c01s + ((size_t)side * H * nt + (size_t)h * nt) * 2;
+  int32_t* len = lens + (size_t)side * H * nt + (size_t)h * nt;
+  for (int i = tid; i < nb; i += 256) {
+    int cnt = 0;
+    for (int w = 0; w < words; ++w) {
+      unsigned long long b = 0;
+      for (int k = 0; k < 64 && w * 64 + k < nb; ++k)
+        if (present(lay, nb, side, h, i, w * 64 + k)) { b |= 1ull << k; ++cnt; }
+      bits[i][w] = b;
+    }
+    size[i] = (short)cnt;
+    used[i] = 0;
+  }
+  __syncthreads();
+  if (block == 128) {                                 // a tile is one block-row; every block brings two chunks
+    for (int i = tid; i < nb; i += 256) { c01[2 * i] = 2 * i; c01[2 * i + 1] = 2 * i + 1; len[i] = 2 * size[i]; }
+    return;
+  }
+  for (int i = tid; i < nb; i += 256) {               // stable order by descending size
+    int pos = 0;
+    for (int y = 0; y < nb; ++y) pos += (size[y] > size[i]) || (size[y] == size[i] && y < i);
+    order[pos] = (short)i;
+  }
+  __syncthreads();
+  int tile = 0;
+  for (int oi = 0; oi < nb; ++oi) {
+    const int u = order[oi];
+    if (used[u]) continue;                            // (uniform: shared memory, read after a barrier)
+    // every thread scores its share of the later unused rows; the best is the highest
+    // |A and B| / |A or B| (two empty sets count as 1), the first in the order among equals
+    int bi = -1, bu = 1, boj = 1 << 30;
+    for (int oj = oi + 1 + tid; oj < nb; oj += 256) {
+      const int v = order[oj];
+      if (used[v]) continue;
+      int inter = 0, uni = 0;
+      for (int w = 0; w < words; ++w) {
+        inter += __popcll(bits[u][w] & bits[v][w]);
+        uni += __popcll(bits[u][w] | bits[v][w]);
+      }
+      if (uni == 0) { inter = 1; uni = 1; }
+      if (bi < 0 || inter * bu > bi * uni) { bi = inter; bu = uni; boj = oj; }      // (own candidates come in order)
+    }
+    red_inter[tid] = bi; red_uni[tid] = bu; red_oj[tid] = boj;
+    __syncthreads();
+    for (int s = 128; s > 0; s >>= 1) {
+      if (tid < s) {
+        const int ai = red_inter[tid], au = red_uni[tid], ao = red_oj[tid];
+        const int ci = red_inter[tid + s], cu = red_uni[tid + s], co = red_oj[tid + s];
+        bool take = false;
+        if (ci >= 0) {
+          if (ai < 0) take = true;
+          else {
+            const int lhs = ci * au, rhs = ai * cu;   // c better than a?
+            take = lhs > rhs || (lhs == rhs && co < ao);
+          }
+        }
+        if (take) { red_inter[tid] = ci; red_uni[tid] = cu; red_oj[tid] = co; }
+      }
+      __syncthreads();
+    }
+    const int best = red_inter[0] >= 0 ? order[red_oj[0]] : -1;
+    if (tid == 0) {
+      used[u] = 1;
+      if (best >= 0) used[best] = 1;
+      c01[2 * tile] = best < 0 ? u : min(u, best);
+      c01[2 * tile + 1] = best < 0 ? -1 : max(u, best);
+      int n = 0;
+      for (int w = 0; w < words; ++w) n += __popcll(bits[u][w] | (best >= 0 ? bits[best][w] : 0ull));
+      len[tile] = n;
+    }
+    ++tile;
+    __syncthreads();
+  }
+}
+
+// ptr arrays of both sides (exclusive scans of the list lengths), totals, header; one CTA
+__global__ void __launch_bounds__(1024) tiles_scan_kernel(const int32_t* __restrict__ lens, int H, int nb, int block, int nt,
+                                                          int fine_block, int32_t* __restrict__ out) {
+  const int n = H * nt;
+  int mx = 0;
+  int32_t* ptr_r = out + BSP_TILES_HEADER + 2 * n;
+  const int er = block_scan(lens, n, ptr_r, &mx);
+  int32_t* ptr_c = out + BSP_TILES_HEADER + (4 * (size_t)n + 1) + 3 * (size_t)er + 2 * n;
+  const int ec = block_scan(lens + n, n, ptr_c, &mx);
+  if (threadIdx.x == 0) {
+    out[0] = BSP_TILES_MAGIC; out[1] = H; out[2] = nb; out[3] = block; out[4] = nt; out[5] = er; out[6] = ec; out[7] = fine_block;
+  }
+}
+
+template <typename L>
+__global__ void tiles_fill_kernel(const L* __restrict__ lay, int H, int nb, int block, int nt,
+                                  const int32_t* __restrict__ c01s, int32_t* __restrict__ out) {
+  const int n = H * nt;
+  const int side = blockIdx.y;
+  const int ti = blockIdx.x * blockDim.x + threadIdx.x;
+  if (ti >= n) return;
+  const int er = out[5], ec = out[6];
+  const int e = side == 0 ? er : ec;
+  int32_t* base = out + BSP_TILES_HEADER + (side == 0 ? 0 : (4 * (size_t)n + 1) + 3 * (size_t)er);
+  int32_t *c01 = base, *ptr = c01 + 2 * n, *chunk = ptr + n + 1, *mask = chunk + e, *sub = mask + e;
+  const int a = c01s[((size_t)side * n + ti) * 2], b = c01s[((size_t)side * n + ti) * 2 + 1];
+  c01[2 * ti] = a; c01[2 * ti + 1] = b;
+  const int h = ti / nt;
+  int p = ptr[ti];
+  if (block == 128) {
+    const int i = a / 2;
+    for (int j = 0; j < nb; ++j)
+      if (present(lay, nb, side, h, i, j))
+        for (int c = 0; c < 2; ++c) { chunk[p] = 2 * j + c; mask[p] = 3; sub[p] = -1; ++p; }
+    return;
+  }
+  for (int j = 0; j < nb; ++j) {
+    int m = present(lay, nb, side, h, a, j) ? 1 : 0;
+    if (b >= 0 && present(lay, nb, side, h, b, j)) m |= 2;
+    if (!m) continue;
+    chunk[p] = j; mask[p] = m;
+    sub[p] = (int32_t)(((m & 1) ? 0xFFFFu : 0u) | ((m & 2) ? 0xFFFF0000u : 0u));
+    ++p;
+  }
+}
+
+// order[pos] = tile with pos = its rank in the stable sort by descending list length
+__global__ void tiles_order_kernel(int H, int nt, int32_t* __restrict__ out) {
+  const int n = H * nt;
+  const int side = blockIdx.y;
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const int er = out[5], ec = out[6];
+  const int e = side == 0 ? er : ec;
+  int32_t* base = out + BSP_TILES_HEADER + (side == 0 ? 0 : (4 * (size_t)n + 1) + 3 * (size_t)er);
+  const int32_t* ptr = base + 2 * n;
+  int32_t* order = base + 2 * n + (n + 1) + 3 * (size_t)e;
+  const int mine = ptr[i + 1] - ptr[i];
+  int pos = 0;
+  for (int y = 0; y < n; ++y) {
+    const int len = ptr[y + 1] - ptr[y];
+    pos += (len > mine) || (len == mine && y < i);
+  }
+  order[pos] = i;
+}
+
+template <typename L>
+int build_tiles(const L* lay, int H, int nb, int block, int nt, int32_t* out, int32_t* scratch, cudaStream_t st) {
+  const int n = H * nt;
+  int32_t* c01s = scratch;
+  int32_t* lens = scratch + 4 * (size_t)n;
+  tiles_pair_kernel<L><<<dim3(H, 2), 256, 0, st>>>(lay, H, nb, block, nt, c01s, lens);
+  tiles_scan_kernel<<<1, 1024, 0, st>>>(lens, H, nb, block, nt, block, out);
+  const int grid = (n + 127) / 128;
+  tiles_fill_kernel<L><<<dim3(grid, 2), 128, 0, st>>>(lay, H, nb, block, nt, c01s, out);
+  tiles_order_kernel<<<dim3(grid, 2), 128, 0, st>>>(H, nt, out);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return fail(BSP_ERR_CUDA, "device tile-list build: launch failed: %s", cudaGetErrorString(e));
+  return BSP_OK;
+}
+
+int64_t tiles_worst_case(int H, int nb, int block) {
+  const int64_t nt = block == 128 ? nb : (nb + 1) / 2, n = (int64_t)H * nt;
+  const int64_t e = block == 128 ? 2 * (int64_t)H * nb * nb : n * nb;       // entries of one side at most
+  return BSP_TILES_HEADER + 2 * (4 * n + 1) + 6 * e;
+}
+
+}  // namespace
+}  // namespace bsp
+
+extern "C" int64_t bsp_attn_tiles_device_capacity(int H, int nb, int block) {
+  if (H <= 0 || nb <= 0 || (block != 64 && block != 128)) return 0;
+  const int64_t nt = block == 128 ? nb : (nb + 1) / 2;
+  return tiles_worst_case(H, nb, block) + 6 * (int64_t)H * nt;               // + pairs and lengths of both sides
+}
+
+extern "C" int bsp_attn_tiles_build_device(const void* layout, int elem_bytes, int H, int nb, int block,
+                                           int32_t* out, int64_t out_cap, int32_t* hdr_host, void* stream) {
+  if (!layout || !out) return fail(BSP_ERR_INVALID, "device tile-list build: NULL pointer");
+  if (H <= 0 || nb <= 0) return fail(BSP_ERR_INVALID, "layout shape [%d,%d,%d] is not positive", H, nb, nb);
+  if (block != 64 && block != 128)
+    return fail(BSP_ERR_UNSUPPORTED, "device tile-list build: blocks 64 and 128 (blocks 16 and 32 are built on the host)");
+  if (nb > kTilesMaxNb) return fail(BSP_ERR_UNSUPPORTED, "device tile-list build: at most %d blocks per side (got %d)", kTilesMaxNb, nb);
+  if (elem_bytes != 1 && elem_bytes != 4 && elem_bytes != 8)
+    return fail(BSP_ERR_INVALID, "device tile-list build: layout elements of 1, 4 or 8 bytes (got %d)", elem_bytes);
+  const int64_t need = bsp_attn_tiles_device_capacity(H, nb, block);
+  if (out_cap < need)
+    return fail(BSP_ERR_CAPACITY, "device tile-list build needs a buffer of %lld ints (worst case), got %lld",
+                (long long)need, (long long)out_cap);
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const int nt = block == 128 ? nb : (nb + 1) / 2;
+  int32_t* scratch = out + tiles_worst_case(H, nb, block);
+  int rc;
+  if (elem_bytes == 8) rc = build_tiles(static_cast<const int64_t*>(layout), H, nb, block, nt, out, scratch, st);
+  else if (elem_bytes == 4) rc = build_tiles(static_cast<const int32_t*>(layout), H, nb, block, nt, out, scratch, st);
+  else rc = build_tiles(static_cast<const uint8_t*>(layout), H, nb, block, nt, out, scratch, st);
+  if (rc) return rc;
+  if (hdr_host) {
+    cudaError_t e = cudaMemcpyAsync(hdr_host, out, BSP_TILES_HEADER * sizeof(int32_t), cudaMemcpyDeviceToHost, st);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+    if (e != cudaSuccess) return fail(BSP_ERR_CUDA, "device tile-list build: reading the header failed: %s", cudaGetErrorString(e));
+  }
+  return BSP_OK;
+}

@@ -19,8 +19,9 @@ from .matmul import _dtype_code, _require_cuda, _stream
 # benchmark to time each kernel inside a full step; None costs nothing.
 PROFILE = None
 
-# Kernel family of the unmasked FP16 / BF16 case on block 64 / 128: 'tc' (tcgen05,
-# tensor memory, TMA) or 'mma' (mma.sync).  Everything else always runs on 'mma'.
+# Kernel family: 'tc' (tcgen05, tensor memory, TMA; FP16 / BF16, head dimension 64 / 128, layouts
+# for which tile lists exist, operands and masks TMA can describe) or 'mma' (mma.sync).  What 'tc'
+# does not cover always runs on 'mma'; the library decides per call.
 PATH = 'tc'
 
 KERNELS_PER_FWD = 1

@@ -237,20 +237,57 @@ def build_meta(layout):
 
 
 class AttnTiles:
-    """Tile lists of the tcgen05 attention kernels: host header + device buffer."""
+    """Tile lists of the tcgen05 attention kernels: host header + device buffer(s).  Built on the
+    host and uploaded once per device, or built on the device the layout lives on."""
 
-    def __init__(self, host):
-        self.host = host
-        self.hdr = host[:8].clone()
+    def __init__(self, host=None, hdr=None, dev=None):
+        self._host = host
+        self.hdr = host[:8].clone() if hdr is None else hdr
         self._dev = {}
+        if dev is not None:
+            self._dev[str(dev.device)] = dev
+
+    @property
+    def host(self):
+        if self._host is None:
+            self._host = next(iter(self._dev.values())).cpu()
+        return self._host
 
     def on(self, device):
-        key = str(device)
+        key = str(torch.device(device)) if not isinstance(device, str) else device
         if key not in self._dev:
             self._dev[key] = self.host.to(device)
             if DEBUG:
                 validate_device_buffer(self._dev[key], tiles=True)
         return self._dev[key]
+
+
+TILES_DEVICE_MAX_BLOCKS = 512
+
+
+def build_attn_tiles_device(layout, block):
+    """Builds the tile lists on the device `layout` lives on (blocks 64 and 128, at most 512
+    blocks per side): only the 8-int header comes back to the host."""
+    if not layout.is_cuda or layout.dim() != 3 or layout.size(1) != layout.size(2):
+        raise ValueError('build_attn_tiles_device: a square [H, nb, nb] CUDA tensor is required')
+    lay = layout
+    if lay.dtype == torch.bool:
+        lay = lay.view(torch.uint8)
+    if lay.element_size() not in (1, 4, 8) or lay.is_floating_point():
+        lay = (layout != 0).view(torch.uint8)
+    lay = lay.contiguous()
+    H, nb, _ = lay.shape
+    L = _lib.lib()
+    cap = L.bsp_attn_tiles_device_capacity(H, nb, block)
+    hdr = torch.zeros(8, dtype=torch.int32)
+    with torch.cuda.device(lay.device):
+        out = torch.empty(max(cap, 8), dtype=torch.int32, device=lay.device)
+        _lib.check(L.bsp_attn_tiles_build_device(lay.data_ptr(), lay.element_size(), H, nb, block, out.data_ptr(), cap,
+                                                 hdr.data_ptr(), torch.cuda.current_stream(lay.device).cuda_stream))
+    n = H * int(hdr[4])
+    total = 8 + 2 * (4 * n + 1) + 3 * int(hdr[5]) + 3 * int(hdr[6])
+    CACHE_STATS['device_builds'] += 1
+    return AttnTiles(hdr=hdr, dev=out[:total].clone())
 
 
 def build_attn_tiles(layout, block):
@@ -264,11 +301,13 @@ def build_attn_tiles(layout, block):
         return None
 
     def build():
-        lay, H, Mb, Nb = _layout_i64(layout)
+        if layout.is_cuda and block >= 64 and Mb <= TILES_DEVICE_MAX_BLOCKS:
+            return build_attn_tiles_device(layout, block)
+        lay, H, Mb_, Nb_ = _layout_i64(layout)
         L = _lib.lib()
 
         def call(ptr, cap, total):
-            return L.bsp_attn_tiles_build(lay.data_ptr(), H, Mb, block, ptr, cap, total)
+            return L.bsp_attn_tiles_build(lay.data_ptr(), H, Mb_, block, ptr, cap, total)
 
         return AttnTiles(_two_pass(call).clone())
     return _cached('tiles', layout, (block,), build)
