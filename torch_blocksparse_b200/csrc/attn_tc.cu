@@ -732,7 +732,6 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
       const float my_b = (KPM && MODE == DKV && row_ok)
           ? kpm_term(static_cast<float>(reinterpret_cast<const T*>(a.kpm)[z * a.kpm_sz + grow]), a.kpm_mul) : 0.f;
       const float my_d = (MODE == DQ && row_ok) ? a.delta[zh + grow] : 0.f;
-      const float my_ds = my_d * a.scale;
       const float2 nd2 = f2(-my_d, -my_d), sl2 = f2(a.scale_log2, a.scale_log2);
       for (int t = 0; ok && t < ntiles; ++t) {
         const uint32_t ts = tmem + (t % NBUF) * C::SCORE_COLS + lane_base + chalf * 32;
@@ -897,14 +896,14 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
               if (MODE == DKV) {                            // per-query lse and delta * scale of this chunk
                 const float4 lv = vec[hv * 4 + i / 4], ev = vec[16 + hv * 4 + i / 4];
                 ls[0] = lv.x; ls[1] = lv.y; ls[2] = lv.z; ls[3] = lv.w;
-                es[0] = ev.x * a.scale; es[1] = ev.y * a.scale; es[2] = ev.z * a.scale; es[3] = ev.w * a.scale;
+                es[0] = ev.x; es[1] = ev.y; es[2] = ev.z; es[3] = ev.w;
                 if (KPM || FINE) {
 #pragma unroll
                   for (int j = 0; j < 4; ++j) ls[j] = ls[j] == kNegInfT ? -kNegInfT : ls[j] - my_b;
                 }
               } else {
 #pragma unroll
-                for (int j = 0; j < 4; ++j) { ls[j] = my_lse; es[j] = my_ds; }
+                for (int j = 0; j < 4; ++j) { ls[j] = my_lse; es[j] = my_d; }
                 if constexpr (KPM) {                        // bias of the four keys
                   const uint2 raw = *reinterpret_cast<const uint2*>(stg + (t % ST) * C::STAGE + 2 * C::CH_BYTES + chalf * 64 + (hv * 16 + i) * 2);
                   const float2 b01 = unpack16<T>(raw.x), b23 = unpack16<T>(raw.y);
@@ -920,14 +919,15 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
                   ls[j] -= MODE == DKV ? xt_term<T>(xt, a.has_rpe, a.am_mode, half, cc + j, trow & 63)
                                        : xt_term<T>(xt, a.has_rpe, a.am_mode, half, trow & 63, cc + j);
               }
-              float pv[4], dv[4];
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                pv[j] = fast_exp2(fmaf(__uint_as_float(sr[i + j]), a.scale_log2, -ls[j]));
-                dv[j] = pv[j] * fmaf(__uint_as_float(qr[i + j]), a.scale, -es[j]);     // P (dP - delta) scale
-              }
-              pr[i / 2] = pack16<T>(pv[0], pv[1]); pr[i / 2 + 1] = pack16<T>(pv[2], pv[3]);
-              dr[i / 2] = pack16<T>(dv[0], dv[1]); dr[i / 2 + 1] = pack16<T>(dv[2], dv[3]);
+              // two elements per instruction: the negated exponent lse - s c, P = 2^-(that), and
+              // dS = P (dP - delta); the score scale is applied when dQ / dK are written
+              const float2 nsl2 = f2(-a.scale_log2, -a.scale_log2), m1 = f2(-1.f, -1.f);
+              const float2 p0 = exp2_pair<-1>(__ffma2_rn(u2f(sr[i], sr[i + 1]), nsl2, f2(ls[0], ls[1])));
+              const float2 p1 = exp2_pair<-1>(__ffma2_rn(u2f(sr[i + 2], sr[i + 3]), nsl2, f2(ls[2], ls[3])));
+              const float2 d0 = __fmul2_rn(p0, __ffma2_rn(f2(es[0], es[1]), m1, u2f(qr[i], qr[i + 1])));
+              const float2 d1 = __fmul2_rn(p1, __ffma2_rn(f2(es[2], es[3]), m1, u2f(qr[i + 2], qr[i + 3])));
+              pr[i / 2] = pack16<T>(p0.x, p0.y); pr[i / 2 + 1] = pack16<T>(p1.x, p1.y);
+              dr[i / 2] = pack16<T>(d0.x, d0.y); dr[i / 2 + 1] = pack16<T>(d1.x, d1.y);
             }
           } else {
 #pragma unroll
@@ -946,8 +946,8 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
           // the two threads of a row split the D output columns
           const uint32_t ta = tmem + C::ACC_BASE + lane_base;
           T* o0 = reinterpret_cast<T*>(a.out0) + (zh + grow) * D;
-          // (the variants that form dS without the score scale apply it here)
-          const float ds_scale = (C::ER || C::ER2) ? a.scale : 1.f;
+          // (dS is formed without the score scale, which is applied here)
+          const float ds_scale = a.scale;
           if (MODE == DQ) {
             store_acc<T>(o0, ta, chalf * (D / 2), D / 2, ds_scale);
           } else {
