@@ -307,7 +307,7 @@ def attention_section(name, c, dev, steps, pk, T, dtype_name):
             'gpu_launches': steps * 4}
 
 
-def matmul_bench(dev, pk, iters=10, z=8):
+def matmul_bench(dev, pk, iters=10, z=8, section='all'):
     """Block-sparse MatMul: configuration 1 (sdd FP32 block 16), configuration 2 (dsd / dds, FP16,
     block 32, Z=8, H=8, 2048^3, layout Bernoulli(0.25)) forward and forward + backward, and blocks
     64 / 128 on a compute-bound shape; TFLOP/s on nonzero-block FLOPs."""
@@ -327,6 +327,8 @@ def matmul_bench(dev, pk, iters=10, z=8):
         torch.cuda.synchronize()
         return e0.elapsed_time(e1) / iters * 1e-3
 
+    if section == 'large':
+        return large_blocks_bench(dev, pk, timed, out)
     c1 = workloads.config1()
     op = MatMul(c1['layout'], 16, 'sdd', trans_a=True, trans_b=False)
     a, b = c1['a'].to(dev), c1['b'].to(dev)
@@ -361,11 +363,18 @@ def matmul_bench(dev, pk, iters=10, z=8):
                 torch.cuda.empty_cache()
     best = max(out['cases'], key=lambda e: e['fwd_tflops'])
     worst = min(out['cases'], key=lambda e: e['fwd_tflops'])
-    out['roofline'] = {'bound': 'tensor', 'kernel': 'dsd_kernel (block 32)', 'achieved': worst['fwd_tflops'],
+    out['roofline'] = {'bound': 'tensor', 'kernel': 'dsd_tc_kernel (block 32)', 'achieved': worst['fwd_tflops'],
                        'achieved_best': best['fwd_tflops'], 'peak': peak_tf, 'unit': UNIT,
                        'frac': worst['fwd_tflops'] / peak_tf, 'traffic': None,
                        'peak_source': pk['source'] + ' (bf16 dense, burst)'}
+    if section == 'config2':
+        return out
+    return large_blocks_bench(dev, pk, timed, out)
 
+
+def large_blocks_bench(dev, pk, timed, out):
+    from torch_blocksparse_b200 import MatMul
+    peak_tf = pk['bf16_tflops']
     # blocks 64 and 128 (the tcgen05 kernels) on a compute-bound shape: Z=2, H=8, M=N=K=4096,
     # layout Bernoulli(0.25), forward only, every mode, plain and one transposed variant
     out['large_blocks'] = {'workload': 'sdd / dsd / dds FP16, block 64 and 128, Z=2, H=8, M=N=K=4096, Bernoulli(0.25) layout, forward',
@@ -577,7 +586,7 @@ def run_ours(args):
     T = Timing(dev, world)
     if args.only_matmul:
         if rank == 0:
-            print(json.dumps({'matmul': matmul_bench(dev, pk, iters=max(1, args.steps), z=args.z)}))
+            print(json.dumps({'matmul': matmul_bench(dev, pk, iters=max(1, args.steps), z=args.z, section=args.matmul_section)}))
         return
     if args.only_softmax:
         if rank == 0:
@@ -737,6 +746,8 @@ def main():
     ap.add_argument('--no-secondary', action='store_true', help='N > 1: skip the head-split and weak-scaling runs')
     ap.add_argument('--only-softmax', action='store_true', help='run only the softmax section (profiling aid)')
     ap.add_argument('--only-matmul', action='store_true', help='run only the MatMul section')
+    ap.add_argument('--matmul-section', choices=['all', 'config2', 'large'], default='all',
+                    help='with --only-matmul: configuration 1 + 2 only, or blocks 64 / 128 only (profiling aid)')
     ap.add_argument('--z', type=int, default=Z_TOTAL, help='batch entries of the problem; anything but 8 is a reduced, '
                     'non-headline workload (profiling aid) and is flagged in the output')
     ap.add_argument('--no-cpu-baseline', action='store_true')

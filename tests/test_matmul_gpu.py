@@ -232,17 +232,17 @@ def test_config2_full_slice(mode, ta, tb):
 @pytest.mark.parametrize('mode', ['dsd', 'dds'])
 @pytest.mark.parametrize('ta', [False, True])
 @pytest.mark.parametrize('tb', [False, True])
-@pytest.mark.parametrize('block', [64, 128])
-@pytest.mark.parametrize('dtype', [torch.float16, torch.bfloat16])
-def test_dsd_dds_tcgen05_kernel(mode, ta, tb, block, dtype):
-    """Block 64 / 128: the products whose sparse operand is taken untransposed run on the
-    tcgen05 kernel, the others on mma.sync.  An odd number of block-rows at block 64 (a tile
-    with one block-row only), a block-row and a block-column without blocks; checked against
-    the dense-masked oracle and against the mma.sync kernels on the same inputs."""
+@pytest.mark.parametrize('block', [32, 64, 128])
+@pytest.mark.parametrize('dtype,width', [(torch.float16, 256), (torch.bfloat16, 384)])
+def test_dsd_dds_tcgen05_kernel(mode, ta, tb, block, dtype, width):
+    """Block 32 / 64 / 128 on the tcgen05 kernel, result tiles 256 and 128 wide.  A number of
+    block-rows that does not fill the last tile (block 32: three of four, block 64: one of two), a
+    block-row and a block-column without blocks, an odd number of columns in a tile's union;
+    checked against the dense-masked oracle and against the mma.sync kernels on the same inputs."""
     from torch_blocksparse_b200 import _lib, fused
     Z, H, K = 2, 2, 384
-    big = 5 * 64 if block == 64 else 384                      # extent of the sparse operand's non-K side
-    M, N = (big, 256) if mode == 'dsd' else (256, big)
+    big = {32: 7 * 32, 64: 5 * 64, 128: 384}[block]           # extent of the sparse operand's non-K side
+    M, N = (big, width) if mode == 'dsd' else (width, big)
     g = torch.Generator().manual_seed(block + 3)
     AS = (K, M) if ta else (M, K)
     BS = (N, K) if tb else (K, N)
@@ -271,16 +271,17 @@ def test_dsd_dds_tcgen05_kernel(mode, ta, tb, block, dtype):
 
 @pytest.mark.parametrize('ta', [False, True])
 @pytest.mark.parametrize('tb', [False, True])
-@pytest.mark.parametrize('block', [64, 128])
+@pytest.mark.parametrize('block', [32, 64, 128])
 @pytest.mark.parametrize('dtype', [torch.float16, torch.bfloat16])
 def test_sdd_tcgen05_kernel(ta, tb, block, dtype):
-    """Block 64 / 128 with K a multiple of 64: sdd on the tcgen05 kernel, every transpose (K- and
-    MN-major tiles of both operands).  An odd number of block-rows and of block-columns at block
-    64, a block-row and a block-column without blocks, rows with one block; checked against the
-    dense-masked oracle and against the mma.sync kernel on the same inputs."""
+    """Block 32 / 64 / 128 with K a multiple of 64: sdd on the tcgen05 kernel, every transpose (K-
+    and MN-major tiles of both operands).  Numbers of block-rows and of block-columns that do not
+    fill the last tile / column group at block 32 and 64, a block-row and a block-column without
+    blocks, rows with one block; checked against the dense-masked oracle and against the mma.sync
+    kernel on the same inputs."""
     from torch_blocksparse_b200 import _lib, fused
     Z, H, K = 2, 2, 192
-    M, N = (5 * 64, 7 * 64) if block == 64 else (384, 256)
+    M, N = {32: (7 * 32, 13 * 32), 64: (5 * 64, 7 * 64), 128: (384, 256)}[block]
     g = torch.Generator().manual_seed(block + 11)
     layout = (torch.rand((H, M // block, N // block), generator=g) > 0.5).long()
     layout[1, 1, :] = 0

@@ -1,6 +1,6 @@
 // Block-sparse dsd (and, through the transposed problem, dds) on the Blackwell tensor
-// path for block 64 and 128: tcgen05.mma with the accumulator in tensor memory,
-// operands brought in by TMA.
+// path for block 32, 64 and 128: tcgen05.mma with the accumulator in tensor memory,
+// operands brought in by TMA, persistent CTAs.
 //
 // Same contract as the mma.sync kernel of dsd_impl.cuh (which replaces the launch of
 // torch_blocksparse/matmul.py:498-504, 545-551): C[rows of a block-row] = sum over the
@@ -8,19 +8,28 @@
 // operand is used as stored (K-major A tiles) or transposed (MN-major A tiles, lists from the
 // CSC side of the metadata).
 //
-// Geometry: every MMA has M = 128.  A CTA owns 128 rows of C (one block-row for block 128,
-// block-rows 2i and 2i + 1 for block 64) and 128 columns, and walks "stages" of K = 64:
-//   block 128  the two halves of every nonzero block of the row;
-//   block 64   the union of the two rows' column blocks, in column order; the half of the
-//              A tile whose row has no block there is filled with zeros by an out-of-range
-//              TMA box.
-// A stage is 16 KB of A (128 rows x 64 k, K-major) and 16 KB of the dense operand (64 k x
-// 128 n), one N = 128 MMA per K-step: n contiguous -> MN-major B (two 64-wide groups, 8 KB
-// apart, in one descriptor); k contiguous -> K-major B.
+// Geometry: every MMA has M = 128.  A tile is 128 rows of C (one block-row for block 128, two
+// for block 64, four for block 32) by TN = 256 columns (128 when the width is no multiple of
+// 256).  The block-rows of a tile are walked together, in column order, over the UNION of
+// their column lists; the piece of the A tile whose row has no block in a column is zero.  A
+// "stage" of the operand ring covers K = 64:
+//   block 128  one half of a nonzero block;
+//   block 64   one column of the union;
+//   block 32   two columns of the union (two sub-tiles of K = 32, 64-byte swizzle; the second
+//              may be absent at the end of a tile).
+// A stage holds 16 KB of A and 64 x TN elements of the dense operand.  Pieces of A that are
+// zero are not loaded when the stage's piece already holds zeros (the ring is cleared once at
+// the start and the loading thread tracks which pieces hold a block); otherwise a TMA box that
+// lies past the last block fills them with zeros.
 //
-// Warps: 0-3 write the result back (tensor memory -> registers -> global), 4 issues the TMA
-// loads (one thread), 5 issues the MMAs (one thread).  mbarriers only; every wait is bounded
-// (tc.cuh) and a wait that expires sets the device status word of the tcgen05 kernels.
+// One CTA per SM walks tiles blockIdx.x, blockIdx.x + gridDim.x, ... (row tiles fastest, so
+// that the CTAs that run together share the dense panel in L2).  Two accumulators in tensor
+// memory: the write-back of a tile overlaps the products of the next one, and the operand
+// ring runs on across tile boundaries.
+//
+// Warps: 0-3 write the result back (tensor memory -> registers -> global), 4 loads the sparse
+// operand, 5 issues the MMAs, 6 loads the dense operand (one thread each).  mbarriers only;
+// every wait is bounded (tc.cuh) and a wait that expires sets the device status word.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include "common.h"
@@ -37,159 +46,310 @@ namespace {
 using namespace tc;
 using namespace mmtc;
 
-constexpr int kTN = 128;          // columns of C per CTA
-constexpr int kStages = 3;
-constexpr int kStageBytes = 32768;
-constexpr int kSmem = kStages * kStageBytes + 1024;
-constexpr int kThreads = 192;
+constexpr int kThreads = 224;
+constexpr int kStageA = 16384;
+constexpr int kFirst = 1, kLast = 2, kEnd = 4, kHalf = 8;   // stage flags
+constexpr int kNone = 0x7fffffff;
+
+template <int TN> struct Geo {
+  static constexpr int kStageB = 64 * TN * 2;
+  static constexpr int kStage = kStageA + kStageB;
+  static constexpr int kStages = TN == 256 ? 4 : 6;
+  static constexpr int kSmem = kStages * kStage + 1024;
+};
 
 struct DsdTcArgs {
   void* c;
   int64_t c_sz, c_sh, c_sm, c_sn;
   int H, Mb, block, rows_total, nnz_rows;   // rows_total = Mb * block; nnz_rows = nnz * block (first out-of-range row of S)
-  int tiles_per_head;
+  int tiles_per_head, n_tiles, total_tiles;
   const int32_t *row_ptr, *blk_col;          // lists of a block-row of op(S): CSR of the layout, or (transposed use) its CSC
   const int32_t* blk_id;                     // storage index of every list entry (NULL: the entry's own position)
+};
+
+BSP_DEVI void tma_load_5d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1, int c2, int c3, int c4) {
+  asm volatile("cp.async.bulk.tensor.5d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
+               ::"r"(saddr(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(saddr(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4)
+               : "memory");
+}
+
+struct Tile { int tr, nt, h, z; };
+BSP_DEVI Tile tile_of(const DsdTcArgs& a, int t) {
+  Tile c;
+  c.tr = t % a.tiles_per_head; t /= a.tiles_per_head;
+  c.nt = t % a.n_tiles; t /= a.n_tiles;
+  c.h = t % a.H;
+  c.z = t / a.H;
+  return c;
+}
+
+// The block-rows of one tile walked together in column order.
+struct Walk {
+  int i[4], e[4], c[4];
+  BSP_DEVI void init(const DsdTcArgs& a, int h, int tr, int R) {
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+      const int br = tr * R + r;
+      i[r] = e[r] = 0;
+      if (r < R && br < a.Mb) { i[r] = a.row_ptr[h * a.Mb + br]; e[r] = a.row_ptr[h * a.Mb + br + 1]; }
+      c[r] = i[r] < e[r] ? a.blk_col[i[r]] : kNone;
+    }
+  }
+  BSP_DEVI bool done() const { return (c[0] & c[1] & c[2] & c[3]) == kNone; }
+  // Next column of the union; id[r] = storage index of row r's block there, or -1.
+  BSP_DEVI int next(const DsdTcArgs& a, int (&id)[4]) {
+    int col = min(min(c[0], c[1]), min(c[2], c[3]));
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+      id[r] = -1;
+      if (c[r] == col) {
+        id[r] = a.blk_id ? a.blk_id[i[r]] : i[r];
+        ++i[r];
+        c[r] = i[r] < e[r] ? a.blk_col[i[r]] : kNone;
+      }
+    }
+    return col;
+  }
 };
 
 // B_KMAJOR: the dense operand has k contiguous ([n][k] in memory); else n contiguous ([k][n]).
 // C_ROWS: the result has unit stride along n (a thread writes its row with 16-byte stores);
 // else unit stride along m (the transposed problem of dds: lanes write neighbouring addresses).
-// A_MN: the sparse operand is used transposed: a stored block [k][m] is an MN-major A tile, two
-// groups of 64 m each holding 64 k-rows of 128 bytes (the second group 8 KB after the first).
-template <typename T, bool A_MN, bool B_KMAJOR, bool C_ROWS>
-__global__ void __launch_bounds__(kThreads, 2)
+// A_MN: the sparse operand is used transposed: a stored block [k][m] is an MN-major A tile.
+template <typename T, int TN, bool A_MN, bool B_KMAJOR, bool C_ROWS>
+__global__ void __launch_bounds__(kThreads, 1)
 dsd_tc_kernel(const __grid_constant__ CUtensorMap m_s, const __grid_constant__ CUtensorMap m_b, DsdTcArgs a) {
+  using G = Geo<TN>;
+  constexpr int S = G::kStages;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = smem_raw + ((1024 - (saddr(smem_raw) & 1023)) & 1023);
-  __shared__ uint64_t bar_full[kStages], bar_empty[kStages], bar_done;
+  __shared__ uint64_t bar_full[S], bar_empty[S], bar_acc_full[2], bar_acc_empty[2];
   __shared__ uint32_t tmem_slot;
-  __shared__ int n_stages, failed[2];
+  __shared__ int failed[2];
+  __shared__ volatile int stage_flags[S];
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int tile = blockIdx.x, n0 = blockIdx.y * kTN, z = blockIdx.z;
-  const int h = tile / a.tiles_per_head, tr = tile % a.tiles_per_head;
   const int block = a.block;
-  // block-rows of this tile and their nonzero lists (CSR order = storage order of the blocks)
-  const int r0 = block == 128 ? tr : 2 * tr;
-  const int r1 = (block == 64 && 2 * tr + 1 < a.Mb) ? 2 * tr + 1 : -1;
-  const int p0 = a.row_ptr[h * a.Mb + r0], e0 = a.row_ptr[h * a.Mb + r0 + 1];
-  const int p1 = r1 >= 0 ? a.row_ptr[h * a.Mb + r1] : 0, e1 = r1 >= 0 ? a.row_ptr[h * a.Mb + r1 + 1] : 0;
+  const int R = 128 / block;
 
   if (tid == 0) {
     failed[0] = 0;
     failed[1] = kWaitBudget;
-    for (int s = 0; s < kStages; ++s) { mbar_init(&bar_full[s], 1); mbar_init(&bar_empty[s], 1); }
-    mbar_init(&bar_done, 1);
+    for (int s = 0; s < S; ++s) { mbar_init(&bar_full[s], 2); mbar_init(&bar_empty[s], 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(&bar_acc_full[b], 1); mbar_init(&bar_acc_empty[b], 4); }
     mbar_init_fence();
-    int n = 0;
-    if (block == 128) {
-      n = 2 * (e0 - p0);
-    } else {                                   // size of the union of the two column lists
-      int i = p0, j = p1;
-      while (i < e0 || j < e1) {
-        const int ci = i < e0 ? a.blk_col[i] : 0x7fffffff, cj = j < e1 ? a.blk_col[j] : 0x7fffffff;
-        if (ci <= cj) ++i;
-        if (cj <= ci) ++j;
-        ++n;
-      }
-    }
-    n_stages = n;
   }
-  if (warp == 1) { tmem_alloc(&tmem_slot, kTN); tmem_relinquish(); }
+  if (warp == 1) { tmem_alloc(&tmem_slot, 2 * TN); tmem_relinquish(); }
+  // the A part of every stage starts as zeros (see the loading thread)
+  for (int i = tid; i < S * (kStageA / 16); i += kThreads)
+    reinterpret_cast<uint4*>(smem + (i / (kStageA / 16)) * G::kStage)[i % (kStageA / 16)] = make_uint4(0, 0, 0, 0);
+  fence_async_smem();
   fence_before();
   __syncthreads();
   fence_after();
   const uint32_t tmem = tmem_slot;
-  const int ns = n_stages;
   volatile int* fl = failed;
 
   if (warp == 4) {
-    // ------------------------------------------------------------------ TMA producer
-    if (lane == 0 && ns > 0) {
-      prefetch_map(&m_s); prefetch_map(&m_b);
-      int i = p0, j = p1;
-      for (int it = 0; it < ns; ++it) {
-        const int s = it % kStages;
-        if (it >= kStages && !mbar_wait(&bar_empty[s], ((it / kStages) - 1) & 1, fl)) break;
-        unsigned char* sp = smem + s * kStageBytes;
-        int krow;                               // first row of the dense operand for this stage
-        mbar_expect_tx(&bar_full[s], kStageBytes);
-        if (block == 128) {
-          const int e = p0 + (it >> 1), kh = it & 1;
-          const int bid = a.blk_id ? a.blk_id[e] : e;
-          if (A_MN) {                               // rows kh * 64 .. of the stored block, its two halves of 64 columns
-            tma_load_3d(sp, &m_s, &bar_full[s], 0, bid * 128 + kh * 64, z);
-            tma_load_3d(sp + 8192, &m_s, &bar_full[s], 64, bid * 128 + kh * 64, z);
+    // ------------------------------------------------------------------ sparse operand
+    if (lane == 0) {
+      prefetch_map(&m_s);
+      uint64_t dirty = 0;                       // 8 bits per stage: which pieces of its A part hold a block
+      int it = 0;
+      bool ok = true;
+      Walk w;
+      for (int t = blockIdx.x; ok && t < a.total_tiles; t += gridDim.x) {
+        const Tile tc_ = tile_of(a, t);
+        w.init(a, tc_.h, tc_.tr, R);
+        int flags = kFirst;
+        int kh = 0, id[4];
+        while (ok && (kh || !w.done())) {
+          const int s = it % S;
+          if (it >= S && !mbar_wait(&bar_empty[s], ((it / S) - 1) & 1, fl)) { ok = false; break; }
+          unsigned char* sp = smem + s * G::kStage;
+          if (block == 128) {
+            if (!kh) w.next(a, id);
+            if (kh && w.done()) flags |= kLast;
+            stage_flags[s] = flags;
+            mbar_expect_tx(&bar_full[s], kStageA);
+            if (A_MN) {                               // rows kh * 64 .. of the stored block, its two halves of 64 columns
+              tma_load_3d(sp, &m_s, &bar_full[s], 0, id[0] * 128 + kh * 64, tc_.z);
+              tma_load_3d(sp + 8192, &m_s, &bar_full[s], 64, id[0] * 128 + kh * 64, tc_.z);
+            } else {
+              tma_load_3d(sp, &m_s, &bar_full[s], kh * 64, id[0] * 128, tc_.z);
+            }
+            kh ^= 1;
           } else {
-            tma_load_3d(sp, &m_s, &bar_full[s], kh * 64, bid * 128, z);
+            // pieces: block 64: row r at r * 8 KB; block 32: sub-tile u at u * 8 KB, row r at r * 2 KB
+            const uint32_t was = (uint32_t)(dirty >> (8 * s)) & 0xffu;
+            uint32_t now = 0, load = 0;
+            int row[8];
+            const int U = block == 64 ? 1 : 2;
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+              if (u < U) {
+                if (u == 1 && w.done()) { flags |= kHalf; now |= was & 0xf0u; break; }
+                w.next(a, id);
+#pragma unroll
+                for (int r = 0; r < 4; ++r) {
+                  const int p = u * 4 + r;
+                  row[p] = a.nnz_rows;
+                  if (id[r] >= 0) { row[p] = id[r] * block; now |= 1u << p; load |= 1u << p; }
+                  else if (was & (1u << p)) load |= 1u << p;
+                }
+              }
+            }
+            if (w.done()) flags |= kLast;
+            dirty = (dirty & ~(0xffull << (8 * s))) | ((uint64_t)now << (8 * s));
+            stage_flags[s] = flags;
+            const int piece = block == 64 ? 8192 : 2048;
+            mbar_expect_tx(&bar_full[s], __popc(load) * piece);
+#pragma unroll
+            for (int p = 0; p < 8; ++p)
+              if (load & (1u << p))
+                tma_load_3d(sp + (block == 64 ? p * 8192 : (p >> 2) * 8192 + (p & 3) * 2048), &m_s, &bar_full[s], 0, row[p], tc_.z);
           }
-          krow = a.blk_col[e] * 128 + kh * 64;
-        } else {
-          const int ci = i < e0 ? a.blk_col[i] : 0x7fffffff, cj = j < e1 ? a.blk_col[j] : 0x7fffffff;
-          const int col = ci < cj ? ci : cj;
-          // a row without a block in this column gets zeros: the box lies past the last block
-          tma_load_3d(sp, &m_s, &bar_full[s], 0, ci == col ? (a.blk_id ? a.blk_id[i] : i) * 64 : a.nnz_rows, z);
-          tma_load_3d(sp + 8192, &m_s, &bar_full[s], 0, cj == col ? (a.blk_id ? a.blk_id[j] : j) * 64 : a.nnz_rows, z);
-          if (ci == col) ++i;
-          if (cj == col) ++j;
-          krow = col * 64;
+          flags = 0;
+          ++it;
         }
-        if (B_KMAJOR) {
-          tma_load_4d(sp + 16384, &m_b, &bar_full[s], krow, n0, h, z);
-        } else {
-          tma_load_4d(sp + 16384, &m_b, &bar_full[s], n0, krow, h, z);
-          tma_load_4d(sp + 16384 + 8192, &m_b, &bar_full[s], n0 + 64, krow, h, z);
+      }
+      if (ok) {                                                    // tells the issuing thread that nothing follows
+        const int s = it % S;
+        if (it < S || mbar_wait(&bar_empty[s], ((it / S) - 1) & 1, fl)) {
+          stage_flags[s] = kEnd;
+          mbar_arrive(&bar_full[s]);
         }
+      }
+    }
+  } else if (warp == 6) {
+    // ------------------------------------------------------------------ dense operand
+    if (lane == 0) {
+      prefetch_map(&m_b);
+      int it = 0;
+      bool ok = true;
+      Walk w;
+      for (int t = blockIdx.x; ok && t < a.total_tiles; t += gridDim.x) {
+        const Tile tc_ = tile_of(a, t);
+        const int n0 = tc_.nt * TN;
+        w.init(a, tc_.h, tc_.tr, R);
+        int kh = 0, id[4], col = 0;
+        while (ok && (kh || !w.done())) {
+          const int s = it % S;
+          if (it >= S && !mbar_wait(&bar_empty[s], ((it / S) - 1) & 1, fl)) { ok = false; break; }
+          unsigned char* sp = smem + s * G::kStage + kStageA;
+          if (block == 32) {
+            const int c0 = w.next(a, id);
+            const bool two = !w.done();
+            const int c1 = two ? w.next(a, id) : 0;
+            mbar_expect_tx(&bar_full[s], two ? G::kStageB : G::kStageB / 2);
+            if (B_KMAJOR) {
+              tma_load_4d(sp, &m_b, &bar_full[s], c0 * 32, n0, tc_.h, tc_.z);
+              if (two) tma_load_4d(sp + G::kStageB / 2, &m_b, &bar_full[s], c1 * 32, n0, tc_.h, tc_.z);
+            } else {
+              tma_load_5d(sp, &m_b, &bar_full[s], 0, c0 * 32, n0 / 64, tc_.h, tc_.z);
+              if (two) tma_load_5d(sp + G::kStageB / 2, &m_b, &bar_full[s], 0, c1 * 32, n0 / 64, tc_.h, tc_.z);
+            }
+          } else {
+            int krow;
+            if (block == 128) {
+              if (!kh) col = w.next(a, id);
+              krow = col * 128 + kh * 64;
+              kh ^= 1;
+            } else {
+              krow = w.next(a, id) * 64;
+            }
+            mbar_expect_tx(&bar_full[s], G::kStageB);
+            if (B_KMAJOR) tma_load_4d(sp, &m_b, &bar_full[s], krow, n0, tc_.h, tc_.z);
+            else tma_load_5d(sp, &m_b, &bar_full[s], 0, krow, n0 / 64, tc_.h, tc_.z);
+          }
+          ++it;
+        }
+      }
+      if (ok) {
+        const int s = it % S;
+        if (it < S || mbar_wait(&bar_empty[s], ((it / S) - 1) & 1, fl)) mbar_arrive(&bar_full[s]);
       }
     }
   } else if (warp == 5) {
     // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0 && ns > 0) {
-      const uint32_t idesc = instr_desc(128, 128, B_KMAJOR ? 0 : 1, Bf<T>::v) | (A_MN ? 1u << 15 : 0u);
-      bool ok = true;
-      for (int it = 0; ok && it < ns; ++it) {
-        const int s = it % kStages;
-        // (MN-major A: 8 KB between its two groups of 64 rows, in the leading-offset field)
-        const uint32_t a_lo = A_MN ? (((saddr(smem + s * kStageBytes) & 0x3FFFF) >> 4) | (512u << 16))
-                                   : desc_lo(saddr(smem + s * kStageBytes));
-        // (MN-major B: 8 KB between its two groups of 64 columns, in the leading-offset field)
-        const uint32_t b_lo = B_KMAJOR ? desc_lo(saddr(smem + s * kStageBytes + 16384))
-                                       : (((saddr(smem + s * kStageBytes + 16384) & 0x3FFFF) >> 4) | (512u << 16));
-        ok = mbar_wait(&bar_full[s], (it / kStages) & 1, fl);
-        if (!ok) break;
+    if (lane == 0) {
+      const uint32_t idesc = instr_desc(128, TN, B_KMAJOR ? 0 : 1, Bf<T>::v) | (A_MN ? 1u << 15 : 0u);
+      // Descriptors.  Blocks 64 / 128: 128-byte swizzle, K-major operands advance 32 bytes per
+      // K-step, MN-major ones 16 rows of 128 bytes; the groups of 64 columns (rows of A) of an
+      // MN-major operand lie 8 KB apart.  Block 32: the sparse operand and a K-major dense
+      // operand use the 64-byte swizzle (8-row groups of 512 bytes; an MN-major A has its
+      // groups of 32 rows 2 KB apart and advances 16 rows of 64 bytes per K-step); an MN-major
+      // dense sub-tile has 32 k-rows, so its groups of 64 columns lie 4 KB apart.
+      constexpr uint32_t kHi64 = (512u >> 4) | (1u << 14) | (4u << 29);
+      const bool b32 = block == 32;
+      const uint32_t a_hi = b32 ? kHi64 : kDescHi;
+      const uint32_t b_hi = (b32 && B_KMAJOR) ? kHi64 : kDescHi;
+      const uint32_t a_lbo = A_MN ? ((b32 ? 2048u : 8192u) >> 4) << 16 : 1u << 16;
+      const uint32_t b_lbo = B_KMAJOR ? 1u << 16 : ((b32 ? 4096u : 8192u) >> 4) << 16;
+      const uint32_t a_step = A_MN ? (b32 ? 64u : 128u) : 2u;
+      const uint32_t b_step = B_KMAJOR ? 2u : 128u;
+      int tiles = 0;
+      uint32_t d = tmem;
+      for (int it = 0;; ++it) {
+        const int s = it % S;
+        if (!mbar_wait(&bar_full[s], (it / S) & 1, fl)) break;
         fence_after();
+        const int f = stage_flags[s];
+        if (f & kEnd) break;
+        if (f & kFirst) {
+          const int buf = tiles & 1;
+          if (tiles >= 2 && !mbar_wait(&bar_acc_empty[buf], ((tiles >> 1) - 1) & 1, fl)) break;
+          fence_after();
+          d = tmem + buf * TN;
+          ++tiles;
+        }
+        const uint32_t a0 = ((saddr(smem + s * G::kStage) & 0x3FFFF) >> 4) | a_lbo;
+        const uint32_t b0 = ((saddr(smem + s * G::kStage + kStageA) & 0x3FFFF) >> 4) | b_lbo;
 #pragma unroll
         for (int ks = 0; ks < 4; ++ks) {
-          const uint32_t acc = (it > 0 || ks > 0) ? 1u : 0u;
-          const uint64_t da = desc_from_lo(a_lo + ks * (A_MN ? 128 : 2));   // per K-step: 32 bytes (K-major), 16 rows (MN-major)
-          // per K-step: 32 bytes (K-major) or 16 rows = 2048 bytes (MN-major)
-          mma_ss(tmem, da, desc_from_lo(b_lo + ks * (B_KMAJOR ? 2 : 128)), idesc, acc);
+          if (b32 && ks >= 2 && (f & kHalf)) break;
+          const uint32_t acc = ((f & kFirst) && ks == 0) ? 0u : 1u;
+          // block 32: K-steps 2, 3 belong to the second sub-tile (8 KB further in A, half a stage further in B)
+          const uint32_t ao = b32 ? (ks >> 1) * (8192u >> 4) + (ks & 1) * a_step : ks * a_step;
+          const uint32_t bo = b32 ? (ks >> 1) * ((uint32_t)(G::kStageB / 2) >> 4) + (ks & 1) * b_step : ks * b_step;
+          const uint64_t da = (static_cast<uint64_t>(a_hi) << 32) | (a0 + ao);
+          const uint64_t db = (static_cast<uint64_t>(b_hi) << 32) | (b0 + bo);
+          mma_ss(d, da, db, idesc, acc);
         }
         commit(&bar_empty[s]);                                      // the stage is free once these MMAs have read it
+        if (f & kLast) commit(&bar_acc_full[(tiles - 1) & 1]);
       }
-      if (ok) commit(&bar_done);
     }
-  } else {
+  } else if (warp < 4) {
     // ------------------------------------------------------------------ write-back
     const int row = warp * 32 + lane;
-    const int grow = (block == 128 ? r0 * 128 : r0 * 64) + row;
-    const bool row_ok = grow < a.rows_total && (block == 128 || row < 64 || r1 >= 0);
-    T* crow = reinterpret_cast<T*>(a.c) + z * a.c_sz + h * a.c_sh + (int64_t)grow * a.c_sm + (int64_t)n0 * a.c_sn;
+    int tiles = 0;
     bool ok = true;
-    if (ns > 0) ok = mbar_wait_warp(&bar_done, 0, fl);
-    if (ok) {
-      fence_after();
-      const uint32_t ta = tmem + ((uint32_t)(warp * 32) << 16);
+    for (int t = blockIdx.x; ok && t < a.total_tiles; t += gridDim.x) {
+      const Tile tc_ = tile_of(a, t);
+      const int br0 = tc_.tr * R;
+      const int br1 = min(br0 + R, a.Mb);
+      const bool any = a.row_ptr[tc_.h * a.Mb + br1] > a.row_ptr[tc_.h * a.Mb + br0];
+      const int grow = tc_.tr * 128 + row;
+      const bool row_ok = grow < a.rows_total;
+      T* crow = reinterpret_cast<T*>(a.c) + tc_.z * a.c_sz + tc_.h * a.c_sh + (int64_t)grow * a.c_sm +
+                (int64_t)(tc_.nt * TN) * a.c_sn;
+      const int buf = tiles & 1;
+      if (any) {
+        ok = mbar_wait_warp(&bar_acc_full[buf], (tiles >> 1) & 1, fl);
+        if (!ok) break;
+        fence_after();
+      }
+      const uint32_t ta = tmem + buf * TN + ((uint32_t)(warp * 32) << 16);
 #pragma unroll 1
-      for (int c = 0; c < kTN; c += 32) {
+      for (int c = 0; c < TN; c += 32) {
         uint32_t r[32];
-        if (ns > 0) {
+        if (any) {
           tmem_ld32(ta + c, r);
           tmem_ld_wait();
         } else {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) r[i] = 0u;                   // a block-row without blocks: zeros, as the reference gives
+          for (int i = 0; i < 32; ++i) r[i] = 0u;                   // block-rows without blocks: zeros, as the reference gives
         }
         if (row_ok) {
           if (C_ROWS) {
@@ -208,45 +368,64 @@ dsd_tc_kernel(const __grid_constant__ CUtensorMap m_s, const __grid_constant__ C
           }
         }
       }
+      if (any) {
+        fence_before();
+        warp_arrive(&bar_acc_empty[buf], lane);
+        ++tiles;
+      }
     }
   }
   fence_before();
   __syncthreads();
-  if (warp == 1) tmem_dealloc(tmem, kTN);
+  if (warp == 1) tmem_dealloc(tmem, 2 * TN);
   if (tid == 0 && failed[0]) atomicExch(&g_dsd_status, 4);
 }
 
-template <typename T, bool AM, bool BK, bool CR>
-int launch(const CUtensorMap& ms, const CUtensorMap& mb, const DsdTcArgs& a, dim3 grid, cudaStream_t st) {
-  auto kern = dsd_tc_kernel<T, AM, BK, CR>;
-  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
+template <typename T, int TN, bool AM, bool BK, bool CR>
+int launch(const CUtensorMap& ms, const CUtensorMap& mb, const DsdTcArgs& a, int grid, cudaStream_t st) {
+  auto kern = dsd_tc_kernel<T, TN, AM, BK, CR>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Geo<TN>::kSmem);
   if (e != cudaSuccess) return fail(BSP_ERR_CUDA, "dsd (tcgen05): cannot reserve shared memory: %s", cudaGetErrorString(e));
-  kern<<<grid, kThreads, kSmem, st>>>(ms, mb, a);
+  kern<<<grid, kThreads, Geo<TN>::kSmem, st>>>(ms, mb, a);
   e = cudaGetLastError();
   if (e != cudaSuccess) return fail(BSP_ERR_CUDA, "dsd (tcgen05) launch failed: %s", cudaGetErrorString(e));
   return BSP_OK;
 }
 
-template <typename T, bool AM>
-int launch_a(bool bk, bool cr, const CUtensorMap& ms, const CUtensorMap& mb, const DsdTcArgs& a, dim3 grid, cudaStream_t st) {
-  if (bk) return cr ? launch<T, AM, true, true>(ms, mb, a, grid, st) : launch<T, AM, true, false>(ms, mb, a, grid, st);
-  return cr ? launch<T, AM, false, true>(ms, mb, a, grid, st) : launch<T, AM, false, false>(ms, mb, a, grid, st);
+template <typename T, int TN, bool AM>
+int launch_a(bool bk, bool cr, const CUtensorMap& ms, const CUtensorMap& mb, const DsdTcArgs& a, int grid, cudaStream_t st) {
+  if (bk) return cr ? launch<T, TN, AM, true, true>(ms, mb, a, grid, st) : launch<T, TN, AM, true, false>(ms, mb, a, grid, st);
+  return cr ? launch<T, TN, AM, false, true>(ms, mb, a, grid, st) : launch<T, TN, AM, false, false>(ms, mb, a, grid, st);
 }
 
-template <typename T>
-int launch_t(bool am, bool bk, bool cr, const CUtensorMap& ms, const CUtensorMap& mb, const DsdTcArgs& a, dim3 grid, cudaStream_t st) {
-  return am ? launch_a<T, true>(bk, cr, ms, mb, a, grid, st) : launch_a<T, false>(bk, cr, ms, mb, a, grid, st);
+template <typename T, int TN>
+int launch_t(bool am, bool bk, bool cr, const CUtensorMap& ms, const CUtensorMap& mb, const DsdTcArgs& a, int grid, cudaStream_t st) {
+  return am ? launch_a<T, TN, true>(bk, cr, ms, mb, a, grid, st) : launch_a<T, TN, false>(bk, cr, ms, mb, a, grid, st);
+}
+
+// Number of SMs of the current device (one persistent CTA each).
+int sm_count() {
+  static thread_local int cached_dev = -1, cached = 0;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return 0;
+  if (dev != cached_dev) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
+    cached = n;
+    cached_dev = dev;
+  }
+  return cached;
 }
 
 }  // namespace
 
-// True when dsd_tc covers the case: FP16 / BF16, block 64 / 128, N a multiple of 128, both dense tensors with one unit inner stride and 16-byte friendly
-// addresses and strides.
+// True when dsd_tc covers the case: FP16 / BF16, block 32 / 64 / 128, N a multiple of 128, both dense tensors with
+// one unit inner stride and 16-byte friendly addresses and strides.
 bool dsd_tc_eligible(const void* s, const void* b, const void* c, int dtype, int block, int N, int trans_s, int64_t s_sz,
                      int64_t b_sz, int64_t b_sh, int64_t b_sk, int64_t b_sn,
                      int64_t c_sz, int64_t c_sh, int64_t c_sm, int64_t c_sn) {
   if (dtype != BSP_F16 && dtype != BSP_BF16) return false;
-  if ((block != 64 && block != 128) || N % kTN) return false;
+  if ((block != 32 && block != 64 && block != 128) || N % 128) return false;
   if ((b_sk != 1) == (b_sn != 1) || (c_sm != 1) == (c_sn != 1)) return false;
   const int64_t b_outer = b_sk == 1 ? b_sn : b_sk;
   if ((reinterpret_cast<uintptr_t>(s) | reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(c)) & 15) return false;
@@ -260,33 +439,51 @@ int dsd_tc(const void* s, const void* b, void* c, int dtype, int block, int Z, i
            int64_t b_sz, int64_t b_sh, int64_t b_sk, int64_t b_sn,
            int64_t c_sz, int64_t c_sh, int64_t c_sm, int64_t c_sn, const Meta& m, cudaStream_t st) {
   const bool bk = b_sk == 1, cr = c_sn == 1;
+  const int TN = N % 256 == 0 ? 256 : 128;
   // op(S) has the layout's rows (and walks its CSR) or, transposed, its columns (CSC)
   const int out_b = trans_s ? m.Nb : m.Mb, red_b = trans_s ? m.Mb : m.Nb;
   const int64_t ktot = (int64_t)red_b * block;
+  const int kbox = block == 32 ? 32 : 64;                  // k extent of one load of the dense operand
+  const int swz = block == 32 ? 64 : 128;
   CUtensorMap ms, mb;
   {
     cuuint64_t dims[3] = {(cuuint64_t)block, (cuuint64_t)m.nnz * block, (cuuint64_t)Z};
     cuuint64_t strides[2] = {(cuuint64_t)block * 2, (cuuint64_t)(Z > 1 ? s_sz : (int64_t)m.nnz * block * block) * 2};
-    cuuint32_t box[3] = {64, (cuuint32_t)((block == 128 && !trans_s) ? 128 : 64), 1};
-    if (int rc = encode(&ms, s, dtype, 3, dims, strides, box)) return rc;
+    cuuint32_t box[3] = {(cuuint32_t)(block == 32 ? 32 : 64),
+                         (cuuint32_t)(block == 32 ? 32 : (block == 128 && !trans_s) ? 128 : 64), 1};
+    if (int rc = encode(&ms, s, dtype, 3, dims, strides, box, swz)) return rc;
   }
-  {
-    const int64_t inner = bk ? ktot : N, outer = bk ? N : ktot, outer_stride = bk ? b_sn : b_sk;
-    cuuint64_t dims[4] = {(cuuint64_t)inner, (cuuint64_t)outer, (cuuint64_t)m.H, (cuuint64_t)Z};
-    cuuint64_t strides[3] = {(cuuint64_t)outer_stride * 2, (cuuint64_t)(m.H > 1 ? b_sh : outer * outer_stride) * 2,
-                             (cuuint64_t)(Z > 1 ? b_sz : (int64_t)m.H * outer * outer_stride) * 2};
-    cuuint32_t box[4] = {64, (cuuint32_t)(bk ? 128 : 64), 1, 1};
-    if (int rc = encode(&mb, b, dtype, 4, dims, strides, box)) return rc;
+  const int64_t outer_n = bk ? b_sn : b_sk;                // stride between rows of the dense operand in memory
+  const int64_t sh = m.H > 1 ? b_sh : (bk ? N : ktot) * outer_n;
+  if (bk) {                                                // [n][k]: boxes of TN rows of kbox elements
+    cuuint64_t dims[4] = {(cuuint64_t)ktot, (cuuint64_t)N, (cuuint64_t)m.H, (cuuint64_t)Z};
+    cuuint64_t strides[3] = {(cuuint64_t)outer_n * 2, (cuuint64_t)sh * 2, (cuuint64_t)(Z > 1 ? b_sz : (int64_t)m.H * sh) * 2};
+    cuuint32_t box[4] = {(cuuint32_t)kbox, (cuuint32_t)TN, 1, 1};
+    if (int rc = encode(&mb, b, dtype, 4, dims, strides, box, swz)) return rc;
+  } else {                                                 // [k][n] seen as (64 n, k, N / 64 groups): one box brings TN / 64 groups of kbox rows
+    cuuint64_t dims[5] = {64, (cuuint64_t)ktot, (cuuint64_t)(N / 64), (cuuint64_t)m.H, (cuuint64_t)Z};
+    cuuint64_t strides[4] = {(cuuint64_t)outer_n * 2, 128, (cuuint64_t)sh * 2, (cuuint64_t)(Z > 1 ? b_sz : (int64_t)m.H * sh) * 2};
+    cuuint32_t box[5] = {64, (cuuint32_t)kbox, (cuuint32_t)(TN / 64), 1, 1};
+    if (int rc = encode(&mb, b, dtype, 5, dims, strides, box, 128)) return rc;
   }
   DsdTcArgs a = {};
   a.c = c; a.c_sz = c_sz; a.c_sh = c_sh; a.c_sm = c_sm; a.c_sn = c_sn;
   a.H = m.H; a.Mb = out_b; a.block = block; a.rows_total = out_b * block; a.nnz_rows = m.nnz * block;
   a.tiles_per_head = (out_b * block + 127) / 128;
+  a.n_tiles = N / TN;
+  const int64_t total = (int64_t)Z * m.H * a.tiles_per_head * a.n_tiles;
+  if (total > 0x7fffffff) return fail(BSP_ERR_INVALID, "dsd: too many tiles");
+  a.total_tiles = (int)total;
   if (trans_s) { a.row_ptr = m.col_ptr; a.blk_col = m.col_row; a.blk_id = m.col_bid; }
   else { a.row_ptr = m.row_ptr; a.blk_col = m.blk_col; a.blk_id = nullptr; }
-  dim3 grid(m.H * a.tiles_per_head, N / kTN, Z);
-  if (dtype == BSP_F16) return launch_t<__half>(trans_s != 0, bk, cr, ms, mb, a, grid, st);
-  return launch_t<__nv_bfloat16>(trans_s != 0, bk, cr, ms, mb, a, grid, st);
+  const int sms = sm_count();
+  if (sms <= 0) return fail(BSP_ERR_CUDA, "dsd (tcgen05): cannot query the device");
+  const int grid = a.total_tiles < sms ? a.total_tiles : sms;
+  if (dtype == BSP_F16)
+    return TN == 256 ? launch_t<__half, 256>(trans_s != 0, bk, cr, ms, mb, a, grid, st)
+                     : launch_t<__half, 128>(trans_s != 0, bk, cr, ms, mb, a, grid, st);
+  return TN == 256 ? launch_t<__nv_bfloat16, 256>(trans_s != 0, bk, cr, ms, mb, a, grid, st)
+                   : launch_t<__nv_bfloat16, 128>(trans_s != 0, bk, cr, ms, mb, a, grid, st);
 }
 
 // 0, or non-zero when a bounded wait inside the kernel above expired (synchronises the device).

@@ -1,6 +1,6 @@
 // Pieces shared by the tcgen05 MatMul kernels (dsd_tc.cu, sdd_tc.cu): 16-bit packing, the
 // 3-D TMA load and the host-side tensor-map encoder (128-byte swizzle, as the MMA descriptors
-// of tc.cuh expect).
+// of tc.cuh expect, or the 64-byte one for tiles whose rows hold 32 elements).
 #pragma once
 #include <cuda.h>
 #include <cuda_bf16.h>
@@ -52,7 +52,7 @@ inline EncodeTiledFn encode_fn() {
 }
 
 inline int encode(CUtensorMap* m, const void* ptr, int dtype, int rank, const cuuint64_t* dims, const cuuint64_t* strides_bytes,
-           const cuuint32_t* box) {
+           const cuuint32_t* box, int swizzle_bytes = 128) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return fail(BSP_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
   // The encoder is a driver call and needs the primary context bound to this thread; a thread
@@ -62,7 +62,7 @@ inline int encode(CUtensorMap* m, const void* ptr, int dtype, int rank, const cu
   cuuint32_t es[5] = {1, 1, 1, 1, 1};
   CUresult r = fn(m, dtype == BSP_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, rank,
                   const_cast<void*>(ptr), dims, strides_bytes, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                  swizzle_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(BSP_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d", (int)r);
   return BSP_OK;
 }

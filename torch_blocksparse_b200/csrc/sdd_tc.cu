@@ -1,4 +1,4 @@
-// Block-sparse sdd on the Blackwell tensor path for block 64 and 128: tcgen05.mma with the
+// Block-sparse sdd on the Blackwell tensor path for block 32, 64 and 128: tcgen05.mma with the
 // accumulator in tensor memory, operands brought in by TMA.
 //
 // Same contract as the mma.sync kernel of sdd_impl.cuh (which replaces the launch of
@@ -8,12 +8,16 @@
 // Geometry: every MMA has M = 128 and the CTA's accumulator is 128 x 128.
 //   block 128  a CTA computes one nonzero block;
 //   block 64   a CTA takes block-rows 2i and 2i + 1 and two consecutive entries of the union
-//              of their column lists: four blocks, of which those the layout holds are stored.
-// The reduction runs over K in stages of 64: 16 KB of A (128 m x 64 k) and 16 KB of B (64 k x
-// 128 n), each as two TMA boxes of 64 x 64.  Either operand may have k or its other dimension
-// contiguous: k contiguous gives K-major tiles, the other case MN-major tiles (two groups of 64
-// rows or columns, 8 KB apart, in one descriptor); every K-step is one 128 x 128 x 16 MMA.  A box that lies outside the tensor (odd number of block-rows, missing second
-// column) is filled with zeros.
+//              of their column lists: four blocks, of which those the layout holds are stored;
+//   block 32   four block-rows and four consecutive entries of the union of their column
+//              lists: sixteen blocks, of which those the layout holds are stored.
+// The reduction runs over K in stages of 64: 16 KB of A (128 m x 64 k, two TMA boxes of 64 x
+// 64) and 16 KB of B (64 k x 128 n, one box per column block).  Either operand may have k or
+// its other dimension contiguous: k contiguous gives K-major tiles, the other case MN-major
+// tiles (groups of 64 rows or columns, 8 KB apart, in one descriptor; the 32 columns of a
+// block-32 column block form groups of 4 KB in the 64-byte swizzle); every K-step is one
+// 128 x 128 x 16 MMA.  A box that lies outside the tensor (block-rows past the last one,
+// missing columns at the end of the union) is filled with zeros.
 //
 // Warps: 0-3 write the blocks back, 4 issues the TMA loads, 5 the MMAs (one thread each).
 // mbarriers only; every wait is bounded and a wait that expires sets a device status word.
@@ -43,6 +47,8 @@ struct SddTcArgs {
   const int32_t *row_ptr, *blk_row, *blk_col, *blk_head;
 };
 
+constexpr int kNone = 0x7fffffff;
+
 template <typename T, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(kThreads, 2)
 sdd_tc_kernel(const __grid_constant__ CUtensorMap m_a, const __grid_constant__ CUtensorMap m_b, SddTcArgs a) {
@@ -51,9 +57,9 @@ sdd_tc_kernel(const __grid_constant__ CUtensorMap m_a, const __grid_constant__ C
   __shared__ uint64_t bar_full[kStages], bar_empty[kStages], bar_done;
   __shared__ uint32_t tmem_slot;
   __shared__ int failed[2];
-  // work of this CTA: head, first row of A, the two 64-wide column blocks (first column of B,
-  // or -1) and the ids of the up to four blocks to store ([row half][column half], -1: none)
-  __shared__ int w_h, w_m0, w_n[2], w_id[2][2];
+  // work of this CTA: head, first row of A, its column blocks (first column of B, or -1; two of
+  // 64 columns or four of 32) and the ids of the blocks to store ([block-row][column block], -1: none)
+  __shared__ int w_h, w_m0, w_n[4], w_id[4][4];
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int z = blockIdx.z, block = a.block;
@@ -61,8 +67,10 @@ sdd_tc_kernel(const __grid_constant__ CUtensorMap m_a, const __grid_constant__ C
   if (tid == 0) {
     failed[0] = 0;
     failed[1] = kWaitBudget;
-    w_n[0] = w_n[1] = -1;
-    w_id[0][0] = w_id[0][1] = w_id[1][0] = w_id[1][1] = -1;
+    for (int i = 0; i < 4; ++i) {
+      w_n[i] = -1;
+      for (int j = 0; j < 4; ++j) w_id[i][j] = -1;
+    }
     if (block == 128) {
       const int e = blockIdx.x;
       w_h = a.blk_head[e];
@@ -72,24 +80,27 @@ sdd_tc_kernel(const __grid_constant__ CUtensorMap m_a, const __grid_constant__ C
       w_id[0][0] = e;
     } else {
       const int tile = blockIdx.y, g = blockIdx.x;   // the groups of a tile are neighbours in the launch: they share A in L2
-      const int h = tile / a.tiles_per_head, r0 = 2 * (tile % a.tiles_per_head), r1 = r0 + 1 < a.Mb ? r0 + 1 : -1;
+      const int R = 128 / block;                      // block-rows of a tile = column blocks of a group
+      const int h = tile / a.tiles_per_head, r0 = R * (tile % a.tiles_per_head);
       w_h = h;
-      w_m0 = r0 * 64;
-      int i = a.row_ptr[h * a.Mb + r0];
-      const int e0 = a.row_ptr[h * a.Mb + r0 + 1];
-      int j = r1 >= 0 ? a.row_ptr[h * a.Mb + r1] : 0;
-      const int e1 = r1 >= 0 ? a.row_ptr[h * a.Mb + r1 + 1] : 0;
-      // entries 2g and 2g + 1 of the union of the two column lists (both in column order)
-      for (int n = 0; (i < e0 || j < e1) && n < 2 * g + 2; ++n) {
-        const int ci = i < e0 ? a.blk_col[i] : 0x7fffffff, cj = j < e1 ? a.blk_col[j] : 0x7fffffff;
-        const int col = ci < cj ? ci : cj;
-        if (n >= 2 * g) {
-          w_n[n - 2 * g] = col * 64;
-          if (ci == col) w_id[0][n - 2 * g] = i;
-          if (cj == col) w_id[1][n - 2 * g] = j;
-        }
-        if (ci == col) ++i;
-        if (cj == col) ++j;
+      w_m0 = r0 * block;
+      int i[4], e[4], c[4];
+      for (int r = 0; r < 4; ++r) {
+        i[r] = e[r] = 0;
+        if (r < R && r0 + r < a.Mb) { i[r] = a.row_ptr[h * a.Mb + r0 + r]; e[r] = a.row_ptr[h * a.Mb + r0 + r + 1]; }
+        c[r] = i[r] < e[r] ? a.blk_col[i[r]] : kNone;
+      }
+      // entries R g .. R g + R - 1 of the union of the column lists (each in column order)
+      for (int n = 0; n < R * g + R; ++n) {
+        const int col = min(min(c[0], c[1]), min(c[2], c[3]));
+        if (col == kNone) break;
+        if (n >= R * g) w_n[n - R * g] = col * block;
+        for (int r = 0; r < 4; ++r)
+          if (c[r] == col) {
+            if (n >= R * g) w_id[r][n - R * g] = i[r];
+            ++i[r];
+            c[r] = i[r] < e[r] ? a.blk_col[i[r]] : kNone;
+          }
       }
     }
     for (int s = 0; s < kStages; ++s) { mbar_init(&bar_full[s], 1); mbar_init(&bar_empty[s], 1); }
@@ -111,8 +122,9 @@ sdd_tc_kernel(const __grid_constant__ CUtensorMap m_a, const __grid_constant__ C
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
       prefetch_map(&m_a); prefetch_map(&m_b);
-      // a missing second column: a box past the end of B, filled with zeros
-      const int nb0 = w_n[0], nb1 = w_n[1] >= 0 ? w_n[1] : a.Nb * block;
+      // a missing column block: a box past the end of B, filled with zeros
+      int nb[4];
+      for (int j = 0; j < 4; ++j) nb[j] = w_n[j] >= 0 ? w_n[j] : a.Nb * block;
       for (int it = 0; it < ns; ++it) {
         const int s = it % kStages, k0 = it * 64;
         if (it >= kStages && !mbar_wait(&bar_empty[s], ((it / kStages) - 1) & 1, fl)) break;
@@ -125,12 +137,18 @@ sdd_tc_kernel(const __grid_constant__ CUtensorMap m_a, const __grid_constant__ C
           tma_load_4d(sp, &m_a, &bar_full[s], k0, m0, h, z);
           tma_load_4d(sp + 8192, &m_a, &bar_full[s], k0, m0 + 64, h, z);
         }
-        if (B_MN) {                               // [k][n]: 64 n x 64 k-rows per box
-          tma_load_4d(sp + 16384, &m_b, &bar_full[s], nb0, k0, h, z);
-          tma_load_4d(sp + 16384 + 8192, &m_b, &bar_full[s], nb1, k0, h, z);
+        if (block == 32) {                        // four column blocks of 32: 4 KB each in either form
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            if (B_MN) tma_load_4d(sp + 16384 + j * 4096, &m_b, &bar_full[s], nb[j], k0, h, z);
+            else tma_load_4d(sp + 16384 + j * 4096, &m_b, &bar_full[s], k0, nb[j], h, z);
+          }
+        } else if (B_MN) {                        // [k][n]: 64 n x 64 k-rows per box
+          tma_load_4d(sp + 16384, &m_b, &bar_full[s], nb[0], k0, h, z);
+          tma_load_4d(sp + 16384 + 8192, &m_b, &bar_full[s], nb[1], k0, h, z);
         } else {                                  // [n][k]: 64 k x 64 n-rows per box
-          tma_load_4d(sp + 16384, &m_b, &bar_full[s], k0, nb0, h, z);
-          tma_load_4d(sp + 16384 + 8192, &m_b, &bar_full[s], k0, nb1, h, z);
+          tma_load_4d(sp + 16384, &m_b, &bar_full[s], k0, nb[0], h, z);
+          tma_load_4d(sp + 16384 + 8192, &m_b, &bar_full[s], k0, nb[1], h, z);
         }
       }
     }
@@ -144,8 +162,12 @@ sdd_tc_kernel(const __grid_constant__ CUtensorMap m_a, const __grid_constant__ C
         // (MN-major A: 8 KB between its two groups of 64 rows, in the leading-offset field)
         const uint32_t a_lo = A_MN ? (((saddr(smem + s * kStageBytes) & 0x3FFFF) >> 4) | (512u << 16))
                                    : desc_lo(saddr(smem + s * kStageBytes));
-        const uint32_t b_lo = B_MN ? (((saddr(smem + s * kStageBytes + 16384) & 0x3FFFF) >> 4) | (512u << 16))
+        // (block 32, MN-major B: groups of 32 columns in the 64-byte swizzle, 64 k-rows of 64 bytes
+        // = 4 KB apart, 8-row groups of 512 bytes, 16 rows = 1 KB per K-step)
+        const bool b64s = B_MN && block == 32;
+        const uint32_t b_lo = B_MN ? (((saddr(smem + s * kStageBytes + 16384) & 0x3FFFF) >> 4) | ((b64s ? 256u : 512u) << 16))
                                    : desc_lo(saddr(smem + s * kStageBytes + 16384));
+        const uint32_t b_hi = b64s ? ((512u >> 4) | (1u << 14) | (4u << 29)) : kDescHi;
         ok = mbar_wait(&bar_full[s], (it / kStages) & 1, fl);
         if (!ok) break;
         fence_after();
@@ -153,7 +175,8 @@ sdd_tc_kernel(const __grid_constant__ CUtensorMap m_a, const __grid_constant__ C
         for (int ks = 0; ks < 4; ++ks) {
           const uint32_t acc = (it > 0 || ks > 0) ? 1u : 0u;
           const uint64_t da = desc_from_lo(a_lo + ks * (A_MN ? 128 : 2));   // per K-step: 16 rows (MN-major), 32 bytes (K-major)
-          mma_ss(tmem, da, desc_from_lo(b_lo + ks * (B_MN ? 128 : 2)), idesc, acc);
+          const uint64_t db = (static_cast<uint64_t>(b_hi) << 32) | (b_lo + ks * (B_MN ? (b64s ? 64 : 128) : 2));
+          mma_ss(tmem, da, db, idesc, acc);
         }
         commit(&bar_empty[s]);
       }
@@ -161,21 +184,24 @@ sdd_tc_kernel(const __grid_constant__ CUtensorMap m_a, const __grid_constant__ C
     }
   } else {
     // ------------------------------------------------------------------ write-back
-    const int row = warp * 32 + lane, rh = row >> 6;
+    const int row = warp * 32 + lane;
+    const int rh = block == 32 ? row >> 5 : row >> 6;
     if (mbar_wait_warp(&bar_done, 0, fl)) {
       fence_after();
       const uint32_t ta = tmem + ((uint32_t)(warp * 32) << 16);
       T* cz = reinterpret_cast<T*>(a.c) + z * a.c_sz;
 #pragma unroll 1
       for (int c = 0; c < 128; c += 32) {
-        // block 128: one block, this thread's row of 128 columns; block 64: block [rh][c / 64]
-        const int id = block == 128 ? w_id[0][0] : w_id[rh][c >> 6];
+        // block 128: one block, this thread's row of 128 columns; block 64: block [rh][c / 64];
+        // block 32: block [rh][c / 32], a whole row of it
+        const int id = block == 128 ? w_id[0][0] : block == 64 ? w_id[rh][c >> 6] : w_id[rh][c >> 5];
         if (id < 0) continue;                                        // uniform per warp
         uint32_t r[32];
         tmem_ld32(ta + c, r);
         tmem_ld_wait();
         T* dst = block == 128 ? cz + (int64_t)id * 16384 + row * 128 + c
-                              : cz + (int64_t)id * 4096 + (row & 63) * 64 + (c & 63);
+                 : block == 64 ? cz + (int64_t)id * 4096 + (row & 63) * 64 + (c & 63)
+                               : cz + (int64_t)id * 1024 + (row & 31) * 32;
 #pragma unroll
         for (int i = 0; i < 32; i += 8) {
           uint4 v;
@@ -211,25 +237,26 @@ int launch_t(bool am, bool bm, const CUtensorMap& ma, const CUtensorMap& mb, con
   return bm ? launch<T, false, true>(ma, mb, a, grid, st) : launch<T, false, false>(ma, mb, a, grid, st);
 }
 
-// [Z, H, outer, inner] dense operand with unit stride on `inner`: boxes of 64 x 64.
+// [Z, H, outer, inner] dense operand with unit stride on `inner`: boxes of 64 x 64, or of the
+// extents given (an inner extent of 32 elements goes with the 64-byte swizzle).
 int dense_map(CUtensorMap* m, const void* p, int dtype, int Z, int H, int64_t inner, int64_t outer,
-              int64_t outer_stride, int64_t sh, int64_t sz) {
+              int64_t outer_stride, int64_t sh, int64_t sz, int box_inner = 64, int box_outer = 64) {
   cuuint64_t dims[4] = {(cuuint64_t)inner, (cuuint64_t)outer, (cuuint64_t)H, (cuuint64_t)Z};
   cuuint64_t strides[3] = {(cuuint64_t)outer_stride * 2, (cuuint64_t)(H > 1 ? sh : outer * outer_stride) * 2,
                            (cuuint64_t)(Z > 1 ? sz : (int64_t)H * outer * outer_stride) * 2};
-  cuuint32_t box[4] = {64, 64, 1, 1};
-  return encode(m, p, dtype, 4, dims, strides, box);
+  cuuint32_t box[4] = {(cuuint32_t)box_inner, (cuuint32_t)box_outer, 1, 1};
+  return encode(m, p, dtype, 4, dims, strides, box, box_inner == 32 ? 64 : 128);
 }
 
 }  // namespace
 
-// True when sdd_tc covers the case: FP16 / BF16, block 64 / 128, K a multiple of 64, dense
+// True when sdd_tc covers the case: FP16 / BF16, block 32 / 64 / 128, K a multiple of 64, dense
 // operands with one unit inner stride and 16-byte friendly addresses and strides.
 bool sdd_tc_eligible(const void* a, const void* b, const void* c, int dtype, int block, int K,
                      int64_t a_sz, int64_t a_sh, int64_t a_sm, int64_t a_sk,
                      int64_t b_sz, int64_t b_sh, int64_t b_sk, int64_t b_sn, int64_t c_sz) {
   if (dtype != BSP_F16 && dtype != BSP_BF16) return false;
-  if ((block != 64 && block != 128) || K % 64) return false;
+  if ((block != 32 && block != 64 && block != 128) || K % 64) return false;
   if ((a_sm != 1) == (a_sk != 1) || (b_sk != 1) == (b_sn != 1)) return false;
   const int64_t a_outer = a_sk == 1 ? a_sm : a_sk, b_outer = b_sk == 1 ? b_sn : b_sk;
   if ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(c)) & 15) return false;
@@ -245,17 +272,21 @@ int sdd_tc(const void* a, const void* b, void* c, int dtype, int block, int Z, i
   const int64_t M = (int64_t)m.Mb * block, N = (int64_t)m.Nb * block;
   CUtensorMap ma, mb;
   if (int rc = am ? dense_map(&ma, a, dtype, Z, m.H, M, K, a_sk, a_sh, a_sz) : dense_map(&ma, a, dtype, Z, m.H, K, M, a_sm, a_sh, a_sz)) return rc;
-  if (int rc = bm ? dense_map(&mb, b, dtype, Z, m.H, N, K, b_sk, b_sh, b_sz) : dense_map(&mb, b, dtype, Z, m.H, K, N, b_sn, b_sh, b_sz)) return rc;
+  // (block 32: one box per column block, 32 columns of 64 k)
+  const int bn = block == 32 ? 32 : 64;
+  if (int rc = bm ? dense_map(&mb, b, dtype, Z, m.H, N, K, b_sk, b_sh, b_sz, bn, 64)
+                  : dense_map(&mb, b, dtype, Z, m.H, K, N, b_sn, b_sh, b_sz, 64, bn)) return rc;
   SddTcArgs p = {};
   p.c = c; p.c_sz = c_sz; p.H = m.H; p.Mb = m.Mb; p.Nb = m.Nb; p.block = block; p.K = K; p.nnz = m.nnz;
-  p.tiles_per_head = (m.Mb + 1) / 2;
+  const int R = 128 / block;                        // block-rows per tile and column blocks per group (block 32 / 64)
+  p.tiles_per_head = (m.Mb + R - 1) / R;
   p.row_ptr = m.row_ptr; p.blk_row = m.blk_row; p.blk_col = m.blk_col; p.blk_head = m.blk_head;
   dim3 grid;
   if (block == 128) {
     grid = dim3(m.nnz, 1, Z);
   } else {
-    // the union of two column lists has at most 2 * max_row entries, and never more than Nb
-    const int groups = std::min((m.Nb + 1) / 2, std::max(m.max_row, 1));
+    // the union of R column lists has at most R * max_row entries, and never more than Nb
+    const int groups = (std::min(m.Nb, R * std::max(m.max_row, 1)) + R - 1) / R;
     grid = dim3(groups, m.H * p.tiles_per_head, Z);
   }
   if (dtype == BSP_F16) return launch_t<__half>(am, bm, ma, mb, p, grid, st);
