@@ -450,11 +450,15 @@ int bsp_device_status(int* status);
 int bsp_debug_attn_wait(int wait_budget, int skip_chunk);
 
 /*
- * Kernel family of bsp_sdd / bsp_dsd / bsp_dds for block 64 / 128 with FP16 /
- * BF16 operands (no counterpart in the reference): non-zero (the default) lets
- * the cases the tcgen05 kernels cover (sdd: K a multiple of 64; dsd / dds: dense
- * width a multiple of 128; TMA-friendly strides) run on them; zero keeps every
- * product on the mma.sync kernels.  Process-wide.
+ * Kernel family of bsp_sdd / bsp_dsd / bsp_dds for block 32 / 64 / 128 with
+ * FP16 / BF16 operands (no counterpart in the reference): non-zero (the default)
+ * lets the cases the tcgen05 kernels cover (sdd: K a multiple of 64; dsd / dds:
+ * dense width a multiple of 128 and at most 1024 blocks on the reduction side;
+ * TMA-friendly strides) run on them; zero keeps every product on the mma.sync
+ * kernels.  Process-wide.  At block 32 / 64 the tcgen05 dsd / dds kernel fills
+ * the places of absent blocks with zeros instead of skipping them, so a
+ * non-finite value of the dense operand can turn into NaN in output rows whose
+ * own blocks do not touch it.
  */
 int bsp_matmul_use_tcgen05(int enable);
 

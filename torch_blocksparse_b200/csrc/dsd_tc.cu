@@ -10,8 +10,10 @@
 //
 // Geometry: every MMA has M = 128.  A tile is 128 rows of C (one block-row for block 128, two
 // for block 64, four for block 32) by TN = 256 columns (128 when the width is no multiple of
-// 256).  The block-rows of a tile are walked together, in column order, over the UNION of
-// their column lists; the piece of the A tile whose row has no block in a column is zero.  A
+// 256).  The block-rows of a tile are walked together, in
+// column order, over the UNION of their column lists; the piece of the A tile whose row has no
+// block in a column is zero (a non-finite value of the dense operand in such a place turns
+// into NaN where the mma.sync kernels, which skip absent blocks, give a finite result).  A
 // "stage" of the operand ring covers K = 64:
 //   block 128  one half of a nonzero block;
 //   block 64   one column of the union;
@@ -19,17 +21,28 @@
 //              may be absent at the end of a tile).
 // A stage holds 16 KB of A and 64 x TN elements of the dense operand.  Pieces of A that are
 // zero are not loaded when the stage's piece already holds zeros (the ring is cleared once at
-// the start and the loading thread tracks which pieces hold a block); otherwise a TMA box that
+// the start and the loading lanes track which pieces hold a block); otherwise a TMA box that
 // lies past the last block fills them with zeros.
 //
-// One CTA per SM walks tiles blockIdx.x, blockIdx.x + gridDim.x, ... (row tiles fastest, so
-// that the CTAs that run together share the dense panel in L2).  Two accumulators in tensor
-// memory: the write-back of a tile overlaps the products of the next one, and the operand
-// ring runs on across tile boundaries.
+// Persistent CTAs: each walks tiles blockIdx.x, blockIdx.x + gridDim.x, ... (row
+// tiles fastest, so that the CTAs that run together share the dense panel in L2) with an
+// operand ring that runs on across tile boundaries.  The hand-offs between the loading, issuing
+// and write-back threads cost several hundred cycles per stage whatever the ring's depth (a
+// kernel with every load, MMA and store taken out ran at 800-950 cycles per stage with one
+// CTA per SM).  For blocks 32 and 64 two CTAs per SM, each with one accumulator and a ring of
+// two stages, hide them (configuration 2: 0.89 -> 0.72 ms, block 64 on the 4096^3 case 0.97 ->
+// 0.87 ms).  Block 128 is bound by the traffic from L2 into shared memory (its loads alone
+// take 0.50 of its 0.65 ms) and keeps one CTA per SM with two accumulators and four stages,
+// whose write-back overlaps the next tile (with unit stride along the rows of the result, the
+// dds case, 0.59 against 0.71 ms).
 //
 // Warps: 0-3 write the result back (tensor memory -> registers -> global), 4 loads the sparse
-// operand, 5 issues the MMAs, 6 loads the dense operand (one thread each).  mbarriers only;
-// every wait is bounded (tc.cuh) and a wait that expires sets the device status word.
+// operand, 5 issues the MMAs (one thread), 6 loads the dense operand (one thread), 7 plans:
+// it turns the tile's column lists into bit masks (the reduction side may have 1024 blocks at
+// most), forms their union and writes one entry per stage (rows of the sparse operand, block
+// columns of the dense one) into a double-buffered plan in shared memory, so that the loading
+// threads do nothing per stage but wait, announce the bytes and issue.  mbarriers only; every
+// wait is bounded (tc.cuh) and a wait that expires sets the device status word.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include "common.h"
@@ -46,15 +59,19 @@ namespace {
 using namespace tc;
 using namespace mmtc;
 
-constexpr int kThreads = 224;
+constexpr int kThreads = 256;
 constexpr int kStageA = 16384;
 constexpr int kFirst = 1, kLast = 2, kEnd = 4, kHalf = 8;   // stage flags
 constexpr int kNone = 0x7fffffff;
 
-template <int TN> struct Geo {
+// CTAS: CTAs per SM.  Two (blocks 32 and 64) have one accumulator and a short ring each; one
+// (block 128) has two accumulators, so that the write-back of a tile overlaps the products of the
+// next one, and a ring twice as deep.
+template <int TN, int CTAS> struct Geo {
+  static constexpr int kAcc = CTAS == 2 ? 1 : 2;
   static constexpr int kStageB = 64 * TN * 2;
   static constexpr int kStage = kStageA + kStageB;
-  static constexpr int kStages = TN == 256 ? 4 : 6;
+  static constexpr int kStages = CTAS == 2 ? (TN == 256 ? 2 : 3) : (TN == 256 ? 4 : 6);
   static constexpr int kSmem = kStages * kStage + 1024;
 };
 
@@ -73,6 +90,20 @@ BSP_DEVI void tma_load_5d(void* dst, const CUtensorMap* map, uint64_t* bar, int 
                : "memory");
 }
 
+// D[tmem] (+)= A[smem] * B[smem] with the descriptors given as their two 32-bit words.
+BSP_DEVI void mma_desc(uint32_t d, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi, uint32_t idesc, uint32_t accumulate) {
+  asm volatile("{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\tsetp.ne.b32 p, %6, 0;\n\t"
+               "mov.b64 da, {%1, %2};\n\tmov.b64 db, {%3, %4};\n\t"
+               "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t}"
+               ::"r"(d), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate) : "memory");
+}
+BSP_DEVI void mma_desc_acc(uint32_t d, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi, uint32_t idesc) {
+  asm volatile("{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\tsetp.eq.b32 p, 0, 0;\n\t"
+               "mov.b64 da, {%1, %2};\n\tmov.b64 db, {%3, %4};\n\t"
+               "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t}"
+               ::"r"(d), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc) : "memory");
+}
+
 struct Tile { int tr, nt, h, z; };
 BSP_DEVI Tile tile_of(const DsdTcArgs& a, int t) {
   Tile c;
@@ -83,50 +114,48 @@ BSP_DEVI Tile tile_of(const DsdTcArgs& a, int t) {
   return c;
 }
 
-// The block-rows of one tile walked together in column order.
-struct Walk {
-  int i[4], e[4], c[4];
-  BSP_DEVI void init(const DsdTcArgs& a, int h, int tr, int R) {
-#pragma unroll
-    for (int r = 0; r < 4; ++r) {
-      const int br = tr * R + r;
-      i[r] = e[r] = 0;
-      if (r < R && br < a.Mb) { i[r] = a.row_ptr[h * a.Mb + br]; e[r] = a.row_ptr[h * a.Mb + br + 1]; }
-      c[r] = i[r] < e[r] ? a.blk_col[i[r]] : kNone;
-    }
-  }
-  BSP_DEVI bool done() const { return (c[0] & c[1] & c[2] & c[3]) == kNone; }
-  // Next column of the union; id[r] = storage index of row r's block there, or -1.
-  BSP_DEVI int next(const DsdTcArgs& a, int (&id)[4]) {
-    int col = min(min(c[0], c[1]), min(c[2], c[3]));
-#pragma unroll
-    for (int r = 0; r < 4; ++r) {
-      id[r] = -1;
-      if (c[r] == col) {
-        id[r] = a.blk_id ? a.blk_id[i[r]] : i[r];
-        ++i[r];
-        c[r] = i[r] < e[r] ? a.blk_col[i[r]] : kNone;
-      }
-    }
-    return col;
-  }
+// The load plan of a tile, written by the planning warp and read by the two loading warps.  One
+// entry per stage (block 128: per nonzero block, i.e. two stages): words 0-7 the first row of the
+// sparse operand's block for every piece of the stage's A part (piece = 4 * sub-tile + block-row;
+// -1: the block-row has no block in that column), words 8 and 9 the block-column of sub-tile 0 / 1
+// (-1: block 32 with an odd number of columns, last entry).  A tile with more than kChunk
+// entries takes several buffers in a row.
+constexpr int kChunk = 64;
+struct Plan {
+  int n, last;                 // entries in this buffer; 1 if the tile ends with it
+  int e[kChunk][12];
 };
+
+BSP_DEVI int warp_exclusive_sum(int v, int lane, int* total) {
+  int x = v;
+#pragma unroll
+  for (int d = 1; d < 32; d <<= 1) {
+    const int y = __shfl_up_sync(0xffffffffu, x, d);
+    if (lane >= d) x += y;
+  }
+  *total = __shfl_sync(0xffffffffu, x, 31);
+  return x - v;
+}
 
 // B_KMAJOR: the dense operand has k contiguous ([n][k] in memory); else n contiguous ([k][n]).
 // C_ROWS: the result has unit stride along n (a thread writes its row with 16-byte stores);
 // else unit stride along m (the transposed problem of dds: lanes write neighbouring addresses).
 // A_MN: the sparse operand is used transposed: a stored block [k][m] is an MN-major A tile.
-template <typename T, int TN, bool A_MN, bool B_KMAJOR, bool C_ROWS>
-__global__ void __launch_bounds__(kThreads, 1)
+template <typename T, int TN, int CTAS, bool A_MN, bool B_KMAJOR, bool C_ROWS>
+__global__ void __launch_bounds__(kThreads, CTAS)
 dsd_tc_kernel(const __grid_constant__ CUtensorMap m_s, const __grid_constant__ CUtensorMap m_b, DsdTcArgs a) {
-  using G = Geo<TN>;
+  using G = Geo<TN, CTAS>;
   constexpr int S = G::kStages;
+  constexpr int kAcc = G::kAcc;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = smem_raw + ((1024 - (saddr(smem_raw) & 1023)) & 1023);
   __shared__ uint64_t bar_full[S], bar_empty[S], bar_acc_full[2], bar_acc_empty[2];
   __shared__ uint32_t tmem_slot;
   __shared__ int failed[2];
   __shared__ volatile int stage_flags[S];
+  __shared__ Plan plan[2];
+  __shared__ uint64_t bar_plan_full[2], bar_plan_empty[2];
+  __shared__ uint32_t row_mask[4][32];           // planning warp: block-row r has a block in column 32 * word + bit
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int block = a.block;
@@ -136,10 +165,13 @@ dsd_tc_kernel(const __grid_constant__ CUtensorMap m_s, const __grid_constant__ C
     failed[0] = 0;
     failed[1] = kWaitBudget;
     for (int s = 0; s < S; ++s) { mbar_init(&bar_full[s], 2); mbar_init(&bar_empty[s], 1); }
-    for (int b = 0; b < 2; ++b) { mbar_init(&bar_acc_full[b], 1); mbar_init(&bar_acc_empty[b], 4); }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&bar_acc_full[b], 1); mbar_init(&bar_acc_empty[b], 4);
+      mbar_init(&bar_plan_full[b], 1); mbar_init(&bar_plan_empty[b], 2);
+    }
     mbar_init_fence();
   }
-  if (warp == 1) { tmem_alloc(&tmem_slot, 2 * TN); tmem_relinquish(); }
+  if (warp == 1) { tmem_alloc(&tmem_slot, kAcc * TN); tmem_relinquish(); }
   // the A part of every stage starts as zeros (see the loading thread)
   for (int i = tid; i < S * (kStageA / 16); i += kThreads)
     reinterpret_cast<uint4*>(smem + (i / (kStageA / 16)) * G::kStage)[i % (kStageA / 16)] = make_uint4(0, 0, 0, 0);
@@ -150,70 +182,165 @@ dsd_tc_kernel(const __grid_constant__ CUtensorMap m_s, const __grid_constant__ C
   const uint32_t tmem = tmem_slot;
   volatile int* fl = failed;
 
-  if (warp == 4) {
-    // ------------------------------------------------------------------ sparse operand
-    if (lane == 0) {
-      prefetch_map(&m_s);
-      uint64_t dirty = 0;                       // 8 bits per stage: which pieces of its A part hold a block
-      int it = 0;
-      bool ok = true;
-      Walk w;
-      for (int t = blockIdx.x; ok && t < a.total_tiles; t += gridDim.x) {
-        const Tile tc_ = tile_of(a, t);
-        w.init(a, tc_.h, tc_.tr, R);
-        int flags = kFirst;
-        int kh = 0, id[4];
-        while (ok && (kh || !w.done())) {
-          const int s = it % S;
-          if (it >= S && !mbar_wait(&bar_empty[s], ((it / S) - 1) & 1, fl)) { ok = false; break; }
-          unsigned char* sp = smem + s * G::kStage;
-          if (block == 128) {
-            if (!kh) w.next(a, id);
-            if (kh && w.done()) flags |= kLast;
-            stage_flags[s] = flags;
-            mbar_expect_tx(&bar_full[s], kStageA);
-            if (A_MN) {                               // rows kh * 64 .. of the stored block, its two halves of 64 columns
-              tma_load_3d(sp, &m_s, &bar_full[s], 0, id[0] * 128 + kh * 64, tc_.z);
-              tma_load_3d(sp + 8192, &m_s, &bar_full[s], 64, id[0] * 128 + kh * 64, tc_.z);
-            } else {
-              tma_load_3d(sp, &m_s, &bar_full[s], kh * 64, id[0] * 128, tc_.z);
-            }
-            kh ^= 1;
-          } else {
-            // pieces: block 64: row r at r * 8 KB; block 32: sub-tile u at u * 8 KB, row r at r * 2 KB
-            const uint32_t was = (uint32_t)(dirty >> (8 * s)) & 0xffu;
-            uint32_t now = 0, load = 0;
-            int row[8];
-            const int U = block == 64 ? 1 : 2;
+  if (warp == 7) {
+    // ------------------------------------------------------------------ planning
+    // The union of the tile's column lists as bit masks: lane w holds columns 32 w .. 32 w + 31
+    // of every block-row (the reduction side has at most 1024 blocks).  Every lane then writes
+    // the entries of its own columns: the position of a column in the union and of a block in
+    // its row's list are prefix counts of set bits.
+    const uint32_t full = 0xffffffffu;
+    int cb = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; ok && t < a.total_tiles; t += gridDim.x) {
+      const Tile tc_ = tile_of(a, t);
+      int rs = 0, re = 0;
+      {
+        const int br = tc_.tr * R + lane;
+        if (lane < R && br < a.Mb) { rs = a.row_ptr[tc_.h * a.Mb + br]; re = a.row_ptr[tc_.h * a.Mb + br + 1]; }
+      }
 #pragma unroll
-            for (int u = 0; u < 2; ++u) {
-              if (u < U) {
-                if (u == 1 && w.done()) { flags |= kHalf; now |= was & 0xf0u; break; }
-                w.next(a, id);
+      for (int r = 0; r < 4; ++r) row_mask[r][lane] = 0;
+      __syncwarp();
+      int start[4];
 #pragma unroll
-                for (int r = 0; r < 4; ++r) {
-                  const int p = u * 4 + r;
-                  row[p] = a.nnz_rows;
-                  if (id[r] >= 0) { row[p] = id[r] * block; now |= 1u << p; load |= 1u << p; }
-                  else if (was & (1u << p)) load |= 1u << p;
-                }
-              }
-            }
-            if (w.done()) flags |= kLast;
-            dirty = (dirty & ~(0xffull << (8 * s))) | ((uint64_t)now << (8 * s));
-            stage_flags[s] = flags;
-            const int piece = block == 64 ? 8192 : 2048;
-            mbar_expect_tx(&bar_full[s], __popc(load) * piece);
-#pragma unroll
-            for (int p = 0; p < 8; ++p)
-              if (load & (1u << p))
-                tma_load_3d(sp + (block == 64 ? p * 8192 : (p >> 2) * 8192 + (p & 3) * 2048), &m_s, &bar_full[s], 0, row[p], tc_.z);
-          }
-          flags = 0;
-          ++it;
+      for (int r = 0; r < 4; ++r) {
+        start[r] = __shfl_sync(full, rs, r);
+        const int end = __shfl_sync(full, re, r);
+        for (int j = start[r] + lane; j < end; j += 32) {
+          const int c = a.blk_col[j];
+          atomicOr(&row_mask[r][c >> 5], 1u << (c & 31));
         }
       }
-      if (ok) {                                                    // tells the issuing thread that nothing follows
+      __syncwarp();
+      uint32_t m[4];
+      int rank0[4];                               // blocks of row r in the columns before this lane's
+      uint32_t u = 0;
+#pragma unroll
+      for (int r = 0; r < 4; ++r) {
+        m[r] = row_mask[r][lane];
+        u |= m[r];
+        int tot;
+        rank0[r] = warp_exclusive_sum(__popc(m[r]), lane, &tot);
+      }
+      int total;
+      const int off = warp_exclusive_sum(__popc(u), lane, &total);
+      const int n_ent = block == 32 ? (total + 1) >> 1 : total;
+      const int chunks = n_ent > kChunk ? (n_ent + kChunk - 1) / kChunk : 1;
+      for (int c = 0; ok && c < chunks; ++c, ++cb) {
+        const int buf = cb & 1;
+        if (cb >= 2) {
+          int k = 1;
+          if (lane == 0) k = mbar_wait(&bar_plan_empty[buf], ((cb >> 1) - 1) & 1, fl) ? 1 : 0;
+          if (!__shfl_sync(full, k, 0)) { ok = false; break; }
+        }
+        const int lo = c * kChunk, hi = min(n_ent, lo + kChunk);
+        uint32_t bits = u;
+        for (int q = off; bits; ++q) {
+          const int bit = __ffs(bits) - 1;
+          bits &= bits - 1;
+          const int e = block == 32 ? q >> 1 : q, sub = block == 32 ? q & 1 : 0;
+          if (e < lo || e >= hi) continue;
+          int* E = plan[buf].e[e - lo];
+          E[8 + sub] = lane * 32 + bit;
+#pragma unroll
+          for (int r = 0; r < 4; ++r) {
+            int v = -1;
+            if ((m[r] >> bit) & 1u) {
+              const int idx = start[r] + rank0[r] + __popc(m[r] & ((1u << bit) - 1u));
+              v = (a.blk_id ? a.blk_id[idx] : idx) * block;
+            }
+            E[sub * 4 + r] = v;
+          }
+        }
+        if (lane == 0) {
+          if (block == 32 && (total & 1) && hi == n_ent && hi > lo) {     // the last entry has one column only
+            int* E = plan[buf].e[hi - 1 - lo];
+            E[9] = -1;
+            E[4] = E[5] = E[6] = E[7] = -1;
+          }
+          plan[buf].n = hi > lo ? hi - lo : 0;
+          plan[buf].last = c == chunks - 1;
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bar_plan_full[buf]);
+      }
+    }
+  } else if (warp == 4) {
+    // ------------------------------------------------------------------ sparse operand
+    // Lanes 0-7, one per piece of a stage's A part (block 64: two pieces of 8 KB, block 32: two
+    // sub-tiles of four pieces of 2 KB; block 128: lane 0, or lanes 0 and 1 for the two halves of
+    // a transposed block).  A piece without a block is loaded (as zeros, from past the last
+    // block) only if it held one.
+    if (lane < 8) {
+      const uint32_t m8 = 0xffu;
+      if (lane == 0) prefetch_map(&m_s);
+      uint32_t dirty = 0;                          // bit s: this lane's piece of ring slot s holds a block
+      int it = 0, cb = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; ok && t < a.total_tiles; t += gridDim.x) {
+        const Tile tc_ = tile_of(a, t);
+        int flags = kFirst, last_chunk = 0;
+        do {
+          const int buf = cb & 1;
+          int k = 1;
+          if (lane == 0) k = mbar_wait(&bar_plan_full[buf], (cb >> 1) & 1, fl) ? 1 : 0;
+          if (!__shfl_sync(m8, k, 0)) { ok = false; break; }
+          const int n = plan[buf].n;
+          last_chunk = plan[buf].last;
+          for (int e = 0; ok && e < n; ++e) {
+            const int* E = plan[buf].e[e];
+            const int mine = E[lane];
+            const bool half = block == 32 && E[9] < 0;
+            const bool last = last_chunk && e == n - 1;
+            const int reps = block == 128 ? 2 : 1;
+            for (int kh = 0; kh < reps; ++kh) {
+              const int s = it % S;
+              if (it >= S) {
+                k = 1;
+                if (lane == 0) k = mbar_wait(&bar_empty[s], ((it / S) - 1) & 1, fl) ? 1 : 0;
+                if (!__shfl_sync(m8, k, 0)) { ok = false; break; }
+              }
+              unsigned char* sp = smem + s * G::kStage;
+              if (block == 128) {
+                if (lane == 0) {
+                  stage_flags[s] = flags | ((last && kh) ? kLast : 0);
+                  mbar_expect_tx(&bar_full[s], kStageA);
+                }
+                __syncwarp(m8);
+                const int row = __shfl_sync(m8, mine, 0);
+                if (A_MN) {                          // rows kh * 64 .. of the stored block, its two halves of 64 columns
+                  if (lane < 2) tma_load_3d(sp + lane * 8192, &m_s, &bar_full[s], lane * 64, row + kh * 64, tc_.z);
+                } else if (lane == 0) {
+                  tma_load_3d(sp, &m_s, &bar_full[s], kh * 64, row, tc_.z);
+                }
+              } else {
+                const bool exists = block == 64 ? lane < 2 : !(half && lane >= 4);
+                bool ld = false;
+                if (exists) {
+                  if (mine >= 0) { ld = true; dirty |= 1u << s; }
+                  else if (dirty & (1u << s)) { ld = true; dirty &= ~(1u << s); }
+                }
+                const int piece = block == 64 ? 8192 : 2048;
+                const int nld = __popc(__ballot_sync(m8, ld));
+                if (lane == 0) {
+                  stage_flags[s] = flags | (last ? kLast : 0) | (half ? kHalf : 0);
+                  mbar_expect_tx(&bar_full[s], nld * piece);
+                }
+                __syncwarp(m8);
+                if (ld)
+                  tma_load_3d(sp + (block == 64 ? lane * 8192 : (lane >> 2) * 8192 + (lane & 3) * 2048), &m_s, &bar_full[s], 0,
+                              mine >= 0 ? mine : a.nnz_rows, tc_.z);
+              }
+              flags = 0;
+              ++it;
+            }
+          }
+          __syncwarp(m8);
+          if (lane == 0) mbar_arrive(&bar_plan_empty[buf]);
+          ++cb;
+        } while (ok && !last_chunk);
+      }
+      if (ok && lane == 0) {                                     // tells the issuing thread that nothing follows
         const int s = it % S;
         if (it < S || mbar_wait(&bar_empty[s], ((it / S) - 1) & 1, fl)) {
           stage_flags[s] = kEnd;
@@ -225,45 +352,46 @@ dsd_tc_kernel(const __grid_constant__ CUtensorMap m_s, const __grid_constant__ C
     // ------------------------------------------------------------------ dense operand
     if (lane == 0) {
       prefetch_map(&m_b);
-      int it = 0;
+      int it = 0, cb = 0;
       bool ok = true;
-      Walk w;
       for (int t = blockIdx.x; ok && t < a.total_tiles; t += gridDim.x) {
         const Tile tc_ = tile_of(a, t);
         const int n0 = tc_.nt * TN;
-        w.init(a, tc_.h, tc_.tr, R);
-        int kh = 0, id[4], col = 0;
-        while (ok && (kh || !w.done())) {
-          const int s = it % S;
-          if (it >= S && !mbar_wait(&bar_empty[s], ((it / S) - 1) & 1, fl)) { ok = false; break; }
-          unsigned char* sp = smem + s * G::kStage + kStageA;
-          if (block == 32) {
-            const int c0 = w.next(a, id);
-            const bool two = !w.done();
-            const int c1 = two ? w.next(a, id) : 0;
-            mbar_expect_tx(&bar_full[s], two ? G::kStageB : G::kStageB / 2);
-            if (B_KMAJOR) {
-              tma_load_4d(sp, &m_b, &bar_full[s], c0 * 32, n0, tc_.h, tc_.z);
-              if (two) tma_load_4d(sp + G::kStageB / 2, &m_b, &bar_full[s], c1 * 32, n0, tc_.h, tc_.z);
-            } else {
-              tma_load_5d(sp, &m_b, &bar_full[s], 0, c0 * 32, n0 / 64, tc_.h, tc_.z);
-              if (two) tma_load_5d(sp + G::kStageB / 2, &m_b, &bar_full[s], 0, c1 * 32, n0 / 64, tc_.h, tc_.z);
+        int last_chunk = 0;
+        do {
+          const int buf = cb & 1;
+          if (!mbar_wait(&bar_plan_full[buf], (cb >> 1) & 1, fl)) { ok = false; break; }
+          const int n = plan[buf].n;
+          last_chunk = plan[buf].last;
+          for (int e = 0; ok && e < n; ++e) {
+            const int c0 = plan[buf].e[e][8], c1 = plan[buf].e[e][9];
+            const int reps = block == 128 ? 2 : 1;
+            for (int kh = 0; kh < reps; ++kh) {
+              const int s = it % S;
+              if (it >= S && !mbar_wait(&bar_empty[s], ((it / S) - 1) & 1, fl)) { ok = false; break; }
+              unsigned char* bp = smem + s * G::kStage + kStageA;
+              if (block == 32) {
+                const bool two = c1 >= 0;
+                mbar_expect_tx(&bar_full[s], two ? G::kStageB : G::kStageB / 2);
+                if (B_KMAJOR) {
+                  tma_load_4d(bp, &m_b, &bar_full[s], c0 * 32, n0, tc_.h, tc_.z);
+                  if (two) tma_load_4d(bp + G::kStageB / 2, &m_b, &bar_full[s], c1 * 32, n0, tc_.h, tc_.z);
+                } else {
+                  tma_load_5d(bp, &m_b, &bar_full[s], 0, c0 * 32, n0 / 64, tc_.h, tc_.z);
+                  if (two) tma_load_5d(bp + G::kStageB / 2, &m_b, &bar_full[s], 0, c1 * 32, n0 / 64, tc_.h, tc_.z);
+                }
+              } else {
+                const int krow = block == 128 ? c0 * 128 + kh * 64 : c0 * 64;
+                mbar_expect_tx(&bar_full[s], G::kStageB);
+                if (B_KMAJOR) tma_load_4d(bp, &m_b, &bar_full[s], krow, n0, tc_.h, tc_.z);
+                else tma_load_5d(bp, &m_b, &bar_full[s], 0, krow, n0 / 64, tc_.h, tc_.z);
+              }
+              ++it;
             }
-          } else {
-            int krow;
-            if (block == 128) {
-              if (!kh) col = w.next(a, id);
-              krow = col * 128 + kh * 64;
-              kh ^= 1;
-            } else {
-              krow = w.next(a, id) * 64;
-            }
-            mbar_expect_tx(&bar_full[s], G::kStageB);
-            if (B_KMAJOR) tma_load_4d(sp, &m_b, &bar_full[s], krow, n0, tc_.h, tc_.z);
-            else tma_load_5d(sp, &m_b, &bar_full[s], 0, krow, n0 / 64, tc_.h, tc_.z);
           }
-          ++it;
-        }
+          mbar_arrive(&bar_plan_empty[buf]);
+          ++cb;
+        } while (ok && !last_chunk);
       }
       if (ok) {
         const int s = it % S;
@@ -288,36 +416,48 @@ dsd_tc_kernel(const __grid_constant__ CUtensorMap m_s, const __grid_constant__ C
       const uint32_t b_lbo = B_KMAJOR ? 1u << 16 : ((b32 ? 4096u : 8192u) >> 4) << 16;
       const uint32_t a_step = A_MN ? (b32 ? 64u : 128u) : 2u;
       const uint32_t b_step = B_KMAJOR ? 2u : 128u;
+      const uint32_t sb = saddr(smem) >> 4;
       int tiles = 0;
-      uint32_t d = tmem;
-      for (int it = 0;; ++it) {
-        const int s = it % S;
-        if (!mbar_wait(&bar_full[s], (it / S) & 1, fl)) break;
-        fence_after();
-        const int f = stage_flags[s];
-        if (f & kEnd) break;
-        if (f & kFirst) {
-          const int buf = tiles & 1;
-          if (tiles >= 2 && !mbar_wait(&bar_acc_empty[buf], ((tiles >> 1) - 1) & 1, fl)) break;
-          fence_after();
-          d = tmem + buf * TN;
-          ++tiles;
-        }
-        const uint32_t a0 = ((saddr(smem + s * G::kStage) & 0x3FFFF) >> 4) | a_lbo;
-        const uint32_t b0 = ((saddr(smem + s * G::kStage + kStageA) & 0x3FFFF) >> 4) | b_lbo;
+      uint32_t d = tmem, ph = 0;
+      bool run = true;
+      // one pass of the loop body per ring slot, so that every descriptor is a constant offset from `sb`
+      while (run) {
 #pragma unroll
-        for (int ks = 0; ks < 4; ++ks) {
-          if (b32 && ks >= 2 && (f & kHalf)) break;
-          const uint32_t acc = ((f & kFirst) && ks == 0) ? 0u : 1u;
-          // block 32: K-steps 2, 3 belong to the second sub-tile (8 KB further in A, half a stage further in B)
-          const uint32_t ao = b32 ? (ks >> 1) * (8192u >> 4) + (ks & 1) * a_step : ks * a_step;
-          const uint32_t bo = b32 ? (ks >> 1) * ((uint32_t)(G::kStageB / 2) >> 4) + (ks & 1) * b_step : ks * b_step;
-          const uint64_t da = (static_cast<uint64_t>(a_hi) << 32) | (a0 + ao);
-          const uint64_t db = (static_cast<uint64_t>(b_hi) << 32) | (b0 + bo);
-          mma_ss(d, da, db, idesc, acc);
+        for (int s = 0; s < S; ++s) {
+          if (!mbar_wait(&bar_full[s], ph, fl)) { run = false; break; }
+          fence_after();
+          const int f = stage_flags[s];
+          if (f & kEnd) { run = false; break; }
+          if (f & kFirst) {
+            const int buf = tiles % kAcc;
+            if (tiles >= kAcc && !mbar_wait(&bar_acc_empty[buf], ((tiles / kAcc) - 1) & 1, fl)) { run = false; break; }
+            fence_after();
+            d = tmem + buf * TN;
+            ++tiles;
+          }
+          const uint32_t a0 = ((sb + ((s * G::kStage) >> 4)) & 0x3FFFu) | a_lbo;
+          const uint32_t b0 = ((sb + ((s * G::kStage + kStageA) >> 4)) & 0x3FFFu) | b_lbo;
+          {
+            if (!b32) {
+              mma_desc(d, a0, a_hi, b0, b_hi, idesc, (f & kFirst) ? 0u : 1u);
+              mma_desc_acc(d, a0 + a_step, a_hi, b0 + b_step, b_hi, idesc);
+              mma_desc_acc(d, a0 + 2 * a_step, a_hi, b0 + 2 * b_step, b_hi, idesc);
+              mma_desc_acc(d, a0 + 3 * a_step, a_hi, b0 + 3 * b_step, b_hi, idesc);
+            } else {
+              // K-steps 2, 3 belong to the second sub-tile (8 KB further in A, half a stage further in B)
+              mma_desc(d, a0, a_hi, b0, b_hi, idesc, (f & kFirst) ? 0u : 1u);
+              mma_desc_acc(d, a0 + a_step, a_hi, b0 + b_step, b_hi, idesc);
+              if (!(f & kHalf)) {
+                const uint32_t a1 = a0 + (8192u >> 4), b1 = b0 + ((uint32_t)(G::kStageB / 2) >> 4);
+                mma_desc_acc(d, a1, a_hi, b1, b_hi, idesc);
+                mma_desc_acc(d, a1 + a_step, a_hi, b1 + b_step, b_hi, idesc);
+              }
+            }
+          }
+          commit(&bar_empty[s]);                                    // the stage is free once these MMAs have read it
+          if (f & kLast) commit(&bar_acc_full[(tiles - 1) % kAcc]);
         }
-        commit(&bar_empty[s]);                                      // the stage is free once these MMAs have read it
-        if (f & kLast) commit(&bar_acc_full[(tiles - 1) & 1]);
+        ph ^= 1;
       }
     }
   } else if (warp < 4) {
@@ -334,9 +474,9 @@ dsd_tc_kernel(const __grid_constant__ CUtensorMap m_s, const __grid_constant__ C
       const bool row_ok = grow < a.rows_total;
       T* crow = reinterpret_cast<T*>(a.c) + tc_.z * a.c_sz + tc_.h * a.c_sh + (int64_t)grow * a.c_sm +
                 (int64_t)(tc_.nt * TN) * a.c_sn;
-      const int buf = tiles & 1;
+      const int buf = tiles % kAcc;
       if (any) {
-        ok = mbar_wait_warp(&bar_acc_full[buf], (tiles >> 1) & 1, fl);
+        ok = mbar_wait_warp_idle(&bar_acc_full[buf], (tiles / kAcc) & 1, fl, lane);
         if (!ok) break;
         fence_after();
       }
@@ -377,30 +517,34 @@ dsd_tc_kernel(const __grid_constant__ CUtensorMap m_s, const __grid_constant__ C
   }
   fence_before();
   __syncthreads();
-  if (warp == 1) tmem_dealloc(tmem, 2 * TN);
+  if (warp == 1) tmem_dealloc(tmem, kAcc * TN);
   if (tid == 0 && failed[0]) atomicExch(&g_dsd_status, 4);
 }
 
-template <typename T, int TN, bool AM, bool BK, bool CR>
-int launch(const CUtensorMap& ms, const CUtensorMap& mb, const DsdTcArgs& a, int grid, cudaStream_t st) {
-  auto kern = dsd_tc_kernel<T, TN, AM, BK, CR>;
-  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Geo<TN>::kSmem);
+template <typename T, int TN, int CTAS, bool AM, bool BK, bool CR>
+int launch(const CUtensorMap& ms, const CUtensorMap& mb, const DsdTcArgs& a, int sms, cudaStream_t st) {
+  auto kern = dsd_tc_kernel<T, TN, CTAS, AM, BK, CR>;
+  constexpr int smem = Geo<TN, CTAS>::kSmem;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e != cudaSuccess) return fail(BSP_ERR_CUDA, "dsd (tcgen05): cannot reserve shared memory: %s", cudaGetErrorString(e));
-  kern<<<grid, kThreads, Geo<TN>::kSmem, st>>>(ms, mb, a);
+  const int grid = a.total_tiles < CTAS * sms ? a.total_tiles : CTAS * sms;
+  kern<<<grid, kThreads, smem, st>>>(ms, mb, a);
   e = cudaGetLastError();
   if (e != cudaSuccess) return fail(BSP_ERR_CUDA, "dsd (tcgen05) launch failed: %s", cudaGetErrorString(e));
   return BSP_OK;
 }
 
-template <typename T, int TN, bool AM>
-int launch_a(bool bk, bool cr, const CUtensorMap& ms, const CUtensorMap& mb, const DsdTcArgs& a, int grid, cudaStream_t st) {
-  if (bk) return cr ? launch<T, TN, AM, true, true>(ms, mb, a, grid, st) : launch<T, TN, AM, true, false>(ms, mb, a, grid, st);
-  return cr ? launch<T, TN, AM, false, true>(ms, mb, a, grid, st) : launch<T, TN, AM, false, false>(ms, mb, a, grid, st);
+template <typename T, int TN, int CTAS, bool AM>
+int launch_a(bool bk, bool cr, const CUtensorMap& ms, const CUtensorMap& mb, const DsdTcArgs& a, int sms, cudaStream_t st) {
+  if (bk) return cr ? launch<T, TN, CTAS, AM, true, true>(ms, mb, a, sms, st) : launch<T, TN, CTAS, AM, true, false>(ms, mb, a, sms, st);
+  return cr ? launch<T, TN, CTAS, AM, false, true>(ms, mb, a, sms, st) : launch<T, TN, CTAS, AM, false, false>(ms, mb, a, sms, st);
 }
 
 template <typename T, int TN>
-int launch_t(bool am, bool bk, bool cr, const CUtensorMap& ms, const CUtensorMap& mb, const DsdTcArgs& a, int grid, cudaStream_t st) {
-  return am ? launch_a<T, TN, true>(bk, cr, ms, mb, a, grid, st) : launch_a<T, TN, false>(bk, cr, ms, mb, a, grid, st);
+int launch_t(bool am, bool bk, bool cr, const CUtensorMap& ms, const CUtensorMap& mb, const DsdTcArgs& a, int sms, cudaStream_t st) {
+  if (a.block == 128)
+    return am ? launch_a<T, TN, 1, true>(bk, cr, ms, mb, a, sms, st) : launch_a<T, TN, 1, false>(bk, cr, ms, mb, a, sms, st);
+  return am ? launch_a<T, TN, 2, true>(bk, cr, ms, mb, a, sms, st) : launch_a<T, TN, 2, false>(bk, cr, ms, mb, a, sms, st);
 }
 
 // Number of SMs of the current device (one persistent CTA each).
@@ -478,12 +622,11 @@ int dsd_tc(const void* s, const void* b, void* c, int dtype, int block, int Z, i
   else { a.row_ptr = m.row_ptr; a.blk_col = m.blk_col; a.blk_id = nullptr; }
   const int sms = sm_count();
   if (sms <= 0) return fail(BSP_ERR_CUDA, "dsd (tcgen05): cannot query the device");
-  const int grid = a.total_tiles < sms ? a.total_tiles : sms;
   if (dtype == BSP_F16)
-    return TN == 256 ? launch_t<__half, 256>(trans_s != 0, bk, cr, ms, mb, a, grid, st)
-                     : launch_t<__half, 128>(trans_s != 0, bk, cr, ms, mb, a, grid, st);
-  return TN == 256 ? launch_t<__nv_bfloat16, 256>(trans_s != 0, bk, cr, ms, mb, a, grid, st)
-                   : launch_t<__nv_bfloat16, 128>(trans_s != 0, bk, cr, ms, mb, a, grid, st);
+    return TN == 256 ? launch_t<__half, 256>(trans_s != 0, bk, cr, ms, mb, a, sms, st)
+                     : launch_t<__half, 128>(trans_s != 0, bk, cr, ms, mb, a, sms, st);
+  return TN == 256 ? launch_t<__nv_bfloat16, 256>(trans_s != 0, bk, cr, ms, mb, a, sms, st)
+                   : launch_t<__nv_bfloat16, 128>(trans_s != 0, bk, cr, ms, mb, a, sms, st);
 }
 
 // 0, or non-zero when a bounded wait inside the kernel above expired (synchronises the device).

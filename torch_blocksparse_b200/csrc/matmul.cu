@@ -86,7 +86,8 @@ int run_dsd(const void* s, const void* b, void* c, int dtype, int block, int Z, 
             const Meta& m, cudaStream_t st) {
   // (a layout without any block has no sparse tensor to describe to the tensor-map encoder: the
   // mma.sync kernel writes the zeros)
-  if (g_matmul_tc.load() && Z <= 65535 && m.nnz > 0 &&
+  // (the tcgen05 kernel plans a tile with one bit per block of the reduction side, 1024 at most)
+  if (g_matmul_tc.load() && m.nnz > 0 && (trans_s ? m.Mb : m.Nb) <= 1024 &&
       dsd_tc_eligible(s, b, c, dtype, block, N, trans_s, s_sz, b_sz, b_sh, b_sk, b_sn, c_sz, c_sh, c_sm, c_sn))
     return dsd_tc(s, b, c, dtype, block, Z, N, s_sz, trans_s, b_sz, b_sh, b_sk, b_sn, c_sz, c_sh, c_sm, c_sn, m, st);
   if (dtype == BSP_F32)
@@ -115,7 +116,8 @@ extern "C" int bsp_sdd(const void* a, const void* b, void* c, int dtype, int blo
   if (int rc = check_sparse("sdd", "c", c, dtype, c_sz)) return rc;
   if (m.nnz == 0) return BSP_OK;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  if (g_matmul_tc.load() && (int64_t)m.H * ((m.Mb + 1) / 2) <= 65535 &&
+  // (the tcgen05 kernel's grid: groups of 128 rows per head in y, the batch in z)
+  if (g_matmul_tc.load() && Z <= 65535 && (int64_t)m.H * ((m.Mb * block + 127) / 128) <= 65535 &&
       sdd_tc_eligible(a, b, c, dtype, block, K, a_sz, a_sh, a_sm, a_sk, b_sz, b_sh, b_sk, b_sn, c_sz))
     return sdd_tc(a, b, c, dtype, block, Z, K, a_sz, a_sh, a_sm, a_sk, b_sz, b_sh, b_sk, b_sn, c_sz, m, st);
   if (dtype == BSP_F32)

@@ -5,22 +5,23 @@
 // torch_blocksparse/matmul.py:354-360): every nonzero block (i, j) of the layout receives
 // op(A)[rows of block-row i, :] . op(B)[:, columns of block-column j].
 //
-// Geometry: every MMA has M = 128 and the CTA's accumulator is 128 x 128.
-//   block 128  a CTA computes one nonzero block;
-//   block 64   a CTA takes block-rows 2i and 2i + 1 and two consecutive entries of the union
-//              of their column lists: four blocks, of which those the layout holds are stored;
-//   block 32   four block-rows and four consecutive entries of the union of their column
-//              lists: sixteen blocks, of which those the layout holds are stored.
-// The reduction runs over K in stages of 64: 16 KB of A (128 m x 64 k, two TMA boxes of 64 x
-// 64) and 16 KB of B (64 k x 128 n, one box per column block).  Either operand may have k or
-// its other dimension contiguous: k contiguous gives K-major tiles, the other case MN-major
-// tiles (groups of 64 rows or columns, 8 KB apart, in one descriptor; the 32 columns of a
-// block-32 column block form groups of 4 KB in the 64-byte swizzle); every K-step is one
-// 128 x 128 x 16 MMA.  A box that lies outside the tensor (block-rows past the last one,
-// missing columns at the end of the union) is filled with zeros.
+// Geometry: every MMA has M = 128 and a CTA's accumulator is 128 x 256: R = 128 / block
+// block-rows by 2 R consecutive entries of the union of their column lists (block 128: two
+// blocks of one row, block 64: 2 x 4, block 32: 4 x 8 candidate blocks), of which those the
+// layout holds are stored.  A group whose entries fill at most half of the 256 columns runs
+// with N = 128.  The reduction runs over K in stages of 64: 16 KB of A (128 m x 64 k, two TMA
+// boxes of 64 x 64) and up to 32 KB of B (64 k x 256 n, one box per column block, two for a
+// block of 128 with n contiguous).  Either operand may have k or its other dimension
+// contiguous: k contiguous gives K-major tiles, the other case MN-major tiles (groups of 64
+// rows or columns, 8 KB apart, in one descriptor; the 32 columns of a block-32 column block
+// form groups of 4 KB in the 64-byte swizzle); every K-step is one 128 x N x 16 MMA.  A box
+// that lies outside the tensor (block-rows past the last one) is filled with zeros; column
+// blocks past the end of the union are neither loaded nor computed (N = 128) or computed on
+// whatever the ring holds and not stored.
 //
-// Warps: 0-3 write the blocks back, 4 issues the TMA loads, 5 the MMAs (one thread each).
-// mbarriers only; every wait is bounded and a wait that expires sets a device status word.
+// Warps: 0-3 write the blocks back, 4 issues the TMA loads (one lane per box), 5 the MMAs
+// (one thread).  Two CTAs per SM, two stages each.  mbarriers only; every wait is bounded
+// and a wait that expires sets a device status word.
 #include <algorithm>
 #include "mm_tc.cuh"
 
@@ -34,16 +35,18 @@ namespace {
 using namespace tc;
 using namespace mmtc;
 
-constexpr int kStages = 3;
-constexpr int kStageBytes = 32768;
+constexpr int kStages = 2;
+constexpr int kStageA = 16384, kStageB = 32768;
+constexpr int kStageBytes = kStageA + kStageB;
 constexpr int kSmem = kStages * kStageBytes + 1024;
 constexpr int kThreads = 192;
+constexpr int kTN = 256;
 
 struct SddTcArgs {
   void* c;
   int64_t c_sz;
   int H, Mb, Nb, block, K, nnz;
-  int tiles_per_head;                          // block 64: pairs of block-rows per head
+  int tiles_per_head;                          // groups of R block-rows per head
   const int32_t *row_ptr, *blk_row, *blk_col, *blk_head;
 };
 
@@ -57,105 +60,111 @@ sdd_tc_kernel(const __grid_constant__ CUtensorMap m_a, const __grid_constant__ C
   __shared__ uint64_t bar_full[kStages], bar_empty[kStages], bar_done;
   __shared__ uint32_t tmem_slot;
   __shared__ int failed[2];
-  // work of this CTA: head, first row of A, its column blocks (first column of B, or -1; two of
-  // 64 columns or four of 32) and the ids of the blocks to store ([block-row][column block], -1: none)
-  __shared__ int w_h, w_m0, w_n[4], w_id[4][4];
+  // work of this CTA: head, first row of A, its column blocks (first column of B, or -1), how
+  // many there are, and the ids of the blocks to store ([block-row][column block], -1: none)
+  __shared__ int w_h, w_m0, w_cols, w_n[8], w_id[4][8];
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int z = blockIdx.z, block = a.block;
+  const int R = 128 / block, NC = 2 * R;        // block-rows of a tile, column blocks of a group
 
   if (tid == 0) {
     failed[0] = 0;
     failed[1] = kWaitBudget;
-    for (int i = 0; i < 4; ++i) {
-      w_n[i] = -1;
-      for (int j = 0; j < 4; ++j) w_id[i][j] = -1;
+    for (int j = 0; j < 8; ++j) {
+      w_n[j] = -1;
+      for (int i = 0; i < 4; ++i) w_id[i][j] = -1;
     }
-    if (block == 128) {
-      const int e = blockIdx.x;
-      w_h = a.blk_head[e];
-      w_m0 = a.blk_row[e] * 128;
-      w_n[0] = a.blk_col[e] * 128;
-      w_n[1] = w_n[0] + 64;
-      w_id[0][0] = e;
-    } else {
-      const int tile = blockIdx.y, g = blockIdx.x;   // the groups of a tile are neighbours in the launch: they share A in L2
-      const int R = 128 / block;                      // block-rows of a tile = column blocks of a group
-      const int h = tile / a.tiles_per_head, r0 = R * (tile % a.tiles_per_head);
-      w_h = h;
-      w_m0 = r0 * block;
-      int i[4], e[4], c[4];
-      for (int r = 0; r < 4; ++r) {
-        i[r] = e[r] = 0;
-        if (r < R && r0 + r < a.Mb) { i[r] = a.row_ptr[h * a.Mb + r0 + r]; e[r] = a.row_ptr[h * a.Mb + r0 + r + 1]; }
-        c[r] = i[r] < e[r] ? a.blk_col[i[r]] : kNone;
+    const int tile = blockIdx.y, g = blockIdx.x;     // the groups of a tile are neighbours in the launch: they share A in L2
+    const int h = tile / a.tiles_per_head, r0 = R * (tile % a.tiles_per_head);
+    w_h = h;
+    w_m0 = r0 * block;
+    int i[4], e[4], c[4];
+    for (int r = 0; r < 4; ++r) {
+      i[r] = e[r] = 0;
+      if (r < R && r0 + r < a.Mb) { i[r] = a.row_ptr[h * a.Mb + r0 + r]; e[r] = a.row_ptr[h * a.Mb + r0 + r + 1]; }
+      c[r] = i[r] < e[r] ? a.blk_col[i[r]] : kNone;
+    }
+    // entries NC g .. NC g + NC - 1 of the union of the column lists (each in column order)
+    int cols = 0;
+    if (R == 1) {                                     // one list: its entries directly
+      const int first = i[0] + NC * g;
+      for (int j = 0; j < NC && first + j < e[0]; ++j) {
+        w_n[j] = a.blk_col[first + j] * block;
+        w_id[0][j] = first + j;
+        cols = j + 1;
       }
-      // entries R g .. R g + R - 1 of the union of the column lists (each in column order)
-      for (int n = 0; n < R * g + R; ++n) {
+    } else {
+      for (int n = 0; n < NC * g + NC; ++n) {
         const int col = min(min(c[0], c[1]), min(c[2], c[3]));
         if (col == kNone) break;
-        if (n >= R * g) w_n[n - R * g] = col * block;
+        if (n >= NC * g) { w_n[n - NC * g] = col * block; cols = n - NC * g + 1; }
         for (int r = 0; r < 4; ++r)
           if (c[r] == col) {
-            if (n >= R * g) w_id[r][n - R * g] = i[r];
+            if (n >= NC * g) w_id[r][n - NC * g] = i[r];
             ++i[r];
             c[r] = i[r] < e[r] ? a.blk_col[i[r]] : kNone;
           }
       }
     }
+    w_cols = cols;
     for (int s = 0; s < kStages; ++s) { mbar_init(&bar_full[s], 1); mbar_init(&bar_empty[s], 1); }
     mbar_init(&bar_done, 1);
     mbar_init_fence();
   }
   __syncthreads();
-  if (w_n[0] < 0) return;                      // this group of columns does not exist (uniform)
-  if (warp == 1) { tmem_alloc(&tmem_slot, 128); tmem_relinquish(); }
+  if (w_cols == 0) return;                     // this group of columns does not exist (uniform)
+  if (warp == 1) { tmem_alloc(&tmem_slot, kTN); tmem_relinquish(); }
   fence_before();
   __syncthreads();
   fence_after();
   const uint32_t tmem = tmem_slot;
   const int ns = a.K / 64;
   const int h = w_h, m0 = w_m0;
+  // columns computed: 128 when the group's column blocks fill at most half of the accumulator
+  const int ncomp = w_cols * block <= 128 ? 128 : 256;
   volatile int* fl = failed;
 
   if (warp == 4) {
     // ------------------------------------------------------------------ TMA producer
-    if (lane == 0) {
-      prefetch_map(&m_a); prefetch_map(&m_b);
-      // a missing column block: a box past the end of B, filled with zeros
-      int nb[4];
-      for (int j = 0; j < 4; ++j) nb[j] = w_n[j] >= 0 ? w_n[j] : a.Nb * block;
+    // lanes 0-7: the boxes of B (block 128 with n contiguous: two per column block; else one per
+    // column block), lanes 8 and 9: the two boxes of A
+    if (lane < 10) {
+      const uint32_t m10 = 0x3ffu;
+      if (lane == 0) { prefetch_map(&m_a); prefetch_map(&m_b); }
+      const bool split = block == 128 && B_MN;                    // a column block of 128 n-contiguous columns takes two boxes of 64
+      const int nbox = split ? 2 * w_cols : w_cols;               // boxes of B that exist
+      const int box_bytes = split ? 8192 : block * 128;
+      const int cj = split ? lane >> 1 : lane;                    // column block of this lane's box
+      const bool mine = lane < 8 && lane < nbox && (split ? lane < 4 : true);
+      const int n_first = mine ? w_n[cj] + (split ? (lane & 1) * 64 : 0) : 0;
+      const uint32_t tx = kStageA + nbox * box_bytes;
+      int ok = 1;
       for (int it = 0; it < ns; ++it) {
         const int s = it % kStages, k0 = it * 64;
-        if (it >= kStages && !mbar_wait(&bar_empty[s], ((it / kStages) - 1) & 1, fl)) break;
-        unsigned char* sp = smem + s * kStageBytes;
-        mbar_expect_tx(&bar_full[s], kStageBytes);
-        if (A_MN) {                               // [k][m] in memory: 64 m x 64 k-rows per box
-          tma_load_4d(sp, &m_a, &bar_full[s], m0, k0, h, z);
-          tma_load_4d(sp + 8192, &m_a, &bar_full[s], m0 + 64, k0, h, z);
-        } else {                                  // [m][k]: 64 k x 64 m-rows per box
-          tma_load_4d(sp, &m_a, &bar_full[s], k0, m0, h, z);
-          tma_load_4d(sp + 8192, &m_a, &bar_full[s], k0, m0 + 64, h, z);
+        if (it >= kStages) {
+          if (lane == 0) ok = mbar_wait(&bar_empty[s], ((it / kStages) - 1) & 1, fl) ? 1 : 0;
+          ok = __shfl_sync(m10, ok, 0);
+          if (!ok) break;
         }
-        if (block == 32) {                        // four column blocks of 32: 4 KB each in either form
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            if (B_MN) tma_load_4d(sp + 16384 + j * 4096, &m_b, &bar_full[s], nb[j], k0, h, z);
-            else tma_load_4d(sp + 16384 + j * 4096, &m_b, &bar_full[s], k0, nb[j], h, z);
-          }
-        } else if (B_MN) {                        // [k][n]: 64 n x 64 k-rows per box
-          tma_load_4d(sp + 16384, &m_b, &bar_full[s], nb[0], k0, h, z);
-          tma_load_4d(sp + 16384 + 8192, &m_b, &bar_full[s], nb[1], k0, h, z);
-        } else {                                  // [n][k]: 64 k x 64 n-rows per box
-          tma_load_4d(sp + 16384, &m_b, &bar_full[s], k0, nb[0], h, z);
-          tma_load_4d(sp + 16384 + 8192, &m_b, &bar_full[s], k0, nb[1], h, z);
+        unsigned char* sp = smem + s * kStageBytes;
+        if (lane == 0) mbar_expect_tx(&bar_full[s], tx);
+        __syncwarp(m10);
+        if (lane >= 8) {
+          const int half = lane - 8;
+          if (A_MN) tma_load_4d(sp + half * 8192, &m_a, &bar_full[s], m0 + half * 64, k0, h, z);   // [k][m]: 64 m x 64 k-rows
+          else tma_load_4d(sp + half * 8192, &m_a, &bar_full[s], k0, m0 + half * 64, h, z);        // [m][k]: 64 k x 64 m-rows
+        } else if (mine) {
+          unsigned char* bp = sp + kStageA + lane * box_bytes;
+          if (B_MN) tma_load_4d(bp, &m_b, &bar_full[s], n_first, k0, h, z);                        // [k][n]
+          else tma_load_4d(bp, &m_b, &bar_full[s], k0, n_first, h, z);                             // [n][k]
         }
       }
     }
   } else if (warp == 5) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
-      const uint32_t idesc = instr_desc(128, 128, B_MN ? 1 : 0, Bf<T>::v) | (A_MN ? 1u << 15 : 0u);
+      const uint32_t idesc = instr_desc(128, ncomp, B_MN ? 1 : 0, Bf<T>::v) | (A_MN ? 1u << 15 : 0u);
       bool ok = true;
       for (int it = 0; ok && it < ns; ++it) {
         const int s = it % kStages;
@@ -165,8 +174,8 @@ sdd_tc_kernel(const __grid_constant__ CUtensorMap m_a, const __grid_constant__ C
         // (block 32, MN-major B: groups of 32 columns in the 64-byte swizzle, 64 k-rows of 64 bytes
         // = 4 KB apart, 8-row groups of 512 bytes, 16 rows = 1 KB per K-step)
         const bool b64s = B_MN && block == 32;
-        const uint32_t b_lo = B_MN ? (((saddr(smem + s * kStageBytes + 16384) & 0x3FFFF) >> 4) | ((b64s ? 256u : 512u) << 16))
-                                   : desc_lo(saddr(smem + s * kStageBytes + 16384));
+        const uint32_t b_lo = B_MN ? (((saddr(smem + s * kStageBytes + kStageA) & 0x3FFFF) >> 4) | ((b64s ? 256u : 512u) << 16))
+                                   : desc_lo(saddr(smem + s * kStageBytes + kStageA));
         const uint32_t b_hi = b64s ? ((512u >> 4) | (1u << 14) | (4u << 29)) : kDescHi;
         ok = mbar_wait(&bar_full[s], (it / kStages) & 1, fl);
         if (!ok) break;
@@ -185,21 +194,20 @@ sdd_tc_kernel(const __grid_constant__ CUtensorMap m_a, const __grid_constant__ C
   } else {
     // ------------------------------------------------------------------ write-back
     const int row = warp * 32 + lane;
-    const int rh = block == 32 ? row >> 5 : row >> 6;
-    if (mbar_wait_warp(&bar_done, 0, fl)) {
+    const int rh = block == 128 ? 0 : block == 64 ? row >> 6 : row >> 5;
+    if (mbar_wait_warp_idle(&bar_done, 0, fl, lane)) {
       fence_after();
       const uint32_t ta = tmem + ((uint32_t)(warp * 32) << 16);
       T* cz = reinterpret_cast<T*>(a.c) + z * a.c_sz;
 #pragma unroll 1
-      for (int c = 0; c < 128; c += 32) {
-        // block 128: one block, this thread's row of 128 columns; block 64: block [rh][c / 64];
-        // block 32: block [rh][c / 32], a whole row of it
-        const int id = block == 128 ? w_id[0][0] : block == 64 ? w_id[rh][c >> 6] : w_id[rh][c >> 5];
+      for (int c = 0; c < ncomp; c += 32) {
+        // the block this thread's 32 columns belong to: [rh][c / block]
+        const int id = block == 128 ? w_id[0][c >> 7] : block == 64 ? w_id[rh][c >> 6] : w_id[rh][c >> 5];
         if (id < 0) continue;                                        // uniform per warp
         uint32_t r[32];
         tmem_ld32(ta + c, r);
         tmem_ld_wait();
-        T* dst = block == 128 ? cz + (int64_t)id * 16384 + row * 128 + c
+        T* dst = block == 128 ? cz + (int64_t)id * 16384 + row * 128 + (c & 127)
                  : block == 64 ? cz + (int64_t)id * 4096 + (row & 63) * 64 + (c & 63)
                                : cz + (int64_t)id * 1024 + (row & 31) * 32;
 #pragma unroll
@@ -216,7 +224,7 @@ sdd_tc_kernel(const __grid_constant__ CUtensorMap m_a, const __grid_constant__ C
   }
   fence_before();
   __syncthreads();
-  if (warp == 1) tmem_dealloc(tmem, 128);
+  if (warp == 1) tmem_dealloc(tmem, kTN);
   if (tid == 0 && failed[0]) atomicExch(&g_sdd_status, 5);
 }
 
@@ -272,23 +280,19 @@ int sdd_tc(const void* a, const void* b, void* c, int dtype, int block, int Z, i
   const int64_t M = (int64_t)m.Mb * block, N = (int64_t)m.Nb * block;
   CUtensorMap ma, mb;
   if (int rc = am ? dense_map(&ma, a, dtype, Z, m.H, M, K, a_sk, a_sh, a_sz) : dense_map(&ma, a, dtype, Z, m.H, K, M, a_sm, a_sh, a_sz)) return rc;
-  // (block 32: one box per column block, 32 columns of 64 k)
-  const int bn = block == 32 ? 32 : 64;
+  // (one box per column block: 32, 64 or 128 columns of 64 k; with n contiguous a box holds 64
+  // columns at most, so a block of 128 takes two)
+  const int bn = block == 32 ? 32 : (bm || block == 64) ? 64 : 128;
   if (int rc = bm ? dense_map(&mb, b, dtype, Z, m.H, N, K, b_sk, b_sh, b_sz, bn, 64)
                   : dense_map(&mb, b, dtype, Z, m.H, K, N, b_sn, b_sh, b_sz, 64, bn)) return rc;
   SddTcArgs p = {};
   p.c = c; p.c_sz = c_sz; p.H = m.H; p.Mb = m.Mb; p.Nb = m.Nb; p.block = block; p.K = K; p.nnz = m.nnz;
-  const int R = 128 / block;                        // block-rows per tile and column blocks per group (block 32 / 64)
+  const int R = 128 / block, NC = 2 * R;            // block-rows per tile, column blocks per group
   p.tiles_per_head = (m.Mb + R - 1) / R;
   p.row_ptr = m.row_ptr; p.blk_row = m.blk_row; p.blk_col = m.blk_col; p.blk_head = m.blk_head;
-  dim3 grid;
-  if (block == 128) {
-    grid = dim3(m.nnz, 1, Z);
-  } else {
-    // the union of R column lists has at most R * max_row entries, and never more than Nb
-    const int groups = (std::min(m.Nb, R * std::max(m.max_row, 1)) + R - 1) / R;
-    grid = dim3(groups, m.H * p.tiles_per_head, Z);
-  }
+  // the union of R column lists has at most R * max_row entries, and never more than Nb
+  const int groups = (std::min(m.Nb, R * std::max(m.max_row, 1)) + NC - 1) / NC;
+  dim3 grid(groups, m.H * p.tiles_per_head, Z);
   if (dtype == BSP_F16) return launch_t<__half>(am, bm, ma, mb, p, grid, st);
   return launch_t<__nv_bfloat16>(am, bm, ma, mb, p, grid, st);
 }

@@ -62,6 +62,24 @@ BSP_DEVI bool mbar_wait_warp(uint64_t* bar, uint32_t parity, volatile int* faile
   return __all_sync(0xffffffffu, mbar_wait(bar, parity, failed));
 }
 
+// A whole warp waiting for something that takes long (a write-back warp waiting for a tile's
+// products): lane 0 alone polls, with a pause between attempts, and shares the outcome, so
+// that the waiting warps leave the shared-memory pipe and the issue slots to the others.
+BSP_DEVI bool mbar_wait_warp_idle(uint64_t* bar, uint32_t parity, volatile int* failed, int lane) {
+  int ok = 1;
+  if (lane == 0) {
+    ok = 0;
+    const int budget = failed[1];
+    for (int i = 0; i < budget; ++i) {
+      if (mbar_try_wait(bar, parity)) { ok = 1; break; }
+      if ((i & 63) == 63 && failed[0]) break;
+      __nanosleep(128);
+    }
+    if (!ok) failed[0] = 1;
+  }
+  return __shfl_sync(0xffffffffu, ok, 0) != 0;
+}
+
 // ---- TMA ----------------------------------------------------------------------
 BSP_DEVI void tma_load_4d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1, int c2, int c3) {
   asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
