@@ -275,8 +275,9 @@ def make_steps(mod, c, dev, n_sets):
     return step, state
 
 
-def attention_section(name, c, dev, steps, pk, T, dtype_name):
-    """One-GPU timing of a whole configuration (extra keys of the N = 1 line)."""
+def attention_section(name, c, dev, steps, pk, T, dtype_name, **extra):
+    """One-GPU timing of a whole configuration (extra keys of the N = 1 line); `extra`: rpe / masks
+    handed to the attention call."""
     from torch_blocksparse_b200 import SparseSelfAttention
     layout, block = c['layout'], c['block']
     Z, _, L, D = c['q'].shape
@@ -286,7 +287,7 @@ def attention_section(name, c, dev, steps, pk, T, dtype_name):
 
     def step(i):
         q.grad = k.grad = v.grad = None
-        mod(q, k, v).backward(do)
+        mod(q, k, v, **extra).backward(do)
 
     _, prof = T.run(step, max(2, steps // 2), warmup=3, profile=True)      # per-kernel durations
     t, _ = T.run(step, steps, warmup=2, profile=False)                     # the step as a user issues it
@@ -709,6 +710,22 @@ def run_ours(args):
             line['config4_' + other] = attention_section('config4 %s, FP16, Z=%d' % (other, Z), cb, dev,
                                                          max(3, args.steps // 2), pk, T1, 'f16')
             del cb
+            torch.cuda.empty_cache()
+            # configuration 4 called with configuration 3's optional inputs: a relative position bias
+            # (broadcast over the batch), a key-padding mask ('add', -inf) and a causal 'mul' mask
+            cm = problem_entries(args.attention, list(range(Z)))
+            gm = torch.Generator(device=dev).manual_seed(3)
+            rpe = 0.1 * torch.randn((HEADS, SEQ, SEQ), generator=gm, device=dev, dtype=torch.float16)
+            lengths = torch.randint(SEQ // 2, SEQ + 1, (Z,), generator=torch.Generator().manual_seed(3))
+            kpm = torch.zeros((Z, SEQ), dtype=torch.float16)
+            kpm[torch.arange(SEQ)[None, :] >= lengths[:, None]] = float('-inf')
+            sec = attention_section('config4 %s, FP16, Z=%d, with rpe [H, L, L], key-padding mask and causal mask'
+                                    % (args.attention, Z), cm, dev, max(3, args.steps // 2), pk, T1, 'f16',
+                                    rpe=rpe, key_padding_mask=kpm.to(dev),
+                                    attn_mask=torch.tril(torch.ones((SEQ, SEQ), dtype=torch.float16, device=dev)))
+            sec['ratio_to_plain_step'] = sec['ms_per_step'] / line['ms_per_step']
+            line['config4_with_config3_inputs'] = sec
+            del cm, rpe, kpm
             torch.cuda.empty_cache()
             # configuration 5 at its full size on one GPU (17 GB of operands and results); the inputs
             # are drawn on the device (the CPU generator needs a minute for 4 x 1 G values)

@@ -269,6 +269,38 @@ def test_dsd_dds_tcgen05_kernel(mode, ta, tb, block, dtype, width):
     assert fused.device_status() == 0
 
 
+@pytest.mark.parametrize('mode,ta,tb', [('dsd', False, False), ('dsd', True, False), ('dds', False, True)])
+@pytest.mark.parametrize('block,nred', [(32, 200), (64, 160), (128, 140), (32, 1056)])
+def test_dsd_dds_long_reduction_side(mode, ta, tb, block, nred):
+    """Many blocks on the reduction side: a tile whose plan does not fit one buffer of the
+    tcgen05 kernel (more than 64 entries: it is handed over in several pieces), and 1056
+    blocks, more than that kernel plans for (the mma.sync kernel takes the call).  Rows that are
+    nearly full, one empty block-row; forward against the dense-masked oracle."""
+    from torch_blocksparse_b200 import fused
+    Z, H = 1, 2
+    nout = 5                                                    # block-rows on the other side: the last tile is not full
+    K, big = nred * block, nout * block
+    M, N = (big, 128) if mode == 'dsd' else (128, big)
+    g = torch.Generator().manual_seed(nred + block)
+    AS = (K, M) if ta else (M, K)
+    BS = (N, K) if tb else (K, N)
+    sshape = AS if mode == 'dsd' else BS
+    layout = (torch.rand((H, sshape[0] // block, sshape[1] // block), generator=g) < 0.7).long()
+    red = (1 if ta else 2) if mode == 'dsd' else (2 if tb else 1)   # the layout dimension that is summed over
+    if red == 2:
+        layout[1, 1, :] = 0
+    else:
+        layout[1, :, 1] = 0
+    x = (torch.randn((Z, H) + AS, generator=g) * K ** -0.5).half()
+    w = (torch.randn((Z, H) + BS, generator=g)).half()
+    a = dm.dense_to_sparse(x, layout, block) if mode == 'dsd' else x
+    b = dm.dense_to_sparse(w, layout, block) if mode == 'dds' else w
+    want = dm.matmul_reference(a, b, mode, ta, tb, layout, block)[0]
+    got = MatMul(layout, block, mode, trans_a=ta, trans_b=tb)(a.to(DEV), b.to(DEV))
+    assert_close(got.cpu(), want, '%s block %d, %d blocks summed' % (mode, block, nred))
+    assert fused.device_status() == 0
+
+
 @pytest.mark.parametrize('ta', [False, True])
 @pytest.mark.parametrize('tb', [False, True])
 @pytest.mark.parametrize('block', [32, 64, 128])

@@ -107,7 +107,8 @@ BSP_DEVI void kpm_terms8(const unsigned char* p, int mul, float (&b)[8]) {
   }
 }
 // Relative position bias and attention mask (XT variants).  Their 64 x 64 pieces for a chunk
-// travel with it: per half of the tile one box of rpe at `xt` and one of the mask 16 KB further,
+// travel with it: per half of the tile one box of rpe at `xt` and one of the mask 16 KB further
+// (at `xt` itself when there is no rpe),
 // rows of 128 bytes, 16-byte units swizzled by the row as TMA writes them.  Rows of a box are
 // query rows, columns key columns.  The terms are added in the base-2 domain; a 'mul' mask
 // turns a zero into -inf and anything else into 0 (softmax.py:104-110 of the reference).
@@ -129,7 +130,7 @@ BSP_DEVI void xt_add8(const unsigned char* xt, const int has_rpe, const int am_m
     }
   }
   if (am_mode) {
-    const uint4 raw = *reinterpret_cast<const uint4*>(xt + 16384 + off);
+    const uint4 raw = *reinterpret_cast<const uint4*>(xt + (has_rpe ? 16384 : 0) + off);
     const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
@@ -151,7 +152,7 @@ BSP_DEVI float xt_term(const unsigned char* xt, const int has_rpe, const int am_
   float t = 0.f;
   if (has_rpe) t = static_cast<float>(*reinterpret_cast<const T*>(xt + off)) * kLog2eT;
   if (am_mode) {
-    const float m = static_cast<float>(*reinterpret_cast<const T*>(xt + 16384 + off));
+    const float m = static_cast<float>(*reinterpret_cast<const T*>(xt + (has_rpe ? 16384 : 0) + off));
     t = am_mode == 2 ? (m == 0.f ? kNegInfT : t) : fmaf(m, kLog2eT, t);
   }
   return t;
@@ -223,7 +224,7 @@ BSP_DEVI float2 exp2_pair(float2 y) {
 template <typename T> struct IsBf16 { static constexpr int v = 0; };
 template <> struct IsBf16<__nv_bfloat16> { static constexpr int v = 1; };
 
-template <int D, int MODE, bool KPM = false, bool XT = false> struct Cfg {
+template <int D, int MODE, bool KPM = false, int XT = 0> struct Cfg {
   static constexpr int ATOMS = D / 64;                         // 64-element (128-byte) column groups
   static constexpr int NRES = MODE == FWD ? 1 : 2;             // resident 128-row operands
   static constexpr int NC = 8;                                 // compute warps: two threads per tile row
@@ -233,16 +234,22 @@ template <int D, int MODE, bool KPM = false, bool XT = false> struct Cfg {
   // A key-padding mask is a bias per key: per column of the scores in the forward and in dQ
   // (64 values travel with every chunk), per row in dK/dV (read once per tile).
   static constexpr bool BIAS = KPM && MODE != DKV;
-  // XT: a relative position bias and / or an attention mask; their 64 x 64 pieces for the chunk
-  // (one box per half of the tile and tensor) travel with it, 32 KB per stage, and the kernel
-  // runs with one CTA per SM.
+  // XT: how many of {relative position bias, attention mask} are read (0, 1, 2); their 64 x 64
+  // pieces for the chunk (one box per half of the tile and tensor) travel with it, 16 KB per
+  // stage and tensor.  With both the kernel runs with one CTA per SM; with one, the forward and
+  // dQ run two CTAs per SM with two stages each at head dimension 64 (forward 0.80 -> 0.50 ms,
+  // dQ 0.78 -> 0.54 ms on configuration 4 at Z=4 with rpe), dK/dV stays with one CTA and four
+  // stages (0.97 against 1.02 ms).
   static constexpr int XT_OFF = 2 * CH_BYTES + 1024;
-  static constexpr int STAGE = 2 * CH_BYTES + ((MODE == DKV || BIAS || XT) ? 1024 : 0) + (XT ? 4 * 8192 : 0);   // + lse / delta, or the bias, of the chunk
+  static constexpr int STAGE = 2 * CH_BYTES + ((MODE == DKV || BIAS || XT) ? 1024 : 0) + XT * 2 * 8192;   // + lse / delta, or the bias, of the chunk
   static constexpr int TAIL_BYTES = MODE == DKV ? 512 : (BIAS ? 128 : 0);
   // score buffers in tensor memory: two (scores of the next chunk are computed while this
   // one is consumed) where the columns allow it with two CTAs per SM, else one
   static constexpr int NBUF = MODE == FWD ? 2 : (D == 64 ? 1 : 2);
-  static constexpr int NSTAGE = XT ? (D == 64 ? (MODE == FWD ? 4 : 3) : 2) : ((MODE != FWD && D == 128) ? 3 : 4);
+  static constexpr bool XT1_PAIR = XT == 1 && D == 64 && MODE != DKV;
+  static constexpr int NSTAGE = XT == 2 ? (D == 64 ? (MODE == FWD ? 4 : 3) : 2)
+                                : XT == 1 ? (D == 64 ? (XT1_PAIR ? 2 : 4) : 3)
+                                          : ((MODE != FWD && D == 128) ? 3 : 4);
   static constexpr int SMEM = NRES * RES_BYTES + NSTAGE * STAGE + 1024;
   static constexpr int SCORE_COLS = MODE == FWD ? 64 : 128;    // per buffer: S (and dP)
   // Early release (dQ at head_dim 64): the packed dS operand of the accumulating product gets
@@ -267,7 +274,7 @@ template <int D, int MODE, bool KPM = false, bool XT = false> struct Cfg {
   static constexpr int RES_BASE = ACC_BASE + ACC_COLS;
   static constexpr int RES_COLS = RES_T ? NRES * (D / 2) : 0;
   static constexpr int TMEM = RES_BASE + RES_COLS <= 256 ? 256 : 512;
-  static constexpr int CTAS = (D == 64 && !XT) ? 2 : 1;
+  static constexpr int CTAS = (D == 64 && (XT == 0 || XT1_PAIR)) ? 2 : 1;
 };
 
 // Writes accumulator columns [c0, c0 + n) of this thread's tensor-memory lane to dst[c0 .. c0 + n) as 16-bit values.
@@ -291,7 +298,7 @@ BSP_DEVI void store_acc(T* dst, uint32_t taddr, int c0, int n, float mul) {
 
 // FINE: the lists come from a layout with blocks smaller than 64 (pieces of a position may be
 // absent); a separate instantiation keeps the other case free of that bookkeeping.
-template <typename T, int D, int MODE, bool KPM, bool FINE, bool XT>
+template <typename T, int D, int MODE, bool KPM, bool FINE, int XT>
 __global__ void __launch_bounds__(Cfg<D, MODE, KPM, XT>::NT, Cfg<D, MODE, KPM, XT>::CTAS)
 attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant__ CUtensorMap m_res1,
                const __grid_constant__ CUtensorMap m_ch0, const __grid_constant__ CUtensorMap m_ch1,
@@ -361,7 +368,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap m_res0, const __grid_constant
         const int outer = (hf == 0 ? c0 : c1) * 64;
         const int col = MODE == DKV ? outer : crow, row = MODE == DKV ? crow : outer;
         if (a.has_rpe) tma_load_4d(sp + C::XT_OFF + hf * 8192, &m_rpe, &bar_full[stage], col, row, h, a.rpe_z ? z : 0);
-        if (a.am_mode) tma_load_4d(sp + C::XT_OFF + 16384 + hf * 8192, &m_am, &bar_full[stage], col, row, 0, 0);
+        if (a.am_mode) tma_load_4d(sp + C::XT_OFF + (a.has_rpe ? 16384 : 0) + hf * 8192, &m_am, &bar_full[stage], col, row, 0, 0);
       }
     }
   };
@@ -1050,7 +1057,7 @@ int decode_tiles(const int32_t* hdr, const int32_t* dev, TilesView& v) {
 // The maps a launch needs: resident operands, chunk operands and (XT variants) rpe / attention mask.
 struct Maps { CUtensorMap r0, r1, c0, c1, rpe, am; };
 
-template <typename T, int D, int MODE, bool KPM, bool FINE, bool XT>
+template <typename T, int D, int MODE, bool KPM, bool FINE, int XT>
 int launch(const Maps& m, const TcArgs& a, int n_tiles, int Z, cudaStream_t st, const char* what) {
   using C = Cfg<D, MODE, KPM, XT>;
   auto kern = attn_tc_kernel<T, D, MODE, KPM, FINE, XT>;
@@ -1066,7 +1073,7 @@ int launch(const Maps& m, const TcArgs& a, int n_tiles, int Z, cudaStream_t st, 
   return BSP_OK;
 }
 
-template <int MODE, bool KPM, bool FINE, bool XT>
+template <int MODE, bool KPM, bool FINE, int XT>
 int launch_dt(int dtype, int D, const Maps& m, const TcArgs& a, int n_tiles, int Z, cudaStream_t st, const char* what) {
   if (dtype == BSP_F16) {
     if (D == 64) return launch<__half, 64, MODE, KPM, FINE, XT>(m, a, n_tiles, Z, st, what);
@@ -1077,16 +1084,20 @@ int launch_dt(int dtype, int D, const Maps& m, const TcArgs& a, int n_tiles, int
 }
 template <int MODE>
 int launch_any(int dtype, int D, const Maps& m, const TcArgs& a, int n_tiles, int Z, cudaStream_t st, const char* what) {
-  if (a.has_rpe || a.am_mode) {           // rpe / an attention mask that is read: the masked code path
-    if (a.kpm) return launch_dt<MODE, true, true, true>(dtype, D, m, a, n_tiles, Z, st, what);
-    return launch_dt<MODE, false, true, true>(dtype, D, m, a, n_tiles, Z, st, what);
+  if (a.has_rpe && a.am_mode) {           // rpe and an attention mask that is read: the masked code path
+    if (a.kpm) return launch_dt<MODE, true, true, 2>(dtype, D, m, a, n_tiles, Z, st, what);
+    return launch_dt<MODE, false, true, 2>(dtype, D, m, a, n_tiles, Z, st, what);
+  }
+  if (a.has_rpe || a.am_mode) {           // one of them
+    if (a.kpm) return launch_dt<MODE, true, true, 1>(dtype, D, m, a, n_tiles, Z, st, what);
+    return launch_dt<MODE, false, true, 1>(dtype, D, m, a, n_tiles, Z, st, what);
   }
   if (a.kpm) {
-    if (a.fine || a.causal) return launch_dt<MODE, true, true, false>(dtype, D, m, a, n_tiles, Z, st, what);
-    return launch_dt<MODE, true, false, false>(dtype, D, m, a, n_tiles, Z, st, what);
+    if (a.fine || a.causal) return launch_dt<MODE, true, true, 0>(dtype, D, m, a, n_tiles, Z, st, what);
+    return launch_dt<MODE, true, false, 0>(dtype, D, m, a, n_tiles, Z, st, what);
   }
-  if (a.fine || a.causal) return launch_dt<MODE, false, true, false>(dtype, D, m, a, n_tiles, Z, st, what);
-  return launch_dt<MODE, false, false, false>(dtype, D, m, a, n_tiles, Z, st, what);
+  if (a.fine || a.causal) return launch_dt<MODE, false, true, 0>(dtype, D, m, a, n_tiles, Z, st, what);
+  return launch_dt<MODE, false, false, 0>(dtype, D, m, a, n_tiles, Z, st, what);
 }
 
 // rpe [Z or 1, H, L, L] and the attention mask [L, L] as maps of 64 x 64 boxes; an absent one gets
