@@ -23,30 +23,62 @@ from . import _lib
 from .matmul import _dtype_code
 
 
-def bind_near_gpu(device):
-    """Restricts the calling process to the CPU cores of the NUMA node the GPU hangs off, so
-    that pinned buffers allocated afterwards (first touch) are local to the GPU's PCIe root.
-    With one process per GPU this keeps the host side of several concurrent pipelines off the
-    inter-socket link.  Returns the node, or None when the topology cannot be read (then
-    nothing is changed).  Linux only."""
-    import os
+def _cpus_near_gpu(device):
+    """(NUMA node or None, set of CPUs next to the GPU or None), from sysfs, else from NVML
+    (read-only queries).  Containers often hide the PCI tree of sysfs; NVML still answers."""
+    p = torch.cuda.get_device_properties(device)
+    bdf = '%04x:%02x:%02x.0' % (p.pci_domain_id, p.pci_bus_id, p.pci_device_id)
     try:
-        p = torch.cuda.get_device_properties(device)
-        bdf = '%04x:%02x:%02x.0' % (p.pci_domain_id, p.pci_bus_id, p.pci_device_id)
         with open('/sys/bus/pci/devices/%s/numa_node' % bdf) as f:
             node = int(f.read())
-        if node < 0:
+        if node >= 0:
+            with open('/sys/devices/system/node/node%d/cpulist' % node) as f:
+                cpus = set()
+                for part in f.read().strip().split(','):
+                    lo, _, hi = part.partition('-')
+                    cpus.update(range(int(lo), int(hi or lo) + 1))
+            return node, cpus
+    except (OSError, ValueError):
+        pass
+    try:
+        import os
+        import pynvml
+        pynvml.nvmlInit()
+        try:
+            h = pynvml.nvmlDeviceGetHandleByPciBusId(('0000' + bdf).encode())
+            words = (max(os.sched_getaffinity(0)) + 64) // 64 + 16
+            mask = pynvml.nvmlDeviceGetCpuAffinity(h, words)
+            cpus = {64 * w + b for w, m in enumerate(mask) for b in range(64) if (int(m) >> b) & 1}
+            node = None
+            if hasattr(pynvml, 'nvmlDeviceGetNumaNodeId'):
+                try:
+                    node = int(pynvml.nvmlDeviceGetNumaNodeId(h))
+                except pynvml.NVMLError:
+                    node = None
+            return node, (cpus or None)
+        finally:
+            pynvml.nvmlShutdown()
+    except Exception:                        # no NVML, an older driver, a query it refuses
+        return None, None
+
+
+def bind_near_gpu(device):
+    """Restricts the calling process to the CPU cores next to the GPU (its NUMA node), so that
+    pinned buffers allocated afterwards (first touch) are local to the GPU's PCIe root.  With one
+    process per GPU this keeps the host side of several concurrent pipelines off the inter-socket
+    link.  Returns the node (or -1 when only the CPU set is known), or None when the topology
+    cannot be read or none of those cores is available to this process (then nothing is
+    changed).  Linux only."""
+    import os
+    try:
+        node, cpus = _cpus_near_gpu(device)
+        if not cpus:
             return None
-        with open('/sys/devices/system/node/node%d/cpulist' % node) as f:
-            cpus = set()
-            for part in f.read().strip().split(','):
-                lo, _, hi = part.partition('-')
-                cpus.update(range(int(lo), int(hi or lo) + 1))
         allowed = cpus & os.sched_getaffinity(0)
         if not allowed:
             return None
         os.sched_setaffinity(0, allowed)
-        return node
+        return -1 if node is None else node
     except (OSError, ValueError, AttributeError):
         return None
 
