@@ -124,3 +124,59 @@ def test_shard_plan():
     lay = tbs.layouts.fixed(4, 8, 4, 'unidirectional')
     per = int(lay[0].sum())
     assert shard.block_range(lay, 1, 3) == (per, 3 * per)
+
+
+def test_bind_near_gpu_with_a_fake_nvml(monkeypatch):
+    """host.bind_near_gpu: sysfs hidden (as in a container), the CPU set comes from NVML; the
+    process is restricted to the cores that are both next to the GPU and available to it, and
+    nothing changes when there are none.  NVML and the device query are fakes: no GPU needed."""
+    import os
+    import sys
+    import types
+    import torch
+    from torch_blocksparse_b200 import host
+
+    avail = sorted(os.sched_getaffinity(0))
+    near = set(avail[: max(1, len(avail) // 2)])
+    calls = {}
+
+    class Props:
+        pci_domain_id, pci_bus_id, pci_device_id = 0, 0x1b, 0
+    fake = types.ModuleType('pynvml')
+    fake.NVMLError = Exception
+    fake.nvmlInit = lambda: calls.setdefault('init', True)
+    fake.nvmlShutdown = lambda: calls.setdefault('shutdown', True)
+
+    def by_bus(bus):
+        calls['bus'] = bus
+        return 'handle'
+    fake.nvmlDeviceGetHandleByPciBusId = by_bus
+
+    def affinity(handle, words):
+        mask = [0] * words
+        for c in calls['cpus']:
+            mask[c // 64] |= 1 << (c % 64)
+        return mask
+    fake.nvmlDeviceGetCpuAffinity = affinity
+    fake.nvmlDeviceGetNumaNodeId = lambda handle: 1
+    monkeypatch.setitem(sys.modules, 'pynvml', fake)
+    monkeypatch.setattr(torch.cuda, 'get_device_properties', lambda device: Props())
+    real_open = open
+
+    def no_sysfs(path, *a, **k):
+        if str(path).startswith('/sys/bus/pci'):
+            raise OSError('hidden')
+        return real_open(path, *a, **k)
+    monkeypatch.setattr('builtins.open', no_sysfs)
+    before = os.sched_getaffinity(0)
+    try:
+        calls['cpus'] = near
+        assert host.bind_near_gpu('cuda:0') == 1
+        assert os.sched_getaffinity(0) == near
+        assert calls['bus'] == b'00000000:1b:00.0' and calls.get('shutdown')
+        os.sched_setaffinity(0, before)
+        calls['cpus'] = {max(avail) + 1000}                     # cores this process may not use
+        assert host.bind_near_gpu('cuda:0') is None
+        assert os.sched_getaffinity(0) == before
+    finally:
+        os.sched_setaffinity(0, before)
