@@ -270,11 +270,11 @@ def test_dsd_dds_tcgen05_kernel(mode, ta, tb, block, dtype, width):
 
 
 @pytest.mark.parametrize('mode,ta,tb', [('dsd', False, False), ('dsd', True, False), ('dds', False, True)])
-@pytest.mark.parametrize('block,nred', [(32, 200), (64, 160), (128, 140), (32, 1056)])
+@pytest.mark.parametrize('block,nred', [(32, 200), (64, 160), (128, 140), (32, 1024), (32, 1056)])
 def test_dsd_dds_long_reduction_side(mode, ta, tb, block, nred):
     """Many blocks on the reduction side: a tile whose plan does not fit one buffer of the
-    tcgen05 kernel (more than 64 entries: it is handed over in several pieces), and 1056
-    blocks, more than that kernel plans for (the mma.sync kernel takes the call).  Rows that are
+    tcgen05 kernel (more than 64 entries: it is handed over in several pieces), the 1024 blocks
+    that kernel plans for at most, and 1056 (the mma.sync kernel takes the call).  Rows that are
     nearly full, one empty block-row; forward against the dense-masked oracle."""
     from torch_blocksparse_b200 import fused
     Z, H = 1, 2
