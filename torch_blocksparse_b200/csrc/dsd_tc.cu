@@ -285,6 +285,7 @@ dsd_tc_kernel(const __grid_constant__ CUtensorMap m_s, const __grid_constant__ C
           int k = 1;
           if (lane == 0) k = mbar_wait(&bar_plan_full[buf], (cb >> 1) & 1, fl) ? 1 : 0;
           if (!__shfl_sync(m8, k, 0)) { ok = false; break; }
+          __syncwarp(m8);                              // lane 0 has acquired the plan; the other lanes read it after this
           const int n = plan[buf].n;
           last_chunk = plan[buf].last;
           for (int e = 0; ok && e < n; ++e) {
