@@ -161,6 +161,19 @@ int bsp_meta_build_device(const void* layout, int elem_bytes, int H, int Mb, int
                           int32_t* out, int64_t out_cap, int32_t* hdr_host, void* stream);
 
 /*
+ * The table of bsp_softmax_lut_build written on the device from the device copy
+ * of the execution metadata (bsp_meta_build or bsp_meta_build_device) of the same
+ * layout: `meta_hdr` the HOST copy of its header, `meta` and `out` DEVICE
+ * pointers.  Same two calls as the host builders (out == NULL: *total and
+ * *maxlut only); bit-identical contents; runs on `stream`, does not
+ * synchronise.  With bsp_meta_build_device a layout that lives in device memory
+ * gets its softmax table without a copy to the host (replaces the host-side
+ * build and `.to(device)` of torch_blocksparse/softmax.py:201-221).
+ */
+int bsp_softmax_lut_from_meta(const int32_t* meta_hdr, const int32_t* meta, int32_t* out, int64_t out_cap,
+                              int64_t* total, int* maxlut, void* stream);
+
+/*
  * Tile lists of the tcgen05 attention kernels (no counterpart in the
  * reference).  Those kernels work on tiles of 128 query rows (forward, dQ) or
  * 128 key rows (dK, dV), made of two 64-row chunks, and walk 64-row chunks of
@@ -186,8 +199,9 @@ int bsp_attn_tiles_build(const int64_t* layout, int H, int nb, int block,
                          int32_t* out, int64_t out_cap, int64_t* total);
 
 /*
- * bsp_attn_tiles_build on the device, for blocks 64 and 128 and at most 512
- * blocks per side (BSP_ERR_UNSUPPORTED otherwise: build on the host): `layout`
+ * bsp_attn_tiles_build on the device, for at most 512 positions of 64 x 64 (128
+ * x 128 for block 128) per side (BSP_ERR_UNSUPPORTED otherwise: build on the
+ * host); blocks 16 and 32 are coarsened on the device as well: `layout`
  * is a DEVICE pointer to [H, nb, nb] elements of elem_bytes (1, 4 or 8) bytes,
  * `out` a DEVICE buffer of at least bsp_attn_tiles_device_capacity(H, nb, block)
  * ints.  Its leading ints are bit-identical to the host builder's output; the

@@ -49,6 +49,45 @@ def test_device_build_equals_host_build_on_1000_random_layouts():
         _check_equal(lay, dtypes[i % 4])
 
 
+def test_softmax_table_from_device_metadata_equals_the_host_table():
+    """bsp_softmax_lut_from_meta (the table written by a kernel from the metadata built on the
+    device) against bsp_softmax_lut_build on the host: fixtures, the benchmark layouts, 200
+    random layouts (odd and even numbers of block-rows, empty rows, an empty layout)."""
+    rng = np.random.default_rng(5)
+    z = load_npz('lut_small.npz')
+    lays = [torch.from_numpy(z[name + '/layout']) for name in sorted({k.split('/')[0] for k in z.files})]
+    lays += [layouts.fixed(16, 128, 4, 'unidirectional'), layouts.bigbird(16, 128, 3, 3, 2, seed=0),
+             layouts.causal_band(16, 64, 4, 1), torch.zeros((2, 3, 5), dtype=torch.long),
+             torch.ones((1, 1, 1), dtype=torch.long)]
+    for i in range(200):
+        H, Mb, Nb = int(rng.integers(1, 6)), int(rng.integers(1, 40)), int(rng.integers(1, 40))
+        p = rng.choice([0.0, 0.05, 0.3, 0.6, 1.0])
+        lays.append(torch.from_numpy((rng.random((H, Mb, Nb)) < p).astype(np.int64)))
+    for lay in lays:
+        tables.clear_cache()
+        want, want_max = tables.make_softmax_lut(lay)
+        got, got_max = tables.make_softmax_lut_device(lay.to(DEV))
+        assert got_max == want_max and got.is_cuda and torch.equal(got.cpu(), want), tuple(lay.shape)
+
+
+def test_softmax_with_a_device_layout_matches_the_host_layout_path(monkeypatch):
+    c = workloads.config3(small=True)
+    tables.clear_cache()
+    x = c['x'].to(DEV)
+    kw = dict(scale=c['scale'], rpe=c['rpe'].to(DEV), key_padding_mask=c['key_padding_mask'].to(DEV),
+              attn_mask=c['attn_mask'].to(DEV), key_padding_mask_mode='add', attn_mask_mode='mul')
+    want = Softmax(c['layout'], c['block'])(x.clone(), **kw)
+    tables.clear_cache()
+    before = dict(tables.CACHE_STATS)
+
+    def host_builder(*args, **kwargs):
+        raise AssertionError('the host builder must not run for a device layout')
+    monkeypatch.setattr(tables, 'make_softmax_lut', host_builder)
+    got = Softmax(c['layout'].to(DEV), c['block'])(x.clone(), **kw)
+    assert torch.equal(got, want)
+    assert tables.CACHE_STATS['host_builds'] == before['host_builds']          # nor the metadata
+
+
 def test_ops_on_one_layout_share_one_buffer_and_a_changed_layout_is_rebuilt():
     tables.clear_cache()
     g = torch.Generator().manual_seed(1)
@@ -120,7 +159,7 @@ def test_validation_accepts_built_buffers_and_names_the_corrupt_entry():
 def test_device_tile_lists_equal_host_tile_lists():
     """Attention tile lists built on the device (greedy pairing of block-rows by similarity, one CTA
     per head and side) against the host builder: fixtures, the benchmark layouts, random layouts
-    with odd counts, empty and identical rows, blocks 64 and 128."""
+    with odd counts, empty and identical rows, blocks 16, 32, 64 and 128."""
     rng = np.random.default_rng(77)
     cases = [(layouts.fixed(16, 128, 4, 'unidirectional'), 64), (layouts.fixed(16, 128, 4, 'bidirectional'), 64),
              (layouts.bigbird(16, 128, 3, 3, 2, seed=0), 128), (layouts.causal_band(4, 64, 4, 1), 64),
@@ -135,6 +174,14 @@ def test_device_tile_lists_equal_host_tile_lists():
         if i % 7 == 0 and nb > 3:
             lay[:, 2] = lay[:, 1]                                # identical rows
         cases.append((lay, 64 if i % 3 else 128))
+    # blocks 16 and 32: coarsened on the device, with the piece masks of every entry
+    for i in range(120):
+        block = 16 if i % 2 else 32
+        f = 64 // block
+        H, nb = int(rng.integers(1, 4)), f * int(rng.integers(1, 24))
+        p = rng.choice([0.0, 0.02, 0.1, 0.4, 0.9, 1.0])
+        cases.append((torch.from_numpy((rng.random((H, nb, nb)) < p).astype(np.int64)), block))
+    cases += [(layouts.fixed(4, 512, 16, 'unidirectional'), 16), (layouts.causal_band(4, 128, 8, 2), 32)]
     for lay, block in cases:
         tables.clear_cache()
         want = tables.build_attn_tiles(lay, block)
@@ -156,3 +203,27 @@ def test_attention_with_a_device_layout_builds_everything_on_the_device():
     from oracle import dense_masked as dm
     want = dm.attention_reference(c['q'], c['k'], c['v'], c['layout'], c['block'], c['scale'])[0]
     assert_close(o, want, 'attention on a device layout')
+
+
+@pytest.mark.parametrize('block', [16, 32])
+def test_attention_with_a_device_layout_at_small_blocks(block):
+    """Blocks 16 / 32 with the layout in device memory: metadata and the coarsened tile lists
+    are built there (no host build), and the tcgen05 kernels run on them."""
+    from oracle import dense_masked as dm
+    from torch_blocksparse_b200 import fused
+    tables.clear_cache()
+    g = torch.Generator().manual_seed(block)
+    H, L, D = 2, 512, 64
+    nb = L // block
+    layout = (torch.rand((H, nb, nb), generator=g) < 0.2).long()
+    layout[:, torch.arange(nb), torch.arange(nb)] = 1
+    q, k, v = ((torch.randn((2, H, L, D), generator=g)).half() for _ in range(3))
+    before = dict(tables.CACHE_STATS)
+    mod = SparseSelfAttention(layout=layout.to(DEV), block=block, fused=True)
+    with torch.no_grad():
+        o = mod(q.to(DEV), k.to(DEV), v.to(DEV))
+    assert tables.CACHE_STATS['device_builds'] == before['device_builds'] + 2
+    assert tables.CACHE_STATS['host_builds'] == before['host_builds']
+    want = dm.attention_reference(q, k, v, layout, block, D ** -0.5)[0]
+    assert_close(o, want, 'attention on a device layout, block %d' % block)
+    assert fused.device_status() == 0

@@ -32,6 +32,7 @@ _SIGNATURES = {
     'bsp_dxx_lut_build': (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
                                   c_void_p, c_int64, _I64P, _IP, _IP]),
     'bsp_softmax_lut_build': (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, c_int64, _I64P, _IP]),
+    'bsp_softmax_lut_from_meta': (c_int, [c_void_p, c_void_p, c_void_p, c_int64, _I64P, _IP, c_void_p]),
     'bsp_fixed_layout_build': (c_int, [c_int] * 7 + [c_void_p]),
     'bsp_window_layout_build': (c_int, [c_int] * 6 + [c_void_p, c_int, c_void_p]),
     'bsp_device_status': (c_int, [_IP]),

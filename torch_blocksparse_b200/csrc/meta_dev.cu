@@ -460,13 +460,57 @@ __global__ void tiles_order_kernel(int H, int nt, int32_t* __restrict__ out) {
   order[pos] = i;
 }
 
+// Blocks 16 and 32: the layout coarsened to 64 x 64 positions (present = some piece present) and,
+// per position, which of its 16 x 16 pieces lie in a nonzero block: pr[h][q][k] with bit 4 a + b
+// for query group a and key group b (the row tiles' view), pc[h][k][q] with bit 4 a + b for key
+// group a and query group b (the column tiles' view).
 template <typename L>
-int build_tiles(const L* lay, int H, int nb, int block, int nt, int32_t* out, int32_t* scratch, cudaStream_t st) {
+__global__ void tiles_coarsen_kernel(const L* __restrict__ lay, int H, int nbf, int fine_block, int nb,
+                                     uint8_t* __restrict__ coarse, uint16_t* __restrict__ pr, uint16_t* __restrict__ pc) {
+  const int64_t idx = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+  if (idx >= (int64_t)H * nb * nb) return;
+  const int j = (int)(idx % nb), i = (int)((idx / nb) % nb), h = (int)(idx / ((int64_t)nb * nb));
+  const L* hl = lay + (size_t)h * nbf * nbf;
+  int vr = 0, vc = 0;
+  for (int a = 0; a < 4; ++a)
+    for (int b = 0; b < 4; ++b) {
+      const int fi = (i * 64 + a * 16) / fine_block, fj = (j * 64 + b * 16) / fine_block;
+      if (hl[(size_t)fi * nbf + fj] != 0) { vr |= 1 << (4 * a + b); vc |= 1 << (4 * b + a); }
+    }
+  coarse[idx] = vr != 0;
+  pr[idx] = (uint16_t)vr;
+  pc[((size_t)h * nb + j) * nb + i] = (uint16_t)vc;
+}
+
+// sub of every entry from the piece masks (blocks 16 and 32); one thread per tile and side
+__global__ void tiles_sub_kernel(int H, int nb, int nt, const uint16_t* __restrict__ pr, const uint16_t* __restrict__ pc,
+                                 int32_t* __restrict__ out) {
+  const int n = H * nt;
+  const int side = blockIdx.y;
+  const int ti = blockIdx.x * blockDim.x + threadIdx.x;
+  if (ti >= n) return;
+  const int er = out[5], ec = out[6];
+  const int e = side == 0 ? er : ec;
+  int32_t* base = out + BSP_TILES_HEADER + (side == 0 ? 0 : (4 * (size_t)n + 1) + 3 * (size_t)er);
+  const int32_t *c01 = base, *ptr = c01 + 2 * n, *chunk = ptr + n + 1, *mask = chunk + e;
+  int32_t* sub = base + 2 * n + (n + 1) + 2 * (size_t)e;
+  const uint16_t* P = (side == 0 ? pr : pc) + (size_t)(ti / nt) * nb * nb;
+  const int a = c01[2 * ti], b = c01[2 * ti + 1];
+  for (int p = ptr[ti]; p < ptr[ti + 1]; ++p) {
+    const int j = chunk[p], m = mask[p];
+    const uint32_t lo = (m & 1) ? P[(size_t)a * nb + j] : 0u, hi = (m & 2) ? P[(size_t)b * nb + j] : 0u;
+    sub[p] = (int32_t)(lo | (hi << 16));
+  }
+}
+
+template <typename L>
+int build_tiles(const L* lay, int H, int nb, int block, int nt, int32_t* out, int32_t* scratch, cudaStream_t st,
+                int fine_block = 0) {
   const int n = H * nt;
   int32_t* c01s = scratch;
   int32_t* lens = scratch + 4 * (size_t)n;
   tiles_pair_kernel<L><<<dim3(H, 2), 256, 0, st>>>(lay, H, nb, block, nt, c01s, lens);
-  tiles_scan_kernel<<<1, 1024, 0, st>>>(lens, H, nb, block, nt, block, out);
+  tiles_scan_kernel<<<1, 1024, 0, st>>>(lens, H, nb, block, nt, fine_block ? fine_block : block, out);
   const int grid = (n + 127) / 128;
   tiles_fill_kernel<L><<<dim3(grid, 2), 128, 0, st>>>(lay, H, nb, block, nt, c01s, out);
   tiles_order_kernel<<<dim3(grid, 2), 128, 0, st>>>(H, nt, out);
@@ -485,21 +529,31 @@ int64_t tiles_worst_case(int H, int nb, int block) {
 }  // namespace bsp
 
 extern "C" int64_t bsp_attn_tiles_device_capacity(int H, int nb, int block) {
-  if (H <= 0 || nb <= 0 || (block != 64 && block != 128)) return 0;
+  if (H <= 0 || nb <= 0 || (block != 16 && block != 32 && block != 64 && block != 128)) return 0;
+  int64_t extra = 0;
+  if (block < 64) {                                                          // coarsened layout and piece masks
+    const int f = 64 / block;
+    if (nb % f) return 0;
+    nb /= f; block = 64;
+    extra = (5 * (int64_t)H * nb * nb + 3) / 4 + 4;
+  }
   const int64_t nt = block == 128 ? nb : (nb + 1) / 2;
-  return tiles_worst_case(H, nb, block) + 6 * (int64_t)H * nt;               // + pairs and lengths of both sides
+  return tiles_worst_case(H, nb, block) + 6 * (int64_t)H * nt + extra;       // + pairs and lengths of both sides
 }
 
 extern "C" int bsp_attn_tiles_build_device(const void* layout, int elem_bytes, int H, int nb, int block,
                                            int32_t* out, int64_t out_cap, int32_t* hdr_host, void* stream) {
   if (!layout || !out) return fail(BSP_ERR_INVALID, "device tile-list build: NULL pointer");
   if (H <= 0 || nb <= 0) return fail(BSP_ERR_INVALID, "layout shape [%d,%d,%d] is not positive", H, nb, nb);
-  if (block != 64 && block != 128)
-    return fail(BSP_ERR_UNSUPPORTED, "device tile-list build: blocks 64 and 128 (blocks 16 and 32 are built on the host)");
-  if (nb > kTilesMaxNb) return fail(BSP_ERR_UNSUPPORTED, "device tile-list build: at most %d blocks per side (got %d)", kTilesMaxNb, nb);
+  if (block != 16 && block != 32 && block != 64 && block != 128)
+    return fail(BSP_ERR_UNSUPPORTED, "attention tiles exist for block 16, 32, 64 and 128 (got %d)", block);
+  const int fine_block = block, nbf = nb, f = block < 64 ? 64 / block : 1;
+  if (nb % f) return fail(BSP_ERR_UNSUPPORTED, "attention tiles for block %d need a number of blocks per side that is a multiple of %d (got %d)", block, f, nb);
+  if (f > 1) { nb /= f; block = 64; }
+  if (nb > kTilesMaxNb) return fail(BSP_ERR_UNSUPPORTED, "device tile-list build: at most %d positions of 64 or 128 per side (got %d)", kTilesMaxNb, nb);
   if (elem_bytes != 1 && elem_bytes != 4 && elem_bytes != 8)
     return fail(BSP_ERR_INVALID, "device tile-list build: layout elements of 1, 4 or 8 bytes (got %d)", elem_bytes);
-  const int64_t need = bsp_attn_tiles_device_capacity(H, nb, block);
+  const int64_t need = bsp_attn_tiles_device_capacity(H, nbf, fine_block);
   if (out_cap < need)
     return fail(BSP_ERR_CAPACITY, "device tile-list build needs a buffer of %lld ints (worst case), got %lld",
                 (long long)need, (long long)out_cap);
@@ -507,14 +561,73 @@ extern "C" int bsp_attn_tiles_build_device(const void* layout, int elem_bytes, i
   const int nt = block == 128 ? nb : (nb + 1) / 2;
   int32_t* scratch = out + tiles_worst_case(H, nb, block);
   int rc;
-  if (elem_bytes == 8) rc = build_tiles(static_cast<const int64_t*>(layout), H, nb, block, nt, out, scratch, st);
-  else if (elem_bytes == 4) rc = build_tiles(static_cast<const int32_t*>(layout), H, nb, block, nt, out, scratch, st);
-  else rc = build_tiles(static_cast<const uint8_t*>(layout), H, nb, block, nt, out, scratch, st);
-  if (rc) return rc;
+  if (f > 1) {
+    // blocks 16 / 32: block-64 lists of the coarsened layout, then the piece masks of every entry
+    const int64_t pos = (int64_t)H * nb * nb;
+    uint16_t* pr = reinterpret_cast<uint16_t*>(scratch + 6 * (size_t)H * nt);
+    uint16_t* pc = pr + pos;
+    uint8_t* coarse = reinterpret_cast<uint8_t*>(pc + pos);
+    const unsigned grid = (unsigned)((pos + 255) / 256);
+    if (elem_bytes == 8) tiles_coarsen_kernel<<<grid, 256, 0, st>>>(static_cast<const int64_t*>(layout), H, nbf, fine_block, nb, coarse, pr, pc);
+    else if (elem_bytes == 4) tiles_coarsen_kernel<<<grid, 256, 0, st>>>(static_cast<const int32_t*>(layout), H, nbf, fine_block, nb, coarse, pr, pc);
+    else tiles_coarsen_kernel<<<grid, 256, 0, st>>>(static_cast<const uint8_t*>(layout), H, nbf, fine_block, nb, coarse, pr, pc);
+    rc = build_tiles(coarse, H, nb, block, nt, out, scratch, st, fine_block);
+    if (rc) return rc;
+    tiles_sub_kernel<<<dim3((H * nt + 127) / 128, 2), 128, 0, st>>>(H, nb, nt, pr, pc, out);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return fail(BSP_ERR_CUDA, "device tile-list build: launch failed: %s", cudaGetErrorString(e));
+  } else {
+    if (elem_bytes == 8) rc = build_tiles(static_cast<const int64_t*>(layout), H, nb, block, nt, out, scratch, st);
+    else if (elem_bytes == 4) rc = build_tiles(static_cast<const int32_t*>(layout), H, nb, block, nt, out, scratch, st);
+    else rc = build_tiles(static_cast<const uint8_t*>(layout), H, nb, block, nt, out, scratch, st);
+    if (rc) return rc;
+  }
   if (hdr_host) {
     cudaError_t e = cudaMemcpyAsync(hdr_host, out, BSP_TILES_HEADER * sizeof(int32_t), cudaMemcpyDeviceToHost, st);
     if (e == cudaSuccess) e = cudaStreamSynchronize(st);
     if (e != cudaSuccess) return fail(BSP_ERR_CUDA, "device tile-list build: reading the header failed: %s", cudaGetErrorString(e));
   }
+  return BSP_OK;
+}
+
+// ---- softmax table from the execution metadata ------------------------------------------
+namespace bsp {
+namespace {
+
+// One thread per row header and per block entry of the table bsp_softmax_lut_build writes.
+__global__ void softmax_lut_kernel(Meta m, int32_t* out) {
+  const int64_t rows = (int64_t)m.H * m.Mb;
+  const int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+  if (i < rows) {
+    const int first = m.row_ptr[i];
+    out[2 * i] = m.row_ptr[i + 1] - first;
+    out[2 * i + 1] = (int32_t)(4 * (int64_t)first + 2 * rows);
+  }
+  if (i < m.nnz) {
+    int32_t* e = out + 2 * rows + 4 * i;
+    e[0] = (int32_t)i; e[1] = m.blk_col[i]; e[2] = m.blk_row[i]; e[3] = m.blk_head[i];
+  }
+}
+
+}  // namespace
+}  // namespace bsp
+
+extern "C" int bsp_softmax_lut_from_meta(const int32_t* meta_hdr, const int32_t* meta, int32_t* out, int64_t out_cap,
+                                         int64_t* total, int* maxlut, void* stream) {
+  using namespace bsp;
+  if (!meta_hdr || !meta || !total || !maxlut) return fail(BSP_ERR_INVALID, "softmax table from metadata: NULL pointer");
+  if (meta_hdr[0] != BSP_META_MAGIC || meta_hdr[1] <= 0 || meta_hdr[2] <= 0 || meta_hdr[3] <= 0 || meta_hdr[4] < 0)
+    return fail(BSP_ERR_INVALID, "metadata header is corrupt");
+  const Meta m = meta_view(meta, meta_hdr[1], meta_hdr[2], meta_hdr[3], meta_hdr[4], meta_hdr[5], meta_hdr[6]);
+  const int64_t rows = (int64_t)m.H * m.Mb;
+  *total = 2 * rows + 4 * (int64_t)m.nnz;
+  *maxlut = m.max_row;
+  if (!out) return BSP_OK;
+  if (out_cap < *total)
+    return fail(BSP_ERR_CAPACITY, "softmax table needs %lld ints, buffer holds %lld", (long long)*total, (long long)out_cap);
+  const int64_t n = rows > m.nnz ? rows : m.nnz;
+  softmax_lut_kernel<<<(unsigned)((n + 255) / 256), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(m, out);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return fail(BSP_ERR_CUDA, "softmax table from metadata: launch failed: %s", cudaGetErrorString(e));
   return BSP_OK;
 }

@@ -28,7 +28,10 @@ class _sparse_softmax(torch.autograd.Function):
 
     @staticmethod
     def make_lut(layout, block, device):
-        """softmax.py:201-221: returns (lut, maxlut)."""
+        """softmax.py:201-221: returns (lut, maxlut).  A layout in device memory gets its table
+        there (from the metadata built on the device), without a copy to the host."""
+        if layout.is_cuda and torch.device(device).type == 'cuda':
+            return tables.make_softmax_lut_device(layout, device)
         return tables.make_softmax_lut(layout, device)
 
     @staticmethod

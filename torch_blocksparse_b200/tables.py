@@ -89,6 +89,25 @@ def make_softmax_lut(layout, device='cpu'):
     return lut.to(device), int(maxlut.value)
 
 
+def make_softmax_lut_device(layout, device=None):
+    """(lut, maxlut) for a layout that lives in device memory: the table is written by a kernel from
+    the metadata built on that device, nothing but the metadata's 8-int header visits the host.
+    Bit-identical to make_softmax_lut."""
+    meta = build_meta(layout)
+    device = layout.device if device is None else torch.device(device)
+    dev = meta.on(device)
+    L = _lib.lib()
+    total, maxlut = ctypes.c_int64(0), ctypes.c_int(0)
+    _lib.check(L.bsp_softmax_lut_from_meta(meta.hdr.data_ptr(), dev.data_ptr(), None, 0, ctypes.byref(total),
+                                           ctypes.byref(maxlut), None))
+    with torch.cuda.device(device):
+        out = torch.empty(int(total.value), dtype=torch.int32, device=device)
+        _lib.check(L.bsp_softmax_lut_from_meta(meta.hdr.data_ptr(), dev.data_ptr(), out.data_ptr(), out.numel(),
+                                               ctypes.byref(total), ctypes.byref(maxlut),
+                                               torch.cuda.current_stream(device).cuda_stream))
+    return out, int(maxlut.value)
+
+
 def make_fixed_layout(num_heads, num_blocks, mode, block_stride, attention, numverts, vertsize):
     """'dense' or 'fixed' layout as an int64 tensor [num_heads, num_blocks, num_blocks]."""
     if mode not in ('dense', 'fixed'):
@@ -266,8 +285,9 @@ TILES_DEVICE_MAX_BLOCKS = 512
 
 
 def build_attn_tiles_device(layout, block):
-    """Builds the tile lists on the device `layout` lives on (blocks 64 and 128, at most 512
-    blocks per side): only the 8-int header comes back to the host."""
+    """Builds the tile lists on the device `layout` lives on (at most 512 positions of 64, or of
+    128 for block 128, per side; blocks 16 and 32 are coarsened there): only the 8-int header comes
+    back to the host."""
     if not layout.is_cuda or layout.dim() != 3 or layout.size(1) != layout.size(2):
         raise ValueError('build_attn_tiles_device: a square [H, nb, nb] CUDA tensor is required')
     lay = layout
@@ -301,7 +321,7 @@ def build_attn_tiles(layout, block):
         return None
 
     def build():
-        if layout.is_cuda and block >= 64 and Mb <= TILES_DEVICE_MAX_BLOCKS:
+        if layout.is_cuda and Mb // max(1, 64 // block) <= TILES_DEVICE_MAX_BLOCKS:
             return build_attn_tiles_device(layout, block)
         lay, H, Mb_, Nb_ = _layout_i64(layout)
         L = _lib.lib()
