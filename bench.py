@@ -399,6 +399,27 @@ def large_blocks_bench(dev, pk, timed, out):
                                                      'fwd_frac_of_measured_peak': flops / t / 1e12 / peak_tf})
         del d1, d2, sp
         torch.cuda.empty_cache()
+    # the same shape on a banded layout of the same density (every block-row sees the 25 % of the
+    # block-columns around its own): neighbouring rows share their columns, so a tile's union of
+    # column lists holds little that is not in the layout
+    from torch_blocksparse_b200 import layouts
+    out['banded'] = {'workload': 'sdd / dsd / dds FP16, block 32, 64 and 128, Z=2, H=8, M=N=K=4096, band of a quarter of '
+                                 'the block-columns around the diagonal, forward', 'cases': []}
+    for block in (32, 64, 128):
+        nb = S // block
+        layout = layouts.window(hh, nb, nb // 8, nb // 8 - 1)
+        nnz = int(layout.sum())
+        d1 = (torch.randn((zz, hh, S, S), generator=g) * S ** -0.5).half().to(dev)
+        d2 = (torch.randn((zz, hh, S, S), generator=g) * S ** -0.5).half().to(dev)
+        sp = (torch.randn((zz, nnz, block, block), generator=g) * S ** -0.5).half().to(dev)
+        flops = 2 * zz * nnz * block * block * S
+        for mode, a, b in (('sdd', d1, d2), ('dsd', sp, d1), ('dds', d1, sp)):
+            op = MatMul(layout, block, mode)
+            t = timed(lambda: op(a, b))
+            out['banded']['cases'].append({'block': block, 'mode': mode, 'fwd_ms': t * 1e3, 'fwd_tflops': flops / t / 1e12,
+                                           'fwd_frac_of_measured_peak': flops / t / 1e12 / peak_tf})
+        del d1, d2, sp
+        torch.cuda.empty_cache()
     return out
 
 
