@@ -84,12 +84,6 @@ struct DsdTcArgs {
   const int32_t* blk_id;                     // storage index of every list entry (NULL: the entry's own position)
 };
 
-BSP_DEVI void tma_load_5d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1, int c2, int c3, int c4) {
-  asm volatile("cp.async.bulk.tensor.5d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
-               ::"r"(saddr(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(saddr(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4)
-               : "memory");
-}
-
 // D[tmem] (+)= A[smem] * B[smem] with the descriptors given as their two 32-bit words.
 BSP_DEVI void mma_desc(uint32_t d, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi, uint32_t idesc, uint32_t accumulate) {
   asm volatile("{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\tsetp.ne.b32 p, %6, 0;\n\t"
@@ -351,8 +345,12 @@ dsd_tc_kernel(const __grid_constant__ CUtensorMap m_s, const __grid_constant__ C
     }
   } else if (warp == 6) {
     // ------------------------------------------------------------------ dense operand
-    if (lane == 0) {
-      prefetch_map(&m_b);
+    // k contiguous: one box of TN rows; n contiguous: one box of 64 columns per lane (the groups
+    // of 64 columns of the MN-major tile), issued together.  Lane 0 waits and announces the bytes.
+    constexpr int NG = B_KMAJOR ? 1 : TN / 64;
+    if (lane < NG) {
+      constexpr uint32_t mg = (1u << NG) - 1u;
+      if (lane == 0) prefetch_map(&m_b);
       int it = 0, cb = 0;
       bool ok = true;
       for (int t = blockIdx.x; ok && t < a.total_tiles; t += gridDim.x) {
@@ -361,7 +359,10 @@ dsd_tc_kernel(const __grid_constant__ CUtensorMap m_s, const __grid_constant__ C
         int last_chunk = 0;
         do {
           const int buf = cb & 1;
-          if (!mbar_wait(&bar_plan_full[buf], (cb >> 1) & 1, fl)) { ok = false; break; }
+          int k = 1;
+          if (lane == 0) k = mbar_wait(&bar_plan_full[buf], (cb >> 1) & 1, fl) ? 1 : 0;
+          if (NG > 1) { k = __shfl_sync(mg, k, 0); __syncwarp(mg); }
+          if (!k) { ok = false; break; }
           const int n = plan[buf].n;
           last_chunk = plan[buf].last;
           for (int e = 0; ok && e < n; ++e) {
@@ -369,32 +370,38 @@ dsd_tc_kernel(const __grid_constant__ CUtensorMap m_s, const __grid_constant__ C
             const int reps = block == 128 ? 2 : 1;
             for (int kh = 0; kh < reps; ++kh) {
               const int s = it % S;
-              if (it >= S && !mbar_wait(&bar_empty[s], ((it / S) - 1) & 1, fl)) { ok = false; break; }
+              if (it >= S) {
+                k = 1;
+                if (lane == 0) k = mbar_wait(&bar_empty[s], ((it / S) - 1) & 1, fl) ? 1 : 0;
+                if (NG > 1) k = __shfl_sync(mg, k, 0);
+                if (!k) { ok = false; break; }
+              }
               unsigned char* bp = smem + s * G::kStage + kStageA;
+              const bool two = block == 32 && c1 >= 0;
+              if (lane == 0) mbar_expect_tx(&bar_full[s], (block == 32 && !two) ? G::kStageB / 2 : G::kStageB);
+              if (NG > 1) __syncwarp(mg);
               if (block == 32) {
-                const bool two = c1 >= 0;
-                mbar_expect_tx(&bar_full[s], two ? G::kStageB : G::kStageB / 2);
                 if (B_KMAJOR) {
                   tma_load_4d(bp, &m_b, &bar_full[s], c0 * 32, n0, tc_.h, tc_.z);
                   if (two) tma_load_4d(bp + G::kStageB / 2, &m_b, &bar_full[s], c1 * 32, n0, tc_.h, tc_.z);
-                } else {
-                  tma_load_5d(bp, &m_b, &bar_full[s], 0, c0 * 32, n0 / 64, tc_.h, tc_.z);
-                  if (two) tma_load_5d(bp + G::kStageB / 2, &m_b, &bar_full[s], 0, c1 * 32, n0 / 64, tc_.h, tc_.z);
+                } else {                                  // groups of 32 k-rows x 128 bytes: 4 KB apart
+                  tma_load_4d(bp + lane * 4096, &m_b, &bar_full[s], n0 + lane * 64, c0 * 32, tc_.h, tc_.z);
+                  if (two) tma_load_4d(bp + G::kStageB / 2 + lane * 4096, &m_b, &bar_full[s], n0 + lane * 64, c1 * 32, tc_.h, tc_.z);
                 }
               } else {
                 const int krow = block == 128 ? c0 * 128 + kh * 64 : c0 * 64;
-                mbar_expect_tx(&bar_full[s], G::kStageB);
                 if (B_KMAJOR) tma_load_4d(bp, &m_b, &bar_full[s], krow, n0, tc_.h, tc_.z);
-                else tma_load_5d(bp, &m_b, &bar_full[s], 0, krow, n0 / 64, tc_.h, tc_.z);
+                else tma_load_4d(bp + lane * 8192, &m_b, &bar_full[s], n0 + lane * 64, krow, tc_.h, tc_.z);
               }
               ++it;
             }
           }
-          mbar_arrive(&bar_plan_empty[buf]);
+          if (NG > 1) __syncwarp(mg);
+          if (lane == 0) mbar_arrive(&bar_plan_empty[buf]);
           ++cb;
         } while (ok && !last_chunk);
       }
-      if (ok) {
+      if (ok && lane == 0) {
         const int s = it % S;
         if (it < S || mbar_wait(&bar_empty[s], ((it / S) - 1) & 1, fl)) mbar_arrive(&bar_full[s]);
       }
@@ -605,11 +612,11 @@ int dsd_tc(const void* s, const void* b, void* c, int dtype, int block, int Z, i
     cuuint64_t strides[3] = {(cuuint64_t)outer_n * 2, (cuuint64_t)sh * 2, (cuuint64_t)(Z > 1 ? b_sz : (int64_t)m.H * sh) * 2};
     cuuint32_t box[4] = {(cuuint32_t)kbox, (cuuint32_t)TN, 1, 1};
     if (int rc = encode(&mb, b, dtype, 4, dims, strides, box, swz)) return rc;
-  } else {                                                 // [k][n] seen as (64 n, k, N / 64 groups): one box brings TN / 64 groups of kbox rows
-    cuuint64_t dims[5] = {64, (cuuint64_t)ktot, (cuuint64_t)(N / 64), (cuuint64_t)m.H, (cuuint64_t)Z};
-    cuuint64_t strides[4] = {(cuuint64_t)outer_n * 2, 128, (cuuint64_t)sh * 2, (cuuint64_t)(Z > 1 ? b_sz : (int64_t)m.H * sh) * 2};
-    cuuint32_t box[5] = {64, (cuuint32_t)kbox, (cuuint32_t)(TN / 64), 1, 1};
-    if (int rc = encode(&mb, b, dtype, 5, dims, strides, box, 128)) return rc;
+  } else {                                                 // [k][n]: boxes of 64 columns x kbox rows, one per group of 64 columns
+    cuuint64_t dims[4] = {(cuuint64_t)N, (cuuint64_t)ktot, (cuuint64_t)m.H, (cuuint64_t)Z};
+    cuuint64_t strides[3] = {(cuuint64_t)outer_n * 2, (cuuint64_t)sh * 2, (cuuint64_t)(Z > 1 ? b_sz : (int64_t)m.H * sh) * 2};
+    cuuint32_t box[4] = {64, (cuuint32_t)kbox, 1, 1};
+    if (int rc = encode(&mb, b, dtype, 4, dims, strides, box, 128)) return rc;
   }
   DsdTcArgs a = {};
   a.c = c; a.c_sz = c_sz; a.c_sh = c_sh; a.c_sm = c_sm; a.c_sn = c_sn;
