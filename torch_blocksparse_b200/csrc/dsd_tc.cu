@@ -37,7 +37,7 @@
 // dds case, 0.59 against 0.71 ms).
 //
 // Warps: 0-3 write the result back (tensor memory -> registers -> global), 4 loads the sparse
-// operand, 5 issues the MMAs (one thread), 6 loads the dense operand (one thread), 7 plans:
+// operand, 5 issues the MMAs (one thread), 6 loads the dense operand, 7 plans:
 // it turns the tile's column lists into bit masks (the reduction side may have 1024 blocks at
 // most), forms their union and writes one entry per stage (rows of the sparse operand, block
 // columns of the dense one) into a double-buffered plan in shared memory, so that the loading
