@@ -269,6 +269,52 @@ def test_dsd_dds_tcgen05_kernel(mode, ta, tb, block, dtype, width):
     assert fused.device_status() == 0
 
 
+def test_tcgen05_kernels_against_mma_sync_on_random_shapes():
+    """Sixty random cases (mode, transposes, block 32 / 64 / 128, layout shape and density, batch,
+    dense extent, dtype): the tcgen05 kernels against the mma.sync kernels on the same device
+    tensors.  Covers tiles with empty block-rows, single blocks, empty heads' neighbours, tails."""
+    import random
+    from torch_blocksparse_b200 import _lib, fused
+    rnd = random.Random(11)
+    L = _lib.lib()
+    for case in range(60):
+        mode = rnd.choice(['sdd', 'dsd', 'dds'])
+        ta, tb = rnd.random() < 0.5, rnd.random() < 0.5
+        block = rnd.choice([32, 64, 128])
+        dtype = rnd.choice([torch.float16, torch.bfloat16])
+        Z, H = rnd.randint(1, 3), rnd.randint(1, 3)
+        n1, n2 = rnd.randint(1, 9), rnd.randint(1, 20)          # blocks of the sparse tensor's two sides
+        dense = rnd.choice([128, 256, 384, 512])
+        g = torch.Generator().manual_seed(1000 + case)
+        p = rnd.choice([0.1, 0.3, 0.6, 1.0])
+        if mode == 'sdd':
+            M, N, K = n1 * block, n2 * block, rnd.choice([64, 128, 320])
+            lshape = (H, n1, n2)
+        elif mode == 'dsd':
+            M, K, N = n1 * block, n2 * block, dense
+            lshape = (H, n2, n1) if ta else (H, n1, n2)
+        else:
+            K, N, M = n1 * block, n2 * block, dense
+            lshape = (H, n2, n1) if tb else (H, n1, n2)
+        layout = (torch.rand(lshape, generator=g) < p).long()
+        layout[:, 0, 0] = 1
+        AS = (K, M) if ta else (M, K)
+        BS = (N, K) if tb else (K, N)
+        x = (torch.randn((Z, H) + AS, generator=g) * 0.2).to(dtype)
+        w = (torch.randn((Z, H) + BS, generator=g) * 0.2).to(dtype)
+        a = dm.dense_to_sparse(x, layout, block) if mode == 'dsd' else x
+        b = dm.dense_to_sparse(w, layout, block) if mode == 'dds' else w
+        op = MatMul(layout, block, mode, trans_a=ta, trans_b=tb)
+        try:
+            c_tc = op(a.to(DEV), b.to(DEV))
+            _lib.check(L.bsp_matmul_use_tcgen05(0))
+            c_mma = op(a.to(DEV), b.to(DEV))
+        finally:
+            _lib.check(L.bsp_matmul_use_tcgen05(1))
+        assert_close(c_tc.cpu(), c_mma.cpu(), 'case %d: %s ta=%d tb=%d block %d layout %s' % (case, mode, ta, tb, block, lshape))
+    assert fused.device_status() == 0
+
+
 @pytest.mark.parametrize('mode,ta,tb', [('dsd', False, False), ('dsd', True, False), ('dds', False, True)])
 @pytest.mark.parametrize('block,nred', [(32, 200), (64, 160), (128, 140), (32, 1024), (32, 1056)])
 def test_dsd_dds_long_reduction_side(mode, ta, tb, block, nred):
