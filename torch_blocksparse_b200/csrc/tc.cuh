@@ -58,6 +58,8 @@ BSP_DEVI bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* failed) {
 }
 
 // mbar_wait for a whole warp: the outcome is made uniform, so that a warp leaves its loop as one.
+// (Every lane waits itself: with lane 0 waiting and a shuffle handing the outcome to the others the
+// attention step was 9 % slower, dK/dV 16 %.)
 BSP_DEVI bool mbar_wait_warp(uint64_t* bar, uint32_t parity, volatile int* failed) {
   return __all_sync(0xffffffffu, mbar_wait(bar, parity, failed));
 }
