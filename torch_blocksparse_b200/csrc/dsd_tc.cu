@@ -291,9 +291,8 @@ dsd_tc_kernel(const __grid_constant__ CUtensorMap m_s, const __grid_constant__ C
             for (int kh = 0; kh < reps; ++kh) {
               const int s = it % S;
               if (it >= S) {
-                k = 1;
-                if (lane == 0) k = mbar_wait(&bar_empty[s], ((it / S) - 1) & 1, fl) ? 1 : 0;
-                if (!__shfl_sync(m8, k, 0)) { ok = false; break; }
+                // (every lane waits itself: cheaper than one waiting lane and a shuffle)
+                if (!__all_sync(m8, mbar_wait(&bar_empty[s], ((it / S) - 1) & 1, fl))) { ok = false; break; }
               }
               unsigned char* sp = smem + s * G::kStage;
               if (block == 128) {
@@ -346,7 +345,7 @@ dsd_tc_kernel(const __grid_constant__ CUtensorMap m_s, const __grid_constant__ C
   } else if (warp == 6) {
     // ------------------------------------------------------------------ dense operand
     // k contiguous: one box of TN rows; n contiguous: one box of 64 columns per lane (the groups
-    // of 64 columns of the MN-major tile), issued together.  Lane 0 waits and announces the bytes.
+    // of 64 columns of the MN-major tile), issued together.  Lane 0 announces the bytes.
     constexpr int NG = B_KMAJOR ? 1 : TN / 64;
     if (lane < NG) {
       constexpr uint32_t mg = (1u << NG) - 1u;
@@ -371,9 +370,8 @@ dsd_tc_kernel(const __grid_constant__ CUtensorMap m_s, const __grid_constant__ C
             for (int kh = 0; kh < reps; ++kh) {
               const int s = it % S;
               if (it >= S) {
-                k = 1;
-                if (lane == 0) k = mbar_wait(&bar_empty[s], ((it / S) - 1) & 1, fl) ? 1 : 0;
-                if (NG > 1) k = __shfl_sync(mg, k, 0);
+                k = mbar_wait(&bar_empty[s], ((it / S) - 1) & 1, fl) ? 1 : 0;
+                if (NG > 1) k = __all_sync(mg, k);
                 if (!k) { ok = false; break; }
               }
               unsigned char* bp = smem + s * G::kStage + kStageA;
