@@ -63,6 +63,7 @@ sdd_tc_kernel(const __grid_constant__ CUtensorMap m_a, const __grid_constant__ C
   // work of this CTA: head, first row of A, its column blocks (first column of B, or -1), how
   // many there are, and the ids of the blocks to store ([block-row][column block], -1: none)
   __shared__ int w_h, w_m0, w_cols, w_n[8], w_id[4][8];
+  __shared__ uint32_t row_mask[4][32];          // set-up: block-row r has a block in column 32 * word + bit
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int z = blockIdx.z, block = a.block;
@@ -71,30 +72,91 @@ sdd_tc_kernel(const __grid_constant__ CUtensorMap m_a, const __grid_constant__ C
   if (tid == 0) {
     failed[0] = 0;
     failed[1] = kWaitBudget;
-    for (int j = 0; j < 8; ++j) {
-      w_n[j] = -1;
-      for (int i = 0; i < 4; ++i) w_id[i][j] = -1;
+    for (int s = 0; s < kStages; ++s) { mbar_init(&bar_full[s], 1); mbar_init(&bar_empty[s], 1); }
+    mbar_init(&bar_done, 1);
+    mbar_init_fence();
+  }
+  if (warp == 0) {
+    // The work of this CTA, found by the whole warp: entries NC g .. NC g + NC - 1 of the union
+    // of the tile's column lists.  Up to 1024 block-columns the lists become bit masks (lane w
+    // holds columns 32 w .. 32 w + 31 of every block-row) and positions are prefix counts of
+    // set bits; beyond that lane 0 merges the lists.
+    const uint32_t full = 0xffffffffu;
+    if (lane < 8) {
+      w_n[lane] = -1;
+      for (int i = 0; i < 4; ++i) w_id[i][lane] = -1;
     }
     const int tile = blockIdx.y, g = blockIdx.x;     // the groups of a tile are neighbours in the launch: they share A in L2
     const int h = tile / a.tiles_per_head, r0 = R * (tile % a.tiles_per_head);
-    w_h = h;
-    w_m0 = r0 * block;
-    int i[4], e[4], c[4];
-    for (int r = 0; r < 4; ++r) {
-      i[r] = e[r] = 0;
-      if (r < R && r0 + r < a.Mb) { i[r] = a.row_ptr[h * a.Mb + r0 + r]; e[r] = a.row_ptr[h * a.Mb + r0 + r + 1]; }
-      c[r] = i[r] < e[r] ? a.blk_col[i[r]] : kNone;
-    }
-    // entries NC g .. NC g + NC - 1 of the union of the column lists (each in column order)
-    int cols = 0;
+    if (lane == 0) { w_h = h; w_m0 = r0 * block; w_cols = 0; }
+    int rs = 0, re = 0;
+    if (lane < R && r0 + lane < a.Mb) { rs = a.row_ptr[h * a.Mb + r0 + lane]; re = a.row_ptr[h * a.Mb + r0 + lane + 1]; }
+    __syncwarp();
     if (R == 1) {                                     // one list: its entries directly
-      const int first = i[0] + NC * g;
-      for (int j = 0; j < NC && first + j < e[0]; ++j) {
-        w_n[j] = a.blk_col[first + j] * block;
-        w_id[0][j] = first + j;
-        cols = j + 1;
+      const int first = __shfl_sync(full, rs, 0) + NC * g, end = __shfl_sync(full, re, 0);
+      if (lane < NC && first + lane < end) {
+        w_n[lane] = a.blk_col[first + lane] * block;
+        w_id[0][lane] = first + lane;
       }
-    } else {
+      if (lane == 0) w_cols = max(0, min(NC, end - first));
+    } else if (a.Nb <= 1024) {
+#pragma unroll
+      for (int r = 0; r < 4; ++r) row_mask[r][lane] = 0;
+      __syncwarp();
+      int start[4];
+#pragma unroll
+      for (int r = 0; r < 4; ++r) {
+        start[r] = __shfl_sync(full, rs, r);
+        const int end = __shfl_sync(full, re, r);
+        for (int j = start[r] + lane; j < end; j += 32) {
+          const int c = a.blk_col[j];
+          atomicOr(&row_mask[r][c >> 5], 1u << (c & 31));
+        }
+      }
+      __syncwarp();
+      uint32_t m[4], u = 0;
+      int rank0[4];
+#pragma unroll
+      for (int r = 0; r < 4; ++r) {
+        m[r] = row_mask[r][lane];
+        u |= m[r];
+        int x = __popc(m[r]);
+        const int v = x;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+          const int y = __shfl_up_sync(full, x, d);
+          if (lane >= d) x += y;
+        }
+        rank0[r] = x - v;
+      }
+      int x = __popc(u);
+      const int v = x;
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        const int y = __shfl_up_sync(full, x, d);
+        if (lane >= d) x += y;
+      }
+      const int total = __shfl_sync(full, x, 31);
+      int q = x - v;                                  // position in the union of this lane's first column
+      for (uint32_t bits = u; bits; ++q) {
+        const int bit = __ffs(bits) - 1;
+        bits &= bits - 1;
+        const int j = q - NC * g;
+        if (j < 0 || j >= NC) continue;
+        w_n[j] = (lane * 32 + bit) * block;
+#pragma unroll
+        for (int r = 0; r < 4; ++r)
+          if ((m[r] >> bit) & 1u) w_id[r][j] = start[r] + rank0[r] + __popc(m[r] & ((1u << bit) - 1u));
+      }
+      if (lane == 0) w_cols = max(0, min(NC, total - NC * g));
+    } else if (lane == 0) {
+      int i[4], e[4], c[4];
+      for (int r = 0; r < 4; ++r) {
+        i[r] = e[r] = 0;
+        if (r < R && r0 + r < a.Mb) { i[r] = a.row_ptr[h * a.Mb + r0 + r]; e[r] = a.row_ptr[h * a.Mb + r0 + r + 1]; }
+        c[r] = i[r] < e[r] ? a.blk_col[i[r]] : kNone;
+      }
+      int cols = 0;
       for (int n = 0; n < NC * g + NC; ++n) {
         const int col = min(min(c[0], c[1]), min(c[2], c[3]));
         if (col == kNone) break;
@@ -106,11 +168,8 @@ sdd_tc_kernel(const __grid_constant__ CUtensorMap m_a, const __grid_constant__ C
             c[r] = i[r] < e[r] ? a.blk_col[i[r]] : kNone;
           }
       }
+      w_cols = cols;
     }
-    w_cols = cols;
-    for (int s = 0; s < kStages; ++s) { mbar_init(&bar_full[s], 1); mbar_init(&bar_empty[s], 1); }
-    mbar_init(&bar_done, 1);
-    mbar_init_fence();
   }
   __syncthreads();
   if (w_cols == 0) return;                     // this group of columns does not exist (uniform)
